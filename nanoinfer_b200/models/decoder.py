@@ -1,0 +1,91 @@
+"""The generic decoder: builds part objects from a ``ModelPlan`` and runs them in schedule order.
+
+One forward runs exactly the tokens of a step: embedding, the schedule's layers (each with the
+cache of its schedule entry), then the final norm and the head on the wanted rows only
+(the reference computes logits for all rows: cpp/src/model.cpp:405-406).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..parts.base import CacheNeed, LayerCache, Runtime, StateNeed, StepContext
+from ..parts.spec import ModelPlan, PartSpec
+from ..registry import get_arrangement, get_part
+
+
+def _build_part(spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
+    cls = get_part(spec.kind)
+    by_role = {role: tensors[ts.name] for role, ts in spec.tensors.items()}
+    return cls(spec, by_role, rt)
+
+
+class DecoderModel:
+    def __init__(self, plan: ModelPlan, tensors: Dict[str, torch.Tensor], rt: Runtime):
+        plan.validate()
+        self.plan, self.rt = plan, rt
+        # A tensor used by two parts (a tied head) is moved to the device once.
+        memo: Dict[Tuple[int, str], torch.Tensor] = {}
+        shared = _SharingRuntime(rt, memo)
+        self.embedding = _build_part(plan.embedding, tensors, shared)
+        self.positions = {name: _build_part(p, tensors, shared) for name, p in plan.positions.items()}
+        self.layers = []
+        for layer in plan.layers:
+            parts = {name: _build_part(p, tensors, shared) for name, p in layer.parts.items()}
+            for part in parts.values():
+                bind = getattr(part, "bind_positions", None)
+                if bind is not None:
+                    bind(self.positions)
+            self.layers.append(get_arrangement(layer.arrangement)(parts))
+        self.final_norm = _build_part(plan.final_norm, tensors, shared)
+        self.head = _build_part(plan.lm_head, tensors, shared)
+        self.schedule = list(plan.schedule)
+
+    # -- what the cache manager has to provide -------------------------------------------------
+    def cache_needs(self) -> List[Tuple[Optional[CacheNeed], Optional[StateNeed], Optional[int]]]:
+        """Per schedule entry: (pages needed, state needed, entry whose cache it reads instead)."""
+        out = []
+        for e in self.schedule:
+            mixer = self.layers[e.layer].mixer
+            need = mixer.cache_need()
+            state = mixer.state_need()
+            if e.reads_cache_of is not None:
+                out.append((None, state, e.reads_cache_of))
+            else:
+                out.append((need, state, None))
+        return out
+
+    # -- one step ------------------------------------------------------------------------------
+    def forward(self, ctx: StepContext, caches: List[LayerCache],
+                want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Runs ``ctx``'s tokens; returns 32-bit logits ``[len(want_rows), vocab]`` (None if nothing is wanted)."""
+        x32 = self.embedding.forward(ctx.token_ids, ctx)
+        for pos in self.positions.values():
+            pos.add_to_embedding(x32, ctx)
+        for i, e in enumerate(self.schedule):
+            self.layers[e.layer].forward(x32, ctx, caches[i])
+        if want_rows is None or want_rows.numel() == 0:
+            return None
+        h = self.final_norm.forward(x32, rows=want_rows)
+        return self.head.forward(h)
+
+
+class _SharingRuntime(Runtime):
+    """A runtime whose ``matrix`` / ``vector32`` return one device copy per source tensor."""
+
+    def __init__(self, rt: Runtime, memo):
+        super().__init__(rt.device, rt.dtype, rt.ops)
+        self._memo = memo
+
+    def matrix(self, t: torch.Tensor) -> torch.Tensor:
+        key = (id(t), "m")
+        if key not in self._memo:
+            self._memo[key] = (t, Runtime.matrix(self, t))
+        return self._memo[key][1]
+
+    def vector32(self, t: torch.Tensor) -> torch.Tensor:
+        key = (id(t), "v")
+        if key not in self._memo:
+            self._memo[key] = (t, Runtime.vector32(self, t))
+        return self._memo[key][1]
