@@ -1,0 +1,149 @@
+"""The engine: a model, its cache, and ONE step function.
+
+``step(entries)`` takes a batch of (request, its next tokens, which of them want logits): portions
+of prompts beside single decoded tokens, cut anywhere. It runs only the tokens it is given, as one
+flat batch, from the cache that earlier steps left, appends their keys and values, and returns the
+32-bit logits at the wanted places. Everything above it (scheduler, generation, trace replay) goes
+through this one function.
+
+The reference has three forwards instead (one request with t tokens; N requests with one token;
+a ragged batch: cpp/src/model.cpp:347-561); the ragged one is the shape generalised here.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.pages import CacheManager, OutOfPages, RequestCache
+from ..cache.storage import CacheStorage
+from ..config.engine_config import EngineConfig
+from ..config.model_config import ModelConfig, read_config_json
+from ..models.decoder import DecoderModel
+from ..parts.base import HostBatch, Runtime, StepContext
+from ..registry import config_from_json_dict, plan_for
+from ..weights.loader import load_tensors
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+@dataclass
+class StepEntry:
+    request: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()     # places among ``tokens`` whose logits are wanted
+
+
+class Engine:
+    def __init__(self, model_dir: str, engine_config: EngineConfig, ops=None):
+        self.engine_config = engine_config
+        self.config: ModelConfig = config_from_json_dict(read_config_json(model_dir))
+        self.plan = plan_for(self.config)
+        tensors = load_tensors(model_dir, self.plan)
+        if ops is None:
+            from ..csrc.lib import load_kernels  # fails loudly when the CUDA library cannot be had
+            ops = load_kernels()
+        self.device = torch.device(engine_config.device)
+        self.dtype = _TORCH_DTYPE[engine_config.dtype]
+        self.rt = Runtime(self.device, self.dtype, ops)
+        self.model = DecoderModel(self.plan, tensors, self.rt)
+        self.storage = CacheStorage(self.model.cache_needs(), engine_config.resolved_num_pages(),
+                                    engine_config.page_size, engine_config.max_batch, self.dtype, self.device)
+        self.cache: CacheManager = self.storage.make_manager(engine_config.max_batch)
+        self.vocab_size = self.plan.vocab_size
+        self.max_positions = self.plan.max_position_embeddings
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ---- requests -------------------------------------------------------------------------
+    def open(self, request_id) -> RequestCache:
+        return self.cache.open(request_id)
+
+    def close(self, rc: RequestCache) -> None:
+        self.cache.close(rc)
+
+    # ---- the step -------------------------------------------------------------------------
+    def _check(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.request.closed:
+                raise ValueError(f"request {e.request.request_id!r} is closed")
+            if id(e.request) in seen:
+                raise ValueError(f"request {e.request.request_id!r} appears twice in one step")
+            seen.add(id(e.request))
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request.request_id!r}: an entry needs at least one token")
+            if e.request.length + n > self.max_positions:
+                raise ValueError(
+                    f"request {e.request.request_id!r}: position {e.request.length + n} exceeds the "
+                    f"model's context length {self.max_positions} (max_position_embeddings)")
+            for t in e.tokens:
+                if not (0 <= int(t) < self.vocab_size):
+                    raise ValueError(f"token id {t} outside the vocabulary 0..{self.vocab_size - 1}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise ValueError(f"wanted place {w} outside the entry's {n} tokens")
+
+    def build_context(self, entries: Sequence[StepEntry]):
+        """Host arrays -> one int32 device buffer -> the views a step needs."""
+        q_lens = [len(e.tokens) for e in entries]
+        r = len(entries)
+        m = sum(q_lens)
+        ctx_lens = [e.request.length + n for e, n in zip(entries, q_lens)]
+        q_start = np.zeros(r + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        positions = np.concatenate([np.arange(e.request.length, e.request.length + n, dtype=np.int32)
+                                    for e, n in zip(entries, q_lens)])
+        req_index = np.repeat(np.arange(r, dtype=np.int32), q_lens)
+        slots = np.asarray([e.request.slot for e in entries], dtype=np.int32)
+        want = np.asarray([q_start[i] + int(w) for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
+        tables = []
+        for g in range(len(self.cache.groups)):
+            width = max(1, max(len(e.request.tables[g]) for e in entries))
+            t = np.full((r, width), -1, dtype=np.int32)
+            for i, e in enumerate(entries):
+                row = e.request.tables[g]
+                t[i, :len(row)] = row
+            tables.append(t)
+        parts = [token_ids, positions, req_index, q_start, np.asarray(ctx_lens, dtype=np.int32), slots, want]
+        parts += [t.reshape(-1) for t in tables]
+        flat = np.concatenate(parts) if parts else np.zeros(0, np.int32)
+        dev = torch.from_numpy(flat).to(self.device)
+        views, off = [], 0
+        for p in parts:
+            views.append(dev[off:off + p.size])
+            off += p.size
+        block_tables = {g: views[7 + g].view(r, tables[g].shape[1]) for g in range(len(tables))}
+        ctx = StepContext(
+            num_tokens=m, token_ids=views[0], positions=views[1], req_index=views[2], q_start=views[3],
+            ctx_lens=views[4], state_slots=views[5],
+            host=HostBatch(q_lens=q_lens, ctx_lens=ctx_lens, slots=slots.tolist()),
+            block_tables=block_tables, rt=self.rt)
+        return ctx, (views[6] if want.size else None)
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch. Returns logits ``[wanted, vocab]`` (float32, on the device) in the order of the
+        entries and of each entry's ``want``; None if nothing is wanted. Raises ``OutOfPages`` before
+        changing anything if the pools cannot hold the new tokens."""
+        self._check(entries)
+        demands = [(e.request, len(e.tokens)) for e in entries]
+        if not self.cache.fits(demands):
+            raise OutOfPages("the step's new tokens do not fit the free cache pages")
+        for rc, n in demands:
+            self.cache.extend(rc, n)
+        self.storage.zero_slots(self.cache.take_fresh_slots())
+        ctx, want_rows = self.build_context(entries)
+        caches = self.storage.layer_caches(ctx.block_tables)
+        logits = self.model.forward(ctx, caches, want_rows)
+        for rc, n in demands:
+            self.cache.commit(rc, n)
+        self.steps_run += 1
+        self.tokens_run += ctx.num_tokens
+        return logits
