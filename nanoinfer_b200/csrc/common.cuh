@@ -1,0 +1,59 @@
+// Shared helpers of the kernel library. Every exported function is extern "C", takes raw device
+// pointers and a stream, allocates nothing, and returns 0 or a non-zero code whose text
+// nib_last_error() gives.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#define NIB_API extern "C" __attribute__((visibility("default")))
+
+enum NibDType : int { NIB_F32 = 0, NIB_BF16 = 1 };
+
+// Sets the message that nib_last_error() returns (thread-local).
+void nib_set_error(const char* fmt, ...);
+
+#define NIB_REQUIRE(cond, ...)            \
+    do {                                  \
+        if (!(cond)) {                    \
+            nib_set_error(__VA_ARGS__);   \
+            return 1;                     \
+        }                                 \
+    } while (0)
+
+#define NIB_CUDA(call)                                                              \
+    do {                                                                            \
+        cudaError_t e__ = (call);                                                   \
+        if (e__ != cudaSuccess) {                                                   \
+            nib_set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__),  \
+                          __FILE__, __LINE__);                                      \
+            return 2;                                                               \
+        }                                                                           \
+    } while (0)
+
+#define NIB_LAUNCH_CHECK() NIB_CUDA(cudaGetLastError())
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }

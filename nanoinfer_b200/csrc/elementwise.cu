@@ -1,0 +1,159 @@
+// Embedding gather, RMSNorm, and rotation of queries and keys fused with the write of keys and
+// values into the cache pages. All arithmetic is 32-bit; T is the storage type of activations,
+// tables and cache (float or bfloat16).
+//
+// Reference formulas: cpp/src/ops.cpp:71-84 (embedding), :272-292 (rmsnorm: eps inside the root),
+// :146-168 (half-split rotation), cpp/src/cuda/cuda_backend.cu:354-367 (page write through the
+// block table). The reference runs these as separate one-thread-per-element kernels
+// (cpp/src/cuda/cuda_elementwise.cu:26-135) with one thread per ROW for the norm.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             float* __restrict__ out, int hidden, int vocab) {
+    const int m = blockIdx.x;
+    const int id = ids[m];
+    float* o = out + (size_t)m * hidden;
+    if (id < 0 || id >= vocab) {  // the engine checks ids on the host; never read outside the table
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)id * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = Elem<T>::load(src + c);
+}
+
+NIB_API int nib_embed(const int* ids, const void* table, float* out, int m, int hidden, int vocab,
+                      int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(m >= 0 && hidden > 0 && vocab > 0, "embed: bad sizes m=%d hidden=%d vocab=%d", m, hidden, vocab);
+    if (m == 0) return 0;
+    const int threads = hidden >= 256 ? 256 : 64;
+    if (dtype == NIB_F32)
+        embed_kernel<float><<<m, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+    else if (dtype == NIB_BF16)
+        embed_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+    else
+        NIB_REQUIRE(false, "embed: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- RMSNorm
+// One block per output row. The sum of squares is reduced in a fixed order (thread-strided partial
+// sums, warp butterflies, then warp 0 over the warps), so a row's result does not depend on which
+// other rows are in the batch.
+template <typename T, int THREADS>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                               const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
+    __shared__ float warp_part[THREADS / 32];
+    __shared__ float s_scale;
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += THREADS) {
+        const float v = xr[c];
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < THREADS / 32 ? warp_part[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) s_scale = 1.0f / sqrtf(v / (float)hidden + eps);
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    T* o = out + (size_t)r * hidden;
+    for (int c = threadIdx.x; c < hidden; c += THREADS) Elem<T>::store(o + c, xr[c] * scale * gain[c]);
+}
+
+NIB_API int nib_rmsnorm(const float* x, const float* gain, const int* rows, void* out, int n_rows,
+                        int hidden, float eps, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(n_rows >= 0 && hidden > 0, "rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    if (n_rows == 0) return 0;
+    if (dtype == NIB_F32)
+        rmsnorm_kernel<float, 256><<<n_rows, 256, 0, stream>>>(x, gain, rows, (float*)out, hidden, eps);
+    else if (dtype == NIB_BF16)
+        rmsnorm_kernel<__nv_bfloat16, 256><<<n_rows, 256, 0, stream>>>(x, gain, rows, (__nv_bfloat16*)out, hidden, eps);
+    else
+        NIB_REQUIRE(false, "rmsnorm: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- rotation + page write
+// qkv row layout: [heads | kv_heads | kv_heads] x head_dim. Queries and keys are rotated in place
+// (pairs d, d + rot/2 for d < rot/2; elements >= rot are left as they are); rotated keys and the
+// values are also written to the page of the token's position, if write_kv.
+// Pages: [num_pages, kv_heads, page_size, head_dim].
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                  const int* __restrict__ req_index, const float* __restrict__ cos_t,
+                                  const float* __restrict__ sin_t, int rot, const int* __restrict__ block_table,
+                                  int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                  int heads, int kv_heads, int head_dim, int num_pages, int write_kv) {
+    const int m = blockIdx.x;
+    const int pos = positions[m];
+    T* row = qkv + (size_t)m * (heads + 2 * kv_heads) * head_dim;
+    const int half = rot / 2;
+    long long page = -1;
+    int off = 0;
+    if (write_kv) {
+        page = block_table[(size_t)req_index[m] * bt_stride + pos / page_size];
+        off = pos % page_size;
+        if (page < 0 || page >= num_pages) page = -1;  // never write outside the pool
+    }
+    // rotated pairs of queries and keys
+    const int pairs = (heads + kv_heads) * half;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int h = i / half, d = i - h * half;
+        const float c = cos_t[(size_t)pos * half + d], s = sin_t[(size_t)pos * half + d];
+        T* p = row + (size_t)h * head_dim;
+        const float x1 = Elem<T>::load(p + d), x2 = Elem<T>::load(p + d + half);
+        const float o1 = x1 * c - x2 * s, o2 = x2 * c + x1 * s;
+        Elem<T>::store(p + d, o1);
+        Elem<T>::store(p + d + half, o2);
+        if (h >= heads && page >= 0) {
+            T* dst = k_pages + (((size_t)page * kv_heads + (h - heads)) * page_size + off) * head_dim;
+            Elem<T>::store(dst + d, o1);
+            Elem<T>::store(dst + d + half, o2);
+        }
+    }
+    if (page < 0) return;
+    // keys beyond the rotated width
+    const int tail = head_dim - rot;
+    for (int i = threadIdx.x; i < kv_heads * tail; i += blockDim.x) {
+        const int h = i / tail, d = rot + (i - h * tail);
+        k_pages[(((size_t)page * kv_heads + h) * page_size + off) * head_dim + d] =
+            row[(size_t)(heads + h) * head_dim + d];
+    }
+    // values
+    for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
+        const int h = i / head_dim, d = i - h * head_dim;
+        v_pages[(((size_t)page * kv_heads + h) * page_size + off) * head_dim + d] =
+            row[(size_t)(heads + kv_heads + h) * head_dim + d];
+    }
+}
+
+NIB_API int nib_rope_store(void* qkv, const int* positions, const int* req_index, const float* cos_t,
+                           const float* sin_t, int rot, const int* block_table, int bt_stride, int page_size,
+                           void* k_pages, void* v_pages, int m, int heads, int kv_heads, int head_dim,
+                           int num_pages, int write_kv, int dtype, cudaStream_t stream) {
+    NIB_REQUIRE(m >= 0 && heads > 0 && kv_heads > 0 && head_dim > 0, "rope_store: bad sizes");
+    NIB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0, "rope_store: rotated width %d must be even and <= head_dim %d", rot, head_dim);
+    NIB_REQUIRE(!write_kv || (block_table && k_pages && v_pages && page_size > 0 && num_pages > 0),
+                "rope_store: write asked for without pages");
+    if (m == 0) return 0;
+    const int threads = 128;
+    if (dtype == NIB_F32)
+        rope_store_kernel<float><<<m, threads, 0, stream>>>((float*)qkv, positions, req_index, cos_t, sin_t, rot,
+            block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, heads, kv_heads, head_dim, num_pages, write_kv);
+    else if (dtype == NIB_BF16)
+        rope_store_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, req_index, cos_t, sin_t, rot,
+            block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, heads, kv_heads, head_dim, num_pages, write_kv);
+    else
+        NIB_REQUIRE(false, "rope_store: unknown dtype %d", dtype);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,189 @@
+"""The kernel library as Python sees it: loads ``libnanoinfer_b200.so`` (building it first if needed)
+and wraps each exported function. There is no other implementation behind these calls: if the
+library cannot be built or loaded, or the device is not a CUDA device, they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_EPI = {"store": 0, "add": 1, "f32": 2, "swiglu": 3}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, dtype, what: str, contiguous: bool = True):
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}, the kernels run on CUDA only")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{what}: tensor must be contiguous")
+
+
+class Kernels:
+    """One instance per process; stateless apart from the loaded library."""
+
+    name = "cuda-sm100a"
+
+    def __init__(self, lib_path: str):
+        self.lib_path = lib_path
+        try:
+            self._lib = ctypes.CDLL(lib_path)
+        except OSError as e:
+            raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
+        self._lib.nib_last_error.restype = ctypes.c_char_p
+        for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
+                     "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
+            getattr(self._lib, name).restype = c_int
+
+    # ---- plumbing ---------------------------------------------------------------------------
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            raise KernelError(f"{what}: {self._lib.nib_last_error().decode()}")
+
+    @staticmethod
+    def _stream() -> c_void_p:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def device_arch(self) -> int:
+        return self._lib.nib_device_arch()
+
+    # ---- kernels ----------------------------------------------------------------------------
+    def embed(self, ids, table, out32):
+        _need(ids, torch.int32, "embed ids"); _need(table, None, "embed table"); _need(out32, torch.float32, "embed out")
+        m, hidden = out32.shape
+        self._check(self._lib.nib_embed(_ptr(ids), _ptr(table), _ptr(out32), c_int(m), c_int(hidden),
+                                        c_int(table.shape[0]), c_int(_DT[table.dtype]), self._stream()), "embed")
+
+    def rmsnorm(self, x32, gain32, eps, out, rows=None):
+        _need(x32, torch.float32, "rmsnorm x"); _need(gain32, torch.float32, "rmsnorm gain"); _need(out, None, "rmsnorm out")
+        if rows is not None:
+            _need(rows, torch.int32, "rmsnorm rows")
+        n, hidden = out.shape
+        if x32.shape[1] != hidden or gain32.numel() != hidden:
+            raise KernelError("rmsnorm: widths differ")
+        self._check(self._lib.nib_rmsnorm(_ptr(x32), _ptr(gain32), _ptr(rows), _ptr(out), c_int(n), c_int(hidden),
+                                          c_float(eps), c_int(_DT[out.dtype]), self._stream()), "rmsnorm")
+
+    def linear(self, a, w, bias32, out, mode):
+        """out[M,N] (=, +=) a[M,K] . w[N,K]^T (+ bias). mode: 'store' | 'add' (float out) | 'f32' (float out)."""
+        _need(a, None, "linear a"); _need(w, a.dtype, "linear w"); _need(out, None, "linear out")
+        if bias32 is not None:
+            _need(bias32, torch.float32, "linear bias")
+        m, k = a.shape
+        n = w.shape[0]
+        if w.shape[1] != k or tuple(out.shape) != (m, n):
+            raise KernelError(f"linear: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
+        want_out = a.dtype if mode == "store" else torch.float32
+        if out.dtype != want_out:
+            raise KernelError(f"linear[{mode}]: out must be {want_out}, got {out.dtype}")
+        self._check(self._lib.nib_gemm_simt(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                            c_int(k), c_int(n), c_int(_EPI[mode]), c_int(_DT[a.dtype]),
+                                            self._stream()), "linear")
+
+    def linear_swiglu(self, a, w_gate_up, out):
+        """out[M,I] = silu(a . w[:I]^T) * (a . w[I:]^T)."""
+        _need(a, None, "swiglu a"); _need(w_gate_up, a.dtype, "swiglu w"); _need(out, a.dtype, "swiglu out")
+        m, k = a.shape
+        inter = w_gate_up.shape[0] // 2
+        if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != k or tuple(out.shape) != (m, inter):
+            raise KernelError("linear_swiglu: shapes do not fit")
+        self._check(self._lib.nib_gemm_simt(_ptr(a), _ptr(w_gate_up), c_void_p(0), _ptr(out), c_int(m), c_int(inter),
+                                            c_int(k), c_int(k), c_int(inter), c_int(_EPI["swiglu"]),
+                                            c_int(_DT[a.dtype]), self._stream()), "linear_swiglu")
+
+    def rope_store(self, qkv, heads, kv_heads, head_dim, positions, req_index, rotary, block_table,
+                   page_size, k_pages, v_pages, writes):
+        _need(qkv, None, "rope qkv"); _need(positions, torch.int32, "positions"); _need(req_index, torch.int32, "req_index")
+        m = qkv.shape[0]
+        if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+            raise KernelError("rope_store: qkv width does not fit the head counts")
+        cos = sin = None
+        rot = 0
+        if rotary is not None:
+            cos, sin, rot = rotary
+            _need(cos, torch.float32, "cos"); _need(sin, torch.float32, "sin")
+            if cos.shape[1] != rot // 2:
+                raise KernelError("rope_store: table width must be rot/2")
+        num_pages = 0
+        bt_stride = 0
+        if writes:
+            _need(block_table, torch.int32, "block_table", contiguous=False)
+            _need(k_pages, qkv.dtype, "k_pages"); _need(v_pages, qkv.dtype, "v_pages")
+            if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim):
+                raise KernelError(f"rope_store: pages {tuple(k_pages.shape)} do not fit kv_heads/page_size/head_dim")
+            if block_table.stride(1) != 1:
+                raise KernelError("rope_store: block_table rows must be dense")
+            num_pages, bt_stride = k_pages.shape[0], block_table.stride(0)
+        self._check(self._lib.nib_rope_store(
+            _ptr(qkv), _ptr(positions), _ptr(req_index), _ptr(cos), _ptr(sin), c_int(rot),
+            _ptr(block_table if writes else None), c_int(bt_stride), c_int(page_size),
+            _ptr(k_pages if writes else None), _ptr(v_pages if writes else None), c_int(m), c_int(heads),
+            c_int(kv_heads), c_int(head_dim), c_int(num_pages), c_int(1 if writes else 0),
+            c_int(_DT[qkv.dtype]), self._stream()), "rope_store")
+
+    def attention(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
+                  page_size, k_pages, v_pages):
+        _need(qkv, None, "attention qkv"); _need(out, qkv.dtype, "attention out")
+        _need(k_pages, qkv.dtype, "k_pages"); _need(v_pages, qkv.dtype, "v_pages")
+        _need(block_table, torch.int32, "block_table", contiguous=False)
+        if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim):
+            raise KernelError(f"attention: pages {tuple(k_pages.shape)} do not fit kv_heads/page_size/head_dim")
+        m = qkv.shape[0]
+        self._check(self._lib.nib_attention_generic(
+            _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table),
+            c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]),
+            c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+            c_int(_DT[qkv.dtype]), self._stream()), "attention")
+
+    def argmax(self, logits, out):
+        _need(logits, torch.float32, "argmax logits"); _need(out, torch.int32, "argmax out")
+        rows, vocab = logits.shape
+        self._check(self._lib.nib_argmax(_ptr(logits), c_int(rows), c_int(vocab), _ptr(out), self._stream()), "argmax")
+
+    def repetition_penalty(self, logits, seen, seen_start, penalty):
+        _need(logits, torch.float32, "penalty logits"); _need(seen, torch.int32, "seen")
+        _need(seen_start, torch.int32, "seen_start"); _need(penalty, torch.float32, "penalty")
+        rows, vocab = logits.shape
+        self._check(self._lib.nib_repetition_penalty(_ptr(logits), c_int(rows), c_int(vocab), _ptr(seen),
+                                                     _ptr(seen_start), _ptr(penalty), self._stream()), "repetition_penalty")
+
+    def sample(self, logits, temperature, top_k, top_p, uniform, out):
+        _need(logits, torch.float32, "sample logits"); _need(temperature, torch.float32, "temperature")
+        _need(top_k, torch.int32, "top_k"); _need(top_p, torch.float32, "top_p")
+        _need(uniform, torch.float32, "uniform"); _need(out, torch.int32, "sample out")
+        rows, vocab = logits.shape
+        self._check(self._lib.nib_sample(_ptr(logits), c_int(rows), c_int(vocab), _ptr(temperature), _ptr(top_k),
+                                         _ptr(top_p), _ptr(uniform), _ptr(out), self._stream()), "sample")
+
+
+_KERNELS: Optional[Kernels] = None
+
+
+def load_kernels(verbose: bool = True) -> Kernels:
+    """The process-wide kernel library; built on first use. Raises if there is no CUDA device."""
+    global _KERNELS
+    if _KERNELS is None:
+        lib_path = _build.build(verbose=verbose)
+        k = Kernels(lib_path)
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine runs on an NVIDIA B200 (sm_100a) only")
+        arch = k.device_arch()
+        if arch != 100:
+            raise KernelError(f"the kernels are built for sm_100a; this device is sm_{arch}")
+        _KERNELS = k
+    return _KERNELS

@@ -1,0 +1,305 @@
+// Choosing the next token on the device from 32-bit logits [rows, vocab].
+//
+// Pipeline, in the reference's order (nanoinfer/sampling.py:126-151, cpp/src/sampling.cpp:90-108):
+// repetition penalty on the raw logits -> greedy (first index of the maximum) when temperature is 0
+// -> logits / temperature -> top-k (ties at the k-th value stay) -> top-p (a token is dropped iff the
+// probability of those before it, in descending order, exceeds p; the first stays) -> softmax ->
+// draw. The draw is an inverse CDF in vocabulary order with a uniform number that the host derives
+// from (seed, number of tokens generated), so a request's tokens do not depend on the batch it
+// was sampled in. The reference samples on the host (cpp/python/ni/scheduler.py:89-147).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------- penalty
+// seen: flat list of distinct token ids per row, seen_start[row]..seen_start[row+1].
+__global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int* __restrict__ seen,
+                               const int* __restrict__ seen_start, const float* __restrict__ penalty) {
+    const int row = blockIdx.x;
+    const float p = penalty[row];
+    if (p == 1.0f) return;
+    float* l = logits + (size_t)row * vocab;
+    for (int i = seen_start[row] + threadIdx.x; i < seen_start[row + 1]; i += blockDim.x) {
+        const int id = seen[i];
+        if (id < 0 || id >= vocab) continue;
+        const float s = l[id];
+        l[id] = s > 0.f ? s / p : s * p;
+    }
+}
+
+NIB_API int nib_repetition_penalty(float* logits, int rows, int vocab, const int* seen, const int* seen_start,
+                                   const float* penalty, cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && vocab > 0, "penalty: bad sizes");
+    if (rows == 0) return 0;
+    penalty_kernel<<<rows, 256, 0, stream>>>(logits, vocab, seen, seen_start, penalty);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- argmax
+constexpr int SAMP_THREADS = 1024;
+
+__device__ __forceinline__ void argmax_combine(float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+
+// First index of the maximum of each row. NaN entries never win.
+__global__ void __launch_bounds__(SAMP_THREADS)
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    __shared__ float sv[SAMP_THREADS / 32];
+    __shared__ int si[SAMP_THREADS / 32];
+    const float* l = logits + (size_t)blockIdx.x * vocab;
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += SAMP_THREADS) argmax_combine(v, idx, l[i], i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_combine(v, idx, ov, oi);
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = v; si[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        v = sv[threadIdx.x];
+        idx = si[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            argmax_combine(v, idx, ov, oi);
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
+NIB_API int nib_argmax(const float* logits, int rows, int vocab, int* out, cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && vocab > 0, "argmax: bad sizes");
+    if (rows == 0) return 0;
+    argmax_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, vocab, out);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------- sampling
+// Order-preserving map from float to unsigned: larger float <-> larger key.
+__device__ __forceinline__ unsigned key_of(float x) {
+    const unsigned b = __float_as_uint(x);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float float_of_key(unsigned k) {
+    const unsigned b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(b);
+}
+
+__device__ float block_max(float v, float* scratch) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = scratch[0];
+    for (int i = 1; i < SAMP_THREADS / 32; ++i) r = fmaxf(r, scratch[i]);
+    __syncthreads();
+    return r;
+}
+
+// Sum over the block in a fixed order.
+__device__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int i = 0; i < SAMP_THREADS / 32; ++i) r += scratch[i];
+    __syncthreads();
+    return r;
+}
+
+// Scaled probabilities are histogrammed as 64-bit fixed point so that sums do not depend on the
+// order in which threads add (integer addition is associative): sampling stays reproducible.
+constexpr float FIX_ONE = 1099511627776.0f;  // 2^40
+
+// One block per row. temperature > 0 for every row given to this kernel.
+__global__ void __launch_bounds__(SAMP_THREADS)
+sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
+              int* __restrict__ out) {
+    __shared__ float scratch[SAMP_THREADS / 32];
+    __shared__ unsigned hist[256];
+    __shared__ unsigned long long mass[256];
+    __shared__ unsigned s_prefix;
+    __shared__ unsigned s_remaining;
+    __shared__ unsigned long long s_above;
+    __shared__ float chunk_sum[SAMP_THREADS];
+    __shared__ int s_pick;
+
+    const int row = blockIdx.x;
+    const float* l = logits + (size_t)row * vocab;
+    const float inv_t = 1.0f / temperature[row];
+    const int tid = threadIdx.x;
+
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += SAMP_THREADS) mx = fmaxf(mx, l[i] * inv_t);
+    mx = block_max(mx, scratch);
+
+    // ---- top-k: key of the k-th largest scaled logit (0 keeps everything)
+    unsigned kth_key = 0u;
+    int k = top_k[row];
+    if (k > 0 && k < vocab) {
+        if (tid == 0) { s_prefix = 0u; s_remaining = (unsigned)k; }
+        __syncthreads();
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += SAMP_THREADS) hist[b] = 0u;
+            __syncthreads();
+            const unsigned prefix = s_prefix;
+            const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+            for (int i = tid; i < vocab; i += SAMP_THREADS) {
+                const unsigned key = key_of(l[i] * inv_t);
+                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned remaining = s_remaining;
+                int b = 255;
+                for (; b > 0; --b) {
+                    if (hist[b] >= remaining) break;
+                    remaining -= hist[b];
+                }
+                s_prefix = prefix | ((unsigned)b << shift);
+                s_remaining = remaining;
+            }
+            __syncthreads();
+        }
+        kth_key = s_prefix;
+    }
+
+    // ---- normaliser over what top-k kept
+    float z = 0.f;
+    for (int i = tid; i < vocab; i += SAMP_THREADS) {
+        const float x = l[i] * inv_t;
+        if (key_of(x) >= kth_key) z += expf(x - mx);
+    }
+    z = block_sum(z, scratch);
+
+    // ---- top-p: smallest key whose "probability of strictly larger keys" is <= p
+    unsigned p_key = kth_key;
+    long long ties_kept = -1;  // -1: every element equal to p_key stays
+    const float tp = top_p[row];
+    if (tp < 1.0f) {
+        const unsigned long long limit = (unsigned long long)((double)tp * (double)FIX_ONE);
+        if (tid == 0) { s_prefix = 0u; s_above = 0ull; }
+        __syncthreads();
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += SAMP_THREADS) { mass[b] = 0ull; hist[b] = 0u; }
+            __syncthreads();
+            const unsigned prefix = s_prefix;
+            const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+            for (int i = tid; i < vocab; i += SAMP_THREADS) {
+                const float x = l[i] * inv_t;
+                const unsigned key = key_of(x);
+                if (key >= kth_key && (key & mask) == prefix) {
+                    const unsigned long long q = (unsigned long long)(expf(x - mx) / z * FIX_ONE);
+                    atomicAdd(&mass[(key >> shift) & 255u], q);
+                    atomicAdd(&hist[(key >> shift) & 255u], 1u);
+                }
+            }
+            __syncthreads();
+            if (tid == 0) {
+                // walk down from the largest bin; stay in the lowest non-empty bin whose
+                // "mass above" is still within the limit
+                unsigned long long above = s_above;
+                int chosen = -1;
+                unsigned long long chosen_above = above;
+                for (int b = 255; b >= 0; --b) {
+                    if (hist[b] == 0u) continue;
+                    if (above <= limit || chosen < 0) {   // the very first (largest) element always stays
+                        if (above <= limit || chosen < 0) { chosen = b; chosen_above = above; }
+                    }
+                    if (above > limit) break;
+                    above += mass[b];
+                }
+                s_prefix = prefix | ((unsigned)(chosen < 0 ? 0 : chosen) << shift);
+                s_above = chosen_above;
+            }
+            __syncthreads();
+        }
+        p_key = s_prefix;
+        if (p_key < kth_key) p_key = kth_key;
+        // ties at p_key: the r-th of them (in vocabulary order) stays iff above + r*q <= limit
+        const float xv = float_of_key(p_key);
+        const unsigned long long q = (unsigned long long)(expf(xv - mx) / z * FIX_ONE);
+        const unsigned long long above = s_above;
+        if (q > 0ull && above <= limit) ties_kept = (long long)((limit - above) / q) + 1;
+        else ties_kept = 1;
+    }
+
+    // ---- inverse CDF in vocabulary order over what is kept
+    const int per = (vocab + SAMP_THREADS - 1) / SAMP_THREADS;
+    const int begin = min(vocab, tid * per), end = min(vocab, begin + per);
+    // rank of ties before this thread's chunk
+    __shared__ int tie_count[SAMP_THREADS];
+    int my_ties = 0;
+    if (ties_kept >= 0)
+        for (int i = begin; i < end; ++i) my_ties += key_of(l[i] * inv_t) == p_key;
+    tie_count[tid] = my_ties;
+    __syncthreads();
+    if (ties_kept >= 0 && tid == 0) {   // exclusive scan, serial (1024 adds)
+        int run = 0;
+        for (int t = 0; t < SAMP_THREADS; ++t) { const int c = tie_count[t]; tie_count[t] = run; run += c; }
+    }
+    __syncthreads();
+    float csum = 0.f;
+    {
+        long long tie_rank = tie_count[tid];
+        for (int i = begin; i < end; ++i) {
+            const float x = l[i] * inv_t;
+            const unsigned key = key_of(x);
+            bool keep = key >= p_key;
+            if (keep && ties_kept >= 0 && key == p_key) keep = (tie_rank++) < ties_kept;
+            if (keep) csum += expf(x - mx);
+        }
+    }
+    chunk_sum[tid] = csum;
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.f;
+        for (int t = 0; t < SAMP_THREADS; ++t) total += chunk_sum[t];
+        const float target = uniform[row] * total;
+        float run = 0.f;
+        int pick = SAMP_THREADS - 1;
+        for (int t = 0; t < SAMP_THREADS; ++t) {
+            if (chunk_sum[t] > 0.f) pick = t;             // last chunk with mass, if rounding runs past
+            if (run + chunk_sum[t] > target && chunk_sum[t] > 0.f) { pick = t; break; }
+            run += chunk_sum[t];
+        }
+        s_pick = pick;
+        scratch[0] = target;
+        // mass before the picked chunk
+        float before = 0.f;
+        for (int t = 0; t < pick; ++t) before += chunk_sum[t];
+        scratch[1] = before;
+    }
+    __syncthreads();
+    if (tid == s_pick) {
+        const float target = scratch[0];
+        float run = scratch[1];
+        long long tie_rank = tie_count[tid];
+        int chosen = -1, last_kept = -1;
+        for (int i = begin; i < end; ++i) {
+            const float x = l[i] * inv_t;
+            const unsigned key = key_of(x);
+            bool keep = key >= p_key;
+            if (keep && ties_kept >= 0 && key == p_key) keep = (tie_rank++) < ties_kept;
+            if (!keep) continue;
+            last_kept = i;
+            run += expf(x - mx);
+            if (run > target) { chosen = i; break; }
+        }
+        out[row] = chosen >= 0 ? chosen : (last_kept >= 0 ? last_kept : 0);
+    }
+}
+
+NIB_API int nib_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,
+                       const float* top_p, const float* uniform, int* out, cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes");
+    if (rows == 0) return 0;
+    sample_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, uniform, out);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,199 @@
+"""Each CUDA kernel alone against its plain PyTorch statement (tests/torch_ops.py), at sizes other
+than the engine's test models: widths and vocabularies that are no power of two, head sizes in steps
+of 16, odd head counts and groups, page sizes 8 and 16, rows that do not fill a tile."""
+import math
+
+import pytest
+import torch
+
+from gpu_util import assert_close, make_paged_batch
+from torch_ops import TorchOps
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+REF = TorchOps()
+
+
+@pytest.fixture(scope="module")
+def K():
+    from nanoinfer_b200.csrc.lib import load_kernels
+    return load_kernels()
+
+
+def rnd(shape, dtype, seed, scale=1.0, device="cuda"):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(device)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,hidden,vocab", [(1, 40, 11), (37, 896, 1000), (5, 1000, 503)])
+def test_embed(K, dtype, m, hidden, vocab):
+    table = rnd((vocab, hidden), dtype, 1)
+    ids = torch.randint(0, vocab, (m,), generator=torch.Generator().manual_seed(2)).int().cuda()
+    out, ref = torch.empty(m, hidden, device="cuda"), torch.empty(m, hidden, device="cuda")
+    K.embed(ids, table, out)
+    REF.embed(ids, table, ref)
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 64, 1e-6), (33, 896, 1e-5), (7, 1000, 1e-3), (300, 24, 1e-6)])
+def test_rmsnorm(K, dtype, rows, hidden, eps):
+    x = rnd((rows, hidden), torch.float32, 3, scale=3.0)
+    gain = 1 + 0.1 * rnd((hidden,), torch.float32, 4)
+    out, ref = torch.empty(rows, hidden, dtype=dtype, device="cuda"), torch.empty(rows, hidden, dtype=dtype, device="cuda")
+    K.rmsnorm(x, gain, eps, out, None)
+    REF.rmsnorm(x, gain, eps, ref, None)
+    assert_close(out, ref, dtype, "rmsnorm")
+    sel = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device="cuda")
+    out2, ref2 = torch.empty(3, hidden, dtype=dtype, device="cuda"), torch.empty(3, hidden, dtype=dtype, device="cuda")
+    K.rmsnorm(x, gain, eps, out2, sel)
+    REF.rmsnorm(x, gain, eps, ref2, sel)
+    assert_close(out2, ref2, dtype, "rmsnorm rows")
+    assert torch.equal(out2, out[sel.long()])   # a row's result does not depend on the batch
+
+
+def _ref_linear_f64(a, w, bias):
+    y = a.double() @ w.double().t()
+    return y if bias is None else y + bias.double()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 503, 192), (3, 64, 64), (65, 130, 72), (200, 896, 896), (17, 1000, 344), (2, 9, 5)])
+def test_linear_modes(K, dtype, m, n, k):
+    a, w = rnd((m, k), dtype, 5), rnd((n, k), dtype, 6, scale=0.05)
+    bias = rnd((n,), torch.float32, 7)
+    ref = _ref_linear_f64(a, w, bias)
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    K.linear(a, w, bias, out, "store")
+    assert_close(out, ref.to(dtype) if dtype == torch.bfloat16 else ref, dtype, "linear store")
+    out32 = torch.empty(m, n, device="cuda")
+    K.linear(a, w, None, out32, "f32")
+    assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "linear f32")
+    res = rnd((m, n), torch.float32, 8)
+    acc = res.clone()
+    K.linear(a, w, None, acc, "add")
+    assert_close(acc, res.double() + _ref_linear_f64(a, w, None), torch.float32, "linear add")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_rows_do_not_depend_on_batch(K, dtype):
+    a, w = rnd((77, 200), dtype, 9), rnd((150, 200), dtype, 10, scale=0.05)
+    full = torch.empty(77, 150, device="cuda")
+    K.linear(a, w, None, full, "f32")
+    for lo, hi in ((0, 1), (5, 8), (60, 77)):
+        part = torch.empty(hi - lo, 150, device="cuda")
+        K.linear(a[lo:hi].contiguous(), w, None, part, "f32")
+        assert torch.equal(part, full[lo:hi])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,inter,k", [(1, 320, 192), (70, 200, 144), (9, 4864, 896)])
+def test_linear_swiglu(K, dtype, m, inter, k):
+    a, w = rnd((m, k), dtype, 11), rnd((2 * inter, k), dtype, 12, scale=0.08)
+    out, ref = torch.empty(m, inter, dtype=dtype, device="cuda"), torch.empty(m, inter, dtype=dtype, device="cuda")
+    K.linear_swiglu(a, w, out)
+    REF.linear_swiglu(a, w, ref)
+    assert_close(out, ref, dtype, "swiglu")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,rot,page", [(4, 2, 16, 16, 16), (6, 1, 32, 32, 8), (3, 3, 48, 48, 8),
+                                                        (14, 2, 64, 64, 16), (5, 5, 80, 32, 4), (2, 1, 128, 128, 64)])
+def test_rope_store(K, dtype, heads, kv_heads, hd, rot, page):
+    from nanoinfer_b200.parts.position import rotary_tables
+    q_lens, before = [5, 1, 19], [0, 37, 11]
+    num_pages = 40
+    ctx, bt = make_paged_batch(q_lens, before, page, num_pages, "cuda", seed=1)
+    m = sum(q_lens)
+    cos, sin = rotary_tables(128, rot, 10000.0)
+    rotary = (cos.cuda(), sin.cuda(), rot)
+    qkv = rnd((m, (heads + 2 * kv_heads) * hd), dtype, 13)
+    qkv_ref = qkv.clone()
+    shape = (num_pages, kv_heads, page, hd)
+    kp, vp = torch.zeros(shape, dtype=dtype, device="cuda"), torch.zeros(shape, dtype=dtype, device="cuda")
+    kr, vr = torch.zeros_like(kp), torch.zeros_like(vp)
+    K.rope_store(qkv, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, kp, vp, True)
+    REF.rope_store(qkv_ref, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, kr, vr, True)
+    assert_close(qkv, qkv_ref, dtype, "rope qkv")
+    assert_close(kp, kr, dtype, "k pages")
+    assert torch.equal(vp, vr)
+    # without writing, pages stay as they are
+    kp2 = torch.zeros_like(kp)
+    q2 = qkv_ref.clone()
+    K.rope_store(q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, None, bt, page, kp2, kp2, False)
+    assert torch.equal(q2, qkv_ref) and not kp2.any()
+
+
+def _fill_cache(ctx, bt, page, num_pages, kv_heads, hd, dtype, seed):
+    """Random keys and values for every position of every request, in pages."""
+    shape = (num_pages, kv_heads, page, hd)
+    kp, vp = rnd(shape, dtype, seed), rnd(shape, dtype, seed + 1)
+    return kp, vp
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,page,window", [
+    (4, 2, 16, 16, 0), (6, 1, 32, 8, 0), (3, 3, 48, 8, 24), (14, 2, 64, 16, 0), (7, 7, 80, 4, 0),
+    (8, 2, 128, 16, 100), (2, 1, 256, 16, 0), (5, 1, 96, 32, 7)])
+def test_attention_mixed_batch(K, dtype, heads, kv_heads, hd, page, window):
+    q_lens, before = [1, 33, 2, 1], [130, 0, 77, 0]
+    num_pages = 64
+    ctx, bt = make_paged_batch(q_lens, before, page, num_pages * (16 // min(page, 16)), "cuda", seed=2)
+    kp, vp = _fill_cache(ctx, bt, page, kp_pages := bt.max().item() + 1, kv_heads, hd, dtype, 20)
+    m = sum(q_lens)
+    qkv = rnd((m, (heads + 2 * kv_heads) * hd), dtype, 22)
+    out, ref = (torch.empty(m, heads * hd, dtype=dtype, device="cuda") for _ in range(2))
+    scale = 1.0 / math.sqrt(hd)
+    K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    assert_close(out, ref, dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 50])
+def test_attention_finds_one_far_key(K, dtype, window):
+    """One key among hundreds carries the whole score: the result must be that key's value. Placed at
+    the first position, at page edges, at the window's first key, at the query's own position; and just
+    outside the window, where it must NOT be seen."""
+    heads, kv_heads, hd, page = 4, 2, 64, 16
+    ctx_len = 403
+    ctx, bt = make_paged_batch([1], [ctx_len - 1], page, 40, "cuda", seed=3)
+    pos = ctx_len - 1
+    lo = max(0, pos - window + 1) if window else 0
+    spots = [lo, lo + 1, pos, pos - 1, (pos // page) * page, (pos // page) * page - 1]
+    if window:
+        spots.append(lo - 1)            # invisible
+    else:
+        spots += [0, 15, 16, 17, 255, 256]
+    for spot in spots:
+        kp, vp = _fill_cache(ctx, bt, page, 40, kv_heads, hd, dtype, 30)
+        kp.mul_(0.05)
+        qkv = rnd((1, (heads + 2 * kv_heads) * hd), dtype, 31)
+        phys = bt[0, spot // page].item()
+        qv = qkv.view(1, heads + 2 * kv_heads, hd)
+        # key at `spot` of kv head 1 is 12 * (query head 3) / |q|: score ~ 12 * |q| * sqrt... dominates
+        q3 = qv[0, 3].float()
+        kp[phys, 1, spot % page] = (q3 / q3.norm() * 40.0).to(dtype)
+        out, ref = (torch.empty(1, heads * hd, dtype=dtype, device="cuda") for _ in range(2))
+        scale = 1.0 / math.sqrt(hd)
+        K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+        REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+        assert_close(out, ref, dtype, f"far key at {spot}")
+        o3 = out.view(heads, hd)[3].float()
+        v_spot = vp[phys, 1, spot % page].float()
+        seen = (o3 - v_spot).abs().max().item() < 0.05
+        assert seen == (spot >= lo), f"key at {spot}: seen={seen}, window starts at {lo}"
+
+
+@pytest.mark.parametrize("vocab", [11, 503, 151936])
+def test_argmax_first_maximum(K, vocab):
+    logits = rnd((5, vocab), torch.float32, 40)
+    logits[1, vocab // 2] = 50.0
+    logits[2, 3] = 60.0
+    logits[2, vocab - 1] = 60.0      # a tie: the first wins
+    logits[3, vocab - 1] = 70.0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    K.argmax(logits, out)
+    assert out.tolist() == torch.argmax(logits.cpu(), dim=-1).tolist()
+    assert out[2].item() == 3 and out[3].item() == vocab - 1
