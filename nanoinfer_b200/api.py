@@ -1,0 +1,62 @@
+"""The Python entry points, in the reference's manner.
+
+* ``load_model(model_dir, dtype=..., ...) -> Model`` (reference: ``nicpp.Model(weights_dir, mode, device)``,
+  cpp/bindings/nicpp.cpp:207-217; ``nanoinfer.weights.load_model``, nanoinfer/weights.py:25-71).
+* ``Model.generate(prompt_ids, max_tokens=20, params=SamplingParams(), seed=0, eos_id=-1) -> list[int]``
+  (cpp/bindings/nicpp.cpp:296-316; loop: cpp/src/generate.cpp:10-42).
+* ``generate(model, tokenizer, prompt, max_tokens=32, sampling=None) -> str`` (nanoinfer/generate.py:33-85).
+* ``Request`` and ``Scheduler`` for many requests (cpp/python/ni/scheduler.py).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+from .config.engine_config import EngineConfig
+from .engine.engine import Engine
+from .engine.scheduler import Request, Scheduler
+from .sampling.params import SamplingParams
+from .sampling.sampler import Sampler
+
+
+class Model:
+    """A loaded model with its cache and sampler: what requests are run on."""
+
+    def __init__(self, model_dir: str, engine_config: EngineConfig, ops=None):
+        self.engine = Engine(model_dir, engine_config, ops=ops)
+        self.config = self.engine.config
+        self.sampler = Sampler(self.engine.rt.ops, self.engine.device)
+        self.eos_token_id = self.engine.plan.eos_token_id
+
+    def generate(self, prompt_ids: List[int], max_tokens: int = 20, params: Optional[SamplingParams] = None,
+                 seed: int = 0, eos_id: int = -1) -> List[int]:
+        """Continue ``prompt_ids`` by up to ``max_tokens`` tokens; EOS ends generation and is not returned."""
+        params = params or SamplingParams()
+        if params.seed is not None:
+            seed = params.seed
+        sched = Scheduler(self)
+        sched.add(Request("generate", list(prompt_ids), max_tokens=max_tokens, temperature=params.temperature,
+                          top_k=params.k, top_p=params.p, repetition_penalty=params.repetition_penalty,
+                          seed=seed, eos_id=eos_id))
+        return sched.run()["generate"]
+
+
+def load_model(model_dir: str, dtype: str = "bfloat16", page_size: int = 16, num_pages: int = 0,
+               max_cache_tokens: int = 0, max_batch: int = 8, max_tokens_per_step: int = 2048,
+               device: str = "cuda:0", cuda_graphs: bool = True) -> Model:
+    if num_pages <= 0 and max_cache_tokens <= 0:
+        max_cache_tokens = 16384
+    cfg = EngineConfig(dtype=dtype, page_size=page_size, num_pages=num_pages, max_cache_tokens=max_cache_tokens,
+                       max_batch=max_batch, max_tokens_per_step=max_tokens_per_step, device=device,
+                       cuda_graphs=cuda_graphs)
+    return Model(model_dir, cfg)
+
+
+def generate(model: Model, tokenizer, prompt: str, max_tokens: int = 32,
+             sampling: Optional[SamplingParams] = None) -> str:
+    """Text in, text out. ``tokenizer`` needs ``encode(str) -> ids`` and ``decode(ids) -> str``."""
+    enc = tokenizer.encode(prompt)
+    ids = list(getattr(enc, "ids", enc))
+    eos = getattr(tokenizer, "eos_token_id", None)
+    out = model.generate(ids, max_tokens=max_tokens, params=sampling or SamplingParams(),
+                         eos_id=eos if eos is not None else -1)
+    return tokenizer.decode(out)

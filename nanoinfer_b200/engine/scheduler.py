@@ -1,0 +1,266 @@
+"""Continuous batching above the step function.
+
+Every step takes, under a token budget, one token from each request that is decoding and a
+portion of the prompt of each request that is still being prefilled, admits waiting requests
+into free places, runs them all as ONE batch, samples where a request's last known token was in
+the batch, and finishes and frees what is done.
+
+The reference's scheduler (cpp/python/ni/scheduler.py:200-375) has the same queues, stop rules and
+counters, but prefills each admitted prompt whole and alone and reserves the worst case of pages up
+front. Here pages are taken step by step. When the pool cannot hold a step's new tokens, the request
+admitted last is preempted: its pages are given back, it returns to the head of the waiting queue
+and is later recomputed from its prompt and the tokens it had generated.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Deque, Dict, List, Optional, Sequence as Seq, Tuple
+
+from ..cache.pages import OutOfPages
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import SampleRow
+from .engine import StepEntry
+
+
+@dataclass
+class Request:
+    """A generation request; the reference's names and defaults (cpp/python/ni/scheduler.py:37-51)."""
+    request_id: str
+    prompt_ids: List[int]
+    max_tokens: int = 32
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0
+    seed: int = 0
+    eos_id: int = -1      # -1: the model's eos_token_id
+
+    def sampling(self) -> SamplingParams:
+        return SamplingParams(temperature=self.temperature, top_k=self.top_k, top_p=self.top_p,
+                              repetition_penalty=self.repetition_penalty, seed=self.seed)
+
+
+class State(Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+class Sequence:
+    """A request at run time: what it has generated, what of it is in the cache."""
+
+    def __init__(self, req: Request, order: int):
+        self.req = req
+        self.params = req.sampling()
+        self.output_ids: List[int] = []
+        self.state = State.WAITING
+        self.cache = None          # RequestCache while running
+        self.fed = 0               # tokens of (prompt + output) that the cache holds
+        self.order = order         # admission order; the largest is preempted first
+        self.preemptions = 0
+
+    @property
+    def all_ids(self) -> List[int]:
+        return self.req.prompt_ids + self.output_ids
+
+    @property
+    def pending(self) -> int:
+        return len(self.req.prompt_ids) + len(self.output_ids) - self.fed
+
+
+@dataclass
+class PlannedEntry:
+    seq: Sequence
+    start: int          # first token (index into all_ids) of the portion
+    count: int
+    samples: bool       # the portion ends at the last known token: a token is sampled from its last row
+
+
+@dataclass
+class StepPlan:
+    entries: List[PlannedEntry] = field(default_factory=list)
+    admitted: List[Sequence] = field(default_factory=list)
+    preempted: List[Sequence] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(e.count for e in self.entries)
+
+
+class Scheduler:
+    """``add()`` requests, then ``run()``; or call ``step()`` yourself.
+
+    ``model`` offers ``engine`` (with ``cache``, ``open``, ``close``, ``step``), ``sampler`` and
+    ``eos_token_id``."""
+
+    def __init__(self, model, max_batch: Optional[int] = None, max_tokens_per_step: Optional[int] = None):
+        self.model = model
+        self.engine = model.engine
+        ec = self.engine.engine_config
+        self.max_batch = min(max_batch or ec.max_batch, ec.max_batch)
+        self.max_tokens_per_step = max_tokens_per_step or ec.max_tokens_per_step
+        if self.max_tokens_per_step < self.max_batch:
+            raise ValueError("max_tokens_per_step must be at least max_batch (one token for each decoding request)")
+        self.waiting: Deque[Sequence] = deque()
+        self.running: List[Sequence] = []
+        self.finished: Dict[str, List[int]] = {}
+        self._eos_default = model.eos_token_id
+        self._order = 0
+        self.steps = 0
+        self.peak_batch = 0
+        self.tokens_run = 0
+        self.preemptions = 0
+
+    # ---- queue ----------------------------------------------------------------------------
+    def add(self, req: Request) -> None:
+        cache = self.engine.cache
+        worst = len(req.prompt_ids) + max(req.max_tokens, 1)
+        need = -(-worst // cache.page_size)
+        if cache.groups and need > cache.num_pages:
+            raise ValueError(f"request {req.request_id} needs {need} pages; the pool has {cache.num_pages} "
+                             f"(raise num_pages or page_size)")
+        if worst > self.engine.max_positions + 1 and len(req.prompt_ids) >= self.engine.max_positions:
+            raise ValueError(f"request {req.request_id}: prompt of {len(req.prompt_ids)} tokens exceeds the "
+                             f"model's context length {self.engine.max_positions}")
+        req.sampling()  # validates
+        self._order += 1
+        self.waiting.append(Sequence(req, self._order))
+
+    def has_work(self) -> bool:
+        return bool(self.running or self.waiting)
+
+    def _finish(self, seq: Sequence) -> None:
+        seq.state = State.FINISHED
+        self.finished[seq.req.request_id] = seq.output_ids
+        if seq.cache is not None:
+            self.engine.close(seq.cache)
+            seq.cache = None
+
+    def _accept(self, seq: Sequence, tok: int) -> bool:
+        """Stop rules, in the reference's order (cpp/python/ni/scheduler.py:250-259): EOS is checked before
+        the token is emitted, so it is not part of the output; then max_tokens."""
+        eos = seq.req.eos_id if seq.req.eos_id >= 0 else self._eos_default
+        if eos >= 0 and tok == eos:
+            return True
+        seq.output_ids.append(tok)
+        if len(seq.all_ids) >= self.engine.max_positions:
+            return True            # no position left for another token
+        return len(seq.output_ids) >= seq.req.max_tokens
+
+    # ---- planning: decisions only, nothing runs -------------------------------------------
+    def _pages_for_new(self, tokens: int) -> int:
+        return -(-tokens // self.engine.cache.page_size)
+
+    def plan(self) -> StepPlan:
+        cache = self.engine.cache
+        plan = StepPlan()
+        budget = self.max_tokens_per_step
+
+        # 1. running requests: decoding ones first (one token each), then prompts in admission order
+        order = sorted(self.running, key=lambda s: (s.pending > 1, s.order))
+        for seq in order:
+            if budget <= 0:
+                break
+            n = min(seq.pending, budget)
+            plan.entries.append(PlannedEntry(seq, seq.fed, n, samples=(n == seq.pending)))
+            budget -= n
+
+        # 2. pages for them; preempt the request admitted last until the step fits
+        def fits() -> bool:
+            return cache.fits([(e.seq.cache, e.count) for e in plan.entries])
+        while plan.entries and not fits():
+            victim = max((e.seq for e in plan.entries), key=lambda s: s.order)
+            if len(self.running) == 1:
+                raise OutOfPages(f"request {victim.req.request_id} alone does not fit the cache pool")
+            plan.entries = [e for e in plan.entries if e.seq is not victim]
+            plan.preempted.append(victim)
+            self._preempt(victim)
+
+        # 3. admit waiting requests, first come first served, while places, budget and pages last
+        free = [cache.num_free(g) for g in range(len(cache.groups))]
+        for e in plan.entries:
+            for g, k in enumerate(cache.pages_needed(e.seq.cache, e.count)):
+                free[g] -= k
+        while self.waiting and len(self.running) < self.max_batch and budget > 0 and not plan.preempted:
+            seq = self.waiting[0]
+            if not seq.req.prompt_ids:
+                self.waiting.popleft()
+                self.finished[seq.req.request_id] = []
+                seq.state = State.FINISHED
+                continue
+            # the whole of what is known of the request, and one more token, must fit what is free now
+            need = self._pages_for_new(len(seq.all_ids) + 1)
+            if any(need > f for f in free):
+                break       # head of the line waits; nobody skips ahead
+            self.waiting.popleft()
+            seq.cache = self.engine.open(seq.req.request_id)
+            seq.state = State.RUNNING
+            seq.fed = 0
+            self.running.append(seq)
+            plan.admitted.append(seq)
+            n = min(seq.pending, budget)
+            plan.entries.append(PlannedEntry(seq, 0, n, samples=(n == seq.pending)))
+            budget -= n
+            free = [f - need for f in free]
+        return plan
+
+    def _preempt(self, seq: Sequence) -> None:
+        self.engine.close(seq.cache)
+        seq.cache = None
+        seq.fed = 0
+        seq.state = State.WAITING
+        seq.preemptions += 1
+        self.preemptions += 1
+        self.running.remove(seq)
+        self.waiting.appendleft(seq)
+
+    # ---- one step -------------------------------------------------------------------------
+    def step(self) -> StepPlan:
+        plan = self.plan()
+        if plan.entries:
+            entries, rows, samplers = [], [], []
+            for e in plan.entries:
+                ids = e.seq.all_ids[e.start:e.start + e.count]
+                wants = e.samples and e.seq.req.max_tokens > 0
+                entries.append(StepEntry(e.seq.cache, ids, [e.count - 1] if wants else []))
+                if wants:
+                    samplers.append(e.seq)
+                    rows.append(SampleRow(e.seq.params, e.seq.all_ids if e.seq.params.repetition_penalty != 1.0 else None,
+                                          len(e.seq.output_ids), e.seq.req.seed))
+            logits = self.engine.step(entries)
+            for e in plan.entries:
+                e.seq.fed += e.count
+            toks = self.model.sampler.sample(logits, rows) if rows else []
+            for seq, tok in zip(samplers, toks):
+                if self._accept(seq, int(tok)):
+                    self._finish(seq)
+            for e in plan.entries:      # prompts that wanted no token at all
+                if e.samples and e.seq.req.max_tokens <= 0 and e.seq.state is State.RUNNING:
+                    self._finish(e.seq)
+            self.tokens_run += plan.num_tokens
+        self.running = [s for s in self.running if s.state is State.RUNNING]
+        self.peak_batch = max(self.peak_batch, len(plan.entries))
+        self.steps += 1
+        return plan
+
+    def cancel(self, request_id: str) -> bool:
+        """Queued: dropped with an empty output. Running: finished with what it has; pages are freed."""
+        for seq in self.waiting:
+            if seq.req.request_id == request_id:
+                self.waiting.remove(seq)
+                self.finished[request_id] = seq.output_ids
+                seq.state = State.FINISHED
+                return True
+        for seq in self.running:
+            if seq.req.request_id == request_id:
+                self._finish(seq)
+                self.running = [s for s in self.running if s.state is State.RUNNING]
+                return True
+        return False
+
+    def run(self) -> Dict[str, List[int]]:
+        while self.has_work():
+            self.step()
+        return self.finished
