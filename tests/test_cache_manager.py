@@ -1,0 +1,127 @@
+"""The cache manager on the host: no page lost, held twice or freed twice, under random orders of
+requests; windows give pages back while a request runs; state slots."""
+import random
+
+import pytest
+
+from nanoinfer_b200.cache import CacheManager, GroupSpec, OutOfPages, OutOfSlots, PagePool
+
+
+def test_pool_hands_out_in_order_and_refuses_double_free():
+    pool = PagePool(3)
+    assert [pool.allocate() for _ in range(3)] == [0, 1, 2]
+    with pytest.raises(OutOfPages):
+        pool.allocate()
+    pool.free(1)
+    with pytest.raises(RuntimeError, match="freed twice"):
+        pool.free(1)
+    with pytest.raises(RuntimeError, match="incref of free"):
+        pool.incref(1)
+    with pytest.raises(IndexError):
+        pool.free(7)
+    assert pool.allocate() == 1          # a freed page is used again
+    pool.incref(0)
+    pool.free(0)
+    assert pool.num_free == 0
+    pool.free(0)
+    assert pool.num_free == 1
+
+
+def groups(window=0):
+    g = [GroupSpec(2, 16, 0, (0, 1))]
+    if window:
+        g.append(GroupSpec(2, 16, window, (2,)))
+    return g
+
+
+def test_extend_commit_close():
+    m = CacheManager(groups(), num_pages=6, page_size=8, max_requests=2)
+    a = m.open("a")
+    assert m.pages_needed(a, 17) == [3]
+    m.extend(a, 17)
+    assert a.tables[0] == [0, 1, 2] and a.length == 0
+    m.commit(a, 17)
+    assert m.pages_needed(a, 7) == [0] and m.pages_needed(a, 8) == [1]
+    b = m.open("b")
+    with pytest.raises(OutOfSlots):
+        m.open("c")
+    with pytest.raises(KeyError):
+        m.open("a")
+    with pytest.raises(OutOfPages):
+        m.extend(b, 25)
+    assert b.tables[0] == [] and m.num_free() == 3       # all or nothing
+    assert m.fits([(a, 8), (b, 16)]) and not m.fits([(a, 8), (b, 17)])
+    m.extend(b, 24)
+    m.commit(b, 24)
+    m.check()
+    m.close(a)
+    with pytest.raises(RuntimeError, match="closed twice"):
+        m.close(a)
+    assert m.num_free() == 3
+    c = m.open("c")
+    assert c.slot == a.slot
+    m.extend(c, 20)
+    assert sorted(c.tables[0]) == [0, 1, 2]              # pages are used again
+    m.check()
+
+
+def test_window_group_returns_pages_while_running():
+    m = CacheManager(groups(window=20), num_pages=16, page_size=8, max_requests=2)
+    r = m.open("r")
+    m.extend(r, 64)
+    assert len(r.tables[0]) == 8 and len(r.tables[1]) == 8
+    m.commit(r, 64)
+    # positions >= 64 read keys >= 64 - 20 + 1 = 45: pages 0..4 (positions 0..39) are dead in the window group
+    assert r.tables[1][:5] == [-1] * 5 and all(p >= 0 for p in r.tables[1][5:])
+    assert all(p >= 0 for p in r.tables[0])
+    assert m.num_free(0) == 8 and m.num_free(1) == 13
+    for _ in range(40):
+        m.extend(r, 1)
+        m.commit(r, 1)
+        m.check()
+        assert r.pages_held(1) <= 4                      # ceil((20 - 1) / 8) + 1 pages at most
+    m.close(r)
+    assert m.num_free(0) == 16 and m.num_free(1) == 16
+    m.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_every_page_accounted_for(seed):
+    rng = random.Random(seed)
+    window = rng.choice([0, 5, 33])
+    m = CacheManager(groups(window), num_pages=rng.choice([7, 20, 41]), page_size=rng.choice([1, 4, 16]),
+                     max_requests=4)
+    live, counter = [], 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and len(live) < 4:
+            counter += 1
+            live.append(m.open(counter))
+        elif op < 0.45 and live:
+            m.close(live.pop(rng.randrange(len(live))))
+        elif live:
+            rc = rng.choice(live)
+            n = rng.choice([1, 1, 1, 2, 7, 30])
+            free_before = [m.num_free(g) for g in range(len(m.groups))]
+            tables_before = [list(t) for t in rc.tables]
+            try:
+                m.extend(rc, n)
+                m.commit(rc, n)
+            except OutOfPages:
+                assert [m.num_free(g) for g in range(len(m.groups))] == free_before
+                assert [list(t) for t in rc.tables] == tables_before
+        m.check()
+    for rc in live:
+        m.close(rc)
+    m.check()
+    assert all(m.num_free(g) == m.num_pages for g in range(len(m.groups)))
+
+
+def test_group_planning_from_needs():
+    from nanoinfer_b200.cache.storage import plan_groups
+    from nanoinfer_b200.parts.base import CacheNeed, StateNeed
+    needs = [(CacheNeed(2, 16, 0), None, None), (CacheNeed(2, 16, 8), None, None), (None, StateNeed((4,)), None),
+             (CacheNeed(2, 16, 0), None, None), (None, None, 1)]
+    g, entry_group = plan_groups(needs)
+    assert [(x.window, x.entries) for x in g] == [(0, (0, 3)), (8, (1,))]
+    assert entry_group == [0, 1, -1, 0, 1]

@@ -1,0 +1,148 @@
+"""The scheduler's decisions, and its results against generation alone, on the CPU with the kernels
+replaced by their plain PyTorch statements."""
+import pytest
+import torch
+
+from plain_qwen2 import PlainModel
+from torch_ops import TorchOps
+
+from nanoinfer_b200 import Model, Request, SamplingParams, Scheduler
+from nanoinfer_b200.config import EngineConfig
+
+
+def make_model(model_dir, page, num_pages=64, max_batch=4, budget=64):
+    cfg = EngineConfig(dtype="float32", page_size=page, num_pages=num_pages, max_batch=max_batch,
+                       max_tokens_per_step=budget, device="cpu")
+    return Model(model_dir, cfg, ops=TorchOps())
+
+
+def prompts(vocab, lengths, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
+
+
+def test_greedy_equals_plain_full_recompute(model_dirs):
+    d, page = model_dirs["A"]
+    model = make_model(d, page)
+    plain = PlainModel(d)
+    for p in prompts(256, [1, 7, 33]):
+        assert model.generate(p, max_tokens=16) == plain.greedy(p, 16)
+    assert model.engine.cache.num_free() == 64
+    model.engine.cache.check()
+
+
+def test_budget_cuts_prompts_and_decodes_come_first(model_dirs):
+    d, page = model_dirs["A"]
+    model = make_model(d, page, budget=10, max_batch=3)
+    s = Scheduler(model)
+    a, b = prompts(256, [25, 8], seed=1)
+    s.add(Request("a", a, max_tokens=4))
+    plan = s.step()
+    assert [(e.seq.req.request_id, e.start, e.count, e.samples) for e in plan.entries] == [("a", 0, 10, False)]
+    s.add(Request("b", b, max_tokens=4))
+    plan = s.step()      # a goes on with its prompt; nothing is left for b
+    assert [(e.seq.req.request_id, e.start, e.count) for e in plan.entries] == [("a", 10, 10)]
+    plan = s.step()      # a's last 5 prompt tokens -> first token; b gets the other 5
+    assert [(e.seq.req.request_id, e.start, e.count, e.samples) for e in plan.entries] == \
+        [("a", 20, 5, True), ("b", 0, 5, False)]
+    plan = s.step()      # a decodes (first in the batch), b finishes its prompt
+    assert [(e.seq.req.request_id, e.count, e.samples) for e in plan.entries] == [("a", 1, True), ("b", 3, True)]
+    out = s.run()
+    assert len(out["a"]) == 4 and len(out["b"]) == 4
+    plain = PlainModel(d)
+    assert out["a"] == plain.greedy(a, 4) and out["b"] == plain.greedy(b, 4)
+
+
+def test_continuous_batching_equals_alone_and_frees_everything(model_dirs):
+    d, page = model_dirs["B"]
+    plain = PlainModel(d)
+    ps = prompts(503, [2, 9, 17, 64, 100], seed=2)
+    alone = [plain.greedy(p, 6) for p in ps]
+    for budget, max_batch, num_pages in ((13, 3, 40), (64, 5, 40), (5, 2, 16)):
+        model = make_model(d, page, num_pages=num_pages, max_batch=max_batch, budget=budget)
+        s = Scheduler(model)
+        for i, p in enumerate(ps):
+            s.add(Request(f"r{i}", p, max_tokens=6))
+        out = s.run()
+        assert [out[f"r{i}"] for i in range(5)] == alone, (budget, max_batch)
+        assert s.peak_batch <= max_batch
+        model.engine.cache.check()
+        assert model.engine.cache.num_free() == num_pages and not model.engine.cache.live
+
+
+def test_when_pages_run_out_the_last_admitted_is_preempted_and_recomputed(model_dirs):
+    d, page = model_dirs["B"]             # page 8
+    plain = PlainModel(d)
+    ps = prompts(503, [30, 30, 30], seed=3)
+    # 14 pages = 112 positions: three prompts of 30 are admitted (4 pages each + watermark), but their
+    # 20 decoded tokens each (3 more pages each) cannot all be held.
+    model = make_model(d, page, num_pages=14, max_batch=3, budget=64)
+    s = Scheduler(model)
+    for i, p in enumerate(ps):
+        s.add(Request(f"r{i}", p, max_tokens=20))
+    preempted = []
+    while s.has_work():
+        plan = s.step()
+        preempted += [v.req.request_id for v in plan.preempted]
+        model.engine.cache.check()
+    assert preempted and set(preempted) <= {"r1", "r2"} and "r0" not in preempted
+    for i, p in enumerate(ps):
+        assert s.finished[f"r{i}"] == plain.greedy(p, 20)
+    assert model.engine.cache.num_free() == 14
+
+
+def test_admission_errors_and_edge_cases(model_dirs):
+    d, page = model_dirs["A"]
+    model = make_model(d, page, num_pages=4)
+    s = Scheduler(model)
+    with pytest.raises(ValueError, match="pages"):
+        s.add(Request("big", list(range(60)), max_tokens=10))
+    with pytest.raises(ValueError):
+        s.add(Request("bad", [1], temperature=-1.0))
+    s.add(Request("empty", [], max_tokens=5))
+    s.add(Request("none", [1, 2, 3], max_tokens=0))
+    out = s.run()
+    assert out["empty"] == [] and out["none"] == []
+    assert model.engine.cache.num_free() == 4
+
+
+def test_eos_ends_generation_and_is_not_emitted(model_dirs):
+    d, page = model_dirs["B"]
+    model = make_model(d, page)
+    p = prompts(503, [5], seed=4)[0]
+    first = PlainModel(d).greedy(p, 12)
+    k = next(i for i in range(1, 12) if first[i] not in first[:i])    # the first new token after the first
+    assert model.generate(p, max_tokens=12, eos_id=first[k]) == first[:k]
+    assert model.generate(p, max_tokens=12, eos_id=first[0]) == []
+
+
+def test_cancel(model_dirs):
+    d, page = model_dirs["A"]
+    model = make_model(d, page, max_batch=1)
+    s = Scheduler(model)
+    s.add(Request("x", [1, 2, 3], max_tokens=50))
+    s.add(Request("y", [4, 5], max_tokens=50))
+    for _ in range(4):
+        s.step()
+    assert s.cancel("y") and s.finished["y"] == []
+    assert s.cancel("x") and len(s.finished["x"]) == 4
+    assert not s.cancel("x") and not s.has_work()
+    assert model.engine.cache.num_free() == 64
+
+
+def test_sampling_is_reproducible_and_independent_of_the_batch(model_dirs):
+    d, page = model_dirs["B"]
+    ps = prompts(503, [9, 17, 40], seed=5)
+    def run(max_batch, budget):
+        model = make_model(d, page, max_batch=max_batch, budget=budget)
+        s = Scheduler(model)
+        for i, p in enumerate(ps):
+            s.add(Request(f"r{i}", p, max_tokens=12, temperature=0.7, seed=11 + i, top_k=50, top_p=0.9))
+        return s.run()
+    a, b = run(1, 64), run(3, 7)
+    assert a == b
+    model = make_model(d, page)
+    alone = model.generate(ps[1], max_tokens=12, params=SamplingParams(temperature=0.7, top_k=50, top_p=0.9, seed=12))
+    assert alone == a["r1"]
+    other = model.generate(ps[1], max_tokens=12, params=SamplingParams(temperature=0.7, top_k=50, top_p=0.9, seed=13))
+    assert other != alone

@@ -87,3 +87,28 @@ class TorchOps:
 
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
+
+    def repetition_penalty(self, logits, seen, seen_start, penalty):
+        starts = seen_start.tolist()
+        for r in range(logits.shape[0]):
+            p = float(penalty[r])
+            if p == 1.0:
+                continue
+            ids = seen[starts[r]:starts[r + 1]].long()
+            s = logits[r, ids]
+            logits[r, ids] = torch.where(s > 0, s / p, s * p)
+
+    def sample(self, logits, temperature, top_k, top_p, uniform, out):
+        """Inverse CDF in vocabulary order over the distribution of tests/plain_qwen2.py."""
+        import numpy as np
+        from plain_qwen2 import sampling_distribution
+        for r in range(logits.shape[0]):
+            probs = sampling_distribution(logits[r].double().cpu().numpy(), [], float(temperature[r]),
+                                          int(top_k[r]), float(top_p[r]), 1.0)
+            cdf = np.cumsum(probs)
+            i = int(np.searchsorted(cdf, float(uniform[r]) * cdf[-1], side="right"))
+            kept = np.nonzero(probs > 0)[0]
+            i = min(i, int(kept[-1]))
+            while probs[i] == 0:
+                i += 1
+            out[r] = i
