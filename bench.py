@@ -1,0 +1,365 @@
+#!/usr/bin/env python3
+"""Headline benchmark: decode throughput of the Qwen2.5-0.5B shape (random weights, bfloat16) at a
+batch of 8 and a context of 4,096 tokens on ONE B200, with prefill of 2,048 tokens, the decode
+roofline and batch 1 / 64 points on the same JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch. ``value`` is decoded tokens per second over K steps
+timed with CUDA events on the launching stream; ``e2e`` is the same through the Python entry point
+(the scheduler: host token ids in, sampled ids out, every step). Inputs larger than L2: every step
+reads all weights (~1 GB) and the live requests' cache, several times the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Layer sizes of the benchmark model: BASELINE.json configs[2], the Qwen2.5-0.5B shape.
+MODEL = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 24, "hidden_size": 896,
+    "num_attention_heads": 14, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 4864,
+    "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 32768, "use_sliding_window": False, "hidden_act": "silu",
+    "torch_dtype": "bfloat16",
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if isinstance(d.get(k), (int, float)) and d[k] > 0:
+                    out[k] = float(d[k])
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(layers: int) -> dict:
+    """Matrix parameters, bytes a decode step has to read, FLOPs of a prefill, from the sizes."""
+    m = MODEL
+    h, inter, v = m["hidden_size"], m["intermediate_size"], m["vocab_size"]
+    nq, nkv, hd = m["num_attention_heads"], m["num_key_value_heads"], m["head_dim"]
+    per_layer = (nq + 2 * nkv) * hd * h + h * nq * hd + 3 * h * inter
+    return {
+        "per_layer_params": per_layer,
+        "weight_bytes": 2 * (layers * per_layer + v * h),           # every matrix once, head included
+        "kv_bytes_per_token": 2 * layers * nkv * hd * 2,
+        "prefill_flops": lambda t: 2.0 * t * layers * per_layer + 2.0 * v * h
+        + layers * 4.0 * nq * hd * t * (t + 1) / 2.0,
+    }
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+    from nanoinfer_b200 import Request, Scheduler, load_model
+    from nanoinfer_b200.engine import StepEntry
+    from nanoinfer_b200.registry import config_from_json_dict
+    from nanoinfer_b200.weights import write_random_model
+
+    pk = peaks()
+    layers = args.layers or MODEL["num_hidden_layers"]
+    cfg_json = dict(MODEL, num_hidden_layers=layers)
+    nums = model_numbers(layers)
+    ctx, batch, steps, warmup = args.context, args.batch, args.steps, max(3, args.warmup)
+    rng = np.random.default_rng(0)
+    vocab = MODEL["vocab_size"]
+
+    tmp = tempfile.mkdtemp(prefix="nanoinfer_b200_bench_")
+    t0 = time.time()
+    write_random_model(config_from_json_dict(cfg_json), tmp, seed=0)
+    max_batch = max(batch, 64)
+    page = 16
+    num_pages = max_batch * (-(-ctx // page) + 1) + 8
+    model = load_model(tmp, dtype="bfloat16", page_size=page, num_pages=num_pages, max_batch=max_batch,
+                       max_tokens_per_step=4096)
+    engine, ops = model.engine, model.engine.rt.ops
+    print(f"[bench] model ready in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+
+    def fill(n_req: int, length: int):
+        """n_req live requests holding ``length`` random tokens each."""
+        reqs = [engine.open(f"b{n_req}_{i}") for i in range(n_req)]
+        for rc in reqs:
+            done = 0
+            while done < length:
+                n = min(2048, length - done)
+                engine.step([StepEntry(rc, rng.integers(0, vocab, n).tolist(), [])])
+                done += n
+        return reqs
+
+    def decode_timed(reqs, n_warm: int, n_steps: int, sample_clocks: bool = False):
+        """Device time of n_steps decode steps (one token for every request, greedy pick on the device)."""
+        out = torch.empty(len(reqs), dtype=torch.int32, device=engine.device)
+        toks = [rng.integers(0, vocab, len(reqs)).tolist() for _ in range(n_warm + n_steps)]
+
+        def one(i):
+            logits = engine.step([StepEntry(rc, [toks[i][j]], [0]) for j, rc in enumerate(reqs)])
+            ops.argmax(logits, out)
+        for i in range(n_warm):
+            one(i)
+        torch.cuda.synchronize()
+        l0 = ops.launches + engine.graph_launches
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler()
+        if sample_clocks:
+            sampler.__enter__()
+        start.record()
+        for i in range(n_warm, n_warm + n_steps):
+            one(i)
+        end.record()
+        torch.cuda.synchronize()
+        if sample_clocks:
+            sampler.__exit__()
+        ms = start.elapsed_time(end)
+        return ms / n_steps, ops.launches + engine.graph_launches - l0, (sampler.summary() if sample_clocks else None)
+
+    def close_all(reqs):
+        for rc in reqs:
+            engine.close(rc)
+
+    # ---- prefill of 2,048 tokens ----------------------------------------------------------
+    t_pre = args.prefill_tokens
+    pre_ms = []
+    for i in range(3 + 3):
+        rc = engine.open(f"p{i}")
+        ids = rng.integers(0, vocab, t_pre).tolist()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        engine.step([StepEntry(rc, ids, [t_pre - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            pre_ms.append(s.elapsed_time(e))
+        engine.close(rc)
+    pre = statistics.median(pre_ms)
+    prefill = {"value": round(t_pre / (pre / 1e3), 1), "tokens": t_pre, "ms": round(pre, 3),
+               "frac": round(nums["prefill_flops"](t_pre) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode points at batch 1 and 64 --------------------------------------------------
+    points = {}
+    for b in (1, 64):
+        n_w, n_s = 4, min(steps, 32)
+        reqs = fill(b, ctx - n_w - n_s - 1)
+        ms, _, _ = decode_timed(reqs, n_w, n_s)
+        points[f"decode_b{b}"] = round(b / (ms / 1e3), 1)
+        close_all(reqs)
+
+    # ---- the headline: batch 8 (default), device-timed -------------------------------------
+    reqs = fill(batch, ctx - warmup - steps - 1)
+    ms_step, launches, clocks = decode_timed(reqs, warmup, steps, sample_clocks=True)
+    mean_ctx = ctx - steps / 2.0
+    step_bytes = nums["weight_bytes"] + batch * mean_ctx * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    close_all(reqs)
+
+    # ---- end to end through the Python entry point (scheduler) -----------------------------
+    sched = Scheduler(model, max_batch=batch, max_tokens_per_step=4096)
+    prompt_len = ctx - warmup - steps - 1
+    for i in range(batch):
+        sched.add(Request(f"e{i}", rng.integers(0, vocab, prompt_len).tolist(), max_tokens=warmup + steps + 1))
+    while any(s.pending > 1 for s in sched.running) or sched.waiting:
+        sched.step()
+    for _ in range(warmup):
+        sched.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_tok = 0
+    for _ in range(steps):
+        n_tok += len(sched.step().entries)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = engine.last_h2d_bytes
+    for rid in [s.req.request_id for s in sched.running]:
+        sched.cancel(rid)
+    e2e = {"value": round(n_tok / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": 4 * batch, "ms_per_step": round(dt / steps * 1e3, 4)}
+
+    value = batch / (ms_step / 1e3)
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B shape, context 4096)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights and random token ids", "impl": "ours",
+        "config": {"model": "Qwen2.5-0.5B shape", "layers": layers, "layers_full": MODEL["num_hidden_layers"],
+                   "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"],
+                   "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
+                   "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "tied_head": True,
+                   "global_batch": batch, "seq_len": ctx, "page_size": page, "prefill_tokens": t_pre,
+                   "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights ~1 GB per step)",
+                   "peaks": pk["source"]},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference (its Python model, installed under baseline/_ref) on the same workload:
+    random weights of the same shape, batch 8 decode at context 4096 through ``Model.forward`` with its
+    ``KVCache`` and ``sample_next_token``, the calls its own generate loop makes (nanoinfer/generate.py:72-83)."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "nanoinfer")):
+        return {"impl": "reference", "unavailable": "baseline/_ref/nanoinfer is not installed (pip install --no-deps --target baseline/_ref <reference>)"}
+    sys.path.insert(0, ref_dir)
+    try:
+        import torch
+        from nanoinfer.config import ModelConfig
+        from nanoinfer.model import Model
+        from nanoinfer.sampling import SamplingParams, sample_next_token
+    except Exception as e:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"cannot import the reference: {type(e).__name__}: {e}"}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+    m = MODEL
+    layers = args.layers or m["num_hidden_layers"]
+    ctx, batch, steps, warmup = args.context, args.batch, args.steps, max(3, args.warmup)
+    cfg = ModelConfig(vocab_size=m["vocab_size"], hidden_size=m["hidden_size"], intermediate_size=m["intermediate_size"],
+                      num_layers=layers, num_attention_heads=m["num_attention_heads"],
+                      num_kv_heads=m["num_key_value_heads"], head_dim=m["head_dim"], rms_norm_eps=m["rms_norm_eps"],
+                      rope_theta=m["rope_theta"], max_position_embeddings=m["max_position_embeddings"],
+                      tie_word_embeddings=True)
+    torch.manual_seed(0)
+    model = Model(cfg).to(device="cuda", dtype=torch.bfloat16).eval()
+    model.lm_head.weight = model.embed_tokens.weight
+    cache = model.init_cache(batch, ctx)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    filled, target = 0, ctx - warmup - steps - 1
+    with torch.no_grad():
+        while filled < target:
+            n = min(512, target - filled)
+            model(torch.randint(0, m["vocab_size"], (batch, n), generator=g).cuda(), cache=cache)
+            filled += n
+        params = SamplingParams()
+        pinned = torch.empty((batch, 1), dtype=torch.long).pin_memory()
+
+        def one():
+            pinned.copy_(torch.randint(0, m["vocab_size"], (batch, 1), generator=g))
+            cur = pinned.to("cuda", non_blocking=True)
+            logits = model(cur, cache=cache)[:, -1, :]
+            return [sample_next_token(logits[b], params) for b in range(batch)]
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler() as cs:
+            t0 = time.perf_counter()
+            s.record()
+            for _ in range(steps):
+                one()
+            e.record()
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+        ms = s.elapsed_time(e) / steps
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B shape, context 4096)", "value": round(batch / (ms / 1e3), 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights and random token ids", "impl": "reference",
+        "config": {"model": "Qwen2.5-0.5B shape", "layers": layers, "layers_full": m["num_hidden_layers"],
+                   "global_batch": batch, "seq_len": ctx, "parallelism": "single-gpu",
+                   "engine": "reference Python model (torch, CUDA)"},
+        "clocks": cs.summary(),
+        "e2e": {"value": round(batch * steps / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch,
+                "d2h_bytes_per_step": 8 * batch},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
+    args = ap.parse_args()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"unavailable": f"this engine runs on one GPU; --gpus {args.gpus} is not supported",
+                              "n_gpus": args.gpus}))
+        return 2
+    if args.steps + args.warmup + 2 >= args.context:
+        print(json.dumps({"unavailable": "steps + warmup must be smaller than the context"}))
+        return 2
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

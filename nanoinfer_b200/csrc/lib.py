@@ -41,6 +41,7 @@ class Kernels:
 
     def __init__(self, lib_path: str):
         self.lib_path = lib_path
+        self.launches = 0           # kernel launches issued through this object (graph replays add theirs)
         try:
             self._lib = ctypes.CDLL(lib_path)
         except OSError as e:
@@ -52,6 +53,7 @@ class Kernels:
 
     # ---- plumbing ---------------------------------------------------------------------------
     def _check(self, rc: int, what: str) -> None:
+        self.launches += 1
         if rc != 0:
             raise KernelError(f"{what}: {self._lib.nib_last_error().decode()}")
 

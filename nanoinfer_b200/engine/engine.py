@@ -56,6 +56,10 @@ class Engine:
         self.max_positions = self.plan.max_position_embeddings
         self.steps_run = 0
         self.tokens_run = 0
+        self.last_h2d_bytes = 0
+        self.graph_launches = 0     # kernel launches replayed from captured graphs
+        self._stage = None          # pinned host buffer of the step's int32 inputs
+        self._stage_event = None
 
     # ---- requests -------------------------------------------------------------------------
     def open(self, request_id) -> RequestCache:
@@ -114,7 +118,7 @@ class Engine:
         parts = [token_ids, positions, req_index, q_start, np.asarray(ctx_lens, dtype=np.int32), slots, want]
         parts += [t.reshape(-1) for t in tables]
         flat = np.concatenate(parts) if parts else np.zeros(0, np.int32)
-        dev = torch.from_numpy(flat).to(self.device)
+        dev = self._to_device(flat)
         views, off = [], 0
         for p in parts:
             views.append(dev[off:off + p.size])
@@ -126,6 +130,22 @@ class Engine:
             host=HostBatch(q_lens=q_lens, ctx_lens=ctx_lens, slots=slots.tolist()),
             block_tables=block_tables, rt=self.rt)
         return ctx, (views[6] if want.size else None)
+
+    def _to_device(self, flat: np.ndarray) -> torch.Tensor:
+        """One host-to-device copy of the step's inputs, from pinned memory when the device is a GPU."""
+        self.last_h2d_bytes = int(flat.nbytes)
+        if self.device.type != "cuda":
+            return torch.from_numpy(flat).to(self.device)
+        if self._stage is None or self._stage.numel() < flat.size:
+            self._stage = torch.empty(max(4096, 2 * flat.size), dtype=torch.int32).pin_memory()
+            self._stage_event = torch.cuda.Event()
+        else:
+            self._stage_event.synchronize()      # the previous step's copy has left the buffer
+        self._stage[:flat.size].numpy()[:] = flat
+        dev = torch.empty(flat.size, dtype=torch.int32, device=self.device)
+        dev.copy_(self._stage[:flat.size], non_blocking=True)
+        self._stage_event.record()
+        return dev
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

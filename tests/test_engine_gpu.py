@@ -1,0 +1,248 @@
+"""The engine on the GPU, in-process: long decoding, the first tokens of a sequence, greedy generation
+through the entry point, continuous batching against generation alone, and each part alone against the
+plain implementation's function for it. In 32-bit and in bfloat16."""
+import math
+
+import pytest
+import torch
+
+from gpu_util import assert_close
+from plain_qwen2 import PlainModel, apply_rope, causal_attention_fast, linear, rms_norm, rope_tables, swiglu
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def engine_for(model_dir, page, dtype, num_pages=128, max_batch=4, **kw):
+    from nanoinfer_b200.config import EngineConfig
+    from nanoinfer_b200.engine import Engine
+    return Engine(model_dir, EngineConfig(dtype=dtype, page_size=page, num_pages=num_pages, max_batch=max_batch, **kw))
+
+
+def tdt(dtype):
+    return torch.float32 if dtype == "float32" else torch.bfloat16
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "W"])
+def test_long_decoding_token_by_token(model_dirs, name, dtype):
+    from nanoinfer_b200.engine import StepEntry
+    d, page = model_dirs[name]
+    plain = PlainModel(d)
+    n = min(plain.cfg["max_pos"], 400)
+    ids = torch.randint(0, plain.cfg["vocab"], (n,), generator=torch.Generator().manual_seed(1)).tolist()
+    want = plain.logits(ids)
+    eng = engine_for(d, page, dtype)
+    rc = eng.open("long")
+    rows = [eng.step([StepEntry(rc, [t], [0])])[0].clone() for t in ids]
+    got = torch.stack(rows)
+    assert_close(got, want, tdt(dtype), f"long decode {name}")
+    eng.close(rc)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens(model_dirs, dtype):
+    """Positions 0, 1, 2: one visible key, then two, then three; alone and as a three-token portion."""
+    from nanoinfer_b200.engine import StepEntry
+    d, page = model_dirs["B"]
+    plain = PlainModel(d)
+    eng = engine_for(d, page, dtype)
+    for ids in ([7], [7, 300], [7, 300, 12]):
+        want = plain.logits(ids)
+        rc = eng.open("f")
+        got = eng.step([StepEntry(rc, ids, list(range(len(ids))))])
+        assert_close(got, want, tdt(dtype), f"first tokens {ids}")
+        eng.close(rc)
+        rc = eng.open("f")
+        got = torch.cat([eng.step([StepEntry(rc, [t], [0])]) for t in ids])
+        assert_close(got, want, tdt(dtype), f"first tokens one by one {ids}")
+        eng.close(rc)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
+    from nanoinfer_b200 import load_model
+    d, page = model_dirs[name]
+    plain = PlainModel(d)
+    model = load_model(d, dtype=dtype, page_size=page, num_pages=64, max_batch=2)
+    g = torch.Generator().manual_seed(2)
+    for n in (1, 7, 33):
+        prompt = torch.randint(0, plain.cfg["vocab"], (n,), generator=g).tolist()
+        got = model.generate(prompt, max_tokens=16)
+        # follow the engine's own tokens with the plain model: at every step the chosen token must be the
+        # plain argmax, or (bfloat16 only) within the rounding of it
+        ids = list(prompt)
+        for tok in got:
+            ref = plain.logits(ids)[-1]
+            if dtype == "float32":
+                assert tok == int(ref.argmax()), (n, ids)
+            else:
+                assert ref[tok] >= ref.max() - 0.06 * ref.pow(2).mean().sqrt(), (n, ids)
+            ids.append(tok)
+        assert len(got) == 16
+    assert model.engine.cache.num_free() == 64
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_scheduler_equals_alone_with_few_pages(model_dirs, dtype):
+    """Six staggered requests under a small token budget and a pool that forces queueing, reuse of pages
+    and preemption: every output equals generation alone (cpp/tests/python/run_serve.py:44-69 is the
+    reference's form of this test)."""
+    from nanoinfer_b200 import Request, Scheduler, load_model
+    d, page = model_dirs["B"]
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 503, (n,), generator=g).tolist() for n in (30, 9, 30, 64, 2, 30)]
+    model = load_model(d, dtype=dtype, page_size=page, num_pages=14, max_batch=3, max_tokens_per_step=24)
+    alone = [model.generate(p, max_tokens=20) for p in prompts]
+    sched = Scheduler(model)
+    for i, p in enumerate(prompts[:3]):
+        sched.add(Request(f"r{i}", p, max_tokens=20))
+    for _ in range(3):
+        sched.step()
+    for i, p in enumerate(prompts[3:], start=3):
+        sched.add(Request(f"r{i}", p, max_tokens=20))
+    out = sched.run()
+    if dtype == "float32":
+        assert [out[f"r{i}"] for i in range(6)] == alone
+    else:
+        assert sum(out[f"r{i}"] == alone[i] for i in range(6)) >= 5   # a rounding tie may flip one
+    assert sched.preemptions > 0
+    model.engine.cache.check()
+    assert model.engine.cache.num_free() == 14
+
+
+# ------------------------------------------------------------------------------- parts alone
+def _runtime(dtype):
+    from nanoinfer_b200.csrc.lib import load_kernels
+    from nanoinfer_b200.parts.base import Runtime
+    return Runtime(torch.device("cuda:0"), tdt(dtype), load_kernels())
+
+
+def _rand(shape, seed, scale=1.0):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_part_rmsnorm(dtype):
+    from nanoinfer_b200.parts.norm import RMSNorm
+    rt = _runtime(dtype)
+    gain = (1 + 0.1 * _rand((200,), 1)).to(torch.bfloat16)
+    part = RMSNorm(RMSNorm.spec(200, 3e-4, "g"), {"gain": gain}, rt)
+    x = _rand((19, 200), 2, 2.0).cuda()
+    assert_close(part.forward(x), rms_norm(x.double().cpu(), gain.double(), 3e-4), rt.dtype, "rmsnorm part")
+
+
+def test_part_rotary_tables():
+    from nanoinfer_b200.parts.position import RotaryEncoding
+    rt = _runtime("float32")
+    part = RotaryEncoding(RotaryEncoding.spec(48, 50000.0, 300), {}, rt)
+    cos, sin, dim = part.rotary()
+    c, s = rope_tables(torch.arange(300), 48, 50000.0)
+    assert dim == 48 and (cos.cpu().double() - c[:, :24]).abs().max() < 1e-7 and (sin.cpu().double() - s[:, :24]).abs().max() < 1e-7
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_part_swiglu(dtype):
+    from nanoinfer_b200.parts.feedforward import SwiGLU
+    rt = _runtime(dtype)
+    w = {"gate_w": _rand((200, 144), 3, 0.08).to(torch.bfloat16), "up_w": _rand((200, 144), 4, 0.08).to(torch.bfloat16),
+         "down_w": _rand((144, 200), 5, 0.08).to(torch.bfloat16)}
+    part = SwiGLU(SwiGLU.spec("mlp", 144, 200), w, rt)
+    h = _rand((23, 144), 6).to(rt.dtype).cuda()
+    res = _rand((23, 144), 7).cuda()
+    want = res.double().cpu() + swiglu(h.double().cpu(), w["gate_w"].double(), w["up_w"].double(), w["down_w"].double())
+    part.forward(h, res, None)
+    assert_close(res, want, rt.dtype, "swiglu part")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_part_embedding_and_head(dtype):
+    from nanoinfer_b200.parts.embedding import LinearHead, TokenEmbedding
+    rt = _runtime(dtype)
+    table = _rand((311, 72), 8, 0.5).to(torch.bfloat16)
+    emb = TokenEmbedding(TokenEmbedding.spec("e", 311, 72), {"table": table}, rt)
+    head = LinearHead(LinearHead.spec("e", 311, 72), {"weight": table}, rt)
+    ids = torch.tensor([0, 310, 5, 5], dtype=torch.int32, device="cuda")
+    x = emb.forward(ids, None)
+    assert torch.equal(x.cpu(), table[ids.long().cpu()].float())
+    h = _rand((4, 72), 9).to(rt.dtype).cuda()
+    assert_close(head.forward(h), linear(h.double().cpu(), table.double()), rt.dtype, "head part")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,hd,window,bias", [(6, 2, 32, 0, True), (3, 3, 48, 9, False), (14, 2, 64, 0, True)])
+def test_part_attention_whole_and_cut(dtype, heads, kv_heads, hd, window, bias):
+    """The attention part alone: a whole sequence in one step equals the plain attention; the same
+    sequence cut into a portion and single tokens gives the same rows."""
+    from gpu_util import make_paged_batch
+    from nanoinfer_b200.parts.attention import GroupedQueryAttention
+    from nanoinfer_b200.parts.base import LayerCache
+    from nanoinfer_b200.parts.position import RotaryEncoding
+    rt = _runtime(dtype)
+    hidden, page, T = 80, 8, 45
+    spec = GroupedQueryAttention.spec("a", hidden, heads, kv_heads, hd, bias, "rot", window)
+    w = {role: _rand(ts.shape, 10 + i, 0.1).to(torch.bfloat16) for i, (role, ts) in enumerate(spec.tensors.items())}
+    part = GroupedQueryAttention(spec, w, rt)
+    part.bind_positions({"rot": RotaryEncoding(RotaryEncoding.spec(hd, 1e4, 64), {}, rt)})
+    h = _rand((T, hidden), 30).to(rt.dtype)
+    # plain
+    wd = {k: v.double() for k, v in w.items()}
+    hd64 = h.double()
+    q = linear(hd64, wd["q_w"], wd.get("q_b")).view(T, heads, hd)
+    k = linear(hd64, wd["k_w"], wd.get("k_b")).view(T, kv_heads, hd)
+    v = linear(hd64, wd["v_w"], wd.get("v_b")).view(T, kv_heads, hd)
+    cos, sin = rope_tables(torch.arange(T), hd, 1e4)
+    a = causal_attention_fast(apply_rope(q, cos, sin), apply_rope(k, cos, sin), v, window)
+    want = linear(a.reshape(T, -1), wd["o_w"])
+
+    shape = (16, kv_heads, page, hd)
+    for cuts in ([T], [20, 1, 1, 13, 10]):
+        kp, vp = torch.zeros(shape, dtype=rt.dtype, device="cuda"), torch.zeros(shape, dtype=rt.dtype, device="cuda")
+        outs, done = [], 0
+        for n in cuts:
+            ctx, bt = make_paged_batch([n], [done], page, 16, "cuda", shuffle=False)
+            res = torch.zeros(n, hidden, device="cuda")
+            part.forward(h[done:done + n].cuda().contiguous(), res, ctx, LayerCache(kp, vp, bt, page, True, None))
+            outs.append(res)
+            done += n
+        assert_close(torch.cat(outs), want, rt.dtype, f"attention part cuts={cuts}")
+
+
+# ------------------------------------------------------------------------------- sampling kernels
+@pytest.mark.parametrize("vocab", [503, 151936])
+def test_sampling_kernels_follow_the_plain_pipeline(vocab):
+    import numpy as np
+    from plain_qwen2 import greedy_pick, sampling_distribution
+    from nanoinfer_b200.csrc.lib import load_kernels
+    from nanoinfer_b200.sampling import SampleRow, Sampler, SamplingParams, uniform_for
+    sampler = Sampler(load_kernels(), "cuda:0")
+    g = torch.Generator().manual_seed(5)
+    base = torch.randn(1, vocab, generator=g) * 3.0
+    base[0, 7] = base[0, 11] = base.max() + 0.5       # a tie at the top
+    context = [7, 3, 3, 100, vocab - 1]
+    cases = [SamplingParams(temperature=0.7), SamplingParams(temperature=1.3, top_k=40),
+             SamplingParams(temperature=0.9, top_p=0.8), SamplingParams(temperature=1.0, top_k=200, top_p=0.5),
+             SamplingParams(temperature=0.5, repetition_penalty=1.7, top_k=5), SamplingParams(temperature=2.0, top_k=1)]
+    for ci, params in enumerate(cases):
+        rows, n = [], 24
+        for i in range(n):
+            rows.append(SampleRow(params, context, generated=i, seed=100 + ci))
+        logits = base.repeat(n, 1).cuda().contiguous()
+        toks = sampler.sample(logits, rows)
+        probs = sampling_distribution(base[0].double().numpy(), context, params.temperature, params.k, params.p,
+                                      params.repetition_penalty)
+        cdf = np.cumsum(probs)
+        for i, tok in enumerate(toks):
+            u = uniform_for(100 + ci, i)
+            assert probs[tok] > 0, (ci, i, tok)
+            lo, hi = cdf[tok] - probs[tok], cdf[tok]
+            assert lo - 2e-5 <= u <= hi + 2e-5, (ci, i, tok, u, lo, hi)
+        if params.top_k == 1:
+            assert set(toks) <= {7, 11}
+    # greedy with a penalty: the first maximum after the penalty
+    rows = [SampleRow(SamplingParams(repetition_penalty=3.0), context, 0), SampleRow(SamplingParams(), None, 0)]
+    toks = sampler.sample(base.repeat(2, 1).cuda().contiguous(), rows)
+    assert toks == [greedy_pick(base[0].numpy(), context, 3.0), 7]
+    assert toks[0] == 11
