@@ -1,0 +1,529 @@
+// Paged attention on the tensor cores (bfloat16 operands, 32-bit accumulation and softmax), for head
+// sizes 16..128 in steps of 16. Two kernels share their building blocks:
+//
+//  * prefill: a tile of 64 rows per CTA, where a row is one (token, query head of the kv group), so
+//    the keys and values of a kv head are read once for all the query heads that share it; key tiles of
+//    64 through the block table, online softmax, causal and window masks by absolute position.
+//  * decode: the rows are the query heads of ONE token's kv group (at most 16); the four warps of a CTA
+//    each take a quarter of every key tile, several CTAs split the keys of a long context, and a
+//    combine kernel merges the partial (max, sum, output) triples in a fixed order.
+//
+// Formula as in attention_generic.cu (cpp/src/ops.cpp:206-270): score = dot * scale, keys lo..p, softmax
+// with the max subtracted, weighted sum of values. The reference's counterparts are SIMT:
+// cpp/src/cuda/cuda_backend.cu:489-575 (tiled prefill), :578-640 and :331-352 (split-KV and combine).
+//
+// Tensor-core path: mma.sync m16n8k16 with ldmatrix from padded shared-memory tiles filled by cp.async.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BLOCK_N = 64;     // keys per tile
+constexpr int WARPS = 4;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Shared-memory tile of BLOCK_N rows of HD bfloat16, each row padded by 16 bytes: the row stride in
+// 32-bit words is 4 mod 8, so the eight rows of an ldmatrix 8x8 block fall into distinct banks.
+template <int HD> struct Tile {
+    static constexpr int ROW_BYTES = HD * 2 + 16;
+    static constexpr int BYTES = BLOCK_N * ROW_BYTES;
+    static constexpr int CHUNKS_PER_ROW = HD / 8;            // 16-byte chunks
+};
+
+// Copies keys key0..key0+63 of one kv head into a tile; rows outside [lo, hi] or without a page are zero.
+template <int HD, int THREADS>
+__device__ __forceinline__ void load_tile(unsigned char* tile, const __nv_bfloat16* __restrict__ pages,
+                                          const int* __restrict__ bt, int page_size, int num_pages,
+                                          int kv_heads, int kvh, int key0, int lo, int hi, int tid) {
+    constexpr int CPR = Tile<HD>::CHUNKS_PER_ROW;
+    constexpr int TOTAL = BLOCK_N * CPR;
+#pragma unroll
+    for (int i = tid; i < TOTAL; i += THREADS) {
+        const int r = i / CPR, c = i - r * CPR;
+        const int j = key0 + r;
+        bool valid = (j >= lo) && (j <= hi);
+        const __nv_bfloat16* src = pages;
+        if (valid) {
+            const int page = bt[j / page_size];
+            valid = page >= 0 && page < num_pages;
+            if (valid) src = pages + (((size_t)page * kv_heads + kvh) * page_size + (j % page_size)) * HD + c * 8;
+        }
+        cp_async_16(tile + r * Tile<HD>::ROW_BYTES + c * 16, src, valid);
+    }
+}
+
+// S[16 x (8*NT)] += Q[16 x HD] . K^T for the key rows row0.. of a tile. q: A fragments per 16 dims.
+template <int HD, int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const unsigned (&q)[HD / 16][4],
+                                        const unsigned char* k_tile, int row0, int lane) {
+    // ldmatrix.x4 addresses: matrices (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 0-7), (keys 8-15, dims 8-15)
+    const int mat = lane >> 3, rr = lane & 7;
+    const int key_off = (mat >> 1) * 8 + rr, dim_off = (mat & 1) * 8;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            unsigned b[4];
+            ldmatrix_x4(b, k_tile + (row0 + np * 16 + key_off) * Tile<HD>::ROW_BYTES + (kk * 16 + dim_off) * 2);
+            mma_bf16(s[2 * np], q[kk], b[0], b[1]);
+            mma_bf16(s[2 * np + 1], q[kk], b[2], b[3]);
+        }
+    }
+}
+
+// O[16 x HD] += P[16 x (16*KB)] . V for the value rows row0.. of a tile. p: A fragments per 16 keys.
+template <int HD, int KB>
+__device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const unsigned (&p)[KB][4],
+                                        const unsigned char* v_tile, int row0, int lane) {
+    // transposed ldmatrix.x4: matrices (keys 0-7, dims 0-7), (keys 8-15, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, dims 8-15)
+    const int mat = lane >> 3, rr = lane & 7;
+    const int key_off = (mat & 1) * 8 + rr, dim_off = (mat >> 1) * 8;
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, v_tile + (row0 + kb * 16 + key_off) * Tile<HD>::ROW_BYTES + (dp * 16 + dim_off) * 2);
+            mma_bf16(o[2 * dp], p[kb], b[0], b[1]);
+            mma_bf16(o[2 * dp + 1], p[kb], b[2], b[3]);
+        }
+    }
+}
+
+// Online-softmax update of one warp's 16 rows with a block of NT*8 score columns.
+// s holds raw dots; scale2 = scale * log2(e). vis_lo/vis_hi: visible key range of the thread's two
+// rows (row g -> [0], row g+8 -> [1]); key_base: key of column 0. Produces P as A fragments.
+template <int HD, int NT>
+__device__ __forceinline__ void softmax_block(float (&s)[NT][4], unsigned (&p)[NT / 2][4], float (&o)[HD / 8][4],
+                                              float (&m_run)[2], float (&l_run)[2], float scale2, int key_base,
+                                              const int (&vis_lo)[2], const int (&vis_hi)[2], int lane) {
+    const int t = lane & 3;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int key = key_base + n * 8 + 2 * t + (e & 1);
+            const bool vis = key >= vis_lo[r] && key <= vis_hi[r];
+            s[n][e] = vis ? s[n][e] * scale2 : -INFINITY;
+            mx[r] = fmaxf(mx[r], s[n][e]);
+        }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;         // nothing visible yet: exp2(-inf - 0) = 0
+        corr[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float pv = exp2f(s[n][e] - m_use[e >> 1]);
+            s[n][e] = pv;
+            sum[e >> 1] += pv;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l_run[r] = l_run[r] * corr[r] + sum[r];
+    }
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kb = 0; kb < NT / 2; ++kb) {
+        p[kb][0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
+        p[kb][1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
+        p[kb][2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+        p[kb][3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+    }
+}
+
+// A fragments of 16 query rows straight from global memory. row_ptr[r]: start of the head's HD elements
+// for the thread's row g (r=0) and g+8 (r=1), or nullptr for a row that does not exist.
+template <int HD>
+__device__ __forceinline__ void load_q(unsigned (&q)[HD / 16][4], const __nv_bfloat16* const (&row_ptr)[2], int lane) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            unsigned lo = 0u, hi = 0u;
+            if (row_ptr[r]) {
+                lo = *reinterpret_cast<const unsigned*>(row_ptr[r] + kk * 16 + 2 * t);
+                hi = *reinterpret_cast<const unsigned*>(row_ptr[r] + kk * 16 + 8 + 2 * t);
+            }
+            q[kk][r] = lo;        // a0 (row g) / a1 (row g+8): dims 2t, 2t+1
+            q[kk][2 + r] = hi;    // a2 / a3: dims 8+2t, 9+2t
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ prefill
+// grid: (row tiles of 64, requests, kv heads). Rows of a request and kv head: r = token * n_rep + g.
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __nv_bfloat16* __restrict__ out,
+                         const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
+                         const int* __restrict__ block_table, int bt_stride, int page_size,
+                         const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                         int num_pages, int heads, int kv_heads, float scale, int window) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int req = blockIdx.y, kvh = blockIdx.z;
+    const int n_rep = heads / kv_heads;
+    const int row_begin = q_start[req], q_len = q_start[req + 1] - row_begin;
+    const int rows_total = q_len * n_rep;
+    const int row0 = blockIdx.x * (WARPS * 16);
+    if (row0 >= rows_total) return;
+    const int ctx = ctx_lens[req];
+    const int pos0 = ctx - q_len;                     // position of the request's first token in this step
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2;
+    const int* bt = block_table + (size_t)req * bt_stride;
+
+    // this thread's two rows
+    int vis_lo[2], vis_hi[2];
+    const __nv_bfloat16* q_ptr[2];
+    int out_off[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + warp * 16 + g + 8 * r;
+        if (row < rows_total) {
+            const int ti = row / n_rep, head = kvh * n_rep + (row - ti * n_rep);
+            const int p = pos0 + ti;
+            vis_hi[r] = p;
+            vis_lo[r] = window > 0 ? max(0, p - window + 1) : 0;
+            q_ptr[r] = qkv + (size_t)(row_begin + ti) * q_stride + (size_t)head * HD;
+            out_off[r] = (row_begin + ti) * heads * HD + head * HD;
+        } else {
+            vis_hi[r] = -1; vis_lo[r] = 0; q_ptr[r] = nullptr; out_off[r] = -1;
+        }
+    }
+    // key range of the whole CTA
+    const int last_row = min(rows_total, row0 + WARPS * 16) - 1;
+    const int hi_cta = pos0 + last_row / n_rep;
+    const int lo_cta = window > 0 ? max(0, pos0 + row0 / n_rep - window + 1) : 0;
+    const int t_begin = lo_cta / BLOCK_N, t_end = hi_cta / BLOCK_N;
+
+    unsigned q[HD / 16][4];
+    load_q<HD>(q, q_ptr, lane);
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const float scale2 = scale * LOG2E;
+
+    unsigned char* k_buf[2] = {smem, smem + 2 * Tile<HD>::BYTES};
+    unsigned char* v_buf[2] = {smem + Tile<HD>::BYTES, smem + 3 * Tile<HD>::BYTES};
+
+    load_tile<HD, WARPS * 32>(k_buf[0], k_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo_cta, hi_cta, tid);
+    load_tile<HD, WARPS * 32>(v_buf[0], v_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo_cta, hi_cta, tid);
+    cp_async_commit();
+
+    for (int tile = t_begin; tile <= t_end; ++tile) {
+        const int cur = (tile - t_begin) & 1;
+        if (tile < t_end) {
+            load_tile<HD, WARPS * 32>(k_buf[cur ^ 1], k_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo_cta, hi_cta, tid);
+            load_tile<HD, WARPS * 32>(v_buf[cur ^ 1], v_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo_cta, hi_cta, tid);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+
+        float s[BLOCK_N / 8][4];
+#pragma unroll
+        for (int n = 0; n < BLOCK_N / 8; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+        qk_tile<HD, BLOCK_N / 8>(s, q, k_buf[cur], 0, lane);
+        unsigned p[BLOCK_N / 16][4];
+        softmax_block<HD, BLOCK_N / 8>(s, p, o, m_run, l_run, scale2, tile * BLOCK_N, vis_lo, vis_hi, lane);
+        pv_tile<HD, BLOCK_N / 16>(o, p, v_buf[cur], 0, lane);
+        __syncthreads();    // the tile may be overwritten by the load issued in the next iteration
+    }
+    cp_async_wait<0>();
+
+    const int t = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        if (out_off[r] < 0) continue;
+        const float inv = l_run[r] > 0.f ? 1.0f / l_run[r] : 0.f;
+        __nv_bfloat16* orow = out + out_off[r];
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d)
+            *reinterpret_cast<unsigned*>(orow + d * 8 + 2 * t) = pack_bf16(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ decode
+// grid: (splits, tokens, kv heads). Every token has q_len 1; its position is ctx_len - 1.
+// part_o: [tokens, heads, splits, HD] float, part_ml: [tokens, heads, splits, 2] (max in log2 units, sum).
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
+                        int page_size, const __nv_bfloat16* __restrict__ k_pages,
+                        const __nv_bfloat16* __restrict__ v_pages, int num_pages, int heads, int kv_heads,
+                        float scale, int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int split = blockIdx.x, token = blockIdx.y, kvh = blockIdx.z;
+    const int n_rep = heads / kv_heads;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int p = ctx_lens[token] - 1;
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int* bt = block_table + (size_t)token * bt_stride;
+
+    // key tiles of this split: tiles are aligned to absolute multiples of 64
+    const int t_first = lo / BLOCK_N, t_last = p / BLOCK_N;
+    const int n_tiles = t_last - t_first + 1;
+    const int per = (n_tiles + splits - 1) / splits;
+    const int t_begin = t_first + split * per;
+    const int t_end = min(t_last, t_begin + per - 1);
+
+    int vis_lo[2] = {lo, lo}, vis_hi[2] = {g < n_rep ? p : -1, -1};      // rows g+8 exist only if n_rep > 8
+    const __nv_bfloat16* q_ptr[2] = {nullptr, nullptr};
+    if (g < n_rep) q_ptr[0] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g) * HD;
+    if (g + 8 < n_rep) { q_ptr[1] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g + 8) * HD; vis_hi[1] = p; }
+    unsigned q[HD / 16][4];
+    load_q<HD>(q, q_ptr, lane);
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const float scale2 = scale * LOG2E;
+
+    unsigned char* k_buf[2] = {smem, smem + 2 * Tile<HD>::BYTES};
+    unsigned char* v_buf[2] = {smem + Tile<HD>::BYTES, smem + 3 * Tile<HD>::BYTES};
+
+    if (t_begin <= t_end) {
+        load_tile<HD, WARPS * 32>(k_buf[0], k_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo, p, tid);
+        load_tile<HD, WARPS * 32>(v_buf[0], v_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo, p, tid);
+    }
+    cp_async_commit();
+    for (int tile = t_begin; tile <= t_end; ++tile) {
+        const int cur = (tile - t_begin) & 1;
+        if (tile < t_end) {
+            load_tile<HD, WARPS * 32>(k_buf[cur ^ 1], k_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo, p, tid);
+            load_tile<HD, WARPS * 32>(v_buf[cur ^ 1], v_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo, p, tid);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        // each warp takes 16 keys of the tile
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        qk_tile<HD, 2>(s, q, k_buf[cur], warp * 16, lane);
+        unsigned pfrag[1][4];
+        softmax_block<HD, 2>(s, pfrag, o, m_run, l_run, scale2, tile * BLOCK_N + warp * 16, vis_lo, vis_hi, lane);
+        pv_tile<HD, 1>(o, pfrag, v_buf[cur], warp * 16, lane);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the four warps through shared memory (the tiles are no longer needed)
+    float* sm_o = reinterpret_cast<float*>(smem);                 // [WARPS][16][HD]
+    float* sm_ml = sm_o + WARPS * 16 * HD;                        // [WARPS][16][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d) {
+            sm_o[(warp * 16 + row) * HD + d * 8 + 2 * t] = o[d][2 * r];
+            sm_o[(warp * 16 + row) * HD + d * 8 + 2 * t + 1] = o[d][2 * r + 1];
+        }
+        if (t == 0) {
+            sm_ml[(warp * 16 + row) * 2] = m_run[r];
+            sm_ml[(warp * 16 + row) * 2 + 1] = l_run[r];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_rep * HD; i += WARPS * 32) {
+        const int row = i / HD, d = i - row * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sm_ml[(w * 16 + row) * 2]);
+        float l = 0.f, acc = 0.f;
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float mw = sm_ml[(w * 16 + row) * 2];
+                const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+                l += sm_ml[(w * 16 + row) * 2 + 1] * f;
+                acc += sm_o[(w * 16 + row) * HD + d] * f;
+            }
+        }
+        const int head = kvh * n_rep + row;
+        if (splits == 1) {
+            out[((size_t)token * heads + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            const size_t slot = ((size_t)token * heads + head) * splits + split;
+            part_o[slot * HD + d] = acc;
+            if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+        }
+    }
+}
+
+// Merges the partial results of the splits, in split order. grid: tokens * heads; block: HD threads (<= 128).
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, int splits, int hd) {
+    const size_t th = blockIdx.x;
+    const int d = threadIdx.x;
+    if (d >= hd) return;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(th * splits + s) * 2]);
+    float l = 0.f, acc = 0.f;
+    if (m != -INFINITY) {
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(th * splits + s) * 2];
+            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+            l += part_ml[(th * splits + s) * 2 + 1] * f;
+            acc += part_o[(th * splits + s) * hd + d] * f;
+        }
+    }
+    out[th * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+}
+
+template <int HD> int prefill_smem() { return 4 * Tile<HD>::BYTES; }
+template <int HD> int decode_smem() {
+    const int tiles = 4 * Tile<HD>::BYTES, merge = WARPS * 16 * (HD + 2) * 4;
+    return tiles > merge ? tiles : merge;
+}
+
+template <int HD>
+int launch_prefill(const void* qkv, int q_stride, void* out, const int* q_start, const int* ctx_lens,
+                   const int* block_table, int bt_stride, int page_size, const void* k_pages, const void* v_pages,
+                   int num_pages, int n_req, int max_q_len, int heads, int kv_heads, float scale, int window,
+                   cudaStream_t stream) {
+    static bool configured = false;
+    const int smem = prefill_smem<HD>();
+    if (!configured) {
+        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    const int n_rep = heads / kv_heads;
+    dim3 grid(ceil_div((long long)max_q_len * n_rep, WARPS * 16), n_req, kv_heads);
+    attention_prefill_kernel<HD><<<grid, WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size,
+        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale, window);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int HD>
+int launch_decode(const void* qkv, int q_stride, void* out, const int* ctx_lens, const int* block_table,
+                  int bt_stride, int page_size, const void* k_pages, const void* v_pages, int num_pages,
+                  int n_tokens, int heads, int kv_heads, float scale, int window, int splits, float* part_o,
+                  float* part_ml, cudaStream_t stream) {
+    static bool configured = false;
+    const int smem = decode_smem<HD>();
+    if (!configured) {
+        NIB_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        configured = true;
+    }
+    dim3 grid(splits, n_tokens, kv_heads);
+    attention_decode_kernel<HD><<<grid, WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
+        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale, window,
+        splits, part_o, part_ml);
+    NIB_LAUNCH_CHECK();
+    if (splits > 1) {
+        attention_combine_kernel<<<n_tokens * heads, HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, splits, HD);
+        NIB_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
+}  // namespace
+
+#define NIB_HD_SWITCH(hd, CALL)                      \
+    switch (hd) {                                    \
+        case 16: return CALL(16);                    \
+        case 32: return CALL(32);                    \
+        case 48: return CALL(48);                    \
+        case 64: return CALL(64);                    \
+        case 80: return CALL(80);                    \
+        case 96: return CALL(96);                    \
+        case 112: return CALL(112);                  \
+        case 128: return CALL(128);                  \
+        default: break;                              \
+    }
+
+// 1 if the tensor-core kernels take this head size and grouping, else 0 (the caller then uses the general kernel).
+NIB_API int nib_attention_mma_supported(int heads, int kv_heads, int head_dim) {
+    if (kv_heads <= 0 || heads % kv_heads) return 0;
+    return head_dim >= 16 && head_dim <= 128 && head_dim % 16 == 0;
+}
+
+// Requests q_start[0..n_req], rows of every request contiguous; bfloat16 only.
+NIB_API int nib_attention_prefill_mma(const void* qkv, int q_stride, void* out, const int* q_start, const int* ctx_lens,
+                                      const int* block_table, int bt_stride, int page_size, const void* k_pages,
+                                      const void* v_pages, int num_pages, int n_req, int max_q_len, int heads,
+                                      int kv_heads, int head_dim, float scale, int window, cudaStream_t stream) {
+    NIB_REQUIRE(nib_attention_mma_supported(heads, kv_heads, head_dim), "attention (tensor cores): head_dim %d with %d/%d heads is not supported", head_dim, heads, kv_heads);
+    NIB_REQUIRE(n_req >= 0 && max_q_len > 0 && page_size > 0 && num_pages > 0 && window >= 0, "attention prefill: bad sizes");
+    NIB_REQUIRE(q_stride % 2 == 0 && head_dim % 8 == 0, "attention prefill: rows must be 4-byte aligned");
+    NIB_REQUIRE(n_req <= 65535 && kv_heads <= 65535, "attention prefill: too many requests or kv heads for one launch");
+    if (n_req == 0) return 0;
+#define CALL(HD) launch_prefill<HD>(qkv, q_stride, out, q_start, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_req, max_q_len, heads, kv_heads, scale, window, stream)
+    NIB_HD_SWITCH(head_dim, CALL)
+#undef CALL
+    NIB_REQUIRE(false, "attention prefill: unreachable head_dim %d", head_dim);
+}
+
+// One token per request (q_len 1). part_o: [n_tokens, heads, splits, head_dim] float and part_ml:
+// [n_tokens, heads, splits, 2] float are scratch, needed only when splits > 1.
+NIB_API int nib_attention_decode_mma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
+                                     const int* block_table, int bt_stride, int page_size, const void* k_pages,
+                                     const void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
+                                     int head_dim, float scale, int window, int splits, float* part_o, float* part_ml,
+                                     cudaStream_t stream) {
+    NIB_REQUIRE(nib_attention_mma_supported(heads, kv_heads, head_dim), "attention (tensor cores): head_dim %d with %d/%d heads is not supported", head_dim, heads, kv_heads);
+    NIB_REQUIRE(heads / kv_heads <= 16, "attention decode: at most 16 query heads per kv head, got %d", heads / kv_heads);
+    NIB_REQUIRE(n_tokens >= 0 && page_size > 0 && num_pages > 0 && window >= 0 && splits >= 1, "attention decode: bad sizes");
+    NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode: splits > 1 need scratch memory");
+    NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode: too many tokens or kv heads for one launch");
+    if (n_tokens == 0) return 0;
+#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, stream)
+    NIB_HD_SWITCH(head_dim, CALL)
+#undef CALL
+    NIB_REQUIRE(false, "attention decode: unreachable head_dim %d", head_dim);
+}

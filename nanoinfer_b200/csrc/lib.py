@@ -42,12 +42,16 @@ class Kernels:
     def __init__(self, lib_path: str):
         self.lib_path = lib_path
         self.launches = 0           # kernel launches issued through this object (graph replays add theirs)
+        self.force_general_attention = False   # tests: run the general attention kernel for bfloat16 too
+        self.fixed_decode_splits = 0           # tests: a fixed split count for the decode kernel
+        self.sm_count = 148
         try:
             self._lib = ctypes.CDLL(lib_path)
         except OSError as e:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
+                     "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
                      "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
@@ -140,17 +144,65 @@ class Kernels:
 
     def attention(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
                   page_size, k_pages, v_pages):
+        """Attention of every token of the step over its request's cached keys (positions lo..own).
+
+        bfloat16 with a supported head size runs on the tensor cores: the leading requests that bring one
+        token each go to the decode kernel (keys split over CTAs), the others to the prefill kernel.
+        Everything else (32-bit, other head sizes) runs the general kernel."""
         _need(qkv, None, "attention qkv"); _need(out, qkv.dtype, "attention out")
         _need(k_pages, qkv.dtype, "k_pages"); _need(v_pages, qkv.dtype, "v_pages")
         _need(block_table, torch.int32, "block_table", contiguous=False)
         if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim):
             raise KernelError(f"attention: pages {tuple(k_pages.shape)} do not fit kv_heads/page_size/head_dim")
+        if block_table.stride(1) != 1:
+            raise KernelError("attention: block_table rows must be dense")
         m = qkv.shape[0]
-        self._check(self._lib.nib_attention_generic(
-            _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table),
-            c_int(block_table.stride(0)), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]),
-            c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window),
-            c_int(_DT[qkv.dtype]), self._stream()), "attention")
+        num_pages, bt_stride = k_pages.shape[0], block_table.stride(0)
+        fast = qkv.dtype == torch.bfloat16 and not self.force_general_attention and \
+            self._lib.nib_attention_mma_supported(c_int(heads), c_int(kv_heads), c_int(head_dim)) == 1
+        if not fast:
+            self._check(self._lib.nib_attention_generic(
+                _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.positions), _ptr(ctx.req_index), _ptr(block_table),
+                c_int(bt_stride), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages),
+                c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+                c_int(_DT[qkv.dtype]), self._stream()), "attention")
+            return
+        q_lens, ctx_lens = ctx.host.q_lens, ctx.host.ctx_lens
+        n_req = len(q_lens)
+        n_dec = 0
+        if heads // kv_heads <= 16:
+            while n_dec < n_req and q_lens[n_dec] == 1:
+                n_dec += 1
+        if n_dec:
+            splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = torch.empty(n_dec * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
+                part_ml = torch.empty(n_dec * heads * splits * 2, dtype=torch.float32, device=qkv.device)
+            self._check(self._lib.nib_attention_decode_mma(
+                _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(bt_stride),
+                c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_dec), c_int(heads),
+                c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits), _ptr(part_o),
+                _ptr(part_ml), self._stream()), "attention decode")
+            if splits > 1:
+                self.launches += 1
+        if n_dec < n_req:
+            self._check(self._lib.nib_attention_prefill_mma(
+                _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), c_void_p(ctx.q_start.data_ptr() + 4 * n_dec),
+                c_void_p(ctx.ctx_lens.data_ptr() + 4 * n_dec), c_void_p(block_table.data_ptr() + 4 * n_dec * bt_stride),
+                c_int(bt_stride), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages),
+                c_int(n_req - n_dec), c_int(max(q_lens[n_dec:])), c_int(heads), c_int(kv_heads), c_int(head_dim),
+                c_float(scale), c_int(window), self._stream()), "attention prefill")
+
+    def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int) -> int:
+        """Into how many CTAs the keys of a decoding token are split: enough CTAs to fill the GPU about
+        twice, each with at least 256 keys."""
+        if self.fixed_decode_splits:
+            return self.fixed_decode_splits
+        keys = min(max_ctx, window) if window > 0 else max_ctx
+        tiles = -(-keys // 64) + 1
+        want = max(1, (2 * self.sm_count) // max(1, n_tokens * kv_heads))
+        return max(1, min(want, tiles // 4, 64))
 
     def argmax(self, logits, out):
         _need(logits, torch.float32, "argmax logits"); _need(out, torch.int32, "argmax out")
@@ -187,5 +239,6 @@ def load_kernels(verbose: bool = True) -> Kernels:
         arch = k.device_arch()
         if arch != 100:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{arch}")
+        k.sm_count = max(1, k._lib.nib_sm_count())
         _KERNELS = k
     return _KERNELS

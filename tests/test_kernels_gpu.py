@@ -197,3 +197,46 @@ def test_argmax_first_maximum(K, vocab):
     K.argmax(logits, out)
     assert out.tolist() == torch.argmax(logits.cpu(), dim=-1).tolist()
     assert out[2].item() == 3 and out[3].item() == vocab - 1
+
+
+@pytest.mark.parametrize("splits", [0, 1, 3, 8])
+@pytest.mark.parametrize("heads,kv_heads,hd,window", [(14, 2, 64, 0), (16, 1, 64, 0), (12, 1, 32, 700), (20, 1, 16, 0),
+                                                       (8, 8, 128, 0), (9, 3, 112, 0)])
+def test_attention_decode_long_context_split_over_ctas(K, heads, kv_heads, hd, window, splits):
+    """Single decoded tokens at contexts from 1 to 3000 keys (tile edges 63, 64, 65), any number of
+    splits, up to 16 query heads per kv head on the decode kernel (20: the prefill kernel takes them)."""
+    dtype, page = torch.bfloat16, 16
+    before = [0, 62, 63, 64, 2999, 1500]
+    q_lens = [1] * len(before)
+    ctx, bt = make_paged_batch(q_lens, before, page, 400, "cuda", seed=5)
+    kp, vp = _fill_cache(ctx, bt, page, 400, kv_heads, hd, dtype, 50)
+    qkv = rnd((len(before), (heads + 2 * kv_heads) * hd), dtype, 52)
+    out, ref = (torch.empty(len(before), heads * hd, dtype=dtype, device="cuda") for _ in range(2))
+    scale = 1.0 / math.sqrt(hd)
+    K.fixed_decode_splits = splits
+    try:
+        K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    finally:
+        K.fixed_decode_splits = 0
+    REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    assert_close(out, ref, dtype, "decode attention")
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page,window", [(14, 2, 64, 16, 0), (6, 1, 32, 8, 0), (3, 3, 48, 8, 24), (8, 2, 128, 16, 0)])
+def test_attention_tensor_core_kernels_agree_with_the_general_kernel(K, heads, kv_heads, hd, page, window):
+    """bfloat16: the same batch through the tensor-core kernels and through the general kernel."""
+    dtype = torch.bfloat16
+    q_lens, before = [1, 1, 150, 7, 1], [500, 0, 100, 0, 64]
+    ctx, bt = make_paged_batch(q_lens, before, page, 200, "cuda", seed=6)
+    kp, vp = _fill_cache(ctx, bt, page, 200, kv_heads, hd, dtype, 60)
+    m = sum(q_lens)
+    qkv = rnd((m, (heads + 2 * kv_heads) * hd), dtype, 62)
+    fast, general = (torch.empty(m, heads * hd, dtype=dtype, device="cuda") for _ in range(2))
+    scale = 1.0 / math.sqrt(hd)
+    K.attention(qkv, fast, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    K.force_general_attention = True
+    try:
+        K.attention(qkv, general, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    finally:
+        K.force_general_attention = False
+    assert_close(fast, general.double(), dtype, "tensor-core vs general attention")
