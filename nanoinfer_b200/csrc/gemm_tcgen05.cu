@@ -1,0 +1,382 @@
+// Matrix product on the 5th-generation tensor cores of sm_100a: out[tokens, N] = A[tokens, K] . W[N, K]^T
+// for bfloat16 operands, 32-bit accumulation in tensor memory (TMEM).
+//
+// Orientation: the WEIGHT rows are the M side of the instruction (tiles of 128 output features =
+// the 128 TMEM lanes), the TOKENS are its N side (16..256 per tile). A decode step with few tokens
+// therefore still fills the 128-row instruction, and streams every weight exactly once; a prefill
+// uses token tiles of 128 or 256. One thread of the epilogue owns one output feature, so bias is a
+// scalar per thread and the residual sum is a coalesced read-modify-write over 32 features.
+//
+// Pipeline per CTA (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane;
+// the warp allocates and frees TMEM), warps 2..5 = epilogue (tcgen05.ld of the warp's lane quadrant).
+// Operand tiles are 64 elements (128 bytes) wide in K with the 128-byte swizzle, written by TMA and
+// read by tcgen05.mma through shared-memory descriptors; STAGES tiles are in flight, tracked by
+// full/empty mbarriers; tcgen05.commit releases a stage when the MMAs that read it are done.
+//
+// Every wait has an iteration limit; a wait that runs out records a code in an error word, the CTA
+// stops issuing, waits (bounded) for its own copies in flight, frees its TMEM and returns.
+//
+// Epilogues: STORE bf16 (+bias), ADD into a float tensor (the residual sum), F32 store (logits),
+// SWIGLU (two accumulators from W rows n and n + N: silu(gate) * up). Reference formulas:
+// cpp/src/ops.cpp:42-69 (linear), :86-93 (silu). The reference's tensor-core GEMMs are wmma kernels
+// for sm_89 (cpp/src/cuda/cuda_gemm.cu:484-622).
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
+
+constexpr int BLOCK_F = 128;     // output features per CTA (UMMA M)
+constexpr int BLOCK_K = 64;      // elements of K per stage: 128 bytes, one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+__device__ int g_tc_error = 0;   // 0, or (code << 16 | blockIdx.x) of the first wait that ran out
+
+// ---------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (i > 128) __nanosleep(100);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned* dst_smem, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned addr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                       unsigned idesc, bool accumulate) {
+    const unsigned acc = accumulate ? 1u : 0u;
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned addr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (cute/arch/mma_sm100_desc.hpp: SmemDescriptor).
+__device__ __forceinline__ unsigned long long smem_desc(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0,14)
+    d |= (unsigned long long)1 << 16;                             // leading byte offset (unused with swizzle), encoded 1
+    d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset: 8 rows * 128 bytes
+    d |= (unsigned long long)1 << 46;                             // descriptor version of sm_100
+    d |= (unsigned long long)2 << 61;                             // layout type: SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = tokens per tile
+// (cute/arch/mma_sm100_desc.hpp: InstrDescriptor).
+__host__ __device__ constexpr unsigned instr_desc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BLOCK_F >> 4) << 24);
+}
+
+constexpr int tmem_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
+
+template <int TOK, bool DUAL> struct Cfg {
+    static constexpr int W_BYTES = BLOCK_F * BLOCK_K * 2;                 // 16 KB
+    static constexpr int A_BYTES = TOK * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * W_BYTES + A_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+    static constexpr int TMEM_COLS = tmem_cols(DUAL ? 2 * TOK : TOK);
+};
+
+// grid: (feature tiles of 128, token tiles of TOK)
+template <int TOK, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+               const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo) {
+    constexpr bool DUAL = (EPI == EPI_SWIGLU);
+    using C = Cfg<TOK, DUAL>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + C::STAGES * C::STAGE_BYTES);
+    unsigned long long* empty_bar = full_bar + C::STAGES;
+    unsigned long long* tmem_full_bar = empty_bar + C::STAGES;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(tmem_full_bar + 1);
+    __shared__ int s_failed;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f0 = blockIdx.x * BLOCK_F, t0 = blockIdx.y * TOK;
+    const int k_blocks = (k_dim + BLOCK_K - 1) / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        s_failed = 0;
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer: TMA loads of W (and the up rows) and A tiles
+        int issued = 0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+            const int s = kb % C::STAGES;
+            if (!mbar_wait(&empty_bar[s], ((kb / C::STAGES) & 1) ^ 1)) {
+                atomicCAS(&g_tc_error, 0, (1 << 16) | (int)blockIdx.x);
+                s_failed = 1;
+                break;
+            }
+            unsigned char* st = smem + s * C::STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+            tma_load_2d(st, &map_w, &full_bar[s], kb * BLOCK_K, f0);
+            if (DUAL) tma_load_2d(st + C::W_BYTES, &map_w, &full_bar[s], kb * BLOCK_K, n_out + f0);
+            tma_load_2d(st + (DUAL ? 2 : 1) * C::W_BYTES, &map_a, &full_bar[s], kb * BLOCK_K, t0);
+            ++issued;
+        }
+        if (s_failed) {
+            // copies already issued still target this CTA's shared memory: wait for them, bounded
+            for (int kb = max(0, issued - C::STAGES); kb < issued; ++kb)
+                mbar_wait(&full_bar[kb % C::STAGES], (kb / C::STAGES) & 1);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        constexpr unsigned idesc = instr_desc(TOK);
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks && ok; ++kb) {
+            const int s = kb % C::STAGES;
+            if (!mbar_wait(&full_bar[s], (kb / C::STAGES) & 1)) {
+                atomicCAS(&g_tc_error, 0, (2 << 16) | (int)blockIdx.x);
+                s_failed = 1;
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const unsigned st = smem_u32(smem + s * C::STAGE_BYTES);
+            const unsigned long long w_desc = smem_desc(st);
+            const unsigned long long u_desc = smem_desc(st + C::W_BYTES);
+            const unsigned long long a_desc = smem_desc(st + (DUAL ? 2 : 1) * C::W_BYTES);
+#pragma unroll
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
+                const bool acc = (kb > 0) || (k > 0);
+                tc_mma(tmem_base, w_desc + adv, a_desc + adv, idesc, acc);
+                if (DUAL) tc_mma(tmem_base + TOK, u_desc + adv, a_desc + adv, idesc, acc);
+            }
+            tc_commit(&empty_bar[s]);        // the stage is free when these MMAs have read it
+        }
+        if (ok) tc_commit(tmem_full_bar);    // the accumulator is complete when all MMAs are done
+    } else if (warp >= 2) {
+        // ---------------- epilogue: TMEM -> registers -> global
+        const int quad = warp & 3;                       // the TMEM lanes this warp may read: 32*quad..
+        const int f = f0 + quad * 32 + lane;             // this thread's output feature
+        bool ok = mbar_wait(tmem_full_bar, 0);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            if (lane == 0) { atomicCAS(&g_tc_error, 0, (3 << 16) | (int)blockIdx.x); s_failed = 1; }
+        } else {
+            tc_fence_after();
+            const float b = (bias != nullptr && f < n_out) ? bias[f] : 0.f;
+            const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < TOK; c += 16) {
+                float v[16], u[16];
+                tmem_ld16(lane_addr + c, v);
+                if (DUAL) tmem_ld16(lane_addr + TOK + c, u);
+                if (f < n_out) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c + j;
+                        if (t >= tokens) break;
+                        const size_t o = (size_t)t * ldo + f;
+                        const float x = v[j] + b;
+                        if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
+                        else if (EPI == EPI_ADD) ((float*)out)[o] += x;
+                        else if (EPI == EPI_F32) ((float*)out)[o] = x;
+                        else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * u[j]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Map of a row-major bfloat16 matrix [rows, k] with row stride ld elements; box = 64 x box_rows, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long k, long long ld, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    NIB_REQUIRE(enc != nullptr, "gemm (tensor cores): cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    NIB_REQUIRE(r == CUDA_SUCCESS, "gemm (tensor cores): cuTensorMapEncodeTiled failed with code %d (rows=%lld k=%lld ld=%lld)", (int)r, rows, k, ld);
+    return 0;
+}
+
+struct MapKey {
+    const void* p; long long rows, k; int box;
+    bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && k == o.k && box == o.box; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& x) const {
+        return std::hash<const void*>()(x.p) ^ (std::hash<long long>()(x.rows) * 31) ^ (std::hash<long long>()(x.k) * 131) ^ (size_t)x.box;
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_weight_maps;   // weights live as long as the model
+std::mutex g_map_mutex;
+
+template <int TOK, int EPI>
+int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens, int n_out,
+              int k, int ldo, cudaStream_t stream) {
+    using C = Cfg<TOK, EPI == EPI_SWIGLU>;
+    static bool configured = false;
+    if (!configured) {
+        NIB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TOK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured = true;
+    }
+    dim3 grid(ceil_div(n_out, BLOCK_F), ceil_div(tokens, TOK));
+    gemm_tc_kernel<TOK, EPI><<<grid, THREADS, C::SMEM, stream>>>(mw, ma, bias, out, tokens, n_out, k, ldo);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int TOK>
+int launch_tc_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens,
+                  int n_out, int k, int ldo, cudaStream_t stream) {
+    switch (epi) {
+        case EPI_STORE: return launch_tc<TOK, EPI_STORE>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_ADD: return launch_tc<TOK, EPI_ADD>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_F32: return launch_tc<TOK, EPI_F32>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_SWIGLU: return launch_tc<TOK, EPI_SWIGLU>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+    }
+    nib_set_error("gemm (tensor cores): unknown epilogue %d", epi);
+    return 1;
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernel takes these operands: K a multiple of 8 (16-byte rows) and 16-byte aligned bases.
+NIB_API int nib_gemm_tc_supported(const void* A, const void* W, int K, int lda) {
+    if (K <= 0 || K % 8 || lda % 8) return 0;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 0;
+    return get_encode() != nullptr;
+}
+
+// The error word of the kernels' bounded waits: 0, or (role << 16 | block) of the first wait that ran
+// out (role 1 producer, 2 MMA issuer, 3 epilogue). Reading it synchronises with the device; it is cleared.
+NIB_API int nib_gemm_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    return v;
+}
+
+// A [tokens, K] bfloat16 with row stride lda; W [N, K] (SWIGLU: [2N, K]); out [tokens, N] with row
+// stride ldo. epi: 0 store bf16, 1 add into float, 2 store float, 3 swiglu. tok_tile: 0 = chosen here.
+NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
+                        int lda, int ldo, int epi, int tok_tile, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm (tensor cores): bad sizes tokens=%d N=%d K=%d", tokens, N, K);
+    NIB_REQUIRE(nib_gemm_tc_supported(A, W, K, lda), "gemm (tensor cores): K=%d / lda=%d must be multiples of 8 and bases 16-byte aligned", K, lda);
+    NIB_REQUIRE(epi != EPI_SWIGLU || bias == nullptr, "gemm (tensor cores): the swiglu epilogue takes no bias");
+    if (tokens == 0) return 0;
+    if (tok_tile == 0) {
+        const int f_tiles = ceil_div(N, BLOCK_F);
+        tok_tile = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
+        // 256 tokens per tile halves the shared-memory traffic per flop; take it when the grid still fills the GPU
+        if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148 && epi != EPI_SWIGLU) tok_tile = 256;
+    }
+    NIB_REQUIRE(ceil_div(tokens, tok_tile) <= 65535, "gemm (tensor cores): too many token tiles");
+    const long long w_rows = (epi == EPI_SWIGLU) ? 2LL * N : N;
+    CUtensorMap mw, ma;
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        MapKey key{W, w_rows, K, BLOCK_F};
+        auto it = g_weight_maps.find(key);
+        if (it == g_weight_maps.end()) {
+            if (make_map(&mw, W, w_rows, K, K, BLOCK_F)) return 1;
+            if (g_weight_maps.size() > 4096) g_weight_maps.clear();
+            g_weight_maps.emplace(key, mw);
+        } else {
+            mw = it->second;
+        }
+    }
+    if (make_map(&ma, A, tokens, K, lda, tok_tile)) return 1;
+    switch (tok_tile) {
+        case 16: return launch_tc_epi<16>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+        case 32: return launch_tc_epi<32>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+        case 64: return launch_tc_epi<64>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+        case 128: return launch_tc_epi<128>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+        case 256: return launch_tc_epi<256>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+    }
+    NIB_REQUIRE(false, "gemm (tensor cores): token tile %d is not one of 16, 32, 64, 128, 256", tok_tile);
+}

@@ -44,6 +44,8 @@ class Kernels:
         self.launches = 0           # kernel launches issued through this object (graph replays add theirs)
         self.force_general_attention = False   # tests: run the general attention kernel for bfloat16 too
         self.fixed_decode_splits = 0           # tests: a fixed split count for the decode kernel
+        self.force_simt_gemm = False           # tests: run the CUDA-core GEMM for bfloat16 too
+        self.tc_token_tile = 0                 # tests: a fixed token tile for the tensor-core GEMM (0 = chosen)
         self.sm_count = 148
         try:
             self._lib = ctypes.CDLL(lib_path)
@@ -51,7 +53,7 @@ class Kernels:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
-                     "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
+                     "nib_gemm_tc", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
                      "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
@@ -97,9 +99,23 @@ class Kernels:
         want_out = a.dtype if mode == "store" else torch.float32
         if out.dtype != want_out:
             raise KernelError(f"linear[{mode}]: out must be {want_out}, got {out.dtype}")
+        self._gemm(a, w, bias32, out, m, n, k, _EPI[mode])
+
+    def _gemm(self, a, w, bias32, out, m, n, k, epi):
+        """bfloat16 operands with 16-byte rows go to the tcgen05 kernel, everything else to the CUDA-core kernel."""
+        if a.dtype == torch.bfloat16 and not self.force_simt_gemm and \
+                self._lib.nib_gemm_tc_supported(_ptr(a), _ptr(w), c_int(k), c_int(a.stride(0))) == 1:
+            self._check(self._lib.nib_gemm_tc(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                              c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi),
+                                              c_int(self.tc_token_tile), self._stream()), "linear (tensor cores)")
+            return
         self._check(self._lib.nib_gemm_simt(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
-                                            c_int(k), c_int(n), c_int(_EPI[mode]), c_int(_DT[a.dtype]),
+                                            c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi), c_int(_DT[a.dtype]),
                                             self._stream()), "linear")
+
+    def gemm_tc_error(self) -> int:
+        """The error word of the tensor-core GEMM's bounded waits (0 = none); synchronises and clears it."""
+        return self._lib.nib_gemm_tc_error()
 
     def linear_swiglu(self, a, w_gate_up, out):
         """out[M,I] = silu(a . w[:I]^T) * (a . w[I:]^T)."""
@@ -108,9 +124,7 @@ class Kernels:
         inter = w_gate_up.shape[0] // 2
         if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != k or tuple(out.shape) != (m, inter):
             raise KernelError("linear_swiglu: shapes do not fit")
-        self._check(self._lib.nib_gemm_simt(_ptr(a), _ptr(w_gate_up), c_void_p(0), _ptr(out), c_int(m), c_int(inter),
-                                            c_int(k), c_int(k), c_int(inter), c_int(_EPI["swiglu"]),
-                                            c_int(_DT[a.dtype]), self._stream()), "linear_swiglu")
+        self._gemm(a, w_gate_up, None, out, m, inter, k, _EPI["swiglu"])
 
     def rope_store(self, qkv, heads, kv_heads, head_dim, positions, req_index, rotary, block_table,
                    page_size, k_pages, v_pages, writes):

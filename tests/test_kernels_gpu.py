@@ -240,3 +240,44 @@ def test_attention_tensor_core_kernels_agree_with_the_general_kernel(K, heads, k
     finally:
         K.force_general_attention = False
     assert_close(fast, general.double(), dtype, "tensor-core vs general attention")
+
+
+@pytest.mark.parametrize("tile", [0, 16, 32, 64, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(1, 503, 192), (7, 128, 64), (65, 130, 72), (200, 896, 896), (130, 1000, 344),
+                                   (300, 311, 4864), (17, 9, 8)])
+def test_tensor_core_gemm_tiles_and_ragged_shapes(K, m, n, k, tile):
+    """The tcgen05 kernel at every token tile, with rows, features and K that do not fill a tile, in all
+    four epilogues, against float64; and against the CUDA-core kernel row by row."""
+    dtype = torch.bfloat16
+    a, w = rnd((m, k), dtype, 70), rnd((n, k), dtype, 71, scale=0.05)
+    bias = rnd((n,), torch.float32, 72)
+    K.tc_token_tile = tile
+    try:
+        out = torch.empty(m, n, dtype=dtype, device="cuda")
+        K.linear(a, w, bias, out, "store")
+        assert_close(out, _ref_linear_f64(a, w, bias), dtype, "tc store")
+        out32 = torch.empty(m, n, device="cuda")
+        K.linear(a, w, None, out32, "f32")
+        assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "tc f32")
+        res = rnd((m, n), torch.float32, 73)
+        acc = res.clone()
+        K.linear(a, w, bias, acc, "add")
+        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "tc add")
+        inter = max(1, n // 2)
+        sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+        K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+        REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+        assert_close(sw, ref, dtype, "tc swiglu")
+    finally:
+        K.tc_token_tile = 0
+    assert K.gemm_tc_error() == 0
+
+
+def test_tensor_core_gemm_refuses_what_it_cannot_take(K):
+    from nanoinfer_b200.csrc.lib import KernelError
+    a, w = rnd((4, 20), torch.bfloat16, 80), rnd((6, 20), torch.bfloat16, 81)      # K = 20: rows are not 16-byte multiples
+    out = torch.empty(4, 6, device="cuda")
+    K.linear(a, w, None, out, "f32")                      # the dispatcher falls back to the CUDA-core kernel
+    assert_close(out, _ref_linear_f64(a, w, None), torch.float32, "odd K")
+    with pytest.raises(KernelError, match="multiples of 8"):
+        K._check(K._lib.nib_gemm_tc(a.data_ptr(), w.data_ptr(), None, out.data_ptr(), 4, 6, 20, 20, 6, 2, 0, None), "direct")
