@@ -162,7 +162,7 @@ def run_ours(args) -> dict:
         toks = [rng.integers(0, vocab, len(reqs)).tolist() for _ in range(n_warm + n_steps)]
 
         def one(i):
-            logits = engine.step([StepEntry(rc, [toks[i][j]], [0]) for j, rc in enumerate(reqs)])
+            logits = engine.step([StepEntry(rc, [toks[i][j]], [0]) for j, rc in enumerate(reqs)], borrow_logits=True)
             ops.argmax(logits, out)
         for i in range(n_warm):
             one(i)
@@ -189,7 +189,7 @@ def run_ours(args) -> dict:
     # ---- prefill of 2,048 tokens ----------------------------------------------------------
     t_pre = args.prefill_tokens
     pre_ms = []
-    for i in range(3 + 3):
+    for i in range((3 + 3) if args.only != "decode" else 0):
         rc = engine.open(f"p{i}")
         ids = rng.integers(0, vocab, t_pre).tolist()
         torch.cuda.synchronize()
@@ -201,13 +201,18 @@ def run_ours(args) -> dict:
         if i >= 3:
             pre_ms.append(s.elapsed_time(e))
         engine.close(rc)
-    pre = statistics.median(pre_ms)
-    prefill = {"value": round(t_pre / (pre / 1e3), 1), "tokens": t_pre, "ms": round(pre, 3),
-               "frac": round(nums["prefill_flops"](t_pre) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    prefill = None
+    if pre_ms:
+        pre = statistics.median(pre_ms)
+        prefill = {"value": round(t_pre / (pre / 1e3), 1), "tokens": t_pre, "ms": round(pre, 3),
+                   "frac": round(nums["prefill_flops"](t_pre) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    if args.only == "prefill":
+        return {"impl": "ours", "only": "prefill", "prefill": prefill, "config": {"layers": layers}}
 
     # ---- decode points at batch 1 and 64 --------------------------------------------------
     points = {}
-    for b in (1, 64):
+    for b in ((1, 64) if args.only == "all" else ()):
         n_w, n_s = 4, min(steps, 32)
         reqs = fill(b, ctx - n_w - n_s - 1)
         ms, _, _ = decode_timed(reqs, n_w, n_s)
@@ -221,6 +226,9 @@ def run_ours(args) -> dict:
     step_bytes = nums["weight_bytes"] + batch * mean_ctx * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms_step / 1e3) / 1e9
     close_all(reqs)
+    if args.only == "decode":
+        return {"impl": "ours", "only": "decode", "value": round(batch / (ms_step / 1e3), 1), "ms_per_step": round(ms_step, 4),
+                "gpu_launches": launches, "config": {"layers": layers, "global_batch": batch, "seq_len": ctx}}
 
     # ---- end to end through the Python entry point (scheduler) -----------------------------
     sched = Scheduler(model, max_batch=batch, max_tokens_per_step=4096)
@@ -347,6 +355,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
+                    help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         if int(os.environ.get("RANK", "0")) == 0:

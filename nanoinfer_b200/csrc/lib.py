@@ -46,6 +46,7 @@ class Kernels:
         self.fixed_decode_splits = 0           # tests: a fixed split count for the decode kernel
         self.force_simt_gemm = False           # tests: run the CUDA-core GEMM for bfloat16 too
         self.tc_token_tile = 0                 # tests: a fixed token tile for the tensor-core GEMM (0 = chosen)
+        self.smallm_ksplit = 0                 # tests: the K split of the small-M GEMM (0 = chosen, 1 or 4)
         self.sm_count = 148
         try:
             self._lib = ctypes.CDLL(lib_path)
@@ -53,7 +54,7 @@ class Kernels:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
-                     "nib_gemm_tc", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
+                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
                      "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
@@ -102,7 +103,14 @@ class Kernels:
         self._gemm(a, w, bias32, out, m, n, k, _EPI[mode])
 
     def _gemm(self, a, w, bias32, out, m, n, k, epi):
-        """bfloat16 operands with 16-byte rows go to the tcgen05 kernel, everything else to the CUDA-core kernel."""
+        """bfloat16: up to 64 tokens stream the weights through the small-M kernel, more go to the tcgen05
+        kernel; shapes neither takes, and 32-bit, run the CUDA-core kernel."""
+        if a.dtype == torch.bfloat16 and not self.force_simt_gemm and self.tc_token_tile == 0 and \
+                self._lib.nib_gemm_smallm_supported(_ptr(a), _ptr(w), c_int(m), c_int(k), c_int(a.stride(0))) == 1:
+            self._check(self._lib.nib_gemm_smallm(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
+                                                  c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi),
+                                                  c_int(self.smallm_ksplit), self._stream()), "linear (small M)")
+            return
         if a.dtype == torch.bfloat16 and not self.force_simt_gemm and \
                 self._lib.nib_gemm_tc_supported(_ptr(a), _ptr(w), c_int(k), c_int(a.stride(0))) == 1:
             self._check(self._lib.nib_gemm_tc(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),

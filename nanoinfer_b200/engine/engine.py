@@ -60,6 +60,10 @@ class Engine:
         self.graph_launches = 0     # kernel launches replayed from captured graphs
         self._stage = None          # pinned host buffer of the step's int32 inputs
         self._stage_event = None
+        self._graphs = None
+        if engine_config.cuda_graphs and self.device.type == "cuda" and self.model.graph_safe():
+            from .graphs import DecodeGraphs
+            self._graphs = DecodeGraphs(self)
 
     # ---- requests -------------------------------------------------------------------------
     def open(self, request_id) -> RequestCache:
@@ -93,23 +97,35 @@ class Engine:
                 if not (0 <= int(w) < n):
                     raise ValueError(f"wanted place {w} outside the entry's {n} tokens")
 
-    def build_context(self, entries: Sequence[StepEntry]):
-        """Host arrays -> one int32 device buffer -> the views a step needs."""
+    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, widths: Optional[List[int]] = None,
+                      static: Optional[torch.Tensor] = None):
+        """Host arrays -> one int32 device buffer -> the views a step needs.
+
+        With ``pad_to`` the batch is padded to that many requests of one token each; a padding row holds
+        no pages (its block-table row is -1, its context length 0), so kernels write nothing for it and
+        its attention is empty. ``widths`` fixes the block-table widths; ``static`` is a device buffer of
+        the right size that is reused (a captured graph reads its inputs there)."""
         q_lens = [len(e.tokens) for e in entries]
-        r = len(entries)
-        m = sum(q_lens)
-        ctx_lens = [e.request.length + n for e, n in zip(entries, q_lens)]
+        r_real = len(entries)
+        r = max(r_real, pad_to)
+        pad = r - r_real
+        m = sum(q_lens) + pad
+        ctx_lens = [e.request.length + n for e, n in zip(entries, q_lens)] + [0] * pad
+        q_lens_p = q_lens + [1] * pad
         q_start = np.zeros(r + 1, dtype=np.int32)
-        np.cumsum(q_lens, out=q_start[1:])
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        np.cumsum(q_lens_p, out=q_start[1:])
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries] + [np.zeros(pad, np.int32)])
         positions = np.concatenate([np.arange(e.request.length, e.request.length + n, dtype=np.int32)
-                                    for e, n in zip(entries, q_lens)])
-        req_index = np.repeat(np.arange(r, dtype=np.int32), q_lens)
-        slots = np.asarray([e.request.slot for e in entries], dtype=np.int32)
-        want = np.asarray([q_start[i] + int(w) for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
+                                    for e, n in zip(entries, q_lens)] + [np.zeros(pad, np.int32)])
+        req_index = np.repeat(np.arange(r, dtype=np.int32), q_lens_p)
+        slots = np.asarray([e.request.slot for e in entries] + [0] * pad, dtype=np.int32)
+        want_list = [q_start[i] + int(w) for i, e in enumerate(entries) for w in e.want]
+        want = np.asarray(want_list, dtype=np.int32)
+        if pad_to:      # a graph computes the logits of every row
+            want = np.arange(r, dtype=np.int32)
         tables = []
         for g in range(len(self.cache.groups)):
-            width = max(1, max(len(e.request.tables[g]) for e in entries))
+            width = widths[g] if widths is not None else max(1, max(len(e.request.tables[g]) for e in entries))
             t = np.full((r, width), -1, dtype=np.int32)
             for i, e in enumerate(entries):
                 row = e.request.tables[g]
@@ -118,7 +134,7 @@ class Engine:
         parts = [token_ids, positions, req_index, q_start, np.asarray(ctx_lens, dtype=np.int32), slots, want]
         parts += [t.reshape(-1) for t in tables]
         flat = np.concatenate(parts) if parts else np.zeros(0, np.int32)
-        dev = self._to_device(flat)
+        dev = self._to_device(flat, static)
         views, off = [], 0
         for p in parts:
             views.append(dev[off:off + p.size])
@@ -127,11 +143,11 @@ class Engine:
         ctx = StepContext(
             num_tokens=m, token_ids=views[0], positions=views[1], req_index=views[2], q_start=views[3],
             ctx_lens=views[4], state_slots=views[5],
-            host=HostBatch(q_lens=q_lens, ctx_lens=ctx_lens, slots=slots.tolist()),
+            host=HostBatch(q_lens=q_lens_p, ctx_lens=ctx_lens, slots=slots.tolist()),
             block_tables=block_tables, rt=self.rt)
-        return ctx, (views[6] if want.size else None)
+        return ctx, (views[6] if want.size else None), want_list
 
-    def _to_device(self, flat: np.ndarray) -> torch.Tensor:
+    def _to_device(self, flat: np.ndarray, static: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One host-to-device copy of the step's inputs, from pinned memory when the device is a GPU."""
         self.last_h2d_bytes = int(flat.nbytes)
         if self.device.type != "cuda":
@@ -142,16 +158,18 @@ class Engine:
         else:
             self._stage_event.synchronize()      # the previous step's copy has left the buffer
         self._stage[:flat.size].numpy()[:] = flat
-        dev = torch.empty(flat.size, dtype=torch.int32, device=self.device)
+        dev = static if static is not None else torch.empty(flat.size, dtype=torch.int32, device=self.device)
+        assert dev.numel() == flat.size
         dev.copy_(self._stage[:flat.size], non_blocking=True)
         self._stage_event.record()
         return dev
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], borrow_logits: bool = False) -> Optional[torch.Tensor]:
         """Run one batch. Returns logits ``[wanted, vocab]`` (float32, on the device) in the order of the
         entries and of each entry's ``want``; None if nothing is wanted. Raises ``OutOfPages`` before
-        changing anything if the pools cannot hold the new tokens."""
+        changing anything if the pools cannot hold the new tokens. With ``borrow_logits`` the result may be
+        a view of a buffer that the next step overwrites (for callers that consume it at once)."""
         self._check(entries)
         demands = [(e.request, len(e.tokens)) for e in entries]
         if not self.cache.fits(demands):
@@ -159,11 +177,16 @@ class Engine:
         for rc, n in demands:
             self.cache.extend(rc, n)
         self.storage.zero_slots(self.cache.take_fresh_slots())
-        ctx, want_rows = self.build_context(entries)
-        caches = self.storage.layer_caches(ctx.block_tables)
-        logits = self.model.forward(ctx, caches, want_rows)
+        if self._graphs is not None and all(n == 1 for _, n in demands) and len(entries) <= self._graphs.max_batch:
+            logits = self._graphs.step(entries, borrow=borrow_logits)
+            m_tokens = len(entries)
+        else:
+            ctx, want_rows, _ = self.build_context(entries)
+            caches = self.storage.layer_caches(ctx.block_tables)
+            logits = self.model.forward(ctx, caches, want_rows)
+            m_tokens = ctx.num_tokens
         for rc, n in demands:
             self.cache.commit(rc, n)
         self.steps_run += 1
-        self.tokens_run += ctx.num_tokens
+        self.tokens_run += m_tokens
         return logits

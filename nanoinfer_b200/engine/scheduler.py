@@ -229,7 +229,7 @@ class Scheduler:
                     samplers.append(e.seq)
                     rows.append(SampleRow(e.seq.params, e.seq.all_ids if e.seq.params.repetition_penalty != 1.0 else None,
                                           len(e.seq.output_ids), e.seq.req.seed))
-            logits = self.engine.step(entries)
+            logits = self.engine.step(entries, borrow_logits=True)
             for e in plan.entries:
                 e.seq.fed += e.count
             toks = self.model.sampler.sample(logits, rows) if rows else []

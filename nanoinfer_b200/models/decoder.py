@@ -56,6 +56,16 @@ class DecoderModel:
                 out.append((need, state, None))
         return out
 
+    def graph_safe(self) -> bool:
+        """True if every part launches the same kernels whatever the batch holds (no host-side branching
+        on requests), so that a decode step can be captured once and replayed."""
+        parts = [self.embedding, self.final_norm, self.head] + list(self.positions.values())
+        for layer in self.layers:
+            parts += [getattr(layer, n) for n in getattr(layer, "part_names", ())]
+            if not getattr(layer, "part_names", ()):
+                return False
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     # -- one step ------------------------------------------------------------------------------
     def forward(self, ctx: StepContext, caches: List[LayerCache],
                 want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:

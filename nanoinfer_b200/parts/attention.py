@@ -27,6 +27,8 @@ class GroupedQueryAttention(Mixer):
     (0 = all keys), ``position`` (name of a shared position encoding), ``scale`` (optional).
     tensors: ``q_w k_w v_w o_w`` and, with bias, ``q_b k_b v_b``."""
 
+    graph_safe = True   # launches do not depend on which requests are in the batch
+
     @staticmethod
     def spec(prefix: str, hidden: int, heads: int, kv_heads: int, head_dim: int, bias: bool,
              position: str, window: int = 0, scale: Optional[float] = None) -> PartSpec:

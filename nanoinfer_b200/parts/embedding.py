@@ -17,6 +17,8 @@ from .spec import PartSpec, TensorSpec
 class TokenEmbedding(Embedding):
     """params: ``vocab``, ``hidden``. tensors: ``table [vocab, hidden]``."""
 
+    graph_safe = True   # launches do not depend on which requests are in the batch
+
     @staticmethod
     def spec(name: str, vocab: int, hidden: int) -> PartSpec:
         return PartSpec("token_embedding", {"vocab": vocab, "hidden": hidden},
@@ -35,6 +37,8 @@ class TokenEmbedding(Embedding):
 
 class LinearHead(Head):
     """params: ``vocab``, ``hidden``. tensors: ``weight [vocab, hidden]`` (the embedding table when tied)."""
+
+    graph_safe = True   # launches do not depend on which requests are in the batch
 
     @staticmethod
     def spec(name: str, vocab: int, hidden: int) -> PartSpec:

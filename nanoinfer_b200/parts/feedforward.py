@@ -18,6 +18,8 @@ class SwiGLU(FeedForward):
     """params: ``hidden``, ``intermediate``. tensors: ``gate_w up_w [intermediate, hidden]``,
     ``down_w [hidden, intermediate]``."""
 
+    graph_safe = True   # launches do not depend on which requests are in the batch
+
     @staticmethod
     def spec(prefix: str, hidden: int, intermediate: int) -> PartSpec:
         return PartSpec("swiglu", {"hidden": hidden, "intermediate": intermediate}, {

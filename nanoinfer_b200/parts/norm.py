@@ -17,6 +17,8 @@ from .spec import PartSpec, TensorSpec
 class RMSNorm(Norm):
     """params: ``size`` (width of a row), ``eps``. tensors: ``gain [size]``."""
 
+    graph_safe = True   # launches do not depend on which requests are in the batch
+
     @staticmethod
     def spec(size: int, eps: float, gain_name: str) -> PartSpec:
         return PartSpec("rmsnorm", {"size": size, "eps": eps},

@@ -29,6 +29,8 @@ def rotary_tables(max_positions: int, dim: int, theta: float):
 class RotaryEncoding(PositionEncoding):
     """params: ``dim`` (rotated width of a head), ``theta``, ``max_positions``. No tensors."""
 
+    graph_safe = True   # launches do not depend on which requests are in the batch
+
     @staticmethod
     def spec(dim: int, theta: float, max_positions: int) -> PartSpec:
         return PartSpec("rotary", {"dim": dim, "theta": theta, "max_positions": max_positions})
@@ -49,6 +51,8 @@ class RotaryEncoding(PositionEncoding):
 
 class NoPositionEncoding(PositionEncoding):
     """Mixers bound to this encoding use their inputs as they are."""
+
+    graph_safe = True   # launches do not depend on which requests are in the batch
 
     @staticmethod
     def spec() -> PartSpec:

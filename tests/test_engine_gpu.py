@@ -246,3 +246,39 @@ def test_sampling_kernels_follow_the_plain_pipeline(vocab):
     toks = sampler.sample(base.repeat(2, 1).cuda().contiguous(), rows)
     assert toks == [greedy_pick(base[0].numpy(), context, 3.0), 7]
     assert toks[0] == 11
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_graphs_padding_wants_and_buckets(model_dirs, dtype):
+    """Pure decode steps are replayed from captured graphs: three live requests in a bucket of four
+    (one padding row), contexts that cross a bucket edge (256), rows that want nothing, and the same
+    without graphs must agree with the plain implementation."""
+    from nanoinfer_b200.engine import StepEntry
+    d, page = model_dirs["B"]
+    plain = PlainModel(d)
+    g = torch.Generator().manual_seed(9)
+    seqs = [torch.randint(0, 503, (n,), generator=g).tolist() for n in (300, 290, 40)]
+    want = [plain.logits(s) for s in seqs]
+    for graphs in (True, False):
+        eng = engine_for(d, page, dtype, num_pages=128, cuda_graphs=graphs)
+        assert (eng._graphs is not None) == graphs
+        rcs = [eng.open(i) for i in range(3)]
+        starts = [240, 250, 5]
+        eng.step([StepEntry(rc, s[:n], []) for rc, s, n in zip(rcs, seqs, starts)])
+        got = [[] for _ in seqs]
+        for step in range(35):
+            entries, rows = [], []
+            for i, (rc, s) in enumerate(zip(rcs, seqs)):
+                pos = starts[i] + step
+                wants = [0] if (step + i) % 3 else []
+                entries.append(StepEntry(rc, [s[pos]], wants))
+                if wants:
+                    rows.append((i, pos))
+            logits = eng.step(entries)
+            for (i, pos), row in zip(rows, logits):
+                got[i].append((pos, row.clone()))
+        if graphs:
+            assert len(eng._graphs.captured) >= 2 and eng.graph_launches > 0
+        for i in range(3):
+            for pos, row in got[i]:
+                assert_close(row, want[i][pos], tdt(dtype), f"graphs={graphs} request {i} position {pos}")

@@ -281,3 +281,35 @@ def test_tensor_core_gemm_refuses_what_it_cannot_take(K):
     assert_close(out, _ref_linear_f64(a, w, None), torch.float32, "odd K")
     with pytest.raises(KernelError, match="multiples of 8"):
         K._check(K._lib.nib_gemm_tc(a.data_ptr(), w.data_ptr(), None, out.data_ptr(), 4, 6, 20, 20, 6, 2, 0, None), "direct")
+
+
+@pytest.mark.parametrize("ksplit", [0, 1, 4])
+@pytest.mark.parametrize("m,n,k", [(1, 503, 192), (8, 896, 896), (9, 130, 64), (16, 1000, 4864), (33, 311, 320), (64, 72, 128)])
+def test_small_m_gemm(K, m, n, k, ksplit):
+    """The decode GEMM (weights streamed into mma.sync fragments) for 1..64 tokens, both K splits, all
+    epilogues; a row's result does not depend on how many rows are in the call."""
+    dtype = torch.bfloat16
+    a, w = rnd((m, k), dtype, 90), rnd((n, k), dtype, 91, scale=0.05)
+    bias = rnd((n,), torch.float32, 92)
+    K.smallm_ksplit = ksplit
+    try:
+        out = torch.empty(m, n, dtype=dtype, device="cuda")
+        K.linear(a, w, bias, out, "store")
+        assert_close(out, _ref_linear_f64(a, w, bias), dtype, "smallm store")
+        out32 = torch.empty(m, n, device="cuda")
+        K.linear(a, w, None, out32, "f32")
+        assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "smallm f32")
+        res = rnd((m, n), torch.float32, 93)
+        acc = res.clone()
+        K.linear(a, w, bias, acc, "add")
+        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "smallm add")
+        inter = n // 2
+        sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+        K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+        REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+        assert_close(sw, ref, dtype, "smallm swiglu")
+        one = torch.empty(1, n, device="cuda")
+        K.linear(a[m - 1:m].contiguous(), w, None, one, "f32")
+        assert torch.equal(one[0], out32[m - 1])
+    finally:
+        K.smallm_ksplit = 0
