@@ -527,3 +527,42 @@ NIB_API int nib_attention_decode_mma(const void* qkv, int q_stride, void* out, c
 #undef CALL
     NIB_REQUIRE(false, "attention decode: unreachable head_dim %d", head_dim);
 }
+
+// ------------------------------------------------------------------------------------------ no allocation
+// The split decode attention for callers that cannot allocate (see no_alloc.h). Its scratch is this
+// file-scope device array. In host code the name `g_noalloc_scratch` is only a handle for the runtime,
+// not a device address: the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+#include "no_alloc.h"
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NIB_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};
+}
+
+NIB_API int nib_attention_decode_noalloc(const void* qkv, int q_stride, void* out, const int* ctx_lens,
+                                         const int* block_table, int bt_stride, int page_size, const void* k_pages,
+                                         const void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
+                                         int head_dim, float scale, int window, int splits, cudaStream_t stream) {
+    NIB_REQUIRE(n_tokens >= 0 && heads > 0 && head_dim > 0 && splits >= 1, "attention decode (no allocation): bad sizes");
+    const unsigned long long need = (unsigned long long)n_tokens * heads * splits * (head_dim + 2) * sizeof(float);
+    NIB_REQUIRE(need <= NIB_NOALLOC_SCRATCH_BYTES,
+                "attention decode (no allocation): %d tokens x %d heads x %d splits x head_dim %d need %llu bytes of scratch, "
+                "the built-in array has %u; use fewer splits or tokens, or nib_attention_decode_mma with your own scratch",
+                n_tokens, heads, splits, head_dim, need, (unsigned)NIB_NOALLOC_SCRATCH_BYTES);
+    int dev = -1;
+    NIB_CUDA(cudaGetDevice(&dev));
+    NIB_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "attention decode (no allocation): device index %d is out of range", dev);
+    if (g_noalloc_ptr[dev] == nullptr) {          // set-up: first call on this device
+        void* p = nullptr;
+        NIB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        NIB_REQUIRE(p != nullptr, "attention decode (no allocation): the scratch array has no address on device %d", dev);
+        g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    float* part_o = g_noalloc_ptr[dev];
+    float* part_ml = part_o + (size_t)n_tokens * heads * splits * head_dim;
+    return nib_attention_decode_mma(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages,
+                                    num_pages, n_tokens, heads, kv_heads, head_dim, scale, window, splits, part_o,
+                                    part_ml, stream);
+}
