@@ -6,27 +6,35 @@
 //
 // K order: within every block of 32 elements thread t of a quad holds elements 8t..8t+7 of its rows
 // and feeds them to two instructions as their columns (2t, 2t+1, 2t+8, 2t+9); the activations are
-// permuted the same way, so the sum over k is unchanged. A dot product is therefore accumulated in a
-// fixed order that depends on K and on the split only: a row's result does not depend on the batch.
+// permuted the same way, so the sum over k is unchanged.
 //
-// Split over K: for narrow outputs (few row groups) the four warps of a CTA take a quarter of K each
-// and are summed through shared memory in warp order. Epilogues as in gemm_tcgen05.cu.
-// The reference's decode GEMV is a warp per output channel on CUDA cores (cpp/src/cuda/cuda_gemm.cu:47-78).
+// Parallelism. Wide outputs (the head: thousands of 16-row groups): one warp per group, whole K.
+// Narrow outputs: the four warps of a CTA take a quarter of K each (summed through shared memory in
+// warp order), and `cross` CTAs split K further: each writes its partial tile to scratch memory, the
+// CTA that arrives last at the group's counter adds the partials IN SPLIT ORDER and runs the
+// epilogue, then resets the counter. The order of every sum is fixed by (K, splits) alone, so a
+// row's result does not depend on the batch and is the same from run to run.
+//
+// Fused RMSNorm (NORM): the A operand is the 32-bit residual stream; every CTA first computes
+// 1/sqrt(mean(x^2) + eps) of each token row, then normalises, applies the gain and rounds to
+// bfloat16 while building its fragments, exactly what the separate norm kernel would have stored.
+//
+// Epilogues as in gemm_tcgen05.cu. The reference's decode GEMV is a warp per output channel on CUDA
+// cores (cpp/src/cuda/cuda_gemm.cu:47-78); its RMSNorm is a separate kernel with one thread per row
+// (cpp/src/cuda/cuda_elementwise.cu:36-46).
 #include "common.cuh"
 
 namespace {
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
 constexpr int WARPS = 4;
+constexpr int MAX_TOKENS = 64;
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint4 ldg16(const __nv_bfloat16* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
 }
 // Weights are read once per step: do not let them push the activations out of L1.
 __device__ __forceinline__ uint4 ldg16_stream(const __nv_bfloat16* p) {
@@ -35,35 +43,71 @@ __device__ __forceinline__ uint4 ldg16_stream(const __nv_bfloat16* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
 
-// NT: token tiles of 8 (tokens <= 8*NT). KSPLIT: 1 (each warp its own 16 rows) or WARPS (the warps share
-// 16 rows and split K). grid.x: groups of 16 rows per CTA = WARPS / KSPLIT.
-template <int NT, int KSPLIT, int EPI>
+// Eight consecutive elements of the A operand for one token, as four packed pairs.
+template <bool NORM>
+__device__ __forceinline__ uint4 load_a(const void* row, int k, float scale, const float4& g0, const float4& g1) {
+    if (!NORM) return __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(row) + k));
+    const float* x = static_cast<const float*>(row) + k;
+    const float4 a = __ldg(reinterpret_cast<const float4*>(x)), b = __ldg(reinterpret_cast<const float4*>(x + 4));
+    uint4 r;
+    r.x = pack2(a.x * scale * g0.x, a.y * scale * g0.y);
+    r.y = pack2(a.z * scale * g0.z, a.w * scale * g0.w);
+    r.z = pack2(b.x * scale * g1.x, b.y * scale * g1.y);
+    r.w = pack2(b.z * scale * g1.z, b.w * scale * g1.w);
+    return r;
+}
+
+// NT: token tiles of 8. KSPLIT: 1 (each warp its own 16 rows, whole K) or WARPS (the warps of a CTA
+// share 16 rows and split K; gridDim.y CTAs split K further). grid.x: CTAs over the row groups.
+template <int NT, int KSPLIT, int EPI, bool NORM>
 __global__ void __launch_bounds__(WARPS * 32)
-gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
-                   const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim,
-                   int lda, int ldo) {
+gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
+                   void* __restrict__ out, int tokens, int n_out, int k_dim, int lda, int ldo,
+                   const float* __restrict__ gain, float eps, float* __restrict__ scratch, int* __restrict__ counters) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
+    constexpr int ACCS = DUAL ? 2 : 1;
     constexpr int GROUPS = WARPS / KSPLIT;
-    __shared__ float part[KSPLIT > 1 ? KSPLIT : 1][DUAL ? 2 : 1][NT][4][32];
+    extern __shared__ float part[];                      // [KSPLIT][ACCS][NT][4][32] when KSPLIT > 1
+    __shared__ float s_scale[NORM ? MAX_TOKENS : 1];
+    __shared__ int s_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int group = blockIdx.x * GROUPS + (KSPLIT > 1 ? 0 : warp);
     const int f0 = group * 16;
-    const int ks = KSPLIT > 1 ? warp : 0;
+    const int cross = gridDim.y;
 
-    // K range of this warp, in blocks of 32
-    const int blocks = k_dim / 32;                       // K % 32 == 0 is required by the launcher
-    const int per = (blocks + KSPLIT - 1) / KSPLIT;
-    const int kb_begin = ks * per, kb_end = min(blocks, kb_begin + per);
-
-    float acc[NT][4], acc2[DUAL ? NT : 1][4];
-#pragma unroll
-    for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
-    if (DUAL) {
-#pragma unroll
-        for (int n = 0; n < (DUAL ? NT : 1); ++n) { acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f; }
+    if (NORM) {
+        // 1/sqrt(mean(x^2) + eps) of every token row; a warp per row, lanes strided over K
+        for (int m = warp; m < tokens; m += WARPS) {
+            const float* x = static_cast<const float*>(A) + (size_t)m * lda;
+            float ss = 0.f;
+            for (int k = lane * 4; k < k_dim; k += 128) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(x + k));
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) s_scale[m] = 1.0f / sqrtf(ss / (float)k_dim + eps);
+        }
+        __syncthreads();
     }
+
+    // K range of this warp, in blocks of 32, out of KSPLIT * cross equal parts
+    const int blocks = k_dim / 32;
+    const int parts = KSPLIT * cross;
+    const int my_part = (KSPLIT > 1 ? warp : 0) + KSPLIT * blockIdx.y;
+    const int per = (blocks + parts - 1) / parts;
+    const int kb_begin = min(blocks, my_part * per), kb_end = min(blocks, kb_begin + per);
+
+    float acc[ACCS][NT][4];
+#pragma unroll
+    for (int a = 0; a < ACCS; ++a)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { acc[a][n][0] = acc[a][n][1] = acc[a][n][2] = acc[a][n][3] = 0.f; }
 
     if (f0 < n_out) {
         // rows past the end are clamped (their results are not stored)
@@ -72,55 +116,99 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         const __nv_bfloat16* w1 = W + (size_t)r1 * k_dim + 8 * t;
         const __nv_bfloat16* u0 = W + (size_t)(n_out + r0) * k_dim + 8 * t;
         const __nv_bfloat16* u1 = W + (size_t)(n_out + r1) * k_dim + 8 * t;
-        const __nv_bfloat16* a_row[NT];
+        const void* a_row[NT];
+        float a_scale[NT];
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
             const int tok = n * 8 + g;
-            a_row[n] = tok < tokens ? A + (size_t)tok * lda + 8 * t : nullptr;
+            a_row[n] = nullptr;
+            a_scale[n] = 0.f;
+            if (tok < tokens) {
+                a_row[n] = NORM ? (const void*)(static_cast<const float*>(A) + (size_t)tok * lda)
+                                : (const void*)(static_cast<const __nv_bfloat16*>(A) + (size_t)tok * lda);
+                if (NORM) a_scale[n] = s_scale[tok];
+            }
         }
-#pragma unroll 2
+#pragma unroll 4
         for (int kb = kb_begin; kb < kb_end; ++kb) {
             const int k0 = kb * 32;
             const uint4 wa = ldg16_stream(w0 + k0), wb = ldg16_stream(w1 + k0);
             uint4 ua, ub;
             if (DUAL) { ua = ldg16_stream(u0 + k0); ub = ldg16_stream(u1 + k0); }
+            float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+            if (NORM) {
+                g0 = __ldg(reinterpret_cast<const float4*>(gain + k0 + 8 * t));
+                g1 = __ldg(reinterpret_cast<const float4*>(gain + k0 + 8 * t + 4));
+            }
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                if (a_row[n]) x = ldg16(a_row[n] + k0);
-                mma_bf16(acc[n], wa.x, wb.x, wa.y, wb.y, x.x, x.y);
-                mma_bf16(acc[n], wa.z, wb.z, wa.w, wb.w, x.z, x.w);
+                if (a_row[n]) x = load_a<NORM>(a_row[n], k0 + 8 * t, a_scale[n], g0, g1);
+                mma_bf16(acc[0][n], wa.x, wb.x, wa.y, wb.y, x.x, x.y);
+                mma_bf16(acc[0][n], wa.z, wb.z, wa.w, wb.w, x.z, x.w);
                 if (DUAL) {
-                    mma_bf16(acc2[n], ua.x, ub.x, ua.y, ub.y, x.x, x.y);
-                    mma_bf16(acc2[n], ua.z, ub.z, ua.w, ub.w, x.z, x.w);
+                    mma_bf16(acc[ACCS - 1][n], ua.x, ub.x, ua.y, ub.y, x.x, x.y);
+                    mma_bf16(acc[ACCS - 1][n], ua.z, ub.z, ua.w, ub.w, x.z, x.w);
                 }
             }
         }
     }
 
     if (KSPLIT > 1) {
+        // the warps of the CTA, in warp order
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
+        for (int a = 0; a < ACCS; ++a)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                part[ks][0][n][e][lane] = acc[n][e];
-                if (DUAL) part[ks][DUAL ? 1 : 0][n][e][lane] = acc2[DUAL ? n : 0][e];
-            }
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) part[(((warp * ACCS + a) * NT + n) * 4 + e) * 32 + lane] = acc[a][n][e];
         __syncthreads();
-        if (warp != 0) return;
+        if (warp != 0) {
+            if (cross == 1) return;
+        } else {
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
+            for (int a = 0; a < ACCS; ++a)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float s = 0.f, s2 = 0.f;
+                for (int n = 0; n < NT; ++n)
 #pragma unroll
-                for (int w = 0; w < KSPLIT; ++w) {
-                    s += part[w][0][n][e][lane];
-                    if (DUAL) s2 += part[w][DUAL ? 1 : 0][n][e][lane];
-                }
-                acc[n][e] = s;
-                if (DUAL) acc2[DUAL ? n : 0][e] = s2;
+                    for (int e = 0; e < 4; ++e) {
+                        float s = 0.f;
+#pragma unroll
+                        for (int w = 0; w < KSPLIT; ++w) s += part[(((w * ACCS + a) * NT + n) * 4 + e) * 32 + lane];
+                        acc[a][n][e] = s;
+                    }
+        }
+        if (cross > 1) {
+            // the CTAs of the group: partial tiles in scratch, summed in split order by the last to arrive
+            constexpr int TILE = ACCS * NT * 4 * 32;
+            float* mine = scratch + ((size_t)blockIdx.x * cross + blockIdx.y) * TILE;
+            if (warp == 0) {
+#pragma unroll
+                for (int a = 0; a < ACCS; ++a)
+#pragma unroll
+                    for (int n = 0; n < NT; ++n)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) mine[((a * NT + n) * 4 + e) * 32 + lane] = acc[a][n][e];
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) s_last = (atomicAdd(&counters[blockIdx.x], 1) == cross - 1) ? 1 : 0;
             }
+            __syncthreads();
+            if (!s_last || warp != 0) return;
+            __threadfence();
+            const float* base = scratch + (size_t)blockIdx.x * cross * TILE;
+#pragma unroll
+            for (int a = 0; a < ACCS; ++a)
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float s = 0.f;
+                        for (int c = 0; c < cross; ++c) s += __ldcg(base + (size_t)c * TILE + ((a * NT + n) * 4 + e) * 32 + lane);
+                        acc[a][n][e] = s;
+                    }
+            if (lane == 0) counters[blockIdx.x] = 0;     // ready for the next launch
+        }
     }
     if (f0 >= n_out) return;
 
@@ -131,58 +219,112 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         for (int e = 0; e < 4; ++e) {
             const int f = f0 + g + 8 * (e >> 1), tok = n * 8 + 2 * t + (e & 1);
             if (f >= n_out || tok >= tokens) continue;
-            const float x = acc[n][e] + (bias ? bias[f] : 0.f);
+            const float x = acc[0][n][e] + (bias ? bias[f] : 0.f);
             const size_t o = (size_t)tok * ldo + f;
             if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
             else if (EPI == EPI_ADD) ((float*)out)[o] += x;
             else if (EPI == EPI_F32) ((float*)out)[o] = x;
-            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * acc2[DUAL ? n : 0][e]);
+            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * acc[ACCS - 1][n][e]);
         }
 }
 
-template <int NT, int KSPLIT>
-int launch_smallm(int epi, const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
-                  int lda, int ldo, cudaStream_t stream) {
-    const int groups = ceil_div(N, 16);
-    const int grid = ceil_div(groups, WARPS / KSPLIT);
-#define L(E) gemm_smallm_kernel<NT, KSPLIT, E><<<grid, WARPS * 32, 0, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias, out, tokens, N, K, lda, ldo)
-    switch (epi) {
-        case EPI_STORE: L(EPI_STORE); break;
-        case EPI_ADD: L(EPI_ADD); break;
-        case EPI_F32: L(EPI_F32); break;
-        case EPI_SWIGLU: L(EPI_SWIGLU); break;
-        default: nib_set_error("gemm (small M): unknown epilogue %d", epi); return 1;
+struct Args {
+    const void* A; const void* W; const float* bias; void* out; int tokens, N, K, lda, ldo;
+    const float* gain; float eps; float* scratch; int* counters; int cross;
+};
+
+template <int NT, int KSPLIT, int EPI, bool NORM>
+int launch_one(const Args& a, cudaStream_t stream) {
+    constexpr int ACCS = (EPI == EPI_SWIGLU) ? 2 : 1;
+    const int groups = ceil_div(a.N, 16);
+    dim3 grid(ceil_div(groups, WARPS / KSPLIT), KSPLIT > 1 ? a.cross : 1);
+    const size_t smem = KSPLIT > 1 ? (size_t)KSPLIT * ACCS * NT * 4 * 32 * sizeof(float) : 0;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        NIB_CUDA(cudaFuncSetAttribute(gemm_smallm_kernel<NT, KSPLIT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
-#undef L
+    configured = true;
+    gemm_smallm_kernel<NT, KSPLIT, EPI, NORM><<<grid, WARPS * 32, smem, stream>>>(
+        a.A, (const __nv_bfloat16*)a.W, a.bias, a.out, a.tokens, a.N, a.K, a.lda, a.ldo, a.gain, a.eps, a.scratch, a.counters);
     NIB_LAUNCH_CHECK();
     return 0;
 }
 
-template <int NT>
-int launch_smallm_split(int ksplit, int epi, const void* A, const void* W, const float* bias, void* out, int tokens,
-                        int N, int K, int lda, int ldo, cudaStream_t stream) {
-    if (ksplit > 1) return launch_smallm<NT, WARPS>(epi, A, W, bias, out, tokens, N, K, lda, ldo, stream);
-    return launch_smallm<NT, 1>(epi, A, W, bias, out, tokens, N, K, lda, ldo, stream);
+template <int NT, int KSPLIT, bool NORM>
+int launch_epi(int epi, const Args& a, cudaStream_t stream) {
+    switch (epi) {
+        case EPI_STORE: return launch_one<NT, KSPLIT, EPI_STORE, NORM>(a, stream);
+        case EPI_ADD: return launch_one<NT, KSPLIT, EPI_ADD, NORM>(a, stream);
+        case EPI_F32: return launch_one<NT, KSPLIT, EPI_F32, NORM>(a, stream);
+        case EPI_SWIGLU: return launch_one<NT, KSPLIT, EPI_SWIGLU, NORM>(a, stream);
+    }
+    nib_set_error("gemm (small M): unknown epilogue %d", epi);
+    return 1;
+}
+
+template <int NT, bool NORM>
+int launch_split(int ksplit, int epi, const Args& a, cudaStream_t stream) {
+    if (ksplit > 1) return launch_epi<NT, WARPS, NORM>(epi, a, stream);
+    return launch_epi<NT, 1, NORM>(epi, a, stream);
+}
+
+template <bool NORM>
+int launch_tokens(int ksplit, int epi, const Args& a, cudaStream_t stream) {
+    if (a.tokens <= 8) return launch_split<1, NORM>(ksplit, epi, a, stream);
+    if (a.tokens <= 16) return launch_split<2, NORM>(ksplit, epi, a, stream);
+    if (a.tokens <= 32) return launch_split<4, NORM>(ksplit, epi, a, stream);
+    return launch_split<8, NORM>(ksplit, epi, a, stream);
 }
 
 }  // namespace
 
 // 1 if the kernel takes these operands: at most 64 tokens, K a multiple of 32, 16-byte aligned rows.
-NIB_API int nib_gemm_smallm_supported(const void* A, const void* W, int tokens, int K, int lda) {
-    if (tokens <= 0 || tokens > 64 || K <= 0 || K % 32 || lda % 8) return 0;
+// elem_bytes: 2 for a bfloat16 A operand, 4 for the 32-bit residual stream of the fused-norm form.
+NIB_API int nib_gemm_smallm_supported(const void* A, const void* W, int tokens, int K, int lda, int elem_bytes) {
+    if (tokens <= 0 || tokens > MAX_TOKENS || K <= 0 || K % 32) return 0;
+    if ((lda * elem_bytes) % 16) return 0;
     return (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) ? 0 : 1;
 }
 
-// Same operands and epilogues as nib_gemm_tc. ksplit: 0 = chosen here, 1, or 4.
+// Floats of scratch and ints of counters that a call with these sizes may use (for the caller's workspace).
+NIB_API long long nib_gemm_smallm_scratch_floats(int N, int cross) {
+    return (long long)ceil_div(N, 16) * cross * 2 * 8 * 4 * 32;
+}
+
+// Same operands and epilogues as nib_gemm_tc. If gain != nullptr, A is the float residual stream
+// [tokens, K] and is RMS-normalised with (gain, eps) on the fly. ksplit: 0 = chosen here, 1 or 4.
+// cross: CTAs that split K further (needs ksplit 4; 0 = chosen here; > 1 needs scratch of
+// nib_gemm_smallm_scratch_floats floats and ceil(N/16) zeroed counters, both reusable between calls).
 NIB_API int nib_gemm_smallm(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
-                            int lda, int ldo, int epi, int ksplit, cudaStream_t stream) {
+                            int lda, int ldo, int epi, const float* gain, float eps, int ksplit, int cross,
+                            float* scratch, int* counters, long long scratch_floats, int counter_ints,
+                            cudaStream_t stream) {
     NIB_REQUIRE(N > 0 && lda >= K && ldo >= N, "gemm (small M): bad sizes tokens=%d N=%d K=%d", tokens, N, K);
-    NIB_REQUIRE(nib_gemm_smallm_supported(A, W, tokens, K, lda), "gemm (small M): needs 1..64 tokens, K %% 32 == 0 and 16-byte aligned rows (tokens=%d K=%d)", tokens, K);
+    NIB_REQUIRE(nib_gemm_smallm_supported(A, W, tokens, K, lda, gain ? 4 : 2),
+                "gemm (small M): needs 1..64 tokens, K %% 32 == 0 and 16-byte aligned rows (tokens=%d K=%d)", tokens, K);
     NIB_REQUIRE(epi != EPI_SWIGLU || bias == nullptr, "gemm (small M): the swiglu epilogue takes no bias");
-    if (ksplit == 0) ksplit = (ceil_div(N, 16) < 4 * 148 && K >= 512) ? WARPS : 1;
+    NIB_REQUIRE(gain == nullptr || (((uintptr_t)gain & 15) == 0), "gemm (small M): the gain must be 16-byte aligned");
+    const int groups = ceil_div(N, 16), blocks = K / 32;
+    if (ksplit == 0) ksplit = (groups < 8 * 148 && blocks >= 8) ? WARPS : 1;
     NIB_REQUIRE(ksplit == 1 || ksplit == WARPS, "gemm (small M): ksplit must be 1 or %d", WARPS);
-    if (tokens <= 8) return launch_smallm_split<1>(ksplit, epi, A, W, bias, out, tokens, N, K, lda, ldo, stream);
-    if (tokens <= 16) return launch_smallm_split<2>(ksplit, epi, A, W, bias, out, tokens, N, K, lda, ldo, stream);
-    if (tokens <= 32) return launch_smallm_split<4>(ksplit, epi, A, W, bias, out, tokens, N, K, lda, ldo, stream);
-    return launch_smallm_split<8>(ksplit, epi, A, W, bias, out, tokens, N, K, lda, ldo, stream);
+    if (ksplit == 1) cross = 1;
+    if (cross == 0) {
+        // enough CTAs to fill the GPU about four times, at least two blocks of K for every warp
+        cross = 1;
+        if (scratch && counters) {
+            const int want = (4 * 148 + groups - 1) / groups, most = blocks / (2 * WARPS);
+            cross = want < 1 ? 1 : want;
+            if (cross > most) cross = most;
+            if (cross > 16) cross = 16;
+            if (cross < 1) cross = 1;
+        }
+    }
+    if (cross > 1) {
+        NIB_REQUIRE(scratch && counters, "gemm (small M): a cross-CTA split needs scratch memory and counters");
+        NIB_REQUIRE(nib_gemm_smallm_scratch_floats(N, cross) <= scratch_floats && groups <= counter_ints,
+                    "gemm (small M): workspace too small for N=%d cross=%d", N, cross);
+    }
+    Args a{A, W, bias, out, tokens, N, K, lda, ldo, gain, eps, scratch, counters, cross};
+    if (gain) return launch_tokens<true>(ksplit, epi, a, stream);
+    return launch_tokens<false>(ksplit, epi, a, stream);
 }

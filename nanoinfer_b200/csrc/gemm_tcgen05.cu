@@ -226,16 +226,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tmem_ld16(lane_addr + c, v);
                 if (DUAL) tmem_ld16(lane_addr + TOK + c, u);
                 if (f < n_out) {
+                    if (EPI == EPI_ADD) {
+                        // read-modify-write of the residual stream: all 16 loads first, so that they are in
+                        // flight together instead of each waiting behind the previous store
+                        float r[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c + j;
-                        if (t >= tokens) break;
-                        const size_t o = (size_t)t * ldo + f;
-                        const float x = v[j] + b;
-                        if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
-                        else if (EPI == EPI_ADD) ((float*)out)[o] += x;
-                        else if (EPI == EPI_F32) ((float*)out)[o] = x;
-                        else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * u[j]);
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            r[j] = t < tokens ? __ldcg((const float*)out + (size_t)t * ldo + f) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            if (t < tokens) ((float*)out)[(size_t)t * ldo + f] = r[j] + v[j] + b;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            if (t >= tokens) break;
+                            const size_t o = (size_t)t * ldo + f;
+                            const float x = v[j] + b;
+                            if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
+                            else if (EPI == EPI_F32) ((float*)out)[o] = x;
+                            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * u[j]);
+                        }
                     }
                 }
             }
@@ -353,7 +368,7 @@ NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* o
         const int f_tiles = ceil_div(N, BLOCK_F);
         tok_tile = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
         // 256 tokens per tile halves the shared-memory traffic per flop; take it when the grid still fills the GPU
-        if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148 && epi != EPI_SWIGLU) tok_tile = 256;
+        if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148) tok_tile = 256;
     }
     NIB_REQUIRE(ceil_div(tokens, tok_tile) <= 65535, "gemm (tensor cores): too many token tiles");
     const long long w_rows = (epi == EPI_SWIGLU) ? 2LL * N : N;

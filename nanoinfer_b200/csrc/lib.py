@@ -5,7 +5,7 @@ library cannot be built or loaded, or the device is not a CUDA device, they rais
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
 import torch
@@ -48,6 +48,9 @@ class Kernels:
         self.tc_token_tile = 0                 # tests: a fixed token tile for the tensor-core GEMM (0 = chosen)
         self.smallm_ksplit = 0                 # tests: the K split of the small-M GEMM (0 = chosen, 1 or 4)
         self.sm_count = 148
+        self.smallm_cross = 0                  # tests: CTAs that split K in the small-M GEMM (0 = chosen)
+        self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
+        self._ws_counters = None
         try:
             self._lib = ctypes.CDLL(lib_path)
         except OSError as e:
@@ -88,16 +91,27 @@ class Kernels:
         self._check(self._lib.nib_rmsnorm(_ptr(x32), _ptr(gain32), _ptr(rows), _ptr(out), c_int(n), c_int(hidden),
                                           c_float(eps), c_int(_DT[out.dtype]), self._stream()), "rmsnorm")
 
+    def ensure_workspace(self, device) -> None:
+        """Scratch memory that kernels share between launches (allocated once, outside any graph capture)."""
+        if self._ws_scratch is None:
+            self._ws_scratch = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=device)
+            self._ws_counters = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
+
     def linear(self, a, w, bias32, out, mode):
-        """out[M,N] (=, +=) a[M,K] . w[N,K]^T (+ bias). mode: 'store' | 'add' (float out) | 'f32' (float out)."""
-        _need(a, None, "linear a"); _need(w, a.dtype, "linear w"); _need(out, None, "linear out")
+        """out[M,N] (=, +=) a[M,K] . w[N,K]^T (+ bias). mode: 'store' | 'add' (float out) | 'f32' (float out).
+        ``a`` may be a DeferredNorm: the small-M kernel then applies the norm while it reads the residual stream."""
+        deferred = a if hasattr(a, "materialize") else None
+        dtype = a.dtype
+        if deferred is None:
+            _need(a, None, "linear a")
+        _need(w, dtype, "linear w"); _need(out, None, "linear out")
         if bias32 is not None:
             _need(bias32, torch.float32, "linear bias")
         m, k = a.shape
         n = w.shape[0]
         if w.shape[1] != k or tuple(out.shape) != (m, n):
             raise KernelError(f"linear: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not fit")
-        want_out = a.dtype if mode == "store" else torch.float32
+        want_out = dtype if mode == "store" else torch.float32
         if out.dtype != want_out:
             raise KernelError(f"linear[{mode}]: out must be {want_out}, got {out.dtype}")
         self._gemm(a, w, bias32, out, m, n, k, _EPI[mode])
@@ -105,14 +119,24 @@ class Kernels:
     def _gemm(self, a, w, bias32, out, m, n, k, epi):
         """bfloat16: up to 64 tokens stream the weights through the small-M kernel, more go to the tcgen05
         kernel; shapes neither takes, and 32-bit, run the CUDA-core kernel."""
-        if a.dtype == torch.bfloat16 and not self.force_simt_gemm and self.tc_token_tile == 0 and \
-                self._lib.nib_gemm_smallm_supported(_ptr(a), _ptr(w), c_int(m), c_int(k), c_int(a.stride(0))) == 1:
-            self._check(self._lib.nib_gemm_smallm(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
-                                                  c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi),
-                                                  c_int(self.smallm_ksplit), self._stream()), "linear (small M)")
-            return
-        if a.dtype == torch.bfloat16 and not self.force_simt_gemm and \
-                self._lib.nib_gemm_tc_supported(_ptr(a), _ptr(w), c_int(k), c_int(a.stride(0))) == 1:
+        deferred = a if hasattr(a, "materialize") else None
+        bf16 = a.dtype == torch.bfloat16 and not self.force_simt_gemm
+        if bf16 and self.tc_token_tile == 0:
+            src = deferred.x32 if deferred is not None else a
+            if self._lib.nib_gemm_smallm_supported(_ptr(src), _ptr(w), c_int(m), c_int(k), c_int(src.stride(0)),
+                                                   c_int(4 if deferred is not None else 2)) == 1:
+                self.ensure_workspace(src.device)
+                gain = deferred.gain32 if deferred is not None else None
+                self._check(self._lib.nib_gemm_smallm(
+                    _ptr(src), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(src.stride(0)),
+                    c_int(out.stride(0)), c_int(epi), _ptr(gain), c_float(deferred.eps if deferred is not None else 0.0),
+                    c_int(self.smallm_ksplit), c_int(self.smallm_cross), _ptr(self._ws_scratch), _ptr(self._ws_counters),
+                    c_longlong(self._ws_scratch.numel()), c_int(self._ws_counters.numel()), self._stream()),
+                    "linear (small M)")
+                return
+        if deferred is not None:
+            a = deferred.materialize()
+        if bf16 and self._lib.nib_gemm_tc_supported(_ptr(a), _ptr(w), c_int(k), c_int(a.stride(0))) == 1:
             self._check(self._lib.nib_gemm_tc(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
                                               c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi),
                                               c_int(self.tc_token_tile), self._stream()), "linear (tensor cores)")
@@ -127,7 +151,9 @@ class Kernels:
 
     def linear_swiglu(self, a, w_gate_up, out):
         """out[M,I] = silu(a . w[:I]^T) * (a . w[I:]^T)."""
-        _need(a, None, "swiglu a"); _need(w_gate_up, a.dtype, "swiglu w"); _need(out, a.dtype, "swiglu out")
+        if not hasattr(a, "materialize"):
+            _need(a, None, "swiglu a")
+        _need(w_gate_up, a.dtype, "swiglu w"); _need(out, a.dtype, "swiglu out")
         m, k = a.shape
         inter = w_gate_up.shape[0] // 2
         if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != k or tuple(out.shape) != (m, inter):
@@ -262,5 +288,6 @@ def load_kernels(verbose: bool = True) -> Kernels:
         if arch != 100:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{arch}")
         k.sm_count = max(1, k._lib.nib_sm_count())
+        k.ensure_workspace(torch.device("cuda", torch.cuda.current_device()))
         _KERNELS = k
     return _KERNELS

@@ -144,7 +144,8 @@ class Engine:
             num_tokens=m, token_ids=views[0], positions=views[1], req_index=views[2], q_start=views[3],
             ctx_lens=views[4], state_slots=views[5],
             host=HostBatch(q_lens=q_lens_p, ctx_lens=ctx_lens, slots=slots.tolist()),
-            block_tables=block_tables, rt=self.rt)
+            block_tables=block_tables, rt=self.rt,
+            all_rows_wanted=(want.size == m and bool((want == np.arange(m, dtype=np.int32)).all())))
         return ctx, (views[6] if want.size else None), want_list
 
     def _to_device(self, flat: np.ndarray, static: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -77,8 +77,9 @@ class DecoderModel:
             self.layers[e.layer].forward(x32, ctx, caches[i])
         if want_rows is None or want_rows.numel() == 0:
             return None
-        h = self.final_norm.forward(x32, rows=want_rows)
-        return self.head.forward(h)
+        if ctx.all_rows_wanted and getattr(self.head, "accepts_deferred_norm", False):
+            return self.head.forward(self.final_norm.deferred(x32))
+        return self.head.forward(self.final_norm.forward(x32, rows=want_rows))
 
 
 class _SharingRuntime(Runtime):

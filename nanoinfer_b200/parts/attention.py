@@ -28,6 +28,7 @@ class GroupedQueryAttention(Mixer):
     tensors: ``q_w k_w v_w o_w`` and, with bias, ``q_b k_b v_b``."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
+    accepts_deferred_norm = True   # its first projection can apply the norm while reading its input
 
     @staticmethod
     def spec(prefix: str, hidden: int, heads: int, kv_heads: int, head_dim: int, bias: bool,

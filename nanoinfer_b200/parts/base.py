@@ -96,6 +96,7 @@ class StepContext:
     host: HostBatch
     block_tables: Dict[int, torch.Tensor] = field(default_factory=dict)  # cache group -> [R, pages]
     rt: Optional[Runtime] = None
+    all_rows_wanted: bool = False  # logits are wanted at every row, in row order
 
 
 @dataclass
@@ -109,6 +110,29 @@ class LayerCache:
     state: Optional[torch.Tensor]       # [slots, *StateNeed.shape]
 
 
+class DeferredNorm:
+    """A norm that has not been computed yet: ``h = norm(x32)``, for a consumer whose kernel can apply the
+    norm while it reads its input (the decode GEMM). It looks like ``h`` (shape, dtype, device); any other
+    consumer gets the tensor from ``materialize()``."""
+
+    def __init__(self, norm: "Norm", x32: torch.Tensor, gain32: torch.Tensor, eps: float, dtype: torch.dtype):
+        self.norm, self.x32, self.gain32, self.eps, self.dtype = norm, x32, gain32, eps, dtype
+        self._tensor: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.x32.shape
+
+    @property
+    def device(self):
+        return self.x32.device
+
+    def materialize(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self.norm.forward(self.x32)
+        return self._tensor
+
+
 class Part:
     def __init__(self, spec: PartSpec, tensors: Dict[str, torch.Tensor], rt: Runtime):
         self.spec, self.rt = spec, rt
@@ -118,6 +142,10 @@ class Part:
 class Norm(Part):
     def forward(self, x32: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
+
+    def deferred(self, x32: torch.Tensor):
+        """``forward(x32)``, or a ``DeferredNorm`` that a consumer with ``accepts_deferred_norm`` resolves."""
+        return self.forward(x32)
 
 
 class PositionEncoding(Part):

@@ -24,8 +24,11 @@ class PreNormBlock:
         self.ffn_norm, self.ffn = parts["ffn_norm"], parts["ffn"]
 
     def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
-        self.mixer.forward(self.mixer_norm.forward(x32), x32, ctx, cache)
-        self.ffn.forward(self.ffn_norm.forward(x32), x32, ctx)
+        # A part that says so takes its norm unresolved and lets its first projection apply it.
+        norm = self.mixer_norm.deferred if getattr(self.mixer, "accepts_deferred_norm", False) else self.mixer_norm.forward
+        self.mixer.forward(norm(x32), x32, ctx, cache)
+        norm = self.ffn_norm.deferred if getattr(self.ffn, "accepts_deferred_norm", False) else self.ffn_norm.forward
+        self.ffn.forward(norm(x32), x32, ctx)
 
 
 register_arrangement("pre_norm", PreNormBlock)

@@ -10,7 +10,7 @@ from typing import Dict, Optional
 import torch
 
 from ..registry import register_part
-from .base import Norm, Runtime
+from .base import DeferredNorm, Norm, Runtime
 from .spec import PartSpec, TensorSpec
 
 
@@ -36,5 +36,9 @@ class RMSNorm(Norm):
         self.ops.rmsnorm(x32, self.gain, self.eps, out, rows)
         return out
 
+    def deferred(self, x32: torch.Tensor):
+        return DeferredNorm(self, x32, self.gain, self.eps, self.rt.dtype)
+
 
 register_part("rmsnorm", RMSNorm)
+

@@ -283,19 +283,22 @@ def test_tensor_core_gemm_refuses_what_it_cannot_take(K):
         K._check(K._lib.nib_gemm_tc(a.data_ptr(), w.data_ptr(), None, out.data_ptr(), 4, 6, 20, 20, 6, 2, 0, None), "direct")
 
 
-@pytest.mark.parametrize("ksplit", [0, 1, 4])
+@pytest.mark.parametrize("ksplit,cross", [(0, 0), (1, 0), (4, 1), (4, 3), (4, 16)])
 @pytest.mark.parametrize("m,n,k", [(1, 503, 192), (8, 896, 896), (9, 130, 64), (16, 1000, 4864), (33, 311, 320), (64, 72, 128)])
-def test_small_m_gemm(K, m, n, k, ksplit):
+def test_small_m_gemm(K, m, n, k, ksplit, cross):
     """The decode GEMM (weights streamed into mma.sync fragments) for 1..64 tokens, both K splits, all
     epilogues; a row's result does not depend on how many rows are in the call."""
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 90), rnd((n, k), dtype, 91, scale=0.05)
     bias = rnd((n,), torch.float32, 92)
-    K.smallm_ksplit = ksplit
+    K.smallm_ksplit, K.smallm_cross = ksplit, cross
     try:
         out = torch.empty(m, n, dtype=dtype, device="cuda")
         K.linear(a, w, bias, out, "store")
         assert_close(out, _ref_linear_f64(a, w, bias), dtype, "smallm store")
+        again = torch.empty_like(out)
+        K.linear(a, w, bias, again, "store")
+        assert torch.equal(out, again)            # the split over CTAs is summed in a fixed order
         out32 = torch.empty(m, n, device="cuda")
         K.linear(a, w, None, out32, "f32")
         assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "smallm f32")
@@ -312,4 +315,35 @@ def test_small_m_gemm(K, m, n, k, ksplit):
         K.linear(a[m - 1:m].contiguous(), w, None, one, "f32")
         assert torch.equal(one[0], out32[m - 1])
     finally:
-        K.smallm_ksplit = 0
+        K.smallm_ksplit = K.smallm_cross = 0
+
+
+@pytest.mark.parametrize("m,n,k,eps", [(1, 1152, 896, 1e-6), (8, 320, 192, 1e-5), (20, 200, 64, 1e-3), (64, 503, 320, 1e-6)])
+def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
+    """The decode GEMM that reads the 32-bit residual stream and applies RMSNorm on the fly, against the
+    separate norm kernel followed by the same GEMM, and against float64."""
+    from nanoinfer_b200.parts.base import DeferredNorm
+
+    class _Norm:
+        def forward(self_, x32, rows=None):
+            out = torch.empty(x32.shape, dtype=torch.bfloat16, device="cuda")
+            K.rmsnorm(x32, gain, eps, out, rows)
+            return out
+
+    x32 = rnd((m, k), torch.float32, 95, scale=2.5)
+    gain = 1 + 0.1 * rnd((k,), torch.float32, 96)
+    w = rnd((n, k), torch.bfloat16, 97, scale=0.05)
+    fused, two_step = torch.empty(m, n, device="cuda"), torch.empty(m, n, device="cuda")
+    K.linear(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w, None, fused, "f32")
+    h = _Norm().forward(x32)
+    K.linear(h, w, None, two_step, "f32")
+    ref = _ref_linear_f64(h, w, None)
+    assert_close(two_step, ref, torch.float32, "norm then gemm")
+    # the fused kernel sums x^2 in another order: its bfloat16 inputs may differ by one rounding
+    exact = (x32.double() * torch.rsqrt(x32.double().pow(2).mean(-1, keepdim=True) + eps) * gain.double()) @ w.double().t()
+    assert_close(fused, exact, torch.bfloat16, "fused norm gemm")
+    inter = n // 2
+    sw, sw_ref = (torch.empty(m, inter, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    K.linear_swiglu(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w[:2 * inter].contiguous(), sw)
+    REF.linear_swiglu(h, w[:2 * inter].contiguous(), sw_ref)
+    assert_close(sw, sw_ref, torch.bfloat16, "fused norm swiglu")

@@ -22,6 +22,7 @@ class TorchOps:
         out.copy_(y.to(out.dtype))
 
     def linear(self, a, w, bias32, out, mode):
+        a = a.materialize() if hasattr(a, "materialize") else a
         y = a.double() @ w.double().t()
         if bias32 is not None:
             y = y + bias32.double()
@@ -33,6 +34,7 @@ class TorchOps:
             raise ValueError(mode)
 
     def linear_swiglu(self, a, w_gate_up, out):
+        a = a.materialize() if hasattr(a, "materialize") else a
         inter = w_gate_up.shape[0] // 2
         g = a.double() @ w_gate_up[:inter].double().t()
         u = a.double() @ w_gate_up[inter:].double().t()
