@@ -141,7 +141,7 @@ def run_ours(args) -> dict:
     page = 16
     num_pages = max_batch * (-(-ctx // page) + 1) + 8
     model = load_model(tmp, dtype="bfloat16", page_size=page, num_pages=num_pages, max_batch=max_batch,
-                       max_tokens_per_step=4096)
+                       max_tokens_per_step=4096, cuda_graphs=not args.no_graphs)
     engine, ops = model.engine, model.engine.rt.ops
     print(f"[bench] model ready in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
 
@@ -355,6 +355,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profilers that filter by kernel name)")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
     args = ap.parse_args()

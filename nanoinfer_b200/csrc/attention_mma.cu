@@ -302,6 +302,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
                         const __nv_bfloat16* __restrict__ v_pages, int num_pages, int heads, int kv_heads,
                         float scale, int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
     const int split = blockIdx.x, token = blockIdx.y, kvh = blockIdx.z;
     const int n_rep = heads / kv_heads;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -320,8 +321,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
     const __nv_bfloat16* q_ptr[2] = {nullptr, nullptr};
     if (g < n_rep) q_ptr[0] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g) * HD;
     if (g + 8 < n_rep) { q_ptr[1] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g + 8) * HD; vis_hi[1] = p; }
-    unsigned q[HD / 16][4];
-    load_q<HD>(q, q_ptr, lane);
 
     float o[HD / 8][4];
 #pragma unroll
@@ -331,20 +330,35 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
 
     unsigned char* k_buf[2] = {smem, smem + 2 * Tile<HD>::BYTES};
     unsigned char* v_buf[2] = {smem + Tile<HD>::BYTES, smem + 3 * Tile<HD>::BYTES};
+    auto issue = [&](int tile, int buf) {
+        load_tile<HD, WARPS * 32>(k_buf[buf], k_pages, bt, page_size, num_pages, kv_heads, kvh, tile * BLOCK_N, lo, p, tid);
+        load_tile<HD, WARPS * 32>(v_buf[buf], v_pages, bt, page_size, num_pages, kv_heads, kvh, tile * BLOCK_N, lo, p, tid);
+    };
 
-    if (t_begin <= t_end) {
-        load_tile<HD, WARPS * 32>(k_buf[0], k_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo, p, tid);
-        load_tile<HD, WARPS * 32>(v_buf[0], v_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo, p, tid);
-    }
+    // Two tiles are kept in flight. Keys and values of positions before p were written by earlier steps,
+    // so tiles that do not hold p may be fetched before the wait for the kernels of this step; the tile
+    // that holds p (this step's own key and value) and the queries only after it.
+    const int own = t_last;                        // the tile that holds position p
+    bool issued0 = false, issued1 = false;
+    if (t_begin <= t_end && t_begin < own) { issue(t_begin, 0); issued0 = true; }
     cp_async_commit();
+    if (issued0 && t_begin + 1 <= t_end && t_begin + 1 < own) { issue(t_begin + 1, 1); issued1 = true; }
+    cp_async_commit();
+    pdl_wait();
+    unsigned q[HD / 16][4];
+    load_q<HD>(q, q_ptr, lane);
+    if (!issued0) {
+        if (t_begin <= t_end) issue(t_begin, 0);
+        cp_async_commit();
+    }
+    if (!issued1) {
+        if (t_begin + 1 <= t_end) issue(t_begin + 1, 1);
+        cp_async_commit();
+    }
+    // groups committed so far, oldest first: tile t_begin, tile t_begin + 1 (possibly with empty groups between)
     for (int tile = t_begin; tile <= t_end; ++tile) {
         const int cur = (tile - t_begin) & 1;
-        if (tile < t_end) {
-            load_tile<HD, WARPS * 32>(k_buf[cur ^ 1], k_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo, p, tid);
-            load_tile<HD, WARPS * 32>(v_buf[cur ^ 1], v_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo, p, tid);
-        }
-        cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<1>();                        // everything but the newest group: tile `tile` has landed
         __syncthreads();
         // each warp takes 16 keys of the tile
         float s[2][4];
@@ -355,6 +369,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
         softmax_block<HD, 2>(s, pfrag, o, m_run, l_run, scale2, tile * BLOCK_N + warp * 16, vis_lo, vis_hi, lane);
         pv_tile<HD, 1>(o, pfrag, v_buf[cur], warp * 16, lane);
         __syncthreads();
+        if (tile + 2 <= t_end) issue(tile + 2, cur);
+        cp_async_commit();
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -402,24 +418,46 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
     }
 }
 
-// Merges the partial results of the splits, in split order. grid: tokens * heads; block: HD threads (<= 128).
-__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         __nv_bfloat16* __restrict__ out, int splits, int hd) {
+// Merges the partial results of the splits, in split order. grid: tokens * heads; block: 128 threads.
+// The (max, sum) pairs of all splits are fetched at once into shared memory, and the partial outputs are
+// read in unrolled batches, so the block waits for memory a few times, not once per split.
+__global__ void __launch_bounds__(128)
+attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                         __nv_bfloat16* __restrict__ out, int splits, int hd) {
+    __shared__ float s_m[64], s_f[64];
+    __shared__ float s_l;
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t th = blockIdx.x;
-    const int d = threadIdx.x;
-    if (d >= hd) return;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(th * splits + s) * 2]);
-    float l = 0.f, acc = 0.f;
-    if (m != -INFINITY) {
+    const int tid = threadIdx.x;
+    if (tid < splits) s_m[tid] = __ldcg(part_ml + (th * splits + tid) * 2);
+    if (tid >= 64 && tid - 64 < splits) s_f[tid - 64] = __ldcg(part_ml + (th * splits + (tid - 64)) * 2 + 1);   // sums, for now
+    __syncthreads();
+    if (tid == 0) {
+        float m = -INFINITY;
+        for (int s = 0; s < splits; ++s) m = fmaxf(m, s_m[s]);
+        float l = 0.f;
         for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[(th * splits + s) * 2];
-            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-            l += part_ml[(th * splits + s) * 2 + 1] * f;
-            acc += part_o[(th * splits + s) * hd + d] * f;
+            const float f = (m == -INFINITY || s_m[s] == -INFINITY) ? 0.f : exp2f(s_m[s] - m);
+            l += s_f[s] * f;
+            s_f[s] = f;                                   // from here on: the factor of split s
         }
+        s_l = l;
     }
-    out[th * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    __syncthreads();
+    if (tid >= hd) return;
+    const float* po = part_o + th * splits * hd + tid;
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 8 <= splits; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + (size_t)(s + u) * hd);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += v[u] * s_f[s + u];
+    }
+    for (; s < splits; ++s) acc += __ldcg(po + (size_t)s * hd) * s_f[s];
+    out[th * hd + tid] = __float2bfloat16_rn(s_l > 0.f ? acc / s_l : 0.f);
 }
 
 template <int HD> int prefill_smem() { return 4 * Tile<HD>::BYTES; }
@@ -460,15 +498,13 @@ int launch_decode(const void* qkv, int q_stride, void* out, const int* ctx_lens,
         configured = true;
     }
     dim3 grid(splits, n_tokens, kv_heads);
-    attention_decode_kernel<HD><<<grid, WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
-        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale, window,
-        splits, part_o, part_ml);
-    NIB_LAUNCH_CHECK();
-    if (splits > 1) {
-        attention_combine_kernel<<<n_tokens * heads, HD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, splits, HD);
-        NIB_LAUNCH_CHECK();
-    }
+    NIB_CUDA(launch_pdl(attention_decode_kernel<HD>, grid, dim3(WARPS * 32), (size_t)smem, stream,
+                        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
+                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
+                        window, splits, part_o, part_ml));
+    if (splits > 1)
+        NIB_CUDA(launch_pdl(attention_combine_kernel, dim3(n_tokens * heads), dim3(128), (size_t)0, stream,
+                            (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, HD));
     return 0;
 }
 
@@ -518,7 +554,7 @@ NIB_API int nib_attention_decode_mma(const void* qkv, int q_stride, void* out, c
                                      cudaStream_t stream) {
     NIB_REQUIRE(nib_attention_mma_supported(heads, kv_heads, head_dim), "attention (tensor cores): head_dim %d with %d/%d heads is not supported", head_dim, heads, kv_heads);
     NIB_REQUIRE(heads / kv_heads <= 16, "attention decode: at most 16 query heads per kv head, got %d", heads / kv_heads);
-    NIB_REQUIRE(n_tokens >= 0 && page_size > 0 && num_pages > 0 && window >= 0 && splits >= 1, "attention decode: bad sizes");
+    NIB_REQUIRE(n_tokens >= 0 && page_size > 0 && num_pages > 0 && window >= 0 && splits >= 1 && splits <= 64, "attention decode: bad sizes (1..64 splits)");
     NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode: splits > 1 need scratch memory");
     NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode: too many tokens or kv heads for one launch");
     if (n_tokens == 0) return 0;

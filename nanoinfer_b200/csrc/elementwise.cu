@@ -93,6 +93,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ sin_t, int rot, const int* __restrict__ block_table,
                                   int bt_stride, int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                   int heads, int kv_heads, int head_dim, int num_pages, int write_kv) {
+    pdl_launch_dependents();
     const int m = blockIdx.x;
     const int pos = positions[m];
     T* row = qkv + (size_t)m * (heads + 2 * kv_heads) * head_dim;
@@ -104,6 +105,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         off = pos % page_size;
         if (page < 0 || page >= num_pages) page = -1;  // never write outside the pool
     }
+    pdl_wait();     // positions and block tables are the step's inputs; qkv is the previous kernel's output
     // rotated pairs of queries and keys
     const int pairs = (heads + kv_heads) * half;
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
@@ -147,11 +149,13 @@ NIB_API int nib_rope_store(void* qkv, const int* positions, const int* req_index
     if (m == 0) return 0;
     const int threads = 128;
     if (dtype == NIB_F32)
-        rope_store_kernel<float><<<m, threads, 0, stream>>>((float*)qkv, positions, req_index, cos_t, sin_t, rot,
-            block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, heads, kv_heads, head_dim, num_pages, write_kv);
+        NIB_CUDA(launch_pdl(rope_store_kernel<float>, dim3(m), dim3(threads), (size_t)0, stream, (float*)qkv, positions, req_index,
+                            cos_t, sin_t, rot, block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, heads,
+                            kv_heads, head_dim, num_pages, write_kv));
     else if (dtype == NIB_BF16)
-        rope_store_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, req_index, cos_t, sin_t, rot,
-            block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, heads, kv_heads, head_dim, num_pages, write_kv);
+        NIB_CUDA(launch_pdl(rope_store_kernel<__nv_bfloat16>, dim3(m), dim3(threads), (size_t)0, stream, (__nv_bfloat16*)qkv,
+                            positions, req_index, cos_t, sin_t, rot, block_table, bt_stride, page_size, (__nv_bfloat16*)k_pages,
+                            (__nv_bfloat16*)v_pages, heads, kv_heads, head_dim, num_pages, write_kv));
     else
         NIB_REQUIRE(false, "rope_store: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();

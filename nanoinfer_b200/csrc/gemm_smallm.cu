@@ -9,15 +9,18 @@
 // permuted the same way, so the sum over k is unchanged.
 //
 // Parallelism. Wide outputs (the head: thousands of 16-row groups): one warp per group, whole K.
-// Narrow outputs: the four warps of a CTA take a quarter of K each (summed through shared memory in
+// Narrow outputs: the eight warps of a CTA take an eighth of K each (summed through shared memory in
 // warp order), and `cross` CTAs split K further: each writes its partial tile to scratch memory, the
 // CTA that arrives last at the group's counter adds the partials IN SPLIT ORDER and runs the
 // epilogue, then resets the counter. The order of every sum is fixed by (K, splits) alone, so a
 // row's result does not depend on the batch and is the same from run to run.
 //
-// Fused RMSNorm (NORM): the A operand is the 32-bit residual stream; every CTA first computes
-// 1/sqrt(mean(x^2) + eps) of each token row, then normalises, applies the gain and rounds to
-// bfloat16 while building its fragments, exactly what the separate norm kernel would have stored.
+// Fused RMSNorm (NORM): the A operand is the 32-bit residual stream x. Since
+// sum_k w[f,k] * (x[k] * s * g[k]) = s * sum_k w[f,k] * (x[k] * g[k]) with s = 1/sqrt(mean(x^2) + eps),
+// the fragments are built from bfloat16(x * gain), the sum of x^2 is accumulated from the very values
+// that are loaded for them (every element of a row is loaded by exactly one thread of the K split),
+// reduced along with the accumulators, and s multiplies the accumulator in the epilogue: the norm
+// costs no extra pass over the row and no extra wait.
 //
 // Epilogues as in gemm_tcgen05.cu. The reference's decode GEMV is a warp per output channel on CUDA
 // cores (cpp/src/cuda/cuda_gemm.cu:47-78); its RMSNorm is a separate kernel with one thread per row
@@ -27,7 +30,7 @@
 namespace {
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
-constexpr int WARPS = 4;
+constexpr int WARPS = 8;
 constexpr int MAX_TOKENS = 64;
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -48,20 +51,6 @@ __device__ __forceinline__ unsigned pack2(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Eight consecutive elements of the A operand for one token, as four packed pairs.
-template <bool NORM>
-__device__ __forceinline__ uint4 load_a(const void* row, int k, float scale, const float4& g0, const float4& g1) {
-    if (!NORM) return __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(row) + k));
-    const float* x = static_cast<const float*>(row) + k;
-    const float4 a = __ldg(reinterpret_cast<const float4*>(x)), b = __ldg(reinterpret_cast<const float4*>(x + 4));
-    uint4 r;
-    r.x = pack2(a.x * scale * g0.x, a.y * scale * g0.y);
-    r.y = pack2(a.z * scale * g0.z, a.w * scale * g0.w);
-    r.z = pack2(b.x * scale * g1.x, b.y * scale * g1.y);
-    r.w = pack2(b.z * scale * g1.z, b.w * scale * g1.w);
-    return r;
-}
-
 // NT: token tiles of 8. KSPLIT: 1 (each warp its own 16 rows, whole K) or WARPS (the warps of a CTA
 // share 16 rows and split K; gridDim.y CTAs split K further). grid.x: CTAs over the row groups.
 template <int NT, int KSPLIT, int EPI, bool NORM>
@@ -72,29 +61,16 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     constexpr int ACCS = DUAL ? 2 : 1;
     constexpr int GROUPS = WARPS / KSPLIT;
-    extern __shared__ float part[];                      // [KSPLIT][ACCS][NT][4][32] when KSPLIT > 1
-    __shared__ float s_scale[NORM ? MAX_TOKENS : 1];
+    constexpr int E = NORM ? 5 : 4;                      // accumulator elements per tile, plus the row's sum of squares
+    extern __shared__ float part[];                      // [KSPLIT][ACCS][NT][E][32] when KSPLIT > 1
     __shared__ int s_last;
 
+    pdl_launch_dependents();
+    bool waited = false;          // pdl_wait() comes after the first batch of weight loads has been issued
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int group = blockIdx.x * GROUPS + (KSPLIT > 1 ? 0 : warp);
     const int f0 = group * 16;
     const int cross = gridDim.y;
-
-    if (NORM) {
-        // 1/sqrt(mean(x^2) + eps) of every token row; a warp per row, lanes strided over K
-        for (int m = warp; m < tokens; m += WARPS) {
-            const float* x = static_cast<const float*>(A) + (size_t)m * lda;
-            float ss = 0.f;
-            for (int k = lane * 4; k < k_dim; k += 128) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(x + k));
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) s_scale[m] = 1.0f / sqrtf(ss / (float)k_dim + eps);
-        }
-        __syncthreads();
-    }
 
     // K range of this warp, in blocks of 32, out of KSPLIT * cross equal parts
     const int blocks = k_dim / 32;
@@ -103,11 +79,14 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
     const int per = (blocks + parts - 1) / parts;
     const int kb_begin = min(blocks, my_part * per), kb_end = min(blocks, kb_begin + per);
 
-    float acc[ACCS][NT][4];
+    // acc[a][n][0..3]: the mma tile; acc[0][n][4] (NORM): sum of x^2 of token n*8+g over this thread's elements
+    float acc[ACCS][NT][E];
 #pragma unroll
     for (int a = 0; a < ACCS; ++a)
 #pragma unroll
-        for (int n = 0; n < NT; ++n) { acc[a][n][0] = acc[a][n][1] = acc[a][n][2] = acc[a][n][3] = 0.f; }
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[a][n][e] = 0.f;
 
     if (f0 < n_out) {
         // rows past the end are clamped (their results are not stored)
@@ -117,40 +96,94 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
         const __nv_bfloat16* u0 = W + (size_t)(n_out + r0) * k_dim + 8 * t;
         const __nv_bfloat16* u1 = W + (size_t)(n_out + r1) * k_dim + 8 * t;
         const void* a_row[NT];
-        float a_scale[NT];
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
             const int tok = n * 8 + g;
             a_row[n] = nullptr;
-            a_scale[n] = 0.f;
-            if (tok < tokens) {
+            if (tok < tokens)
                 a_row[n] = NORM ? (const void*)(static_cast<const float*>(A) + (size_t)tok * lda)
                                 : (const void*)(static_cast<const __nv_bfloat16*>(A) + (size_t)tok * lda);
-                if (NORM) a_scale[n] = s_scale[tok];
-            }
         }
-#pragma unroll 4
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-            const int k0 = kb * 32;
-            const uint4 wa = ldg16_stream(w0 + k0), wb = ldg16_stream(w1 + k0);
-            uint4 ua, ub;
-            if (DUAL) { ua = ldg16_stream(u0 + k0); ub = ldg16_stream(u1 + k0); }
-            float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
-            if (NORM) {
-                g0 = __ldg(reinterpret_cast<const float4*>(gain + k0 + 8 * t));
-                g1 = __ldg(reinterpret_cast<const float4*>(gain + k0 + 8 * t + 4));
-            }
+        // Batches of UN blocks: every load of a batch is issued before the first mma that needs one, so a
+        // warp waits for memory once per batch, not once per block (a warp issues in order).
+        constexpr int UN = (NORM || DUAL) ? (NT <= 2 ? 4 : 2) : (NT <= 2 ? 8 : (NT == 4 ? 4 : 2));
+        for (int base = kb_begin; base < kb_end; base += UN) {
+            uint4 wa[UN], wb[UN], ua[DUAL ? UN : 1], ub[DUAL ? UN : 1];
+            uint4 xb[NORM ? 1 : UN][NORM ? 1 : NT];
+            float4 xf[NORM ? UN : 1][NORM ? NT : 1][2], gf[NORM ? UN : 1][2];
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                uint4 x = make_uint4(0u, 0u, 0u, 0u);
-                if (a_row[n]) x = load_a<NORM>(a_row[n], k0 + 8 * t, a_scale[n], g0, g1);
-                mma_bf16(acc[0][n], wa.x, wb.x, wa.y, wb.y, x.x, x.y);
-                mma_bf16(acc[0][n], wa.z, wb.z, wa.w, wb.w, x.z, x.w);
-                if (DUAL) {
-                    mma_bf16(acc[ACCS - 1][n], ua.x, ub.x, ua.y, ub.y, x.x, x.y);
-                    mma_bf16(acc[ACCS - 1][n], ua.z, ub.z, ua.w, ub.w, x.z, x.w);
+            for (int u = 0; u < UN; ++u) {
+                const bool live = base + u < kb_end;
+                const int k0 = (live ? base + u : kb_begin) * 32;      // a block past the end re-reads a valid one and is zeroed
+                wa[u] = ldg16_stream(w0 + k0);
+                wb[u] = ldg16_stream(w1 + k0);
+                if (DUAL) { ua[DUAL ? u : 0] = ldg16_stream(u0 + k0); ub[DUAL ? u : 0] = ldg16_stream(u1 + k0); }
+                if (NORM) {
+                    gf[NORM ? u : 0][0] = __ldg(reinterpret_cast<const float4*>(gain + k0 + 8 * t));
+                    gf[NORM ? u : 0][1] = __ldg(reinterpret_cast<const float4*>(gain + k0 + 8 * t + 4));
                 }
             }
+            if (!waited) { pdl_wait(); waited = true; }     // weights are nobody's output; the activations are
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                const bool live = base + u < kb_end;
+                const int k0 = (live ? base + u : kb_begin) * 32;
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    if (NORM) {
+                        float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                        xf[NORM ? u : 0][NORM ? n : 0][0] = z;
+                        xf[NORM ? u : 0][NORM ? n : 0][1] = z;
+                        if (a_row[n] && live) {
+                            const float* x = static_cast<const float*>(a_row[n]) + k0 + 8 * t;
+                            xf[NORM ? u : 0][NORM ? n : 0][0] = __ldcg(reinterpret_cast<const float4*>(x));
+                            xf[NORM ? u : 0][NORM ? n : 0][1] = __ldcg(reinterpret_cast<const float4*>(x + 4));
+                        }
+                    } else {
+                        xb[NORM ? 0 : u][NORM ? 0 : n] = make_uint4(0u, 0u, 0u, 0u);
+                        if (a_row[n] && live)
+                            xb[NORM ? 0 : u][NORM ? 0 : n] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a_row[n]) + k0 + 8 * t));
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    uint4 x;
+                    if (NORM) {
+                        const float4 xa = xf[NORM ? u : 0][NORM ? n : 0][0], xc = xf[NORM ? u : 0][NORM ? n : 0][1];
+                        const float4 g0 = gf[NORM ? u : 0][0], g1 = gf[NORM ? u : 0][1];
+                        float& ss = acc[0][n][E - 1];
+                        ss = fmaf(xa.x, xa.x, ss); ss = fmaf(xa.y, xa.y, ss); ss = fmaf(xa.z, xa.z, ss); ss = fmaf(xa.w, xa.w, ss);
+                        ss = fmaf(xc.x, xc.x, ss); ss = fmaf(xc.y, xc.y, ss); ss = fmaf(xc.z, xc.z, ss); ss = fmaf(xc.w, xc.w, ss);
+                        x.x = pack2(xa.x * g0.x, xa.y * g0.y);
+                        x.y = pack2(xa.z * g0.z, xa.w * g0.w);
+                        x.z = pack2(xc.x * g1.x, xc.y * g1.y);
+                        x.w = pack2(xc.z * g1.z, xc.w * g1.w);
+                    } else {
+                        x = xb[NORM ? 0 : u][NORM ? 0 : n];
+                    }
+                    // a block past the end has zero activations: it adds nothing
+                    mma_bf16(*reinterpret_cast<float(*)[4]>(&acc[0][n][0]), wa[u].x, wb[u].x, wa[u].y, wb[u].y, x.x, x.y);
+                    mma_bf16(*reinterpret_cast<float(*)[4]>(&acc[0][n][0]), wa[u].z, wb[u].z, wa[u].w, wb[u].w, x.z, x.w);
+                    if (DUAL) {
+                        mma_bf16(*reinterpret_cast<float(*)[4]>(&acc[ACCS - 1][n][0]), ua[DUAL ? u : 0].x, ub[DUAL ? u : 0].x, ua[DUAL ? u : 0].y, ub[DUAL ? u : 0].y, x.x, x.y);
+                        mma_bf16(*reinterpret_cast<float(*)[4]>(&acc[ACCS - 1][n][0]), ua[DUAL ? u : 0].z, ub[DUAL ? u : 0].z, ua[DUAL ? u : 0].w, ub[DUAL ? u : 0].w, x.z, x.w);
+                    }
+                }
+            }
+        }
+    }
+    if (!waited) pdl_wait();      // before the first write (shared results, scratch, output)
+    if (NORM) {
+        // the four threads of a quad hold the same token's partial sums: add them (fixed order)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            float v = acc[0][n][E - 1];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            acc[0][n][E - 1] = v;
         }
     }
 
@@ -161,7 +194,7 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
 #pragma unroll
             for (int n = 0; n < NT; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) part[(((warp * ACCS + a) * NT + n) * 4 + e) * 32 + lane] = acc[a][n][e];
+                for (int e = 0; e < E; ++e) part[(((warp * ACCS + a) * NT + n) * E + e) * 32 + lane] = acc[a][n][e];
         __syncthreads();
         if (warp != 0) {
             if (cross == 1) return;
@@ -171,16 +204,16 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
+                    for (int e = 0; e < E; ++e) {
                         float s = 0.f;
 #pragma unroll
-                        for (int w = 0; w < KSPLIT; ++w) s += part[(((w * ACCS + a) * NT + n) * 4 + e) * 32 + lane];
+                        for (int w = 0; w < KSPLIT; ++w) s += part[(((w * ACCS + a) * NT + n) * E + e) * 32 + lane];
                         acc[a][n][e] = s;
                     }
         }
         if (cross > 1) {
             // the CTAs of the group: partial tiles in scratch, summed in split order by the last to arrive
-            constexpr int TILE = ACCS * NT * 4 * 32;
+            constexpr int TILE = ACCS * NT * E * 32;
             float* mine = scratch + ((size_t)blockIdx.x * cross + blockIdx.y) * TILE;
             if (warp == 0) {
 #pragma unroll
@@ -188,7 +221,7 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
 #pragma unroll
                     for (int n = 0; n < NT; ++n)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) mine[((a * NT + n) * 4 + e) * 32 + lane] = acc[a][n][e];
+                        for (int e = 0; e < E; ++e) mine[((a * NT + n) * E + e) * 32 + lane] = acc[a][n][e];
                 __threadfence();
                 __syncwarp();
                 if (lane == 0) s_last = (atomicAdd(&counters[blockIdx.x], 1) == cross - 1) ? 1 : 0;
@@ -202,9 +235,9 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
+                    for (int e = 0; e < E; ++e) {
                         float s = 0.f;
-                        for (int c = 0; c < cross; ++c) s += __ldcg(base + (size_t)c * TILE + ((a * NT + n) * 4 + e) * 32 + lane);
+                        for (int c = 0; c < cross; ++c) s += __ldcg(base + (size_t)c * TILE + ((a * NT + n) * E + e) * 32 + lane);
                         acc[a][n][e] = s;
                     }
             if (lane == 0) counters[blockIdx.x] = 0;     // ready for the next launch
@@ -212,19 +245,38 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
     }
     if (f0 >= n_out) return;
 
-    // accumulator element e of tile n: feature f0 + g + 8*(e/2), token n*8 + 2t + (e&1)
+    // accumulator element e of tile n: feature f0 + g + 8*(e/2), token n*8 + 2t + (e&1);
+    // the sum of squares of token n*8 + j sits in the lanes of quad j
+    const float bias0 = (bias && f0 + g < n_out) ? bias[f0 + g] : 0.f;
+    const float bias1 = (bias && f0 + g + 8 < n_out) ? bias[f0 + g + 8] : 0.f;
+    float res[NT][4];
+    if (EPI == EPI_ADD) {
+        // the residual stream is read-modify-written: all loads first, so that they wait together
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int f = f0 + g + 8 * (e >> 1), tok = n * 8 + 2 * t + (e & 1);
+                res[n][e] = (f < n_out && tok < tokens) ? __ldcg((const float*)out + (size_t)tok * ldo + f) : 0.f;
+            }
+    }
 #pragma unroll
     for (int n = 0; n < NT; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int f = f0 + g + 8 * (e >> 1), tok = n * 8 + 2 * t + (e & 1);
+            float scale = 1.f;
+            if (NORM) {
+                const float ss = __shfl_sync(0xffffffffu, acc[0][n][E - 1], (2 * t + (e & 1)) * 4);
+                scale = 1.0f / sqrtf(ss / (float)k_dim + eps);
+            }
             if (f >= n_out || tok >= tokens) continue;
-            const float x = acc[0][n][e] + (bias ? bias[f] : 0.f);
+            const float x = acc[0][n][e] * scale + ((e >> 1) ? bias1 : bias0);
             const size_t o = (size_t)tok * ldo + f;
             if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
-            else if (EPI == EPI_ADD) ((float*)out)[o] += x;
+            else if (EPI == EPI_ADD) ((float*)out)[o] = res[n][e] + x;
             else if (EPI == EPI_F32) ((float*)out)[o] = x;
-            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * acc[ACCS - 1][n][e]);
+            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * (acc[ACCS - 1][n][e] * scale));
         }
 }
 
@@ -238,15 +290,15 @@ int launch_one(const Args& a, cudaStream_t stream) {
     constexpr int ACCS = (EPI == EPI_SWIGLU) ? 2 : 1;
     const int groups = ceil_div(a.N, 16);
     dim3 grid(ceil_div(groups, WARPS / KSPLIT), KSPLIT > 1 ? a.cross : 1);
-    const size_t smem = KSPLIT > 1 ? (size_t)KSPLIT * ACCS * NT * 4 * 32 * sizeof(float) : 0;
+    const size_t smem = KSPLIT > 1 ? (size_t)KSPLIT * ACCS * NT * (NORM ? 5 : 4) * 32 * sizeof(float) : 0;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         NIB_CUDA(cudaFuncSetAttribute(gemm_smallm_kernel<NT, KSPLIT, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     }
     configured = true;
-    gemm_smallm_kernel<NT, KSPLIT, EPI, NORM><<<grid, WARPS * 32, smem, stream>>>(
-        a.A, (const __nv_bfloat16*)a.W, a.bias, a.out, a.tokens, a.N, a.K, a.lda, a.ldo, a.gain, a.eps, a.scratch, a.counters);
-    NIB_LAUNCH_CHECK();
+    NIB_CUDA(launch_pdl(gemm_smallm_kernel<NT, KSPLIT, EPI, NORM>, grid, dim3(WARPS * 32), smem, stream,
+                        a.A, (const __nv_bfloat16*)a.W, a.bias, a.out, a.tokens, a.N, a.K, a.lda, a.ldo, a.gain, a.eps,
+                        a.scratch, a.counters));
     return 0;
 }
 
@@ -288,12 +340,12 @@ NIB_API int nib_gemm_smallm_supported(const void* A, const void* W, int tokens, 
 
 // Floats of scratch and ints of counters that a call with these sizes may use (for the caller's workspace).
 NIB_API long long nib_gemm_smallm_scratch_floats(int N, int cross) {
-    return (long long)ceil_div(N, 16) * cross * 2 * 8 * 4 * 32;
+    return (long long)ceil_div(N, 16) * cross * 2 * 8 * 5 * 32;
 }
 
 // Same operands and epilogues as nib_gemm_tc. If gain != nullptr, A is the float residual stream
-// [tokens, K] and is RMS-normalised with (gain, eps) on the fly. ksplit: 0 = chosen here, 1 or 4.
-// cross: CTAs that split K further (needs ksplit 4; 0 = chosen here; > 1 needs scratch of
+// [tokens, K] and is RMS-normalised with (gain, eps) on the fly. ksplit: 0 = chosen here, 1 or 8.
+// cross: CTAs that split K further (needs ksplit 8; 0 = chosen here; > 1 needs scratch of
 // nib_gemm_smallm_scratch_floats floats and ceil(N/16) zeroed counters, both reusable between calls).
 NIB_API int nib_gemm_smallm(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
                             int lda, int ldo, int epi, const float* gain, float eps, int ksplit, int cross,
@@ -305,18 +357,17 @@ NIB_API int nib_gemm_smallm(const void* A, const void* W, const float* bias, voi
     NIB_REQUIRE(epi != EPI_SWIGLU || bias == nullptr, "gemm (small M): the swiglu epilogue takes no bias");
     NIB_REQUIRE(gain == nullptr || (((uintptr_t)gain & 15) == 0), "gemm (small M): the gain must be 16-byte aligned");
     const int groups = ceil_div(N, 16), blocks = K / 32;
-    if (ksplit == 0) ksplit = (groups < 8 * 148 && blocks >= 8) ? WARPS : 1;
+    if (ksplit == 0) ksplit = (groups < 8 * 148 && blocks >= 8) ? WARPS : 1;   // wide outputs: a warp per row group
     NIB_REQUIRE(ksplit == 1 || ksplit == WARPS, "gemm (small M): ksplit must be 1 or %d", WARPS);
     if (ksplit == 1) cross = 1;
     if (cross == 0) {
-        // enough CTAs to fill the GPU about four times, at least two blocks of K for every warp
+        // a warp keeps about eight blocks of K in flight; only a longer K is worth the extra
+        // hand-over between CTAs (a fence, a counter and a second read of the partial tiles)
         cross = 1;
         if (scratch && counters) {
-            const int want = (4 * 148 + groups - 1) / groups, most = blocks / (2 * WARPS);
-            cross = want < 1 ? 1 : want;
-            if (cross > most) cross = most;
+            cross = ceil_div(blocks, WARPS * 4);
             if (cross > 16) cross = 16;
-            if (cross < 1) cross = 1;
+            while (cross > 1 && (long long)groups * cross > 8 * 148) --cross;
         }
     }
     if (cross > 1) {

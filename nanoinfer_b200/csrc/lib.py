@@ -243,14 +243,15 @@ class Kernels:
                 c_float(scale), c_int(window), self._stream()), "attention prefill")
 
     def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int) -> int:
-        """Into how many CTAs the keys of a decoding token are split: enough CTAs to fill the GPU about
-        twice, each with at least 256 keys."""
+        """Into how many CTAs the keys of a decoding token are split: two key tiles per CTA (both are in
+        flight at once, so a CTA waits for memory once), as long as that does not make more CTAs than
+        fill the GPU about four times."""
         if self.fixed_decode_splits:
             return self.fixed_decode_splits
         keys = min(max_ctx, window) if window > 0 else max_ctx
         tiles = -(-keys // 64) + 1
-        want = max(1, (2 * self.sm_count) // max(1, n_tokens * kv_heads))
-        return max(1, min(want, tiles // 4, 64))
+        most = max(1, (4 * self.sm_count) // max(1, n_tokens * kv_heads))
+        return max(1, min(-(-tiles // 2), most, 64))
 
     def argmax(self, logits, out):
         _need(logits, torch.float32, "argmax logits"); _need(out, torch.int32, "argmax out")

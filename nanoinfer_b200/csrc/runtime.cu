@@ -30,3 +30,8 @@ NIB_API int nib_sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
     return n;
 }
+
+// Programmatic dependent launch of the decode kernels: on unless switched off (nib_set_pdl(0)).
+static int g_pdl = 1;
+bool nib_pdl_enabled() { return g_pdl != 0; }
+NIB_API void nib_set_pdl(int on) { g_pdl = on; }

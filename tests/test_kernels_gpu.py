@@ -283,7 +283,7 @@ def test_tensor_core_gemm_refuses_what_it_cannot_take(K):
         K._check(K._lib.nib_gemm_tc(a.data_ptr(), w.data_ptr(), None, out.data_ptr(), 4, 6, 20, 20, 6, 2, 0, None), "direct")
 
 
-@pytest.mark.parametrize("ksplit,cross", [(0, 0), (1, 0), (4, 1), (4, 3), (4, 16)])
+@pytest.mark.parametrize("ksplit,cross", [(0, 0), (1, 0), (8, 1), (8, 3), (8, 16)])
 @pytest.mark.parametrize("m,n,k", [(1, 503, 192), (8, 896, 896), (9, 130, 64), (16, 1000, 4864), (33, 311, 320), (64, 72, 128)])
 def test_small_m_gemm(K, m, n, k, ksplit, cross):
     """The decode GEMM (weights streamed into mma.sync fragments) for 1..64 tokens, both K splits, all
