@@ -54,6 +54,7 @@ class Sequence:
     def __init__(self, req: Request, order: int):
         self.req = req
         self.params = req.sampling()
+        self.ids: List[int] = list(req.prompt_ids)   # prompt + output, grown in place
         self.output_ids: List[int] = []
         self.state = State.WAITING
         self.cache = None          # RequestCache while running
@@ -63,11 +64,15 @@ class Sequence:
 
     @property
     def all_ids(self) -> List[int]:
-        return self.req.prompt_ids + self.output_ids
+        return self.ids
 
     @property
     def pending(self) -> int:
-        return len(self.req.prompt_ids) + len(self.output_ids) - self.fed
+        return len(self.ids) - self.fed
+
+    def emit(self, tok: int) -> None:
+        self.output_ids.append(tok)
+        self.ids.append(tok)
 
 
 @dataclass
@@ -144,8 +149,8 @@ class Scheduler:
         eos = seq.req.eos_id if seq.req.eos_id >= 0 else self._eos_default
         if eos >= 0 and tok == eos:
             return True
-        seq.output_ids.append(tok)
-        if len(seq.all_ids) >= self.engine.max_positions:
+        seq.emit(tok)
+        if len(seq.ids) >= self.engine.max_positions:
             return True            # no position left for another token
         return len(seq.output_ids) >= seq.req.max_tokens
 
@@ -222,7 +227,7 @@ class Scheduler:
         if plan.entries:
             entries, rows, samplers = [], [], []
             for e in plan.entries:
-                ids = e.seq.all_ids[e.start:e.start + e.count]
+                ids = e.seq.ids[e.start:e.start + e.count]
                 wants = e.samples and e.seq.req.max_tokens > 0
                 entries.append(StepEntry(e.seq.cache, ids, [e.count - 1] if wants else []))
                 if wants:
