@@ -207,6 +207,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __
                          const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
                          int num_pages, int heads, int kv_heads, float scale, int window) {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
     const int req = blockIdx.y, kvh = blockIdx.z;
     const int n_rep = heads / kv_heads;
     const int row_begin = q_start[req], q_len = q_start[req + 1] - row_begin;
@@ -242,6 +243,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __
     const int lo_cta = window > 0 ? max(0, pos0 + row0 / n_rep - window + 1) : 0;
     const int t_begin = lo_cta / BLOCK_N, t_end = hi_cta / BLOCK_N;
 
+    pdl_wait();     // queries, and the keys and values of this step's tokens, come from the kernels before
     unsigned q[HD / 16][4];
     load_q<HD>(q, q_ptr, lane);
 
@@ -479,10 +481,10 @@ int launch_prefill(const void* qkv, int q_stride, void* out, const int* q_start,
     }
     const int n_rep = heads / kv_heads;
     dim3 grid(ceil_div((long long)max_q_len * n_rep, WARPS * 16), n_req, kv_heads);
-    attention_prefill_kernel<HD><<<grid, WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size,
-        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale, window);
-    NIB_LAUNCH_CHECK();
+    NIB_CUDA(launch_pdl(attention_prefill_kernel<HD>, grid, dim3(WARPS * 32), (size_t)smem, stream,
+                        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride,
+                        page_size, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads,
+                        scale, window));
     return 0;
 }
 

@@ -47,6 +47,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
     __shared__ float warp_part[THREADS / 32];
     __shared__ float s_scale;
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * hidden;
     float ss = 0.f;
@@ -73,9 +75,10 @@ NIB_API int nib_rmsnorm(const float* x, const float* gain, const int* rows, void
     NIB_REQUIRE(n_rows >= 0 && hidden > 0, "rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
     if (n_rows == 0) return 0;
     if (dtype == NIB_F32)
-        rmsnorm_kernel<float, 256><<<n_rows, 256, 0, stream>>>(x, gain, rows, (float*)out, hidden, eps);
+        NIB_CUDA(launch_pdl(rmsnorm_kernel<float, 256>, dim3(n_rows), dim3(256), (size_t)0, stream, x, gain, rows, (float*)out, hidden, eps));
     else if (dtype == NIB_BF16)
-        rmsnorm_kernel<__nv_bfloat16, 256><<<n_rows, 256, 0, stream>>>(x, gain, rows, (__nv_bfloat16*)out, hidden, eps);
+        NIB_CUDA(launch_pdl(rmsnorm_kernel<__nv_bfloat16, 256>, dim3(n_rows), dim3(256), (size_t)0, stream, x, gain, rows,
+                            (__nv_bfloat16*)out, hidden, eps));
     else
         NIB_REQUIRE(false, "rmsnorm: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();

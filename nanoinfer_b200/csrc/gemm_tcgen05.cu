@@ -7,11 +7,13 @@
 // uses token tiles of 128 or 256. One thread of the epilogue owns one output feature, so bias is a
 // scalar per thread and the residual sum is a coalesced read-modify-write over 32 features.
 //
-// Pipeline per CTA (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane;
-// the warp allocates and frees TMEM), warps 2..5 = epilogue (tcgen05.ld of the warp's lane quadrant).
-// Operand tiles are 64 elements (128 bytes) wide in K with the 128-byte swizzle, written by TMA and
-// read by tcgen05.mma through shared-memory descriptors; STAGES tiles are in flight, tracked by
-// full/empty mbarriers; tcgen05.commit releases a stage when the MMAs that read it are done.
+// Persistent CTAs (at most one per SM) walk over the output tiles. Per CTA (192 threads): warp 0 = TMA
+// producer (one lane), warp 1 = MMA issuer (one lane; the warp allocates and frees TMEM), warps 2..5 =
+// epilogue (tcgen05.ld of the warp's lane quadrant). Operand tiles are 64 elements (128 bytes) wide in K
+// with the 128-byte swizzle, written by TMA and read by tcgen05.mma through shared-memory descriptors;
+// STAGES tiles are in flight, tracked by full/empty mbarriers that run on across output tiles;
+// tcgen05.commit releases a stage when the MMAs that read it are done. The accumulator is double
+// buffered in TMEM: while the epilogue warps drain tile i, the MMA warp already fills tile i+1.
 //
 // Every wait has an iteration limit; a wait that runs out records a code in an error word, the CTA
 // stops issuing, waits (bounded) for its own copies in flight, frees its TMEM and returns.
@@ -121,10 +123,16 @@ template <int TOK, bool DUAL> struct Cfg {
     static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * W_BYTES + A_BYTES;
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
-    static constexpr int TMEM_COLS = tmem_cols(DUAL ? 2 * TOK : TOK);
+    static constexpr int ACC_COLS = (DUAL ? 2 : 1) * TOK;                 // columns of one accumulator buffer
+    static constexpr int TMEM_COLS = tmem_cols(2 * ACC_COLS);             // two buffers
+    static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 };
 
-// grid: (feature tiles of 128, token tiles of TOK)
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// grid: persistent CTAs; tile index -> (feature tile, token tile), feature tiles fastest
 template <int TOK, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -135,18 +143,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + C::STAGES * C::STAGE_BYTES);
     unsigned long long* empty_bar = full_bar + C::STAGES;
-    unsigned long long* tmem_full_bar = empty_bar + C::STAGES;
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(tmem_full_bar + 1);
-    __shared__ int s_failed;
+    unsigned long long* acc_full_bar = empty_bar + C::STAGES;     // [2]
+    unsigned long long* acc_empty_bar = acc_full_bar + 2;         // [2]
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty_bar + 2);
+    __shared__ volatile int s_failed;
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int f0 = blockIdx.x * BLOCK_F, t0 = blockIdx.y * TOK;
+    const int f_tiles = (n_out + BLOCK_F - 1) / BLOCK_F, t_tiles = (tokens + TOK - 1) / TOK;
+    const int tiles = f_tiles * t_tiles;
     const int k_blocks = (k_dim + BLOCK_K - 1) / BLOCK_K;
 
     if (threadIdx.x == 0) {
         s_failed = 0;
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_a) : "memory");
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(tmem_full_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full_bar[b], 1); mbar_init(&acc_empty_bar[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -158,68 +171,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
+    pdl_wait();         // from here on the kernel reads what earlier kernels wrote (activations, the residual stream)
 
     if (warp == 0 && lane == 0) {
-        // ---------------- producer: TMA loads of W (and the up rows) and A tiles
-        int issued = 0;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-            const int s = kb % C::STAGES;
-            if (!mbar_wait(&empty_bar[s], ((kb / C::STAGES) & 1) ^ 1)) {
-                atomicCAS(&g_tc_error, 0, (1 << 16) | (int)blockIdx.x);
-                s_failed = 1;
-                break;
+        // ---------------- producer: TMA loads of W (and the up rows) and A tiles, stage after stage across tiles
+        int it = 0, issued = 0;
+        for (int tile = blockIdx.x; tile < tiles && !s_failed; tile += gridDim.x) {
+            const int f0 = (tile % f_tiles) * BLOCK_F, t0 = (tile / f_tiles) * TOK;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % C::STAGES;
+                if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1)) {
+                    atomicCAS(&g_tc_error, 0, (1 << 16) | (int)blockIdx.x);
+                    s_failed = 1;
+                    break;
+                }
+                unsigned char* st = smem + s * C::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+                tma_load_2d(st, &map_w, &full_bar[s], kb * BLOCK_K, f0);
+                if (DUAL) tma_load_2d(st + C::W_BYTES, &map_w, &full_bar[s], kb * BLOCK_K, n_out + f0);
+                tma_load_2d(st + (DUAL ? 2 : 1) * C::W_BYTES, &map_a, &full_bar[s], kb * BLOCK_K, t0);
+                issued = it + 1;
             }
-            unsigned char* st = smem + s * C::STAGE_BYTES;
-            mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
-            tma_load_2d(st, &map_w, &full_bar[s], kb * BLOCK_K, f0);
-            if (DUAL) tma_load_2d(st + C::W_BYTES, &map_w, &full_bar[s], kb * BLOCK_K, n_out + f0);
-            tma_load_2d(st + (DUAL ? 2 : 1) * C::W_BYTES, &map_a, &full_bar[s], kb * BLOCK_K, t0);
-            ++issued;
         }
         if (s_failed) {
             // copies already issued still target this CTA's shared memory: wait for them, bounded
-            for (int kb = max(0, issued - C::STAGES); kb < issued; ++kb)
-                mbar_wait(&full_bar[kb % C::STAGES], (kb / C::STAGES) & 1);
+            for (int i = max(0, issued - C::STAGES); i < issued; ++i)
+                mbar_wait(&full_bar[i % C::STAGES], (i / C::STAGES) & 1);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
         constexpr unsigned idesc = instr_desc(TOK);
-        bool ok = true;
-        for (int kb = 0; kb < k_blocks && ok; ++kb) {
-            const int s = kb % C::STAGES;
-            if (!mbar_wait(&full_bar[s], (kb / C::STAGES) & 1)) {
-                atomicCAS(&g_tc_error, 0, (2 << 16) | (int)blockIdx.x);
+        int it = 0, local = 0;
+        for (int tile = blockIdx.x; tile < tiles && !s_failed; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            // the epilogue has drained this buffer (two tiles ago)
+            if (!mbar_wait(&acc_empty_bar[buf], ((local >> 1) & 1) ^ 1)) {
+                atomicCAS(&g_tc_error, 0, (4 << 16) | (int)blockIdx.x);
                 s_failed = 1;
-                ok = false;
                 break;
             }
             tc_fence_after();
-            const unsigned st = smem_u32(smem + s * C::STAGE_BYTES);
-            const unsigned long long w_desc = smem_desc(st);
-            const unsigned long long u_desc = smem_desc(st + C::W_BYTES);
-            const unsigned long long a_desc = smem_desc(st + (DUAL ? 2 : 1) * C::W_BYTES);
+            const unsigned acc = tmem_base + buf * C::ACC_COLS;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % C::STAGES;
+                if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1)) {
+                    atomicCAS(&g_tc_error, 0, (2 << 16) | (int)blockIdx.x);
+                    s_failed = 1;
+                    break;
+                }
+                tc_fence_after();
+                const unsigned st = smem_u32(smem + s * C::STAGE_BYTES);
+                const unsigned long long w_desc = smem_desc(st);
+                const unsigned long long u_desc = smem_desc(st + C::W_BYTES);
+                const unsigned long long a_desc = smem_desc(st + (DUAL ? 2 : 1) * C::W_BYTES);
 #pragma unroll
-            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
-                const bool acc = (kb > 0) || (k > 0);
-                tc_mma(tmem_base, w_desc + adv, a_desc + adv, idesc, acc);
-                if (DUAL) tc_mma(tmem_base + TOK, u_desc + adv, a_desc + adv, idesc, acc);
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
+                    const bool accumulate = (kb > 0) || (k > 0);
+                    tc_mma(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
+                    if (DUAL) tc_mma(acc + TOK, u_desc + adv, a_desc + adv, idesc, accumulate);
+                }
+                tc_commit(&empty_bar[s]);        // the stage is free when these MMAs have read it
             }
-            tc_commit(&empty_bar[s]);        // the stage is free when these MMAs have read it
+            if (s_failed) break;
+            tc_commit(&acc_full_bar[buf]);       // the accumulator is complete when all MMAs are done
         }
-        if (ok) tc_commit(tmem_full_bar);    // the accumulator is complete when all MMAs are done
     } else if (warp >= 2) {
-        // ---------------- epilogue: TMEM -> registers -> global
+        // ---------------- epilogue: TMEM -> registers -> global, one output feature per thread
         const int quad = warp & 3;                       // the TMEM lanes this warp may read: 32*quad..
-        const int f = f0 + quad * 32 + lane;             // this thread's output feature
-        bool ok = mbar_wait(tmem_full_bar, 0);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-            if (lane == 0) { atomicCAS(&g_tc_error, 0, (3 << 16) | (int)blockIdx.x); s_failed = 1; }
-        } else {
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int f0 = (tile % f_tiles) * BLOCK_F, t0 = (tile / f_tiles) * TOK;
+            const int f = f0 + quad * 32 + lane;
+            bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0 && !s_failed) { atomicCAS(&g_tc_error, 0, (3 << 16) | (int)blockIdx.x); s_failed = 1; }
+                break;
+            }
             tc_fence_after();
             const float b = (bias != nullptr && f < n_out) ? bias[f] : 0.f;
-            const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
+            const unsigned lane_addr = tmem_base + buf * C::ACC_COLS + ((unsigned)(quad * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < TOK; c += 16) {
                 float v[16], u[16];
@@ -254,6 +287,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     }
                 }
             }
+            // this warp has read its part of the buffer: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
         }
     }
     tc_fence_before();
@@ -319,9 +356,15 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, v
         NIB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TOK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
-    dim3 grid(ceil_div(n_out, BLOCK_F), ceil_div(tokens, TOK));
-    gemm_tc_kernel<TOK, EPI><<<grid, THREADS, C::SMEM, stream>>>(mw, ma, bias, out, tokens, n_out, k, ldo);
-    NIB_LAUNCH_CHECK();
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        NIB_CUDA(cudaGetDevice(&dev));
+        NIB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const int tiles = ceil_div(n_out, BLOCK_F) * ceil_div(tokens, TOK);
+    NIB_CUDA(launch_pdl(gemm_tc_kernel<TOK, EPI>, dim3(tiles < sms ? tiles : sms), dim3(THREADS), (size_t)C::SMEM, stream,
+                        mw, ma, bias, out, tokens, n_out, k, ldo));
     return 0;
 }
 
@@ -332,7 +375,9 @@ int launch_tc_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const f
         case EPI_STORE: return launch_tc<TOK, EPI_STORE>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
         case EPI_ADD: return launch_tc<TOK, EPI_ADD>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
         case EPI_F32: return launch_tc<TOK, EPI_F32>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
-        case EPI_SWIGLU: return launch_tc<TOK, EPI_SWIGLU>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_SWIGLU:
+            if constexpr (TOK <= 128) return launch_tc<TOK, EPI_SWIGLU>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+            break;
     }
     nib_set_error("gemm (tensor cores): unknown epilogue %d", epi);
     return 1;
@@ -368,7 +413,7 @@ NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* o
         const int f_tiles = ceil_div(N, BLOCK_F);
         tok_tile = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
         // 256 tokens per tile halves the shared-memory traffic per flop; take it when the grid still fills the GPU
-        if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148) tok_tile = 256;
+        if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148 && epi != EPI_SWIGLU) tok_tile = 256;
     }
     NIB_REQUIRE(ceil_div(tokens, tok_tile) <= 65535, "gemm (tensor cores): too many token tiles");
     const long long w_rows = (epi == EPI_SWIGLU) ? 2LL * N : N;
@@ -391,7 +436,9 @@ NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* o
         case 32: return launch_tc_epi<32>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
         case 64: return launch_tc_epi<64>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
         case 128: return launch_tc_epi<128>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
-        case 256: return launch_tc_epi<256>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+        case 256:
+            NIB_REQUIRE(epi != EPI_SWIGLU, "gemm (tensor cores): the swiglu epilogue takes token tiles up to 128 (two accumulators, double buffered)");
+            return launch_tc_epi<256>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
     }
     NIB_REQUIRE(false, "gemm (tensor cores): token tile %d is not one of 16, 32, 64, 128, 256", tok_tile);
 }

@@ -265,6 +265,8 @@ def test_tensor_core_gemm_tiles_and_ragged_shapes(K, m, n, k, tile):
         assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "tc add")
         inter = max(1, n // 2)
         sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+        if tile == 256:
+            K.tc_token_tile = 128      # two accumulators, double buffered: up to 128 tokens per tile
         K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
         REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
         assert_close(sw, ref, dtype, "tc swiglu")
