@@ -282,3 +282,33 @@ def test_decode_graphs_padding_wants_and_buckets(model_dirs, dtype):
         for i in range(3):
             for pos, row in got[i]:
                 assert_close(row, want[i][pos], tdt(dtype), f"graphs={graphs} request {i} position {pos}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_real_layer_widths(tmp_path, dtype):
+    """Two layers with the widths of the 0.5B model (hidden 896, 14/2 heads of 64, intermediate 4864,
+    vocabulary 151936, theta 1e6): a prompt in one step, then cut into portions and single tokens."""
+    from nanoinfer_b200.engine import StepEntry
+    from nanoinfer_b200.registry import config_from_json_dict
+    from nanoinfer_b200.weights import write_random_model
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 2, "hidden_size": 896,
+           "num_attention_heads": 14, "num_key_value_heads": 2, "intermediate_size": 4864, "vocab_size": 151936,
+           "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 4096}
+    d = str(tmp_path / "m")
+    write_random_model(config_from_json_dict(cfg), d, seed=11)
+    plain = PlainModel(d, torch.float32 if dtype == "bfloat16" else torch.float64)
+    ids = torch.randint(0, 151936, (150,), generator=torch.Generator().manual_seed(12)).tolist()
+    want = plain.logits(ids)[[0, 63, 64, 100, 149]]
+    eng = engine_for(d, 16, dtype, num_pages=32)
+    rc = eng.open("whole")
+    got = eng.step([StepEntry(rc, ids, [0, 63, 64, 100, 149])])
+    assert_close(got, want, tdt(dtype), "real widths, whole")
+    eng.close(rc)
+    rc = eng.open("cut")
+    rows = [eng.step([StepEntry(rc, ids[:64], [0, 63])]), eng.step([StepEntry(rc, ids[64:100], [0])])]
+    rows.append(eng.step([StepEntry(rc, [ids[100]], [0])]).clone())
+    for t in ids[101:149]:
+        eng.step([StepEntry(rc, [t], [])])
+    rows.append(eng.step([StepEntry(rc, [ids[149]], [0])]).clone())
+    assert_close(torch.cat(rows), want, tdt(dtype), "real widths, cut")
+    eng.close(rc)
