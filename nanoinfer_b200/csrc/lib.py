@@ -44,6 +44,7 @@ class Kernels:
         self.launches = 0           # kernel launches issued through this object (graph replays add theirs)
         self.force_general_attention = False   # tests: run the general attention kernel for bfloat16 too
         self.fixed_decode_splits = 0           # tests: a fixed split count for the decode kernel
+        self.force_mma_prefill = False         # tests: prompt portions on the mma.sync kernel instead of tcgen05
         self.force_simt_gemm = False           # tests: run the CUDA-core GEMM for bfloat16 too
         self.tc_token_tile = 0                 # tests: a fixed token tile for the tensor-core GEMM (0 = chosen)
         self.smallm_ksplit = 0                 # tests: the K split of the small-M GEMM (0 = chosen, 1 or 4)
@@ -235,12 +236,26 @@ class Kernels:
             if splits > 1:
                 self.launches += 1
         if n_dec < n_req:
-            self._check(self._lib.nib_attention_prefill_mma(
-                _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), c_void_p(ctx.q_start.data_ptr() + 4 * n_dec),
-                c_void_p(ctx.ctx_lens.data_ptr() + 4 * n_dec), c_void_p(block_table.data_ptr() + 4 * n_dec * bt_stride),
-                c_int(bt_stride), c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages),
-                c_int(n_req - n_dec), c_int(max(q_lens[n_dec:])), c_int(heads), c_int(kv_heads), c_int(head_dim),
-                c_float(scale), c_int(window), self._stream()), "attention prefill")
+            q_start = c_void_p(ctx.q_start.data_ptr() + 4 * n_dec)
+            lens = c_void_p(ctx.ctx_lens.data_ptr() + 4 * n_dec)
+            table = c_void_p(block_table.data_ptr() + 4 * n_dec * bt_stride)
+            if not self.force_mma_prefill and self._lib.nib_attention_prefill_tc_supported(
+                    c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(page_size), c_int(qkv.stride(0))) == 1:
+                self._check(self._lib.nib_attention_prefill_tc(
+                    _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), q_start, lens, table, c_int(bt_stride), c_int(page_size),
+                    _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_req - n_dec), c_int(max(q_lens[n_dec:])),
+                    c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+                    self._stream()), "attention prefill (tcgen05)")
+            else:
+                self._check(self._lib.nib_attention_prefill_mma(
+                    _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), q_start, lens, table, c_int(bt_stride), c_int(page_size),
+                    _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_req - n_dec), c_int(max(q_lens[n_dec:])),
+                    c_int(heads), c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), self._stream()),
+                    "attention prefill")
+
+    def attention_tc_error(self) -> int:
+        """The error word of the tcgen05 attention's bounded waits (0 = none); synchronises and clears it."""
+        return self._lib.nib_attention_tc_error()
 
     def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int) -> int:
         """Into how many CTAs the keys of a decoding token are split: two key tiles per CTA (both are in

@@ -349,3 +349,32 @@ def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     K.linear_swiglu(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w[:2 * inter].contiguous(), sw)
     REF.linear_swiglu(h, w[:2 * inter].contiguous(), sw_ref)
     assert_close(sw, sw_ref, torch.bfloat16, "fused norm swiglu")
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page,window", [
+    (14, 2, 64, 16, 0), (12, 2, 128, 16, 0), (4, 4, 64, 8, 0), (7, 1, 64, 64, 0), (16, 2, 128, 32, 200),
+    (3, 1, 64, 16, 100), (28, 4, 128, 128, 0)])
+def test_attention_tcgen05_prefill(K, heads, kv_heads, hd, page, window):
+    """Prompt portions on the tcgen05 kernel (head sizes 64 and 128): portions that start at position 0
+    and inside a context, one token, tile edges at 127/128/129 keys, several requests, pages handed out
+    in shuffled order; against float64 and against the mma.sync kernel."""
+    dtype = torch.bfloat16
+    q_lens, before = [300, 1, 129, 40, 128], [0, 127, 200, 515, 0]
+    total = sum(a + b for a, b in zip(q_lens, before))
+    pages = total // page + 8
+    ctx, bt = make_paged_batch(q_lens, before, page, pages, "cuda", seed=7)
+    kp, vp = _fill_cache(ctx, bt, page, pages, kv_heads, hd, dtype, 110)
+    m = sum(q_lens)
+    qkv = rnd((m, (heads + 2 * kv_heads) * hd), dtype, 112)
+    fast, legacy, ref = (torch.empty(m, heads * hd, dtype=dtype, device="cuda") for _ in range(3))
+    scale = 1.0 / math.sqrt(hd)
+    K.attention(qkv, fast, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    assert K.attention_tc_error() == 0
+    K.force_mma_prefill = True
+    try:
+        K.attention(qkv, legacy, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    finally:
+        K.force_mma_prefill = False
+    assert_close(fast, legacy.double(), dtype, "tcgen05 vs mma.sync attention")
+    REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    assert_close(fast, ref, dtype, "tcgen05 attention")
