@@ -3,10 +3,12 @@
 //
 // A CTA owns a tile of up to 128 rows, where a row is one (token, query head of the kv group): the keys
 // and values of a kv head are read once for all the query heads that share it. For every block of 128
-// keys:   S = Q . K^T      (tcgen05.mma, accumulator S in TMEM, double buffered)
+// keys:   S = Q . K^T      (tcgen05.mma, accumulator S in TMEM)
 //         P = exp2(S*scale - max), row sums       (128 threads, one row each: no shuffles)
 //         O_blk = P . V    (tcgen05.mma, P from shared memory, V as the MN-major operand)
 //         O = O * corr + O_blk                     (registers, 32-bit)
+// S, P and O_blk are double buffered: the softmax of block j+1 runs while the tensor core multiplies
+// P_j by V_j, and the scores of block j+2 are computed meanwhile.
 // Q, K and V tiles arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle): Q through a 3-D map over
 // (head dim, heads of the group, tokens), K and V through a 3-D map over the page pool, one box per
 // page of the block table; a page the request does not hold is fetched from an out-of-range coordinate
@@ -77,8 +79,14 @@ __device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_des
                  " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(unsigned addr, float (&v)[32]) {
-    unsigned r[32];
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// 32 columns of this thread's TMEM lane; the values may be used only after tmem_wait_ld().
+__device__ __forceinline__ void tmem_ld32_async(unsigned addr, unsigned (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
@@ -86,11 +94,7 @@ __device__ __forceinline__ void tmem_ld32(unsigned addr, float (&v)[32]) {
                    "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-
 // K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ unsigned long long desc_kmajor(unsigned smem_addr) {
     unsigned long long d = 0;
@@ -125,15 +129,16 @@ template <int HD> struct Cfg {
     static constexpr int KV_BYTES = SUB * SUBTILE;            // one block of 128 keys (or values)
     static constexpr int P_BYTES = 2 * SUBTILE;               // [128 rows x 128 keys]
     static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;
-    static constexpr int SMEM = OFF_BAR + 256 + 1024;
-    static constexpr int TMEM_COLS = 512;                     // S x2 (256) + O block (HD), rounded up
+    static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+    static constexpr int SMEM = OFF_BAR + 128 + 1024;
+    static constexpr int TMEM_COLS = 512;                     // S x2 (256 columns) + O block x2 (2 x HD)
     static constexpr int COL_S = 0, COL_O = 256;
+    static constexpr int CTAS_PER_SM = 1;
 };
 
 // grid: (row tiles, requests, kv heads)
-template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int HD, bool LOOKAHEAD>
+__global__ void __launch_bounds__(THREADS, Cfg<HD>::CTAS_PER_SM)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
@@ -149,9 +154,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned long long* v_full = bars + 5;        // 2
     unsigned long long* v_empty = bars + 7;       // 2
     unsigned long long* s_full = bars + 9;        // 2
-    unsigned long long* p_full = bars + 11;       // 1, 128 arrivals
-    unsigned long long* o_full = bars + 12;       // 1
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 13);
+    unsigned long long* p_full = bars + 11;       // 2, 128 arrivals each
+    unsigned long long* o_full = bars + 13;       // 2
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
     __shared__ volatile int s_failed;
 
     pdl_launch_dependents();
@@ -160,7 +165,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int tpt = ROWS / n_rep;                         // tokens per tile
     const int rows_tile = tpt * n_rep;
     const int row_begin = q_start[req], q_len = q_start[req + 1] - row_begin;
-    const int tok0 = blockIdx.x * tpt;                    // first token of this tile within the request's portion
+    // tiles late in the portion see the most keys: they start first
+    const int tok0 = (gridDim.x - 1 - blockIdx.x) * tpt;  // first token of this tile within the request's portion
     if (tok0 >= q_len) return;
     const int n_tok = min(tpt, q_len - tok0);
     const int ctx = ctx_lens[req];
@@ -181,9 +187,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&o_full[i], 1);
         }
-        mbar_init(p_full, 128);
-        mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -248,23 +254,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!ok) { atomicCAS(&g_attn_error, 0, (2 << 16) | (int)blockIdx.x); s_failed = 1; }
         auto issue_pv = [&](int j) -> bool {
             const int st = j & 1;
-            if (!mbar_wait(p_full, j & 1) || !mbar_wait(&v_full[st], (j >> 1) & 1)) return false;
+            if (!mbar_wait(&p_full[st], (j >> 1) & 1) || !mbar_wait(&v_full[st], (j >> 1) & 1)) return false;
             tc_fence_after();
             const unsigned v_addr = smem_u32(smem + C::OFF_V + st * C::KV_BYTES);
+            const unsigned pj_addr = p_addr + st * C::P_BYTES;
 #pragma unroll
             for (int kk = 0; kk < KEYS / 16; ++kk) {
                 // P: sub-tile kk/4 (64 keys each), 32 bytes per step inside it; V: 16 keys = 2048 bytes further down
-                const unsigned long long a = desc_kmajor(p_addr + (kk >> 2) * C::SUBTILE) + (unsigned long long)(((kk & 3) * 32) >> 4);
+                const unsigned long long a = desc_kmajor(pj_addr + (kk >> 2) * C::SUBTILE) + (unsigned long long)(((kk & 3) * 32) >> 4);
                 const unsigned long long b = desc_mnmajor(v_addr + kk * 16 * 128, C::SUBTILE);
-                tc_mma(tmem_base + C::COL_O, a, b, idesc_o, kk > 0);
+                tc_mma(tmem_base + C::COL_O + st * HD, a, b, idesc_o, kk > 0);
             }
-            tc_commit(o_full);
+            tc_commit(&o_full[st]);
             tc_commit(&v_empty[st]);
             return true;
         };
-        for (int j = 0; j < n_blk && ok; ++j) {
+        auto issue_qk = [&](int j) -> bool {
             const int st = j & 1;
-            if (!mbar_wait(&k_full[st], (j >> 1) & 1)) { ok = false; break; }
+            if (!mbar_wait(&k_full[st], (j >> 1) & 1)) return false;
             tc_fence_after();
             const unsigned k_addr = smem_u32(smem + C::OFF_K + st * C::KV_BYTES);
 #pragma unroll
@@ -275,9 +282,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             tc_commit(&s_full[st]);
             tc_commit(&k_empty[st]);
-            if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
+            return true;
+        };
+        // QK(0), QK(1), PV(0), QK(2), PV(1), ...: S[b] is free for QK(j+2) once P_j is complete (PV(j) waited for it)
+        if (ok) ok = issue_qk(0);
+        for (int j = 0; j < n_blk && ok; ++j) {
+            if (j + 1 < n_blk) ok = issue_qk(j + 1);
+            if (ok) ok = issue_pv(j);
         }
-        if (ok && !issue_pv(n_blk - 1)) ok = false;
         if (!ok && !s_failed) { atomicCAS(&g_attn_error, 0, (3 << 16) | (int)blockIdx.x); s_failed = 1; }
     } else if (warp >= 2) {
         // ---------------- softmax and output: one row per thread
@@ -294,71 +306,110 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int d = 0; d < HD; ++d) o[d] = 0.f;
         unsigned char* p_row = smem + C::OFF_P + (row >> 3) * 1024 + (row & 7) * 128;
         bool ok = true;
-        for (int j = 0; j < n_blk; ++j) {
-            const int st = j & 1;
-            ok = !s_failed && mbar_wait(&s_full[st], (j >> 1) & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+        float corr_of[2] = {0.f, 0.f};          // the factor that block j applies to the running output, by j & 1
+
+        // Scores of block j -> probabilities in P[j & 1], running max and sum; signals p_full[j & 1].
+        auto softmax_block = [&](int j) -> bool {
+            const int sb = j & 1;
+            bool good = !s_failed && mbar_wait(&s_full[sb], (j >> 1) & 1);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
             tc_fence_after();
             const int key0 = (b_begin + j) * KEYS;
-            const unsigned s_addr = lane_addr + C::COL_S + st * KEYS;
-            // pass 1: the row's maximum over the visible keys of this block
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < KEYS; c += 32) {
-                float v[32];
-                tmem_ld32(s_addr + c, v);
+            const unsigned s_addr = lane_addr + C::COL_S + sb * KEYS;
+            const bool all_visible = key0 >= lo && key0 + KEYS - 1 <= hi;     // no mask needed for this row and block
+            float sum = 0.f;
+            // Scores of the row: four TMEM loads in flight, one wait. Head size 64 keeps all 128 in registers;
+            // head size 128 (128 output registers already) reads them twice instead.
+            unsigned raw[4][32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c + i;
-                    if (key >= lo && key <= hi) mx = fmaxf(mx, v[i] * scale2);
-                }
+            for (int c = 0; c < 4; ++c) tmem_ld32_async(s_addr + c * 32, raw[c]);
+            tmem_wait_ld();
+            float mx = -INFINITY;
+            if (all_visible) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[c][i]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + c * 32 + i;
+                        if (!(key >= lo && key <= hi)) raw[c][i] = 0xff800000u;      // -inf
+                        mx = fmaxf(mx, __uint_as_float(raw[c][i]));
+                    }
             }
+            mx *= scale2;                                                     // scale2 > 0: the max of the scaled scores
             const float m_new = fmaxf(m_run, mx);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
+            corr_of[sb] = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
             m_run = m_new;
-            // pass 2: probabilities, their sum, and the bfloat16 P tile (swizzled rows of 128 bytes per 64 keys)
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < KEYS; c += 32) {
-                float v[32];
-                tmem_ld32(s_addr + c, v);
+            if (HD > 64) {
+                // second read (the registers of the first were given up to keep the output in registers)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32_async(s_addr + c * 32, raw[c]);
+                tmem_wait_ld();
+                if (!all_visible) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int key = key0 + c * 32 + i;
+                            if (!(key >= lo && key <= hi)) raw[c][i] = 0xff800000u;
+                        }
+                }
+            }
+            unsigned char* pj_row = p_row + sb * C::P_BYTES;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
                 unsigned pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const int key = key0 + c + i;
-                    const float p0 = (key >= lo && key <= hi) ? exp2f(v[i] * scale2 - m_use) : 0.f;
-                    const float p1 = (key + 1 >= lo && key + 1 <= hi) ? exp2f(v[i + 1] * scale2 - m_use) : 0.f;
+                    const float p0 = ex2(fmaf(__uint_as_float(raw[c][i]), scale2, -m_use));       // ex2(-inf) = 0
+                    const float p1 = ex2(fmaf(__uint_as_float(raw[c][i + 1]), scale2, -m_use));
+                    sum += p0 + p1;
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    // the sum is taken over the rounded values that the tensor core will multiply
-                    sum += __low2float(h) + __high2float(h);
                     pk[i >> 1] = *reinterpret_cast<unsigned*>(&h);
                 }
-                unsigned char* sub = p_row + (c >> 6) * C::SUBTILE;
+                unsigned char* sub = pj_row + (c >> 1) * C::SUBTILE;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 63) >> 3) + q4;                   // 16-byte chunk within the 128-byte row
+                    const int chunk = ((c & 1) << 2) + q4;                   // 16-byte chunk within the 128-byte row
                     *reinterpret_cast<uint4*>(sub + ((chunk ^ (row & 7)) << 4)) =
                         make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
                 }
             }
-            l_run = l_run * corr + sum;
+            l_run = l_run * corr_of[sb] + sum;
             // P is read by the tensor core through the async proxy
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
-            mbar_arrive(p_full);
-            // O = O * corr + P . V
-            ok = mbar_wait(o_full, j & 1);
+            mbar_arrive(&p_full[sb]);
+            return true;
+        };
+
+        if (LOOKAHEAD) ok = softmax_block(0);
+        for (int j = 0; j < n_blk && ok; ++j) {
+            // the softmax of the next block runs while the tensor core multiplies P_j by V_j; P[(j+1)&1] and
+            // O[(j+1)&1] are free: block j-1, their last user, was accumulated at the end of the last iteration
+            if (LOOKAHEAD) { if (j + 1 < n_blk) { ok = softmax_block(j + 1); if (!ok) break; } }
+            else { ok = softmax_block(j); if (!ok) break; }
+            // O = O * corr_j + P_j . V_j
+            ok = mbar_wait(&o_full[j & 1], (j >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            {
+                const float corr = corr_of[j & 1];
+                unsigned ov[HD / 32][32];
 #pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                float v[32];
-                tmem_ld32(lane_addr + C::COL_O + c, v);
+                for (int c = 0; c < HD / 32; ++c) tmem_ld32_async(lane_addr + C::COL_O + (j & 1) * HD + c * 32, ov[c]);
+                tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr, v[i]);
+                for (int c = 0; c < HD / 32; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(ov[c][i]));
             }
             tc_fence_before();
         }
@@ -421,20 +472,28 @@ int make_map3(CUtensorMap* map, const void* ptr, long long d0, long long d1, lon
     return 0;
 }
 
+int g_lookahead = 0;
+
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
            const int* ctx_lens, const int* block_table, int bt_stride, int page_size, int num_pages, int n_req,
            int max_q_len, int heads, int kv_heads, float scale, int window, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
         configured = true;
     }
     const int tpt = ROWS / (heads / kv_heads);
     dim3 grid(ceil_div(max_q_len, tpt), n_req, kv_heads);
-    NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
-                        (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
-                        kv_heads, scale, window));
+    if (g_lookahead)
+        NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD, true>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
+                            (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
+                            kv_heads, scale, window));
+    else
+        NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD, false>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
+                            (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
+                            kv_heads, scale, window));
     return 0;
 }
 
@@ -449,6 +508,9 @@ NIB_API int nib_attention_prefill_tc_supported(int heads, int kv_heads, int head
     if (q_stride % 8) return 0;
     return get_encode() != nullptr;
 }
+
+// 1: the softmax of block j+1 is computed before block j's P.V is collected; 0 (default, measured faster): in order.
+NIB_API void nib_attention_tc_lookahead(int on) { g_lookahead = on; }
 
 // The error word of the kernel's bounded waits (0 = none); synchronises with the device and clears it.
 NIB_API int nib_attention_tc_error() {
