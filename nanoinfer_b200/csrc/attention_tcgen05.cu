@@ -4,16 +4,17 @@
 // A CTA owns a tile of up to 128 rows, where a row is one (token, query head of the kv group): the keys
 // and values of a kv head are read once for all the query heads that share it. For every block of 128
 // keys:   S = Q . K^T      (tcgen05.mma, accumulator S in TMEM)
-//         P = exp2(S*scale - max), row sums       (128 threads, one row each: no shuffles)
+//         P = exp2(S*scale - max), row sums       (two threads per row: no shuffles, one exchange of maxima)
 //         O_blk = P . V    (tcgen05.mma, P from shared memory, V as the MN-major operand)
 //         O = O * corr + O_blk                     (registers, 32-bit)
-// S, P and O_blk are double buffered: the softmax of block j+1 runs while the tensor core multiplies
-// P_j by V_j, and the scores of block j+2 are computed meanwhile.
+// S and O_blk are double buffered in TMEM: the scores of block j+1 are computed while the softmax of
+// block j runs.
 // Q, K and V tiles arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle): Q through a 3-D map over
 // (head dim, heads of the group, tokens), K and V through a 3-D map over the page pool, one box per
 // page of the block table; a page the request does not hold is fetched from an out-of-range coordinate
 // and arrives as zeros. Roles: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..5 =
-// softmax and output. Every wait is bounded; a wait that runs out records an error word, the CTA stops,
+// softmax and output (eight warps: the 128 keys of a block and the head dim are split between two threads
+// per row, so that every scheduler has two warps to alternate between). Every wait is bounded; a wait that runs out records an error word, the CTA stops,
 // drains its copies, frees its TMEM and returns.
 //
 // Formula as in attention_generic.cu (cpp/src/ops.cpp:206-270); the reference's prefill attention is a
@@ -27,7 +28,7 @@ namespace {
 
 constexpr int ROWS = 128;        // rows of a tile (UMMA M): TMEM lanes
 constexpr int KEYS = 128;        // keys per block (UMMA N of S, K of P.V)
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;     // TMA warp, MMA warp, eight softmax warps (two threads per row)
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -129,15 +130,16 @@ template <int HD> struct Cfg {
     static constexpr int KV_BYTES = SUB * SUBTILE;            // one block of 128 keys (or values)
     static constexpr int P_BYTES = 2 * SUBTILE;               // [128 rows x 128 keys]
     static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_P = OFF_V + 2 * KV_BYTES;
-    static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
-    static constexpr int SMEM = OFF_BAR + 128 + 1024;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;
+    static constexpr int OFF_XCH = OFF_BAR + 256;                // [2][2][128] floats: partial row maxima (and sums)
+    static constexpr int SMEM = OFF_XCH + 2 * 2 * 128 * 4 + 1024;
     static constexpr int TMEM_COLS = 512;                     // S x2 (256 columns) + O block x2 (2 x HD)
     static constexpr int COL_S = 0, COL_O = 256;
     static constexpr int CTAS_PER_SM = 1;
 };
 
 // grid: (row tiles, requests, kv heads)
-template <int HD, bool LOOKAHEAD>
+template <int HD>
 __global__ void __launch_bounds__(THREADS, Cfg<HD>::CTAS_PER_SM)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -156,7 +158,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned long long* s_full = bars + 9;        // 2
     unsigned long long* p_full = bars + 11;       // 2, 128 arrivals each
     unsigned long long* o_full = bars + 13;       // 2
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
+    unsigned long long* xch_bar = bars + 15;      // 2, 256 arrivals each: the two halves of a row have exchanged their maxima
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 17);
+    float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
     __shared__ volatile int s_failed;
 
     pdl_launch_dependents();
@@ -187,7 +191,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
+            mbar_init(&p_full[i], 256);
+            mbar_init(&xch_bar[i], 256);
             mbar_init(&o_full[i], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -203,42 +208,55 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned tmem_base = *tmem_slot;
     pdl_wait();
 
-    if (warp == 0 && lane == 0) {
-        // ---------------- producer
-        mbar_expect_tx(q_full, (unsigned)(rows_tile * 128 * C::SUB));
+    if (warp == 0) {
+        // ---------------- producer: lane 0 fetches Q and arms the barriers; lane i fetches page i of every
+        // block of 128 keys (its block-table entry is read one block ahead, so that the look-up of a page
+        // never stands between two copies)
+        if (lane == 0) {
+            mbar_expect_tx(q_full, (unsigned)(rows_tile * 128 * C::SUB));
 #pragma unroll
-        for (int s = 0; s < C::SUB; ++s)
-            tma_load_3d(smem + C::OFF_Q + s * C::SUBTILE, &map_q, q_full, s * 64, kvh * n_rep, row_begin + tok0);
+            for (int s = 0; s < C::SUB; ++s)
+                tma_load_3d(smem + C::OFF_Q + s * C::SUBTILE, &map_q, q_full, s * 64, kvh * n_rep, row_begin + tok0);
+        }
         const int pages_per_block = KEYS / page_size;
         const int oob = num_pages * kv_heads;             // a coordinate outside the pool: the box arrives as zeros
+        auto plane_of = [&](int j) -> int {               // third coordinate of this lane's page in block j
+            const int key = (b_begin + j) * KEYS + lane * page_size;
+            if (lane >= pages_per_block || key > hi_cta || key + page_size <= lo_cta) return oob;
+            const int page = __ldg(bt + key / page_size);
+            return (page >= 0 && page < num_pages) ? page * kv_heads + kvh : oob;
+        };
+        int z_next = plane_of(0);
         int issued = 0;
-        for (int j = 0; j < n_blk && !s_failed; ++j) {
+        for (int j = 0; j < n_blk; ++j) {
             const int st = j & 1;
-            const unsigned par = ((j >> 1) & 1) ^ 1;
-            if (!mbar_wait(&k_empty[st], par) || !mbar_wait(&v_empty[st], par)) {
-                atomicCAS(&g_attn_error, 0, (1 << 16) | (int)blockIdx.x);
-                s_failed = 1;
-                break;
-            }
-            mbar_expect_tx(&k_full[st], C::KV_BYTES);
-            mbar_expect_tx(&v_full[st], C::KV_BYTES);
-            const int key0 = (b_begin + j) * KEYS;
-            for (int i = 0; i < pages_per_block; ++i) {
-                const int key = key0 + i * page_size;
-                int z = oob;
-                if (key <= hi_cta && key + page_size > lo_cta) {
-                    const int page = bt[key / page_size];
-                    if (page >= 0 && page < num_pages) z = page * kv_heads + kvh;
+            const int z = z_next;
+            if (j + 1 < n_blk) z_next = plane_of(j + 1);
+            int ok = 1;
+            if (lane == 0) {
+                const unsigned par = ((j >> 1) & 1) ^ 1;
+                ok = !s_failed && mbar_wait(&k_empty[st], par) && mbar_wait(&v_empty[st], par);
+                if (ok) {
+                    mbar_expect_tx(&k_full[st], C::KV_BYTES);
+                    mbar_expect_tx(&v_full[st], C::KV_BYTES);
+                } else if (!s_failed) {
+                    atomicCAS(&g_attn_error, 0, (1 << 16) | (int)blockIdx.x);
+                    s_failed = 1;
                 }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < pages_per_block) {
 #pragma unroll
                 for (int s = 0; s < C::SUB; ++s) {
-                    tma_load_3d(smem + C::OFF_K + st * C::KV_BYTES + s * C::SUBTILE + i * page_size * 128, &map_k, &k_full[st], s * 64, 0, z);
-                    tma_load_3d(smem + C::OFF_V + st * C::KV_BYTES + s * C::SUBTILE + i * page_size * 128, &map_v, &v_full[st], s * 64, 0, z);
+                    tma_load_3d(smem + C::OFF_K + st * C::KV_BYTES + s * C::SUBTILE + lane * page_size * 128, &map_k, &k_full[st], s * 64, 0, z);
+                    tma_load_3d(smem + C::OFF_V + st * C::KV_BYTES + s * C::SUBTILE + lane * page_size * 128, &map_v, &v_full[st], s * 64, 0, z);
                 }
             }
             issued = j + 1;
         }
-        if (s_failed) {
+        if (s_failed && lane == 0) {
+            // copies already issued still target this CTA's shared memory: wait for them, bounded
             mbar_wait(q_full, 0);
             for (int j = max(0, issued - 2); j < issued; ++j) {
                 mbar_wait(&k_full[j & 1], (j >> 1) & 1);
@@ -257,7 +275,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!mbar_wait(&p_full[st], (j >> 1) & 1) || !mbar_wait(&v_full[st], (j >> 1) & 1)) return false;
             tc_fence_after();
             const unsigned v_addr = smem_u32(smem + C::OFF_V + st * C::KV_BYTES);
-            const unsigned pj_addr = p_addr + st * C::P_BYTES;
+            const unsigned pj_addr = p_addr;      // one P tile: the softmax of block j+1 starts after P_j . V_j was collected
 #pragma unroll
             for (int kk = 0; kk < KEYS / 16; ++kk) {
                 // P: sub-tile kk/4 (64 keys each), 32 bytes per step inside it; V: 16 keys = 2048 bytes further down
@@ -292,48 +310,45 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         if (!ok && !s_failed) { atomicCAS(&g_attn_error, 0, (3 << 16) | (int)blockIdx.x); s_failed = 1; }
     } else if (warp >= 2) {
-        // ---------------- softmax and output: one row per thread
-        const int quad = warp & 3, row = quad * 32 + lane;
+        // ---------------- softmax and output: two threads per row. `half` 0 takes keys 0..63 of every block
+        // and output columns 0..HD/2-1, `half` 1 the rest; a warp may read the TMEM lanes 32*(warp%4)...
+        constexpr int HK = KEYS / 2, HO = HD / 2;
+        const int half = (warp - 2) >> 2, quad = warp & 3, row = quad * 32 + lane;
         const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
         const bool live = row < n_tok * n_rep;
         const int ti = row / n_rep, head = kvh * n_rep + (row - ti * n_rep);
         const int hi = live ? pos0 + ti : -1;
         const int lo = window > 0 ? max(0, hi - window + 1) : 0;
         const float scale2 = scale * LOG2E;
-        float m_run = -INFINITY, l_run = 0.f;
-        float o[HD];
+        float m_run = -INFINITY, l_run = 0.f;       // l_run: the sum over this thread's half of the keys
+        float o[HO];
 #pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
-        unsigned char* p_row = smem + C::OFF_P + (row >> 3) * 1024 + (row & 7) * 128;
+        for (int d = 0; d < HO; ++d) o[d] = 0.f;
+        // this thread's half of the row in P: sub-tile `half` (64 keys), row `row`
+        unsigned char* p_row = smem + C::OFF_P + half * C::SUBTILE + (row >> 3) * 1024 + (row & 7) * 128;
         bool ok = true;
-        float corr_of[2] = {0.f, 0.f};          // the factor that block j applies to the running output, by j & 1
-
-        // Scores of block j -> probabilities in P[j & 1], running max and sum; signals p_full[j & 1].
-        auto softmax_block = [&](int j) -> bool {
+        for (int j = 0; j < n_blk && ok; ++j) {
             const int sb = j & 1;
-            bool good = !s_failed && mbar_wait(&s_full[sb], (j >> 1) & 1);
-            good = __all_sync(0xffffffffu, good);
-            if (!good) return false;
+            ok = !s_failed && mbar_wait(&s_full[sb], (j >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             tc_fence_after();
-            const int key0 = (b_begin + j) * KEYS;
-            const unsigned s_addr = lane_addr + C::COL_S + sb * KEYS;
-            const bool all_visible = key0 >= lo && key0 + KEYS - 1 <= hi;     // no mask needed for this row and block
-            float sum = 0.f;
-            // Scores of the row: four TMEM loads in flight, one wait. Head size 64 keeps all 128 in registers;
-            // head size 128 (128 output registers already) reads them twice instead.
-            unsigned raw[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32_async(s_addr + c * 32, raw[c]);
+            const int key0 = (b_begin + j) * KEYS + half * HK;
+            const unsigned s_addr = lane_addr + C::COL_S + sb * KEYS + half * HK;
+            const bool all_visible = key0 >= lo && key0 + HK - 1 <= hi;       // no mask needed for this thread's keys
+            unsigned raw[2][32];
+            tmem_ld32_async(s_addr, raw[0]);
+            tmem_ld32_async(s_addr + 32, raw[1]);
             tmem_wait_ld();
             float mx = -INFINITY;
             if (all_visible) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[c][i]));
             } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = key0 + c * 32 + i;
@@ -341,29 +356,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         mx = fmaxf(mx, __uint_as_float(raw[c][i]));
                     }
             }
-            mx *= scale2;                                                     // scale2 > 0: the max of the scaled scores
+            // the row's maximum needs the other half: exchange through shared memory
+            xch[(sb * 2 + half) * 128 + row] = mx;
+            mbar_arrive(&xch_bar[sb]);
+            ok = mbar_wait(&xch_bar[sb], (j >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            mx = fmaxf(mx, xch[(sb * 2 + (half ^ 1)) * 128 + row]) * scale2;   // scale2 > 0
             const float m_new = fmaxf(m_run, mx);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            corr_of[sb] = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
+            const float corr = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
             m_run = m_new;
-            if (HD > 64) {
-                // second read (the registers of the first were given up to keep the output in registers)
+            float sum = 0.f;
+            unsigned char* pj_row = p_row;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32_async(s_addr + c * 32, raw[c]);
-                tmem_wait_ld();
-                if (!all_visible) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int key = key0 + c * 32 + i;
-                            if (!(key >= lo && key <= hi)) raw[c][i] = 0xff800000u;
-                        }
-                }
-            }
-            unsigned char* pj_row = p_row + sb * C::P_BYTES;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 unsigned pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -373,53 +380,51 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     pk[i >> 1] = *reinterpret_cast<unsigned*>(&h);
                 }
-                unsigned char* sub = pj_row + (c >> 1) * C::SUBTILE;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 1) << 2) + q4;                   // 16-byte chunk within the 128-byte row
-                    *reinterpret_cast<uint4*>(sub + ((chunk ^ (row & 7)) << 4)) =
+                    const int chunk = (c << 2) + q4;                         // 16-byte chunk within the 128-byte row
+                    *reinterpret_cast<uint4*>(pj_row + ((chunk ^ (row & 7)) << 4)) =
                         make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
                 }
             }
-            l_run = l_run * corr_of[sb] + sum;
+            l_run = l_run * corr + sum;
             // P is read by the tensor core through the async proxy
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
             mbar_arrive(&p_full[sb]);
-            return true;
-        };
-
-        if (LOOKAHEAD) ok = softmax_block(0);
-        for (int j = 0; j < n_blk && ok; ++j) {
-            // the softmax of the next block runs while the tensor core multiplies P_j by V_j; P[(j+1)&1] and
-            // O[(j+1)&1] are free: block j-1, their last user, was accumulated at the end of the last iteration
-            if (LOOKAHEAD) { if (j + 1 < n_blk) { ok = softmax_block(j + 1); if (!ok) break; } }
-            else { ok = softmax_block(j); if (!ok) break; }
-            // O = O * corr_j + P_j . V_j
-            ok = mbar_wait(&o_full[j & 1], (j >> 1) & 1);
+            // O = O * corr + P . V, this thread's half of the columns
+            ok = mbar_wait(&o_full[sb], (j >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             {
-                const float corr = corr_of[j & 1];
-                unsigned ov[HD / 32][32];
+                unsigned ov[HO / 32][32];
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) tmem_ld32_async(lane_addr + C::COL_O + (j & 1) * HD + c * 32, ov[c]);
+                for (int c = 0; c < HO / 32; ++c) tmem_ld32_async(lane_addr + C::COL_O + sb * HD + half * HO + c * 32, ov[c]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c)
+                for (int c = 0; c < HO / 32; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(ov[c][i]));
             }
             tc_fence_before();
         }
+        // the row's sum: both halves. The exchange buffers alternate with the blocks; use the next one.
+        if (ok) {
+            const int sb = n_blk & 1;
+            xch[(sb * 2 + half) * 128 + row] = l_run;
+            mbar_arrive(&xch_bar[sb]);
+            ok = mbar_wait(&xch_bar[sb], (n_blk >> 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) l_run += xch[(sb * 2 + (half ^ 1)) * 128 + row];
+        }
         if (!ok) {
             if (lane == 0 && !s_failed) { atomicCAS(&g_attn_error, 0, (4 << 16) | (int)blockIdx.x); s_failed = 1; }
         } else if (live) {
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            __nv_bfloat16* orow = out + ((size_t)(row_begin + tok0 + ti) * heads + head) * HD;
+            __nv_bfloat16* orow = out + ((size_t)(row_begin + tok0 + ti) * heads + head) * HD + half * HO;
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
+            for (int d = 0; d < HO; d += 8) {
                 uint4 w;
                 __nv_bfloat162 h0 = __floats2bfloat162_rn(o[d] * inv, o[d + 1] * inv), h1 = __floats2bfloat162_rn(o[d + 2] * inv, o[d + 3] * inv);
                 __nv_bfloat162 h2 = __floats2bfloat162_rn(o[d + 4] * inv, o[d + 5] * inv), h3 = __floats2bfloat162_rn(o[d + 6] * inv, o[d + 7] * inv);
@@ -472,28 +477,20 @@ int make_map3(CUtensorMap* map, const void* ptr, long long d0, long long d1, lon
     return 0;
 }
 
-int g_lookahead = 0;
-
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* q_start,
            const int* ctx_lens, const int* block_table, int bt_stride, int page_size, int num_pages, int n_req,
            int max_q_len, int heads, int kv_heads, float scale, int window, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
-        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
         configured = true;
     }
     const int tpt = ROWS / (heads / kv_heads);
     dim3 grid(ceil_div(max_q_len, tpt), n_req, kv_heads);
-    if (g_lookahead)
-        NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD, true>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
-                            (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
-                            kv_heads, scale, window));
-    else
-        NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD, false>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
-                            (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
-                            kv_heads, scale, window));
+    NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
+                        (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
+                        kv_heads, scale, window));
     return 0;
 }
 
@@ -508,9 +505,6 @@ NIB_API int nib_attention_prefill_tc_supported(int heads, int kv_heads, int head
     if (q_stride % 8) return 0;
     return get_encode() != nullptr;
 }
-
-// 1: the softmax of block j+1 is computed before block j's P.V is collected; 0 (default, measured faster): in order.
-NIB_API void nib_attention_tc_lookahead(int on) { g_lookahead = on; }
 
 // The error word of the kernel's bounded waits (0 = none); synchronises with the device and clears it.
 NIB_API int nib_attention_tc_error() {
