@@ -51,9 +51,10 @@ __device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parit
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+    // hand-overs between the roles are short: spin first, back off only when a wait drags on
     for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
         if (mbar_try(bar, parity)) return true;
-        if (i > 128) __nanosleep(100);
+        if (i > 4096) __nanosleep(100);
     }
     return false;
 }
@@ -327,16 +328,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // this thread's half of the row in P: sub-tile `half` (64 keys), row `row`
         unsigned char* p_row = smem + C::OFF_P + half * C::SUBTILE + (row >> 3) * 1024 + (row & 7) * 128;
         bool ok = true;
-        for (int j = 0; j < n_blk && ok; ++j) {
+        unsigned raw[2][32];                      // this thread's 64 scores of the block in work
+        float m_use = 0.f, corr = 0.f;            // of the block in work
+
+        // First half of a block's softmax: scores from TMEM, mask, the row's maximum (exchanged with the
+        // thread that holds the other 64 keys), running max and the factor for the running output.
+        auto scores_and_max = [&](int j) -> bool {
             const int sb = j & 1;
-            ok = !s_failed && mbar_wait(&s_full[sb], (j >> 1) & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            bool good = !s_failed && mbar_wait(&s_full[sb], (j >> 1) & 1);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
             tc_fence_after();
             const int key0 = (b_begin + j) * KEYS + half * HK;
             const unsigned s_addr = lane_addr + C::COL_S + sb * KEYS + half * HK;
             const bool all_visible = key0 >= lo && key0 + HK - 1 <= hi;       // no mask needed for this thread's keys
-            unsigned raw[2][32];
             tmem_ld32_async(s_addr, raw[0]);
             tmem_ld32_async(s_addr + 32, raw[1]);
             tmem_wait_ld();
@@ -356,19 +361,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         mx = fmaxf(mx, __uint_as_float(raw[c][i]));
                     }
             }
-            // the row's maximum needs the other half: exchange through shared memory
             xch[(sb * 2 + half) * 128 + row] = mx;
             mbar_arrive(&xch_bar[sb]);
-            ok = mbar_wait(&xch_bar[sb], (j >> 1) & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            good = mbar_wait(&xch_bar[sb], (j >> 1) & 1);
+            good = __all_sync(0xffffffffu, good);
+            if (!good) return false;
             mx = fmaxf(mx, xch[(sb * 2 + (half ^ 1)) * 128 + row]) * scale2;   // scale2 > 0
             const float m_new = fmaxf(m_run, mx);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
+            m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            corr = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
             m_run = m_new;
+            return true;
+        };
+
+        ok = scores_and_max(0);
+        for (int j = 0; j < n_blk && ok; ++j) {
+            const int sb = j & 1;
+            // second half: probabilities of block j into P, their sum
             float sum = 0.f;
-            unsigned char* pj_row = p_row;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 unsigned pk[16];
@@ -383,16 +393,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const int chunk = (c << 2) + q4;                         // 16-byte chunk within the 128-byte row
-                    *reinterpret_cast<uint4*>(pj_row + ((chunk ^ (row & 7)) << 4)) =
+                    *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) =
                         make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
                 }
             }
             l_run = l_run * corr + sum;
+            const float corr_j = corr;
             // P is read by the tensor core through the async proxy
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
             mbar_arrive(&p_full[sb]);
-            // O = O * corr + P . V, this thread's half of the columns
+            // while the tensor core multiplies P_j by V_j: the scores and the maximum of block j+1
+            if (j + 1 < n_blk) { ok = scores_and_max(j + 1); if (!ok) break; }
+            // O = O * corr_j + P_j . V_j, this thread's half of the columns
             ok = mbar_wait(&o_full[sb], (j >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -405,7 +418,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int c = 0; c < HO / 32; ++c)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr, __uint_as_float(ov[c][i]));
+                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], corr_j, __uint_as_float(ov[c][i]));
             }
             tc_fence_before();
         }
