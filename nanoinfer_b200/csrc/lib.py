@@ -50,6 +50,7 @@ class Kernels:
         self.smallm_ksplit = 0                 # tests: the K split of the small-M GEMM (0 = chosen, 1 or 4)
         self.sm_count = 148
         self.smallm_cross = 0                  # tests: CTAs that split K in the small-M GEMM (0 = chosen)
+        self.smallm_max_tokens = 16            # more tokens than this go to the tcgen05 GEMM (measured crossover)
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
         try:
@@ -122,7 +123,7 @@ class Kernels:
         kernel; shapes neither takes, and 32-bit, run the CUDA-core kernel."""
         deferred = a if hasattr(a, "materialize") else None
         bf16 = a.dtype == torch.bfloat16 and not self.force_simt_gemm
-        if bf16 and self.tc_token_tile == 0:
+        if bf16 and self.tc_token_tile == 0 and (m <= self.smallm_max_tokens or self.smallm_ksplit or self.smallm_cross):
             src = deferred.x32 if deferred is not None else a
             if self._lib.nib_gemm_smallm_supported(_ptr(src), _ptr(w), c_int(m), c_int(k), c_int(src.stride(0)),
                                                    c_int(4 if deferred is not None else 2)) == 1:
@@ -260,12 +261,12 @@ class Kernels:
     def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int) -> int:
         """Into how many CTAs the keys of a decoding token are split: two key tiles per CTA (both are in
         flight at once, so a CTA waits for memory once), as long as that does not make more CTAs than
-        fill the GPU about four times."""
+        fill the GPU about eight times."""
         if self.fixed_decode_splits:
             return self.fixed_decode_splits
         keys = min(max_ctx, window) if window > 0 else max_ctx
         tiles = -(-keys // 64) + 1
-        most = max(1, (4 * self.sm_count) // max(1, n_tokens * kv_heads))
+        most = max(1, (8 * self.sm_count) // max(1, n_tokens * kv_heads))
         return max(1, min(-(-tiles // 2), most, 64))
 
     def argmax(self, logits, out):

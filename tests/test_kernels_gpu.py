@@ -293,7 +293,7 @@ def test_small_m_gemm(K, m, n, k, ksplit, cross):
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 90), rnd((n, k), dtype, 91, scale=0.05)
     bias = rnd((n,), torch.float32, 92)
-    K.smallm_ksplit, K.smallm_cross = ksplit, cross
+    K.smallm_ksplit, K.smallm_cross, K.smallm_max_tokens = ksplit, cross, 64
     try:
         out = torch.empty(m, n, dtype=dtype, device="cuda")
         K.linear(a, w, bias, out, "store")
@@ -318,6 +318,7 @@ def test_small_m_gemm(K, m, n, k, ksplit, cross):
         assert torch.equal(one[0], out32[m - 1])
     finally:
         K.smallm_ksplit = K.smallm_cross = 0
+        K.smallm_max_tokens = 16
 
 
 @pytest.mark.parametrize("m,n,k,eps", [(1, 1152, 896, 1e-6), (8, 320, 192, 1e-5), (20, 200, 64, 1e-3), (64, 503, 320, 1e-6)])
@@ -336,6 +337,7 @@ def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     gain = 1 + 0.1 * rnd((k,), torch.float32, 96)
     w = rnd((n, k), torch.bfloat16, 97, scale=0.05)
     fused, two_step = torch.empty(m, n, device="cuda"), torch.empty(m, n, device="cuda")
+    K.smallm_max_tokens = 64
     K.linear(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w, None, fused, "f32")
     h = _Norm().forward(x32)
     K.linear(h, w, None, two_step, "f32")
@@ -347,6 +349,7 @@ def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     inter = n // 2
     sw, sw_ref = (torch.empty(m, inter, dtype=torch.bfloat16, device="cuda") for _ in range(2))
     K.linear_swiglu(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w[:2 * inter].contiguous(), sw)
+    K.smallm_max_tokens = 16
     REF.linear_swiglu(h, w[:2 * inter].contiguous(), sw_ref)
     assert_close(sw, sw_ref, torch.bfloat16, "fused norm swiglu")
 
