@@ -232,9 +232,12 @@ def run_ours(args) -> dict:
 
     # ---- end to end through the Python entry point (scheduler) -----------------------------
     sched = Scheduler(model, max_batch=batch, max_tokens_per_step=4096)
-    prompt_len = ctx - warmup - steps - 4     # the last timed step stays inside the context (and its graph bucket)
+    # Requests admitted first decode while the later prompts are still being prefilled (about one step per
+    # prompt), so they are ahead by up to `batch` tokens when timing starts; nobody may finish, and nobody may
+    # leave the context (and with it the captured graph's bucket), before the timed steps end.
+    prompt_len = ctx - warmup - steps - 2 * batch - 8
     for i in range(batch):
-        sched.add(Request(f"e{i}", rng.integers(0, vocab, prompt_len).tolist(), max_tokens=warmup + steps + 2))
+        sched.add(Request(f"e{i}", rng.integers(0, vocab, prompt_len).tolist(), max_tokens=ctx))
     while any(s.pending > 1 for s in sched.running) or sched.waiting:
         sched.step()
     for _ in range(warmup):

@@ -302,8 +302,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
                         const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
                         int page_size, const __nv_bfloat16* __restrict__ k_pages,
                         const __nv_bfloat16* __restrict__ v_pages, int num_pages, int heads, int kv_heads,
-                        float scale, int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        float scale, int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int* __restrict__ counters) {
     extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int s_last;
     pdl_launch_dependents();
     const int split = blockIdx.x, token = blockIdx.y, kvh = blockIdx.z;
     const int n_rep = heads / kv_heads;
@@ -418,6 +420,54 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
             if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
         }
     }
+    if (splits == 1 || counters == nullptr) return;     // without counters a second kernel merges the splits
+
+    // The CTA that arrives last at this (token, kv head)'s counter merges the splits, in split order.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(&counters[token * kv_heads + kvh], 1) == splits - 1) ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float* c_m = reinterpret_cast<float*>(smem);                 // [n_rep][splits] maxima, then factors
+    float* c_l = c_m + 16 * 64;                                  // [n_rep] sums
+    const size_t th0 = (size_t)token * heads + (size_t)kvh * n_rep;
+    for (int i = tid; i < n_rep * splits; i += WARPS * 32) {
+        const int row = i / splits, sp = i - row * splits;
+        c_m[row * 64 + sp] = __ldcg(part_ml + ((th0 + row) * splits + sp) * 2);
+    }
+    __syncthreads();
+    if (tid < n_rep) {
+        float m = -INFINITY;
+        for (int sp = 0; sp < splits; ++sp) m = fmaxf(m, c_m[tid * 64 + sp]);
+        float l = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+            const float ms = c_m[tid * 64 + sp];
+            const float f = (m == -INFINITY || ms == -INFINITY) ? 0.f : exp2f(ms - m);
+            l += __ldcg(part_ml + ((th0 + tid) * splits + sp) * 2 + 1) * f;
+            c_m[tid * 64 + sp] = f;
+        }
+        c_l[tid] = l;
+    }
+    __syncthreads();
+    for (int i = tid; i < n_rep * HD; i += WARPS * 32) {
+        const int row = i / HD, d = i - row * HD;
+        const float* po = part_o + (th0 + row) * splits * HD + d;
+        const float* f = c_m + row * 64;
+        float acc = 0.f;
+        int sp = 0;
+        for (; sp + 8 <= splits; sp += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(po + (size_t)(sp + u) * HD);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += v[u] * f[sp + u];
+        }
+        for (; sp < splits; ++sp) acc += __ldcg(po + (size_t)sp * HD) * f[sp];
+        const float l = c_l[row];
+        out[(th0 + row) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+    if (tid == 0) counters[token * kv_heads + kvh] = 0;         // ready for the next launch
 }
 
 // Merges the partial results of the splits, in split order. grid: tokens * heads; block: 128 threads.
@@ -464,8 +514,9 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
 
 template <int HD> int prefill_smem() { return 4 * Tile<HD>::BYTES; }
 template <int HD> int decode_smem() {
-    const int tiles = 4 * Tile<HD>::BYTES, merge = WARPS * 16 * (HD + 2) * 4;
-    return tiles > merge ? tiles : merge;
+    const int tiles = 4 * Tile<HD>::BYTES, merge = WARPS * 16 * (HD + 2) * 4, combine = (16 * 64 + 16) * 4;
+    const int a = tiles > merge ? tiles : merge;
+    return a > combine ? a : combine;
 }
 
 template <int HD>
@@ -492,7 +543,7 @@ template <int HD>
 int launch_decode(const void* qkv, int q_stride, void* out, const int* ctx_lens, const int* block_table,
                   int bt_stride, int page_size, const void* k_pages, const void* v_pages, int num_pages,
                   int n_tokens, int heads, int kv_heads, float scale, int window, int splits, float* part_o,
-                  float* part_ml, cudaStream_t stream) {
+                  float* part_ml, int* counters, cudaStream_t stream) {
     static bool configured = false;
     const int smem = decode_smem<HD>();
     if (!configured) {
@@ -503,8 +554,8 @@ int launch_decode(const void* qkv, int q_stride, void* out, const int* ctx_lens,
     NIB_CUDA(launch_pdl(attention_decode_kernel<HD>, grid, dim3(WARPS * 32), (size_t)smem, stream,
                         (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
                         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
-                        window, splits, part_o, part_ml));
-    if (splits > 1)
+                        window, splits, part_o, part_ml, counters));
+    if (splits > 1 && counters == nullptr)
         NIB_CUDA(launch_pdl(attention_combine_kernel, dim3(n_tokens * heads), dim3(128), (size_t)0, stream,
                             (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, HD));
     return 0;
@@ -548,19 +599,21 @@ NIB_API int nib_attention_prefill_mma(const void* qkv, int q_stride, void* out, 
 }
 
 // One token per request (q_len 1). part_o: [n_tokens, heads, splits, head_dim] float and part_ml:
-// [n_tokens, heads, splits, 2] float are scratch, needed only when splits > 1.
+// [n_tokens, heads, splits, 2] float are scratch, needed only when splits > 1. counters: n_tokens *
+// kv_heads ints that are zero between launches (the kernel leaves them zero); with them the CTA that
+// finishes last merges the splits, without them (nullptr) a second kernel does.
 NIB_API int nib_attention_decode_mma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
                                      const int* block_table, int bt_stride, int page_size, const void* k_pages,
                                      const void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
                                      int head_dim, float scale, int window, int splits, float* part_o, float* part_ml,
-                                     cudaStream_t stream) {
+                                     int* counters, cudaStream_t stream) {
     NIB_REQUIRE(nib_attention_mma_supported(heads, kv_heads, head_dim), "attention (tensor cores): head_dim %d with %d/%d heads is not supported", head_dim, heads, kv_heads);
     NIB_REQUIRE(heads / kv_heads <= 16, "attention decode: at most 16 query heads per kv head, got %d", heads / kv_heads);
     NIB_REQUIRE(n_tokens >= 0 && page_size > 0 && num_pages > 0 && window >= 0 && splits >= 1 && splits <= 64, "attention decode: bad sizes (1..64 splits)");
     NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode: splits > 1 need scratch memory");
     NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode: too many tokens or kv heads for one launch");
     if (n_tokens == 0) return 0;
-#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, stream)
+#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, counters, stream)
     NIB_HD_SWITCH(head_dim, CALL)
 #undef CALL
     NIB_REQUIRE(false, "attention decode: unreachable head_dim %d", head_dim);
@@ -602,5 +655,5 @@ NIB_API int nib_attention_decode_noalloc(const void* qkv, int q_stride, void* ou
     float* part_ml = part_o + (size_t)n_tokens * heads * splits * head_dim;
     return nib_attention_decode_mma(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages,
                                     num_pages, n_tokens, heads, kv_heads, head_dim, scale, window, splits, part_o,
-                                    part_ml, stream);
+                                    part_ml, nullptr, stream);
 }

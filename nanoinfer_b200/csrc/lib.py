@@ -53,6 +53,8 @@ class Kernels:
         self.smallm_max_tokens = 16            # more tokens than this go to the tcgen05 GEMM (measured crossover)
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
+        self._ws_attn_counters = None
+        self.separate_combine = True           # merge the decode splits in a second kernel (measured faster than letting the last CTA do it)
         try:
             self._lib = ctypes.CDLL(lib_path)
         except OSError as e:
@@ -98,6 +100,7 @@ class Kernels:
         if self._ws_scratch is None:
             self._ws_scratch = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=device)
             self._ws_counters = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
+            self._ws_attn_counters = torch.zeros(64 * 1024, dtype=torch.int32, device=device)
 
     def linear(self, a, w, bias32, out, mode):
         """out[M,N] (=, +=) a[M,K] . w[N,K]^T (+ bias). mode: 'store' | 'add' (float out) | 'f32' (float out).
@@ -225,7 +228,10 @@ class Kernels:
                 n_dec += 1
         if n_dec:
             splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window)
-            part_o = part_ml = None
+            part_o = part_ml = counters = None
+            if splits > 1 and not self.separate_combine and n_dec * kv_heads <= 64 * 1024:
+                self.ensure_workspace(qkv.device)
+                counters = self._ws_attn_counters
             if splits > 1:
                 part_o = torch.empty(n_dec * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
                 part_ml = torch.empty(n_dec * heads * splits * 2, dtype=torch.float32, device=qkv.device)
@@ -233,8 +239,8 @@ class Kernels:
                 _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(bt_stride),
                 c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_dec), c_int(heads),
                 c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits), _ptr(part_o),
-                _ptr(part_ml), self._stream()), "attention decode")
-            if splits > 1:
+                _ptr(part_ml), _ptr(counters), self._stream()), "attention decode")
+            if splits > 1 and counters is None:
                 self.launches += 1
         if n_dec < n_req:
             q_start = c_void_p(ctx.q_start.data_ptr() + 4 * n_dec)

@@ -214,12 +214,17 @@ def test_attention_decode_long_context_split_over_ctas(K, heads, kv_heads, hd, w
     out, ref = (torch.empty(len(before), heads * hd, dtype=dtype, device="cuda") for _ in range(2))
     scale = 1.0 / math.sqrt(hd)
     K.fixed_decode_splits = splits
+    two = torch.empty_like(out)
     try:
         K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+        K.separate_combine = False          # the splits merged by the CTA that finishes last: the same sums in the same order
+        K.attention(qkv, two, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     finally:
         K.fixed_decode_splits = 0
+        K.separate_combine = True
     REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert_close(out, ref, dtype, "decode attention")
+    assert_close(two, ref, dtype, "decode attention, merged by the last CTA")
 
 
 @pytest.mark.parametrize("heads,kv_heads,hd,page,window", [(14, 2, 64, 16, 0), (6, 1, 32, 8, 0), (3, 3, 48, 8, 24), (8, 2, 128, 16, 0)])

@@ -26,7 +26,7 @@ def _call(lib, fn, qkv, out, ctx, bt, page, kp, vp, heads, kv_heads, hd, window,
             c_int(kp.shape[0]), c_int(qkv.shape[0]), c_int(heads), c_int(kv_heads), c_int(hd),
             c_float(1.0 / math.sqrt(hd)), c_int(window), c_int(splits)]
     if scratch is not None:
-        args += [c_void_p(scratch[0].data_ptr()), c_void_p(scratch[1].data_ptr())]
+        args += [c_void_p(scratch[0].data_ptr()), c_void_p(scratch[1].data_ptr()), c_void_p(0)]
     args.append(c_void_p(torch.cuda.current_stream().cuda_stream))
     return fn(*args)
 
