@@ -57,11 +57,14 @@ template <int HD> struct Tile {
     static constexpr int CHUNKS_PER_ROW = HD / 8;            // 16-byte chunks
 };
 
-// Copies keys key0..key0+63 of one kv head into a tile; rows outside [lo, hi] or without a page are zero.
+// Copies keys and values key0..key0+63 of one kv head into a K tile and a V tile; rows outside [lo, hi] or
+// without a page are zero. A row's page is looked up once for both tensors; for the usual power-of-two page
+// sizes the division is a shift (shift >= 0).
 template <int HD, int THREADS>
-__device__ __forceinline__ void load_tile(unsigned char* tile, const __nv_bfloat16* __restrict__ pages,
-                                          const int* __restrict__ bt, int page_size, int num_pages,
-                                          int kv_heads, int kvh, int key0, int lo, int hi, int tid) {
+__device__ __forceinline__ void load_tiles(unsigned char* k_tile, unsigned char* v_tile,
+                                           const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
+                                           const int* __restrict__ bt, int page_size, int shift, int num_pages,
+                                           int kv_heads, int kvh, int key0, int lo, int hi, int tid) {
     constexpr int CPR = Tile<HD>::CHUNKS_PER_ROW;
     constexpr int TOTAL = BLOCK_N * CPR;
 #pragma unroll
@@ -69,13 +72,16 @@ __device__ __forceinline__ void load_tile(unsigned char* tile, const __nv_bfloat
         const int r = i / CPR, c = i - r * CPR;
         const int j = key0 + r;
         bool valid = (j >= lo) && (j <= hi);
-        const __nv_bfloat16* src = pages;
+        size_t off = 0;
         if (valid) {
-            const int page = bt[j / page_size];
+            const int lp = shift >= 0 ? (j >> shift) : (j / page_size);
+            const int slot = shift >= 0 ? (j & (page_size - 1)) : (j - lp * page_size);
+            const int page = bt[lp];
             valid = page >= 0 && page < num_pages;
-            if (valid) src = pages + (((size_t)page * kv_heads + kvh) * page_size + (j % page_size)) * HD + c * 8;
+            if (valid) off = (((size_t)page * kv_heads + kvh) * page_size + slot) * HD + c * 8;
         }
-        cp_async_16(tile + r * Tile<HD>::ROW_BYTES + c * 16, src, valid);
+        cp_async_16(k_tile + r * Tile<HD>::ROW_BYTES + c * 16, k_pages + off, valid);
+        cp_async_16(v_tile + r * Tile<HD>::ROW_BYTES + c * 16, v_pages + off, valid);
     }
 }
 
@@ -218,6 +224,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __
     const int pos0 = ctx - q_len;                     // position of the request's first token in this step
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2;
     const int* bt = block_table + (size_t)req * bt_stride;
+    const int shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
     // this thread's two rows
     int vis_lo[2], vis_hi[2];
@@ -256,15 +263,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __
     unsigned char* k_buf[2] = {smem, smem + 2 * Tile<HD>::BYTES};
     unsigned char* v_buf[2] = {smem + Tile<HD>::BYTES, smem + 3 * Tile<HD>::BYTES};
 
-    load_tile<HD, WARPS * 32>(k_buf[0], k_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo_cta, hi_cta, tid);
-    load_tile<HD, WARPS * 32>(v_buf[0], v_pages, bt, page_size, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo_cta, hi_cta, tid);
+    load_tiles<HD, WARPS * 32>(k_buf[0], v_buf[0], k_pages, v_pages, bt, page_size, shift, num_pages, kv_heads, kvh, t_begin * BLOCK_N, lo_cta, hi_cta, tid);
     cp_async_commit();
 
     for (int tile = t_begin; tile <= t_end; ++tile) {
         const int cur = (tile - t_begin) & 1;
         if (tile < t_end) {
-            load_tile<HD, WARPS * 32>(k_buf[cur ^ 1], k_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo_cta, hi_cta, tid);
-            load_tile<HD, WARPS * 32>(v_buf[cur ^ 1], v_pages, bt, page_size, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo_cta, hi_cta, tid);
+            load_tiles<HD, WARPS * 32>(k_buf[cur ^ 1], v_buf[cur ^ 1], k_pages, v_pages, bt, page_size, shift, num_pages, kv_heads, kvh, (tile + 1) * BLOCK_N, lo_cta, hi_cta, tid);
         }
         cp_async_commit();
         cp_async_wait<1>();
@@ -313,6 +318,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
     const int p = ctx_lens[token] - 1;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int* bt = block_table + (size_t)token * bt_stride;
+    const int shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
     // key tiles of this split: tiles are aligned to absolute multiples of 64
     const int t_first = lo / BLOCK_N, t_last = p / BLOCK_N;
@@ -335,8 +341,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
     unsigned char* k_buf[2] = {smem, smem + 2 * Tile<HD>::BYTES};
     unsigned char* v_buf[2] = {smem + Tile<HD>::BYTES, smem + 3 * Tile<HD>::BYTES};
     auto issue = [&](int tile, int buf) {
-        load_tile<HD, WARPS * 32>(k_buf[buf], k_pages, bt, page_size, num_pages, kv_heads, kvh, tile * BLOCK_N, lo, p, tid);
-        load_tile<HD, WARPS * 32>(v_buf[buf], v_pages, bt, page_size, num_pages, kv_heads, kvh, tile * BLOCK_N, lo, p, tid);
+        load_tiles<HD, WARPS * 32>(k_buf[buf], v_buf[buf], k_pages, v_pages, bt, page_size, shift, num_pages, kv_heads, kvh, tile * BLOCK_N, lo, p, tid);
     };
 
     // Two tiles are kept in flight. Keys and values of positions before p were written by earlier steps,
