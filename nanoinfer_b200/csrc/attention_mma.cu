@@ -203,6 +203,44 @@ __device__ __forceinline__ void load_q(unsigned (&q)[HD / 16][4], const __nv_bfl
     }
 }
 
+// Rotation of one even/odd pair (d, d+1) of a head for the token's position: cos/sin rows hold rot/2 values;
+// d < rot/2 pairs with d + rot/2 (x*c - partner*s), rot/2 <= d < rot with d - rot/2 (x*c + partner*s),
+// d >= rot is left as it is. rot/2 is even, so a pair never straddles the halves. The result is rounded to
+// bfloat16 exactly as the separate rotation kernel rounds it.
+__device__ __forceinline__ unsigned rotated_pair(const __nv_bfloat16* x, int d, const float* cos_row, const float* sin_row, int rot) {
+    const int half = rot >> 1;
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + d);
+    if (d >= rot) return *reinterpret_cast<const unsigned*>(&v);
+    const bool low = d < half;
+    const int f = low ? d : d - half;
+    const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(x + (low ? d + half : d - half));
+    const float2 c = *reinterpret_cast<const float2*>(cos_row + f), sn = *reinterpret_cast<const float2*>(sin_row + f);
+    const float a0 = __low2float(v), a1 = __high2float(v), b0 = __low2float(w), b1 = __high2float(w);
+    const float r0 = low ? a0 * c.x - b0 * sn.x : a0 * c.x + b0 * sn.x;
+    const float r1 = low ? a1 * c.y - b1 * sn.y : a1 * c.y + b1 * sn.y;
+    return pack_bf16(r0, r1);
+}
+
+// As load_q, with the rotation applied on the way (the fused decode path: q comes straight from the projection).
+template <int HD>
+__device__ __forceinline__ void load_q_rotated(unsigned (&q)[HD / 16][4], const __nv_bfloat16* const (&row_ptr)[2], int lane,
+                                               const float* cos_row, const float* sin_row, int rot) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            unsigned lo = 0u, hi = 0u;
+            if (row_ptr[r]) {
+                lo = rotated_pair(row_ptr[r], kk * 16 + 2 * t, cos_row, sin_row, rot);
+                hi = rotated_pair(row_ptr[r], kk * 16 + 8 + 2 * t, cos_row, sin_row, rot);
+            }
+            q[kk][r] = lo;
+            q[kk][2 + r] = hi;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------ prefill
 // grid: (row tiles of 64, requests, kv heads). Rows of a request and kv head: r = token * n_rep + g.
 template <int HD>
@@ -301,14 +339,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __
 // ------------------------------------------------------------------------------------------ decode
 // grid: (splits, tokens, kv heads). Every token has q_len 1; its position is ctx_len - 1.
 // part_o: [tokens, heads, splits, HD] float, part_ml: [tokens, heads, splits, 2] (max in log2 units, sum).
-template <int HD>
+// FUSED: qkv is the raw projection; the kernel rotates the queries as it loads them, and the CTA whose keys
+// include the token's own position rotates the new key, puts key and value into its tiles and into the page.
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
-                        int page_size, const __nv_bfloat16* __restrict__ k_pages,
-                        const __nv_bfloat16* __restrict__ v_pages, int num_pages, int heads, int kv_heads,
+                        int page_size, __nv_bfloat16* k_pages, __nv_bfloat16* v_pages, int num_pages, int heads, int kv_heads,
                         float scale, int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int* __restrict__ counters) {
+                        int* __restrict__ counters, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_last;
     pdl_launch_dependents();
@@ -355,7 +394,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
     cp_async_commit();
     pdl_wait();
     unsigned q[HD / 16][4];
-    load_q<HD>(q, q_ptr, lane);
+    const float* cos_row = FUSED ? cos_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;      // p < 0: a padding row
+    const float* sin_row = FUSED ? sin_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;
+    if (FUSED) load_q_rotated<HD>(q, q_ptr, lane, cos_row, sin_row, rot);
+    else load_q<HD>(q, q_ptr, lane);
     if (!issued0) {
         if (t_begin <= t_end) issue(t_begin, 0);
         cp_async_commit();
@@ -369,6 +411,27 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
         const int cur = (tile - t_begin) & 1;
         cp_async_wait<1>();                        // everything but the newest group: tile `tile` has landed
         __syncthreads();
+        if (FUSED && tile == own && p >= 0) {
+            // this step's own key (rotated) and value: into the tiles, and into the page for the steps to come
+            const __nv_bfloat16* k_new = qkv + (size_t)token * q_stride + (size_t)(heads + kvh) * HD;
+            const __nv_bfloat16* v_new = qkv + (size_t)token * q_stride + (size_t)(heads + kv_heads + kvh) * HD;
+            const int r = p - own * BLOCK_N;
+            const int page = bt[shift >= 0 ? (p >> shift) : (p / page_size)];
+            const int slot = shift >= 0 ? (p & (page_size - 1)) : (p % page_size);
+            const bool has_page = page >= 0 && page < num_pages;
+            const size_t off = has_page ? (((size_t)page * kv_heads + kvh) * page_size + slot) * HD : 0;
+            for (int d = 2 * tid; d < HD; d += 2 * WARPS * 32) {
+                const unsigned kr = rotated_pair(k_new, d, cos_row, sin_row, rot);
+                const unsigned vr = *reinterpret_cast<const unsigned*>(v_new + d);
+                *reinterpret_cast<unsigned*>(k_buf[cur] + r * Tile<HD>::ROW_BYTES + d * 2) = kr;
+                *reinterpret_cast<unsigned*>(v_buf[cur] + r * Tile<HD>::ROW_BYTES + d * 2) = vr;
+                if (has_page) {
+                    *reinterpret_cast<unsigned*>(k_pages + off + d) = kr;
+                    *reinterpret_cast<unsigned*>(v_pages + off + d) = vr;
+                }
+            }
+            __syncthreads();
+        }
         // each warp takes 16 keys of the tile
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
@@ -385,15 +448,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
     __syncthreads();
 
     // merge the four warps through shared memory (the tiles are no longer needed)
-    float* sm_o = reinterpret_cast<float*>(smem);                 // [WARPS][16][HD]
-    float* sm_ml = sm_o + WARPS * 16 * HD;                        // [WARPS][16][2]
+    constexpr int MS = HD + 4;                                    // row stride of the merge buffer (padded against bank conflicts)
+    float* sm_o = reinterpret_cast<float*>(smem);                 // [WARPS][16][MS]
+    float* sm_ml = sm_o + WARPS * 16 * MS;                        // [WARPS][16][2]
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = g + 8 * r;
 #pragma unroll
         for (int d = 0; d < HD / 8; ++d) {
-            sm_o[(warp * 16 + row) * HD + d * 8 + 2 * t] = o[d][2 * r];
-            sm_o[(warp * 16 + row) * HD + d * 8 + 2 * t + 1] = o[d][2 * r + 1];
+            *reinterpret_cast<float2*>(&sm_o[(warp * 16 + row) * MS + d * 8 + 2 * t]) = make_float2(o[d][2 * r], o[d][2 * r + 1]);
         }
         if (t == 0) {
             sm_ml[(warp * 16 + row) * 2] = m_run[r];
@@ -413,7 +476,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
                 const float mw = sm_ml[(w * 16 + row) * 2];
                 const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
                 l += sm_ml[(w * 16 + row) * 2 + 1] * f;
-                acc += sm_o[(w * 16 + row) * HD + d] * f;
+                acc += sm_o[(w * 16 + row) * MS + d] * f;
             }
         }
         const int head = kvh * n_rep + row;
@@ -519,7 +582,7 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
 
 template <int HD> int prefill_smem() { return 4 * Tile<HD>::BYTES; }
 template <int HD> int decode_smem() {
-    const int tiles = 4 * Tile<HD>::BYTES, merge = WARPS * 16 * (HD + 2) * 4, combine = (16 * 64 + 16) * 4;
+    const int tiles = 4 * Tile<HD>::BYTES, merge = WARPS * 16 * (HD + 4 + 2) * 4, combine = (16 * 64 + 16) * 4;
     const int a = tiles > merge ? tiles : merge;
     return a > combine ? a : combine;
 }
@@ -546,20 +609,28 @@ int launch_prefill(const void* qkv, int q_stride, void* out, const int* q_start,
 
 template <int HD>
 int launch_decode(const void* qkv, int q_stride, void* out, const int* ctx_lens, const int* block_table,
-                  int bt_stride, int page_size, const void* k_pages, const void* v_pages, int num_pages,
+                  int bt_stride, int page_size, void* k_pages, void* v_pages, int num_pages,
                   int n_tokens, int heads, int kv_heads, float scale, int window, int splits, float* part_o,
-                  float* part_ml, int* counters, cudaStream_t stream) {
+                  float* part_ml, int* counters, const float* cos_t, const float* sin_t, int rot, bool fused,
+                  cudaStream_t stream) {
     static bool configured = false;
     const int smem = decode_smem<HD>();
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        NIB_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        NIB_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
     dim3 grid(splits, n_tokens, kv_heads);
-    NIB_CUDA(launch_pdl(attention_decode_kernel<HD>, grid, dim3(WARPS * 32), (size_t)smem, stream,
-                        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
-                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
-                        window, splits, part_o, part_ml, counters));
+    if (fused)
+        NIB_CUDA(launch_pdl(attention_decode_kernel<HD, true>, grid, dim3(WARPS * 32), (size_t)smem, stream,
+                            (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
+                            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
+                            window, splits, part_o, part_ml, counters, cos_t, sin_t, rot));
+    else
+        NIB_CUDA(launch_pdl(attention_decode_kernel<HD, false>, grid, dim3(WARPS * 32), (size_t)smem, stream,
+                            (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
+                            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
+                            window, splits, part_o, part_ml, counters, cos_t, sin_t, rot));
     if (splits > 1 && counters == nullptr)
         NIB_CUDA(launch_pdl(attention_combine_kernel, dim3(n_tokens * heads), dim3(128), (size_t)0, stream,
                             (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, HD));
@@ -618,7 +689,31 @@ NIB_API int nib_attention_decode_mma(const void* qkv, int q_stride, void* out, c
     NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode: splits > 1 need scratch memory");
     NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode: too many tokens or kv heads for one launch");
     if (n_tokens == 0) return 0;
-#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, counters, stream)
+#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, const_cast<void*>(k_pages), const_cast<void*>(v_pages), num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, counters, nullptr, nullptr, 0, false, stream)
+    NIB_HD_SWITCH(head_dim, CALL)
+#undef CALL
+    NIB_REQUIRE(false, "attention decode: unreachable head_dim %d", head_dim);
+}
+
+// The decode attention fused with what precedes it in a decode step: qkv is the raw projection [n_tokens,
+// (heads + 2 kv_heads) * head_dim]; queries and the new key are rotated with the tables' row of the token's
+// position (ctx_len - 1), the new key and value are written into the token's page and used at once. The
+// rotated width must be a multiple of 4 and at most head_dim. Otherwise as nib_attention_decode_mma.
+NIB_API int nib_attention_decode_fused_mma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
+                                           const int* block_table, int bt_stride, int page_size, void* k_pages,
+                                           void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
+                                           int head_dim, float scale, int window, int splits, float* part_o,
+                                           float* part_ml, int* counters, const float* cos_t, const float* sin_t, int rot,
+                                           cudaStream_t stream) {
+    NIB_REQUIRE(nib_attention_mma_supported(heads, kv_heads, head_dim), "attention (tensor cores): head_dim %d with %d/%d heads is not supported", head_dim, heads, kv_heads);
+    NIB_REQUIRE(heads / kv_heads <= 16, "attention decode: at most 16 query heads per kv head, got %d", heads / kv_heads);
+    NIB_REQUIRE(n_tokens >= 0 && page_size > 0 && num_pages > 0 && window >= 0 && splits >= 1 && splits <= 64, "attention decode: bad sizes (1..64 splits)");
+    NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode: splits > 1 need scratch memory");
+    NIB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 4 == 0 && (rot == 0 || (cos_t && sin_t)), "attention decode (fused): rotated width %d must be a multiple of 4 and at most head_dim", rot);
+    NIB_REQUIRE(q_stride % 2 == 0, "attention decode (fused): rows must be 4-byte aligned");
+    NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode: too many tokens or kv heads for one launch");
+    if (n_tokens == 0) return 0;
+#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, counters, cos_t, sin_t, rot, true, stream)
     NIB_HD_SWITCH(head_dim, CALL)
 #undef CALL
     NIB_REQUIRE(false, "attention decode: unreachable head_dim %d", head_dim);

@@ -54,7 +54,7 @@ __device__ __forceinline__ unsigned pack2(float lo, float hi) {
 // NT: token tiles of 8. KSPLIT: 1 (each warp its own 16 rows, whole K) or WARPS (the warps of a CTA
 // share 16 rows and split K; gridDim.y CTAs split K further). grid.x: CTAs over the row groups.
 template <int NT, int KSPLIT, int EPI, bool NORM>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 2)      // two CTAs per SM: a projection's 300 row groups fit one wave
 gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
                    void* __restrict__ out, int tokens, int n_out, int k_dim, int lda, int ldo,
                    const float* __restrict__ gain, float eps, float* __restrict__ scratch, int* __restrict__ counters) {
@@ -365,7 +365,9 @@ NIB_API int nib_gemm_smallm(const void* A, const void* W, const float* bias, voi
         // hand-over between CTAs (a fence, a counter and a second read of the partial tiles)
         cross = 1;
         if (scratch && counters) {
-            cross = ceil_div(blocks, WARPS * 4);
+            // measured: the hand-over between CTAs (fence, counter, second read of the partials) costs more
+            // than it saves until a warp would have to stream more than ~32 blocks of K on its own
+            cross = ceil_div(blocks, WARPS * 32);
             if (cross > 16) cross = 16;
             while (cross > 1 && (long long)groups * cross > 8 * 148) --cross;
         }

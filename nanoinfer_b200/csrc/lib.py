@@ -54,6 +54,7 @@ class Kernels:
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
         self._ws_attn_counters = None
+        self.fuse_decode = True                # pure decode steps: rotation and cache write inside the attention kernel
         self.separate_combine = True           # merge the decode splits in a second kernel (measured faster than letting the last CTA do it)
         try:
             self._lib = ctypes.CDLL(lib_path)
@@ -263,6 +264,45 @@ class Kernels:
     def attention_tc_error(self) -> int:
         """The error word of the tcgen05 attention's bounded waits (0 = none); synchronises and clears it."""
         return self._lib.nib_attention_tc_error()
+
+    def can_fuse_decode(self, dtype, heads, kv_heads, head_dim, rotary) -> bool:
+        """True if ``attention_decode_fused`` takes this shape (bfloat16, a tensor-core head size, at most
+        16 query heads per kv head, a rotated width that is a multiple of 4)."""
+        if dtype != torch.bfloat16 or self.force_general_attention or not self.fuse_decode:
+            return False
+        if self._lib.nib_attention_mma_supported(c_int(heads), c_int(kv_heads), c_int(head_dim)) != 1:
+            return False
+        rot = 0 if rotary is None else rotary[2]
+        return heads // kv_heads <= 16 and rot % 4 == 0
+
+    def attention_decode_fused(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
+                               page_size, k_pages, v_pages, rotary):
+        """A pure decode step's rotation, cache write and attention in one kernel: ``qkv`` is the raw
+        projection; every request brings exactly one token."""
+        _need(qkv, torch.bfloat16, "attention qkv"); _need(out, torch.bfloat16, "attention out")
+        _need(k_pages, torch.bfloat16, "k_pages"); _need(v_pages, torch.bfloat16, "v_pages")
+        _need(block_table, torch.int32, "block_table", contiguous=False)
+        if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim) or block_table.stride(1) != 1:
+            raise KernelError("attention_decode_fused: pages or block table do not fit")
+        n = qkv.shape[0]
+        if any(q != 1 for q in ctx.host.q_lens):
+            raise KernelError("attention_decode_fused: every request must bring exactly one token")
+        cos = sin = None
+        rot = 0
+        if rotary is not None:
+            cos, sin, rot = rotary
+        splits = self.decode_splits(n, kv_heads, max(ctx.host.ctx_lens), window)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty(n * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty(n * heads * splits * 2, dtype=torch.float32, device=qkv.device)
+        self._check(self._lib.nib_attention_decode_fused_mma(
+            _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(block_table.stride(0)),
+            c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(n), c_int(heads),
+            c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits), _ptr(part_o), _ptr(part_ml),
+            c_void_p(0), _ptr(cos), _ptr(sin), c_int(rot), self._stream()), "attention decode (fused)")
+        if splits > 1:
+            self.launches += 1
 
     def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int) -> int:
         """Into how many CTAs the keys of a decoding token are split: two key tiles per CTA (both are in

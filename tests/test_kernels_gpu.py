@@ -386,3 +386,38 @@ def test_attention_tcgen05_prefill(K, heads, kv_heads, hd, page, window):
     assert_close(fast, legacy.double(), dtype, "tcgen05 vs mma.sync attention")
     REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert_close(fast, ref, dtype, "tcgen05 attention")
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,rot,page,window", [(14, 2, 64, 64, 16, 0), (6, 1, 32, 32, 8, 0), (3, 3, 48, 48, 8, 24),
+                                                               (16, 1, 128, 64, 16, 0), (4, 2, 16, 16, 16, 0)])
+def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads, hd, rot, page, window):
+    """The fused decode kernel (rotate q and the new k, write k and v into the page, attend) against the
+    separate rotation kernel followed by the decode kernel: same output, same pages."""
+    from nanoinfer_b200.parts.position import rotary_tables
+    dtype = torch.bfloat16
+    before = [0, 63, 64, 300, 1000, 17]
+    n = len(before)
+    ctx, bt = make_paged_batch([1] * n, before, page, 200 * (16 // min(page, 16)), "cuda", seed=8)
+    pages = int(bt.max().item()) + 1
+    kp, vp = _fill_cache(ctx, bt, page, pages, kv_heads, hd, dtype, 120)
+    kp2, vp2 = kp.clone(), vp.clone()
+    cos, sin = rotary_tables(1100, rot, 10000.0)
+    rotary = (cos.cuda(), sin.cuda(), rot)
+    raw = rnd((n, (heads + 2 * kv_heads) * hd), dtype, 122)
+    scale = 1.0 / math.sqrt(hd)
+    assert K.can_fuse_decode(dtype, heads, kv_heads, hd, rotary)
+    for splits in (0, 1, 5):
+        K.fixed_decode_splits = splits
+        try:
+            fused = torch.empty(n, heads * hd, dtype=dtype, device="cuda")
+            a = kp.clone(), vp.clone()
+            K.attention_decode_fused(raw.clone(), fused, heads, kv_heads, hd, scale, window, ctx, bt, page, a[0], a[1], rotary)
+            two = torch.empty_like(fused)
+            b = kp2.clone(), vp2.clone()
+            q2 = raw.clone()
+            K.rope_store(q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, b[0], b[1], True)
+            K.attention(q2, two, heads, kv_heads, hd, scale, window, ctx, bt, page, b[0], b[1])
+        finally:
+            K.fixed_decode_splits = 0
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "pages differ"
+        assert torch.equal(fused, two), f"outputs differ with splits={splits}"
