@@ -86,6 +86,7 @@ class RequestCache:
         self.length = 0                                   # positions committed
         self.tables: List[List[int]] = [[] for _ in range(num_groups)]
         self.first_live: List[int] = [0] * num_groups     # first logical page still held
+        self.version = 0                                  # counts the changes of the block tables
         self.closed = False
 
     def pages_held(self, group: int) -> int:
@@ -165,6 +166,8 @@ class CacheManager:
         for g, k in enumerate(need):
             for _ in range(k):
                 rc.tables[g].append(self.pools[g].allocate())
+            if k:
+                rc.version += 1
 
     def commit(self, rc: RequestCache, n_new: int) -> None:
         """The step wrote ``n_new`` positions: advance, and return pages that a window has passed."""
@@ -179,6 +182,7 @@ class CacheManager:
                 if table[lp] >= 0:
                     self.pools[g].free(table[lp])
                     table[lp] = -1
+                    rc.version += 1
             rc.first_live[g] = max(rc.first_live[g], min(first, len(table)))
 
     # ---- views ----------------------------------------------------------------------------

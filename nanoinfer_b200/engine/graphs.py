@@ -17,6 +17,7 @@ import weakref
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -33,6 +34,66 @@ class _Captured:
     inputs: torch.Tensor
     logits: torch.Tensor
     launches: int
+    mirror: "_InputMirror" = None
+
+
+class _InputMirror:
+    """Pinned host copy of a captured graph's input buffer, kept up to date row by row.
+
+    Between two decode steps of the same requests only the token, the position and the context length
+    of a row change, and now and then one block-table entry; the mirror rewrites a row's block table
+    only when the request in that row, or the version of its tables, differs from what the row holds.
+    The layout is the one ``Engine.build_context`` produces for a padded batch of one-token requests."""
+
+    def __init__(self, rb: int, widths: List[int], device: torch.device):
+        sizes = [rb, rb, rb, rb + 1, rb, rb, rb] + [rb * w for w in widths]
+        self.size = sum(sizes)
+        self.host = torch.empty(self.size, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.event.record()
+        h = self.host.numpy()
+        offs = np.concatenate([[0], np.cumsum(sizes)])
+        cut = [h[offs[i]:offs[i + 1]] for i in range(len(sizes))]
+        self.tok, self.pos, req_index, q_start, self.ctx, self.slots, want = cut[:7]
+        self.tables = [cut[7 + g].reshape(rb, w) for g, w in enumerate(widths)]
+        h[:] = 0
+        req_index[:] = np.arange(rb)
+        q_start[:] = np.arange(rb + 1)
+        want[:] = np.arange(rb)
+        for t in self.tables:
+            t[:] = -1
+        self.rb = rb
+        self.row_req = [None] * rb          # the request whose pages a row's block tables list
+        self.row_ver = [-1] * rb
+
+    def fill(self, entries) -> None:
+        self.event.synchronize()            # the previous copy has left the buffer
+        n = len(entries)
+        self.tok[:n] = [e.tokens[0] for e in entries]
+        lens = np.fromiter((e.request.length for e in entries), dtype=np.int32, count=n)
+        self.pos[:n] = lens
+        self.ctx[:n] = lens + 1
+        row_req, row_ver = self.row_req, self.row_ver
+        for i, e in enumerate(entries):
+            rc = e.request
+            if row_req[i] is not rc or row_ver[i] != rc.version:
+                for t, held in zip(self.tables, rc.tables):
+                    t[i, :len(held)] = held
+                    t[i, len(held):] = -1
+                self.slots[i] = rc.slot
+                row_req[i], row_ver[i] = rc, rc.version
+        for i in range(n, self.rb):         # rows that a request has left become padding again
+            if row_req[i] is None:
+                continue
+            self.tok[i] = self.pos[i] = self.ctx[i] = self.slots[i] = 0
+            for t in self.tables:
+                t[i, :] = -1
+            row_req[i], row_ver[i] = None, -1
+
+    def send(self, device_buffer: torch.Tensor) -> int:
+        device_buffer.copy_(self.host, non_blocking=True)
+        self.event.record()
+        return self.size * 4
 
 
 class DecodeGraphs:
@@ -69,7 +130,9 @@ class DecodeGraphs:
                 ctx, want_rows, _ = eng.build_context(entries)
                 return eng.model.forward(ctx, eng.storage.layer_caches(ctx.block_tables), want_rows)
             cap = self._capture(key, entries, rb, cb, widths)
-        _, _, want_list = eng.build_context(entries, pad_to=rb, widths=widths, static=cap.inputs)
+        cap.mirror.fill(entries)
+        eng.last_h2d_bytes = cap.mirror.send(cap.inputs)
+        want_list = [i for i, e in enumerate(entries) for _ in e.want]
         cap.graph.replay()
         eng.graph_launches += cap.launches
         if not want_list:
@@ -109,6 +172,7 @@ class DecodeGraphs:
         finally:
             if gc_was_on:
                 gc.enable()
-        cap = _Captured(graph, static, logits, ops.launches - before)
+        cap = _Captured(graph, static, logits, ops.launches - before, _InputMirror(rb, widths, eng.device))
+        assert cap.mirror.size == size
         self.captured[key] = cap
         return cap

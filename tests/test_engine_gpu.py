@@ -285,6 +285,49 @@ def test_decode_graphs_padding_wants_and_buckets(model_dirs, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "W"])
+def test_decode_graphs_rows_change_hands(model_dirs, name, dtype):
+    """A captured graph's input rows are refreshed in place. A request ends and the others move up a
+    row, a new request takes the first row, the batch shrinks so that a row becomes padding and grows
+    again, and (model W) a window frees pages in the middle of it: every row must still show its own
+    request's pages."""
+    from nanoinfer_b200.engine import StepEntry
+    d, page = model_dirs[name]
+    plain = PlainModel(d)
+    g = torch.Generator().manual_seed(4)
+    n = min(plain.cfg["max_pos"], 120)
+    seqs = {k: torch.randint(0, plain.cfg["vocab"], (n,), generator=g).tolist() for k in "abcd"}
+    want = {k: plain.logits(s) for k, s in seqs.items()}
+    eng = engine_for(d, page, dtype, num_pages=64)
+    fed, rcs = {}, {}
+
+    def prompt(k, count):
+        rcs[k] = eng.open(k)
+        eng.step([StepEntry(rcs[k], seqs[k][:count], [])])
+        fed[k] = count
+
+    def decode(order, steps):
+        for _ in range(steps):
+            logits = eng.step([StepEntry(rcs[k], [seqs[k][fed[k]]], [0]) for k in order])
+            for k, row in zip(order, logits):
+                assert_close(row, want[k][fed[k]], tdt(dtype), f"{name} request {k} position {fed[k]}")
+                fed[k] += 1
+
+    prompt("a", 30); prompt("b", 7); prompt("c", 19)
+    decode("abc", 20)
+    eng.close(rcs.pop("a"))
+    decode("bc", 6)                 # b and c move up; the third row is padding of another bucket
+    prompt("d", 3)
+    decode("dbc", 20)               # d takes the first row, pages that a held are used again
+    decode("c", 5)
+    decode("cbd", 10)
+    assert eng.graph_launches > 0
+    for rc in rcs.values():
+        eng.close(rc)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_real_layer_widths(tmp_path, dtype):
     """Two layers with the widths of the 0.5B model (hidden 896, 14/2 heads of 64, intermediate 4864,
     vocabulary 151936, theta 1e6): a prompt in one step, then cut into portions and single tokens."""
