@@ -33,6 +33,14 @@ MODEL = {
     "max_position_embeddings": 32768, "use_sliding_window": False, "hidden_act": "silu",
     "torch_dtype": "bfloat16",
 }
+# the other sizes of the family that the baseline names; --shape selects one (the default run is the 0.5B shape)
+SHAPES = {
+    "0.5b": {},
+    "1.5b": {"num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12, "num_key_value_heads": 2,
+             "head_dim": 128, "intermediate_size": 8960},
+    "7b": {"num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
+           "head_dim": 128, "intermediate_size": 18944, "vocab_size": 152064, "tie_word_embeddings": False},
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
@@ -257,16 +265,16 @@ def run_ours(args) -> dict:
 
     value = batch / (ms_step / 1e3)
     return {
-        "metric": "decode tok/s at batch 8 (Qwen2.5-0.5B shape, context 4096)", "value": round(value, 1),
+        "metric": f"decode tok/s at batch {batch} (Qwen2.5-{args.shape.upper()} shape, context {ctx})", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights and random token ids", "impl": "ours",
-        "config": {"model": "Qwen2.5-0.5B shape", "layers": layers, "layers_full": MODEL["num_hidden_layers"],
+        "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers, "layers_full": MODEL["num_hidden_layers"],
                    "hidden": MODEL["hidden_size"], "heads": MODEL["num_attention_heads"],
                    "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"],
-                   "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "tied_head": True,
+                   "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "tied_head": MODEL["tie_word_embeddings"],
                    "global_batch": batch, "seq_len": ctx, "page_size": page, "prefill_tokens": t_pre,
-                   "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights ~1 GB per step)",
+                   "parallelism": "single-gpu", "l2": f"inputs larger than L2 (weights {nums['weight_bytes'] / 1e9:.1f} GB per step)",
                    "peaks": pk["source"]},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         "prefill": prefill,
@@ -338,7 +346,7 @@ def run_reference(args) -> dict:
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights and random token ids", "impl": "reference",
-        "config": {"model": "Qwen2.5-0.5B shape", "layers": layers, "layers_full": m["num_hidden_layers"],
+        "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers, "layers_full": m["num_hidden_layers"],
                    "global_batch": batch, "seq_len": ctx, "parallelism": "single-gpu",
                    "engine": "reference Python model (torch, CUDA)"},
         "clocks": cs.summary(),
@@ -361,7 +369,9 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profilers that filter by kernel name)")
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
                     help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
+    ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes: the family's 0.5B (default), 1.5B or 7B")
     args = ap.parse_args()
+    MODEL.update(SHAPES[args.shape])
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"unavailable": f"this engine runs on one GPU; --gpus {args.gpus} is not supported",

@@ -15,6 +15,15 @@
 // tcgen05.commit releases a stage when the MMAs that read it are done. The accumulator is double
 // buffered in TMEM: while the epilogue warps drain tile i, the MMA warp already fills tile i+1.
 //
+// Split K: with few output tiles (a decode step of a narrow projection) the K range of a tile is cut
+// into `splits` work items that different CTAs run at the same time, so that all SMs stream weights.
+// The ADD epilogue then adds each item's partial sums into the 32-bit output with reductions in
+// memory (red.global.add.f32; the order of the additions, and with it the last bit, is not fixed).
+// The other epilogues leave the partial sums in a scratch buffer; per (tile, 32-feature quadrant) a
+// counter tells the warp that arrives last, and that warp adds the partials in the fixed order of the
+// splits and runs the epilogue (chosen for up to 16 tokens only: one warp reads all of them).
+// Nobody waits for anybody.
+//
 // Every wait has an iteration limit; a wait that runs out records a code in an error word, the CTA
 // stops issuing, waits (bounded) for its own copies in flight, frees its TMEM and returns.
 //
@@ -132,11 +141,45 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// The epilogue of 16 consecutive tokens (first_token ..) of output feature f: v = accumulator, u = the
+// second accumulator of the swiglu form, b = bias.
+template <int EPI>
+__device__ __forceinline__ void emit16(void* __restrict__ out, const float (&v)[16], const float (&u)[16], float b, int f,
+                                       int first_token, int tokens, int ldo) {
+    if (EPI == EPI_ADD) {
+        // read-modify-write of the residual stream: all 16 loads first, so that they are in flight
+        // together instead of each waiting behind the previous store
+        float r[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = first_token + j;
+            r[j] = t < tokens ? __ldcg((const float*)out + (size_t)t * ldo + f) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = first_token + j;
+            if (t < tokens) ((float*)out)[(size_t)t * ldo + f] = r[j] + v[j] + b;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = first_token + j;
+            if (t >= tokens) break;
+            const size_t o = (size_t)t * ldo + f;
+            const float x = v[j] + b;
+            if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
+            else if (EPI == EPI_F32) ((float*)out)[o] = x;
+            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * u[j]);
+        }
+    }
+}
+
 // grid: persistent CTAs; tile index -> (feature tile, token tile), feature tiles fastest
 template <int TOK, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-               const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo) {
+               const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo,
+               int splits, int kb_per_split, float* __restrict__ scratch, int* __restrict__ counters) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     using C = Cfg<TOK, DUAL>;
     extern __shared__ unsigned char smem_raw[];
@@ -151,7 +194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f_tiles = (n_out + BLOCK_F - 1) / BLOCK_F, t_tiles = (tokens + TOK - 1) / TOK;
-    const int tiles = f_tiles * t_tiles;
+    const int items = f_tiles * t_tiles * splits;       // work item = (output tile, split of K), splits fastest
     const int k_blocks = (k_dim + BLOCK_K - 1) / BLOCK_K;
 
     if (threadIdx.x == 0) {
@@ -176,9 +219,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0 && lane == 0) {
         // ---------------- producer: TMA loads of W (and the up rows) and A tiles, stage after stage across tiles
         int it = 0, issued = 0;
-        for (int tile = blockIdx.x; tile < tiles && !s_failed; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < items && !s_failed; item += gridDim.x) {
+            const int tile = item / splits, split = item - tile * splits;
             const int f0 = (tile % f_tiles) * BLOCK_F, t0 = (tile / f_tiles) * TOK;
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int kb_end = min(k_blocks, (split + 1) * kb_per_split);
+            for (int kb = split * kb_per_split; kb < kb_end; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1)) {
                     atomicCAS(&g_tc_error, 0, (1 << 16) | (int)blockIdx.x);
@@ -202,8 +247,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---------------- MMA issuer
         constexpr unsigned idesc = instr_desc(TOK);
         int it = 0, local = 0;
-        for (int tile = blockIdx.x; tile < tiles && !s_failed; tile += gridDim.x, ++local) {
+        for (int item = blockIdx.x; item < items && !s_failed; item += gridDim.x, ++local) {
             const int buf = local & 1;
+            const int split = item % splits;
+            const int kb_begin = split * kb_per_split, kb_end = min(k_blocks, kb_begin + kb_per_split);
             // the epilogue has drained this buffer (two tiles ago)
             if (!mbar_wait(&acc_empty_bar[buf], ((local >> 1) & 1) ^ 1)) {
                 atomicCAS(&g_tc_error, 0, (4 << 16) | (int)blockIdx.x);
@@ -212,7 +259,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             tc_fence_after();
             const unsigned acc = tmem_base + buf * C::ACC_COLS;
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1)) {
                     atomicCAS(&g_tc_error, 0, (2 << 16) | (int)blockIdx.x);
@@ -227,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
-                    const bool accumulate = (kb > 0) || (k > 0);
+                    const bool accumulate = (kb > kb_begin) || (k > 0);
                     tc_mma(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
                     if (DUAL) tc_mma(acc + TOK, u_desc + adv, a_desc + adv, idesc, accumulate);
                 }
@@ -240,8 +287,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---------------- epilogue: TMEM -> registers -> global, one output feature per thread
         const int quad = warp & 3;                       // the TMEM lanes this warp may read: 32*quad..
         int local = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+        for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
             const int buf = local & 1;
+            const int tile = item / splits;
             const int f0 = (tile % f_tiles) * BLOCK_F, t0 = (tile / f_tiles) * TOK;
             const int f = f0 + quad * 32 + lane;
             bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
@@ -253,44 +301,87 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tc_fence_after();
             const float b = (bias != nullptr && f < n_out) ? bias[f] : 0.f;
             const unsigned lane_addr = tmem_base + buf * C::ACC_COLS + ((unsigned)(quad * 32) << 16);
+            if (splits == 1) {
 #pragma unroll 1
-            for (int c = 0; c < TOK; c += 16) {
+                for (int c = 0; c < TOK; c += 16) {
+                    float v[16], u[16];
+                    tmem_ld16(lane_addr + c, v);
+                    if (DUAL) tmem_ld16(lane_addr + TOK + c, u);
+                    if (f < n_out) emit16<EPI>(out, v, u, b, f, t0 + c, tokens, ldo);
+                }
+                // this warp has read its part of the buffer: hand it back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+                continue;
+            }
+            if (EPI == EPI_ADD) {
+                // ---- split K into a 32-bit sum: every item adds its part, the first one the bias too
+                const float b0 = (item - tile * splits == 0) ? b : 0.f;
+                const int live = min(TOK, tokens - t0);
+#pragma unroll 1
+                for (int c = 0; c < live; c += 16) {
+                    float v[16];
+                    tmem_ld16(lane_addr + c, v);
+                    if (f < n_out) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c + j < live) atomicAdd((float*)out + (size_t)(t0 + c + j) * ldo + f, v[j] + b0);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+                continue;
+            }
+            // ---- split K: leave the partial sums, count, and let the last warp of this quadrant finish the tile
+            constexpr int ITEM_FLOATS = (DUAL ? 2 : 1) * TOK * BLOCK_F;
+            const int live = min(TOK, tokens - t0);             // token rows of this tile that exist
+            float* part = scratch + (size_t)item * ITEM_FLOATS + quad * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < live; c += 16) {
                 float v[16], u[16];
                 tmem_ld16(lane_addr + c, v);
                 if (DUAL) tmem_ld16(lane_addr + TOK + c, u);
-                if (f < n_out) {
-                    if (EPI == EPI_ADD) {
-                        // read-modify-write of the residual stream: all 16 loads first, so that they are in
-                        // flight together instead of each waiting behind the previous store
-                        float r[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            r[j] = t < tokens ? __ldcg((const float*)out + (size_t)t * ldo + f) : 0.f;
-                        }
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            if (t < tokens) ((float*)out)[(size_t)t * ldo + f] = r[j] + v[j] + b;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            if (t >= tokens) break;
-                            const size_t o = (size_t)t * ldo + f;
-                            const float x = v[j] + b;
-                            if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
-                            else if (EPI == EPI_F32) ((float*)out)[o] = x;
-                            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * u[j]);
-                        }
+                for (int j = 0; j < 16; ++j) {
+                    if (c + j < live) {
+                        __stcg(part + (size_t)(c + j) * BLOCK_F, v[j]);
+                        if (DUAL) __stcg(part + (size_t)(TOK + c + j) * BLOCK_F, u[j]);
                     }
                 }
             }
-            // this warp has read its part of the buffer: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+            __threadfence();                                    // the partials are visible before the count
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                last = (atomicAdd(&counters[tile * 4 + quad], 1) == splits - 1);
+                if (last) counters[tile * 4 + quad] = 0;        // ready for the next launch
+                __threadfence();
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (!last) continue;
+            const float* first = scratch + (size_t)tile * splits * ITEM_FLOATS + quad * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < live; c += 16) {
+                float v[16], u[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { v[j] = 0.f; u[j] = 0.f; }
+                for (int sp = 0; sp < splits; ++sp) {
+                    const float* src = first + (size_t)sp * ITEM_FLOATS;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c + j < live) {
+                            v[j] += __ldcg(src + (size_t)(c + j) * BLOCK_F);
+                            if (DUAL) u[j] += __ldcg(src + (size_t)(TOK + c + j) * BLOCK_F);
+                        }
+                    }
+                }
+                if (f < n_out) emit16<EPI>(out, v, u, b, f, t0 + c, tokens, ldo);
+            }
         }
     }
     tc_fence_before();
@@ -347,36 +438,60 @@ struct MapKeyHash {
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_weight_maps;   // weights live as long as the model
 std::mutex g_map_mutex;
 
+struct SplitK {
+    int splits = 1;          // work items per output tile
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    long long scratch_floats = 0, counter_ints = 0;
+};
+
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sms = 1;
+    }
+    return sms;
+}
+
 template <int TOK, int EPI>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens, int n_out,
-              int k, int ldo, cudaStream_t stream) {
+              int k, int ldo, const SplitK& sk, cudaStream_t stream) {
     using C = Cfg<TOK, EPI == EPI_SWIGLU>;
     static bool configured = false;
     if (!configured) {
         NIB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TOK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        NIB_CUDA(cudaGetDevice(&dev));
-        NIB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int sms = sm_count();
     const int tiles = ceil_div(n_out, BLOCK_F) * ceil_div(tokens, TOK);
-    NIB_CUDA(launch_pdl(gemm_tc_kernel<TOK, EPI>, dim3(tiles < sms ? tiles : sms), dim3(THREADS), (size_t)C::SMEM, stream,
-                        mw, ma, bias, out, tokens, n_out, k, ldo));
+    const int k_blocks = ceil_div(k, BLOCK_K);
+    int splits = sk.splits < 1 ? 1 : sk.splits;
+    if (splits > k_blocks) splits = k_blocks;
+    int kb_per_split = ceil_div(k_blocks, splits);
+    splits = ceil_div(k_blocks, kb_per_split);               // no split without work
+    if (splits > 1 && EPI != EPI_ADD) {
+        const long long need = (long long)tiles * splits * (EPI == EPI_SWIGLU ? 2 : 1) * TOK * BLOCK_F;
+        NIB_REQUIRE(sk.scratch != nullptr && sk.counters != nullptr && need <= sk.scratch_floats && 4LL * tiles <= sk.counter_ints,
+                    "gemm (tensor cores): %d splits of %d tiles need %lld floats of scratch and %d counters (have %lld, %lld)",
+                    splits, tiles, need, 4 * tiles, sk.scratch_floats, sk.counter_ints);
+    }
+    const int items = tiles * splits;
+    NIB_CUDA(launch_pdl(gemm_tc_kernel<TOK, EPI>, dim3(items < sms ? items : sms), dim3(THREADS), (size_t)C::SMEM, stream,
+                        mw, ma, bias, out, tokens, n_out, k, ldo, splits, kb_per_split, sk.scratch, sk.counters));
     return 0;
 }
 
 template <int TOK>
 int launch_tc_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens,
-                  int n_out, int k, int ldo, cudaStream_t stream) {
+                  int n_out, int k, int ldo, const SplitK& sk, cudaStream_t stream) {
     switch (epi) {
-        case EPI_STORE: return launch_tc<TOK, EPI_STORE>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
-        case EPI_ADD: return launch_tc<TOK, EPI_ADD>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
-        case EPI_F32: return launch_tc<TOK, EPI_F32>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_STORE: return launch_tc<TOK, EPI_STORE>(mw, ma, bias, out, tokens, n_out, k, ldo, sk, stream);
+        case EPI_ADD: return launch_tc<TOK, EPI_ADD>(mw, ma, bias, out, tokens, n_out, k, ldo, sk, stream);
+        case EPI_F32: return launch_tc<TOK, EPI_F32>(mw, ma, bias, out, tokens, n_out, k, ldo, sk, stream);
         case EPI_SWIGLU:
-            if constexpr (TOK <= 128) return launch_tc<TOK, EPI_SWIGLU>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+            if constexpr (TOK <= 128) return launch_tc<TOK, EPI_SWIGLU>(mw, ma, bias, out, tokens, n_out, k, ldo, sk, stream);
             break;
     }
     nib_set_error("gemm (tensor cores): unknown epilogue %d", epi);
@@ -403,19 +518,46 @@ NIB_API int nib_gemm_tc_error() {
 
 // A [tokens, K] bfloat16 with row stride lda; W [N, K] (SWIGLU: [2N, K]); out [tokens, N] with row
 // stride ldo. epi: 0 store bf16, 1 add into float, 2 store float, 3 swiglu. tok_tile: 0 = chosen here.
-NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
-                        int lda, int ldo, int epi, int tok_tile, cudaStream_t stream) {
+// splits: work items per output tile along K; 0 = chosen here (more than one only when the tiles alone
+// leave SMs idle and the scratch holds the partial sums), 1 = none. scratch/counters: a float buffer and
+// a zeroed int buffer that the kernels of one stream share (the counters are left zeroed).
+NIB_API int nib_gemm_tc_splitk(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
+                               int lda, int ldo, int epi, int tok_tile, int splits, float* scratch, int* counters,
+                               long long scratch_floats, long long counter_ints, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm (tensor cores): bad sizes tokens=%d N=%d K=%d", tokens, N, K);
     NIB_REQUIRE(nib_gemm_tc_supported(A, W, K, lda), "gemm (tensor cores): K=%d / lda=%d must be multiples of 8 and bases 16-byte aligned", K, lda);
     NIB_REQUIRE(epi != EPI_SWIGLU || bias == nullptr, "gemm (tensor cores): the swiglu epilogue takes no bias");
+    NIB_REQUIRE(splits >= 0, "gemm (tensor cores): splits=%d", splits);
     if (tokens == 0) return 0;
+    const int f_tiles = ceil_div(N, BLOCK_F);
     if (tok_tile == 0) {
-        const int f_tiles = ceil_div(N, BLOCK_F);
         tok_tile = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
         // 256 tokens per tile halves the shared-memory traffic per flop; take it when the grid still fills the GPU
         if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148 && epi != EPI_SWIGLU) tok_tile = 256;
     }
     NIB_REQUIRE(ceil_div(tokens, tok_tile) <= 65535, "gemm (tensor cores): too many token tiles");
+    SplitK sk;
+    sk.scratch = scratch; sk.counters = counters; sk.scratch_floats = scratch_floats; sk.counter_ints = counter_ints;
+    sk.splits = splits;
+    if (splits == 0) {
+        // Fill the SMs: as many items as SMs, but at least 4 blocks of K (256 elements) per item, and only
+        // what the scratch holds. The partial sums cost traffic of their own, so wide token tiles stay whole.
+        const long long tiles = (long long)f_tiles * ceil_div(tokens, tok_tile);
+        const int sms = sm_count(), k_blocks = ceil_div(K, BLOCK_K);
+        int want = 1;
+        if (tiles * 2 <= sms) {
+            want = (int)(sms / tiles);
+            if (want > k_blocks / 4) want = k_blocks / 4;
+            if (epi != EPI_ADD) {
+                // partial sums through the scratch: one warp adds them up, which pays for few tokens only
+                const long long per_split = tiles * (epi == EPI_SWIGLU ? 2 : 1) * tok_tile * BLOCK_F;
+                if (scratch == nullptr || counters == nullptr || tok_tile > 16 || 4 * tiles > counter_ints) want = 1;
+                else if ((long long)want * per_split > scratch_floats) want = (int)(scratch_floats / per_split);
+            }
+            if (want < 1) want = 1;
+        }
+        sk.splits = want;
+    }
     const long long w_rows = (epi == EPI_SWIGLU) ? 2LL * N : N;
     CUtensorMap mw, ma;
     {
@@ -432,13 +574,19 @@ NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* o
     }
     if (make_map(&ma, A, tokens, K, lda, tok_tile)) return 1;
     switch (tok_tile) {
-        case 16: return launch_tc_epi<16>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
-        case 32: return launch_tc_epi<32>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
-        case 64: return launch_tc_epi<64>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
-        case 128: return launch_tc_epi<128>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+        case 16: return launch_tc_epi<16>(epi, mw, ma, bias, out, tokens, N, K, ldo, sk, stream);
+        case 32: return launch_tc_epi<32>(epi, mw, ma, bias, out, tokens, N, K, ldo, sk, stream);
+        case 64: return launch_tc_epi<64>(epi, mw, ma, bias, out, tokens, N, K, ldo, sk, stream);
+        case 128: return launch_tc_epi<128>(epi, mw, ma, bias, out, tokens, N, K, ldo, sk, stream);
         case 256:
             NIB_REQUIRE(epi != EPI_SWIGLU, "gemm (tensor cores): the swiglu epilogue takes token tiles up to 128 (two accumulators, double buffered)");
-            return launch_tc_epi<256>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+            return launch_tc_epi<256>(epi, mw, ma, bias, out, tokens, N, K, ldo, sk, stream);
     }
     NIB_REQUIRE(false, "gemm (tensor cores): token tile %d is not one of 16, 32, 64, 128, 256", tok_tile);
+}
+
+// The same without split K (no scratch).
+NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
+                        int lda, int ldo, int epi, int tok_tile, cudaStream_t stream) {
+    return nib_gemm_tc_splitk(A, W, bias, out, tokens, N, K, lda, ldo, epi, tok_tile, 1, nullptr, nullptr, 0, 0, stream);
 }

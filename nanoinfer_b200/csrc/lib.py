@@ -50,7 +50,8 @@ class Kernels:
         self.smallm_ksplit = 0                 # tests: the K split of the small-M GEMM (0 = chosen, 1 or 4)
         self.sm_count = 148
         self.smallm_cross = 0                  # tests: CTAs that split K in the small-M GEMM (0 = chosen)
-        self.smallm_max_tokens = 16            # more tokens than this go to the tcgen05 GEMM (measured crossover)
+        self.gemm_route = None                 # tests: "smallm" | "smallm_fused" | "tc" instead of the measured choice
+        self.tc_splits = 0                     # tests: work items along K per tile of the tcgen05 GEMM (0 = chosen, 1 = none)
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
         self._ws_attn_counters = None
@@ -62,7 +63,7 @@ class Kernels:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
-                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
+                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
                      "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
@@ -122,15 +123,42 @@ class Kernels:
             raise KernelError(f"linear[{mode}]: out must be {want_out}, got {out.dtype}")
         self._gemm(a, w, bias32, out, m, n, k, _EPI[mode])
 
+    def _route(self, m: int, rows: int, k: int, epi: int, has_norm: bool):
+        """Which kernel multiplies ``m`` tokens with ``rows x k`` bfloat16 weights, and whether a deferred
+        norm is applied inside it. Measured on B200 with cold weights at the projection sizes of the 0.5B,
+        1.5B and 7B models: the small-M kernel (weights streamed straight into mma.sync fragments) wins
+        while the weights are few or the tcgen05 kernel would have few tiles and cannot split K cheaply;
+        the tcgen05 kernel wins for wide outputs, for more tokens, and, with K split over CTAs and summed
+        by reductions in memory, for every sum into the residual stream with a long K. The fused norm
+        re-reads the 32-bit activations in every CTA, which pays only for few tokens and narrow outputs."""
+        if self.gemm_route is not None:
+            return ("tc", False) if self.gemm_route == "tc" else ("smallm", has_norm and self.gemm_route == "smallm_fused")
+        if self.smallm_ksplit or self.smallm_cross:
+            return "smallm", has_norm
+        weight_bytes = 2 * rows * k
+        if epi == _EPI["add"]:
+            small = m <= 16 and k <= 2048
+        elif epi == _EPI["store"]:
+            small = m <= 64 and rows <= 6144
+        elif epi == _EPI["swiglu"]:
+            small = (m <= 8 and weight_bytes <= 64e6) or (m <= 16 and weight_bytes <= 12e6)
+        else:
+            small = m <= 16 and weight_bytes <= 32e6
+        fuse = has_norm and small and epi != _EPI["swiglu"] and (m <= 8 or (m <= 16 and k <= 1024))
+        return ("smallm" if small else "tc"), fuse
+
     def _gemm(self, a, w, bias32, out, m, n, k, epi):
-        """bfloat16: up to 64 tokens stream the weights through the small-M kernel, more go to the tcgen05
-        kernel; shapes neither takes, and 32-bit, run the CUDA-core kernel."""
+        """bfloat16 goes to the small-M kernel or to the tcgen05 kernel (see ``_route``); shapes neither
+        takes, and 32-bit, run the CUDA-core kernel."""
         deferred = a if hasattr(a, "materialize") else None
         bf16 = a.dtype == torch.bfloat16 and not self.force_simt_gemm
-        if bf16 and self.tc_token_tile == 0 and (m <= self.smallm_max_tokens or self.smallm_ksplit or self.smallm_cross):
+        if bf16 and self.tc_token_tile == 0:
+            kernel, fuse = self._route(m, w.shape[0], k, epi, deferred is not None)
+            if deferred is not None and not fuse:
+                a, deferred = deferred.materialize(), None
             src = deferred.x32 if deferred is not None else a
-            if self._lib.nib_gemm_smallm_supported(_ptr(src), _ptr(w), c_int(m), c_int(k), c_int(src.stride(0)),
-                                                   c_int(4 if deferred is not None else 2)) == 1:
+            if kernel == "smallm" and self._lib.nib_gemm_smallm_supported(
+                    _ptr(src), _ptr(w), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if deferred is not None else 2)) == 1:
                 self.ensure_workspace(src.device)
                 gain = deferred.gain32 if deferred is not None else None
                 self._check(self._lib.nib_gemm_smallm(
@@ -143,9 +171,12 @@ class Kernels:
         if deferred is not None:
             a = deferred.materialize()
         if bf16 and self._lib.nib_gemm_tc_supported(_ptr(a), _ptr(w), c_int(k), c_int(a.stride(0))) == 1:
-            self._check(self._lib.nib_gemm_tc(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
-                                              c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi),
-                                              c_int(self.tc_token_tile), self._stream()), "linear (tensor cores)")
+            self.ensure_workspace(a.device)
+            self._check(self._lib.nib_gemm_tc_splitk(
+                _ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
+                c_int(out.stride(0)), c_int(epi), c_int(self.tc_token_tile), c_int(self.tc_splits),
+                _ptr(self._ws_scratch), _ptr(self._ws_counters), c_longlong(self._ws_scratch.numel()),
+                c_longlong(self._ws_counters.numel()), self._stream()), "linear (tensor cores)")
             return
         self._check(self._lib.nib_gemm_simt(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
                                             c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi), c_int(_DT[a.dtype]),

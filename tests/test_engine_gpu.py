@@ -107,7 +107,20 @@ def test_scheduler_equals_alone_with_few_pages(model_dirs, dtype):
     if dtype == "float32":
         assert [out[f"r{i}"] for i in range(6)] == alone
     else:
-        assert sum(out[f"r{i}"] == alone[i] for i in range(6)) >= 5   # a rounding tie may flip one
+        # bfloat16 rounds differently in different batches, so a near tie may turn another way and the
+        # continuation then differs. What must hold: every token emitted is, under the plain model fed
+        # the same tokens, within twice the element tolerance of the best one.
+        from gpu_util import BF16_MAX, BF16_ULP
+        plain = PlainModel(d)
+        for i, p in enumerate(prompts):
+            for got in (out[f"r{i}"], alone[i]):
+                assert len(got) == 20
+                ref = plain.logits(p + got).double()
+                for j, tok in enumerate(got):
+                    row = ref[len(p) + j - 1]
+                    slack = 2 * (BF16_MAX * row.pow(2).mean().sqrt().item() + BF16_ULP * row.abs().max().item())
+                    assert row.max().item() - row[tok].item() <= slack, f"request {i} token {j}: not the best within rounding"
+        assert sum(out[f"r{i}"] == alone[i] for i in range(6)) >= 3
     assert sched.preemptions > 0
     model.engine.cache.check()
     assert model.engine.cache.num_free() == 14

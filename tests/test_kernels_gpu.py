@@ -280,6 +280,41 @@ def test_tensor_core_gemm_tiles_and_ragged_shapes(K, m, n, k, tile):
     assert K.gemm_tc_error() == 0
 
 
+@pytest.mark.parametrize("splits", [0, 2, 5, 64])
+@pytest.mark.parametrize("m,n,k", [(1, 896, 4864), (8, 130, 1000), (16, 503, 328), (40, 896, 896), (64, 200, 2048)])
+def test_tensor_core_gemm_split_k(K, m, n, k, splits):
+    """K cut into work items that different CTAs run: partial sums through the scratch and the last
+    warp (store, f32, swiglu; the same bits on every call) or added in memory (add); more splits than
+    blocks of K, a ragged last split, and the counters left ready for the next call."""
+    dtype = torch.bfloat16
+    a, w = rnd((m, k), dtype, 74), rnd((n, k), dtype, 75, scale=0.05)
+    bias = rnd((n,), torch.float32, 76)
+    K.gemm_route, K.tc_splits = "tc", splits
+    try:
+        for _ in range(2):
+            out = torch.empty(m, n, dtype=dtype, device="cuda")
+            K.linear(a, w, bias, out, "store")
+            assert_close(out, _ref_linear_f64(a, w, bias), dtype, "split store")
+            out32 = torch.empty(m, n, device="cuda")
+            K.linear(a, w, None, out32, "f32")
+            assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "split f32")
+            again = torch.empty_like(out32)
+            K.linear(a, w, None, again, "f32")
+            assert torch.equal(out32, again)
+            res = rnd((m, n), torch.float32, 77)
+            acc = res.clone()
+            K.linear(a, w, bias, acc, "add")
+            assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "split add")
+            inter = n // 2
+            sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+            K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+            REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+            assert_close(sw, ref, dtype, "split swiglu")
+    finally:
+        K.gemm_route, K.tc_splits = None, 0
+    assert K.gemm_tc_error() == 0
+
+
 def test_tensor_core_gemm_refuses_what_it_cannot_take(K):
     from nanoinfer_b200.csrc.lib import KernelError
     a, w = rnd((4, 20), torch.bfloat16, 80), rnd((6, 20), torch.bfloat16, 81)      # K = 20: rows are not 16-byte multiples
@@ -298,7 +333,7 @@ def test_small_m_gemm(K, m, n, k, ksplit, cross):
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 90), rnd((n, k), dtype, 91, scale=0.05)
     bias = rnd((n,), torch.float32, 92)
-    K.smallm_ksplit, K.smallm_cross, K.smallm_max_tokens = ksplit, cross, 64
+    K.smallm_ksplit, K.smallm_cross, K.gemm_route = ksplit, cross, "smallm"
     try:
         out = torch.empty(m, n, dtype=dtype, device="cuda")
         K.linear(a, w, bias, out, "store")
@@ -323,7 +358,7 @@ def test_small_m_gemm(K, m, n, k, ksplit, cross):
         assert torch.equal(one[0], out32[m - 1])
     finally:
         K.smallm_ksplit = K.smallm_cross = 0
-        K.smallm_max_tokens = 16
+        K.gemm_route = None
 
 
 @pytest.mark.parametrize("m,n,k,eps", [(1, 1152, 896, 1e-6), (8, 320, 192, 1e-5), (20, 200, 64, 1e-3), (64, 503, 320, 1e-6)])
@@ -342,8 +377,9 @@ def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     gain = 1 + 0.1 * rnd((k,), torch.float32, 96)
     w = rnd((n, k), torch.bfloat16, 97, scale=0.05)
     fused, two_step = torch.empty(m, n, device="cuda"), torch.empty(m, n, device="cuda")
-    K.smallm_max_tokens = 64
+    K.gemm_route = "smallm_fused"
     K.linear(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w, None, fused, "f32")
+    K.gemm_route = "smallm"
     h = _Norm().forward(x32)
     K.linear(h, w, None, two_step, "f32")
     ref = _ref_linear_f64(h, w, None)
@@ -353,8 +389,9 @@ def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     assert_close(fused, exact, torch.bfloat16, "fused norm gemm")
     inter = n // 2
     sw, sw_ref = (torch.empty(m, inter, dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    K.gemm_route = "smallm_fused"
     K.linear_swiglu(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w[:2 * inter].contiguous(), sw)
-    K.smallm_max_tokens = 16
+    K.gemm_route = None
     REF.linear_swiglu(h, w[:2 * inter].contiguous(), sw_ref)
     assert_close(sw, sw_ref, torch.bfloat16, "fused norm swiglu")
 
