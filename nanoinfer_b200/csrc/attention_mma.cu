@@ -13,13 +13,12 @@
 // cpp/src/cuda/cuda_backend.cu:489-575 (tiled prefill), :578-640 and :331-352 (split-KV and combine).
 //
 // Tensor-core path: mma.sync m16n8k16 with ldmatrix from padded shared-memory tiles filled by cp.async.
-#include "common.cuh"
+#include "attention_common.cuh"
 
 namespace {
 
 constexpr int BLOCK_N = 64;     // keys per tile
 constexpr int WARPS = 4;
-constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -28,26 +27,6 @@ __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool v
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<unsigned*>(&v);
-}
 
 // Shared-memory tile of BLOCK_N rows of HD bfloat16, each row padded by 16 bytes: the row stride in
 // 32-bit words is 4 mod 8, so the eight rows of an ldmatrix 8x8 block fall into distinct banks.
@@ -119,124 +98,6 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const unsigned (&
             ldmatrix_x4_trans(b, v_tile + (row0 + kb * 16 + key_off) * Tile<HD>::ROW_BYTES + (dp * 16 + dim_off) * 2);
             mma_bf16(o[2 * dp], p[kb], b[0], b[1]);
             mma_bf16(o[2 * dp + 1], p[kb], b[2], b[3]);
-        }
-    }
-}
-
-// Online-softmax update of one warp's 16 rows with a block of NT*8 score columns.
-// s holds raw dots; scale2 = scale * log2(e). vis_lo/vis_hi: visible key range of the thread's two
-// rows (row g -> [0], row g+8 -> [1]); key_base: key of column 0. Produces P as A fragments.
-template <int HD, int NT>
-__device__ __forceinline__ void softmax_block(float (&s)[NT][4], unsigned (&p)[NT / 2][4], float (&o)[HD / 8][4],
-                                              float (&m_run)[2], float (&l_run)[2], float scale2, int key_base,
-                                              const int (&vis_lo)[2], const int (&vis_hi)[2], int lane) {
-    const int t = lane & 3;
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int n = 0; n < NT; ++n) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1;
-            const int key = key_base + n * 8 + 2 * t + (e & 1);
-            const bool vis = key >= vis_lo[r] && key <= vis_hi[r];
-            s[n][e] = vis ? s[n][e] * scale2 : -INFINITY;
-            mx[r] = fmaxf(mx[r], s[n][e]);
-        }
-    }
-    float corr[2], m_use[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m_run[r], mx[r]);
-        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;         // nothing visible yet: exp2(-inf - 0) = 0
-        corr[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_use[r]);
-        m_run[r] = m_new;
-    }
-    float sum[2] = {0.f, 0.f};
-#pragma unroll
-    for (int n = 0; n < NT; ++n) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float pv = exp2f(s[n][e] - m_use[e >> 1]);
-            s[n][e] = pv;
-            sum[e >> 1] += pv;
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-        l_run[r] = l_run[r] * corr[r] + sum[r];
-    }
-#pragma unroll
-    for (int d = 0; d < HD / 8; ++d) {
-        o[d][0] *= corr[0]; o[d][1] *= corr[0];
-        o[d][2] *= corr[1]; o[d][3] *= corr[1];
-    }
-#pragma unroll
-    for (int kb = 0; kb < NT / 2; ++kb) {
-        p[kb][0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
-        p[kb][1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
-        p[kb][2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
-        p[kb][3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
-    }
-}
-
-// A fragments of 16 query rows straight from global memory. row_ptr[r]: start of the head's HD elements
-// for the thread's row g (r=0) and g+8 (r=1), or nullptr for a row that does not exist.
-template <int HD>
-__device__ __forceinline__ void load_q(unsigned (&q)[HD / 16][4], const __nv_bfloat16* const (&row_ptr)[2], int lane) {
-    const int t = lane & 3;
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            unsigned lo = 0u, hi = 0u;
-            if (row_ptr[r]) {
-                lo = *reinterpret_cast<const unsigned*>(row_ptr[r] + kk * 16 + 2 * t);
-                hi = *reinterpret_cast<const unsigned*>(row_ptr[r] + kk * 16 + 8 + 2 * t);
-            }
-            q[kk][r] = lo;        // a0 (row g) / a1 (row g+8): dims 2t, 2t+1
-            q[kk][2 + r] = hi;    // a2 / a3: dims 8+2t, 9+2t
-        }
-    }
-}
-
-// Rotation of one even/odd pair (d, d+1) of a head for the token's position: cos/sin rows hold rot/2 values;
-// d < rot/2 pairs with d + rot/2 (x*c - partner*s), rot/2 <= d < rot with d - rot/2 (x*c + partner*s),
-// d >= rot is left as it is. rot/2 is even, so a pair never straddles the halves. The result is rounded to
-// bfloat16 exactly as the separate rotation kernel rounds it.
-__device__ __forceinline__ unsigned rotated_pair(const __nv_bfloat16* x, int d, const float* cos_row, const float* sin_row, int rot) {
-    const int half = rot >> 1;
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + d);
-    if (d >= rot) return *reinterpret_cast<const unsigned*>(&v);
-    const bool low = d < half;
-    const int f = low ? d : d - half;
-    const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(x + (low ? d + half : d - half));
-    const float2 c = *reinterpret_cast<const float2*>(cos_row + f), sn = *reinterpret_cast<const float2*>(sin_row + f);
-    const float a0 = __low2float(v), a1 = __high2float(v), b0 = __low2float(w), b1 = __high2float(w);
-    const float r0 = low ? a0 * c.x - b0 * sn.x : a0 * c.x + b0 * sn.x;
-    const float r1 = low ? a1 * c.y - b1 * sn.y : a1 * c.y + b1 * sn.y;
-    return pack_bf16(r0, r1);
-}
-
-// As load_q, with the rotation applied on the way (the fused decode path: q comes straight from the projection).
-template <int HD>
-__device__ __forceinline__ void load_q_rotated(unsigned (&q)[HD / 16][4], const __nv_bfloat16* const (&row_ptr)[2], int lane,
-                                               const float* cos_row, const float* sin_row, int rot) {
-    const int t = lane & 3;
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            unsigned lo = 0u, hi = 0u;
-            if (row_ptr[r]) {
-                lo = rotated_pair(row_ptr[r], kk * 16 + 2 * t, cos_row, sin_row, rot);
-                hi = rotated_pair(row_ptr[r], kk * 16 + 8 + 2 * t, cos_row, sin_row, rot);
-            }
-            q[kk][r] = lo;
-            q[kk][2 + r] = hi;
         }
     }
 }
@@ -651,6 +512,17 @@ int launch_decode(const void* qkv, int q_stride, void* out, const int* ctx_lens,
         case 128: return CALL(128);                  \
         default: break;                              \
     }
+
+// Merges the partial (max, sum, output) triples of `splits` key ranges, in split order: part_o [rows, splits,
+// head_dim], part_ml [rows, splits, 2] (max in log2 units, sum) -> out [rows, head_dim] bfloat16.
+NIB_API int nib_attention_combine(const float* part_o, const float* part_ml, void* out, int rows, int splits,
+                                  int head_dim, cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && splits >= 1 && splits <= 64 && head_dim >= 1 && head_dim <= 128, "attention combine: bad sizes");
+    if (rows == 0) return 0;
+    NIB_CUDA(launch_pdl(attention_combine_kernel, dim3(rows), dim3(128), (size_t)0, stream, part_o, part_ml,
+                        (__nv_bfloat16*)out, splits, head_dim));
+    return 0;
+}
 
 // 1 if the tensor-core kernels take this head size and grouping, else 0 (the caller then uses the general kernel).
 NIB_API int nib_attention_mma_supported(int heads, int kv_heads, int head_dim) {

@@ -56,6 +56,7 @@ class Kernels:
         self._ws_counters = None
         self._ws_attn_counters = None
         self.fuse_decode = True                # pure decode steps: rotation and cache write inside the attention kernel
+        self.decode_tma = True                 # decode attention with TMA page loads where the shape allows (else mma.sync + cp.async)
         self.separate_combine = True           # merge the decode splits in a second kernel (measured faster than letting the last CTA do it)
         try:
             self._lib = ctypes.CDLL(lib_path)
@@ -63,7 +64,7 @@ class Kernels:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
-                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma",
+                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
                      "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
@@ -259,7 +260,8 @@ class Kernels:
             while n_dec < n_req and q_lens[n_dec] == 1:
                 n_dec += 1
         if n_dec:
-            splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window)
+            tma = self._decode_tma_ok(heads, kv_heads, head_dim, page_size)
+            splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window, tma)
             part_o = part_ml = counters = None
             if splits > 1 and not self.separate_combine and n_dec * kv_heads <= 64 * 1024:
                 self.ensure_workspace(qkv.device)
@@ -267,11 +269,16 @@ class Kernels:
             if splits > 1:
                 part_o = torch.empty(n_dec * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
                 part_ml = torch.empty(n_dec * heads * splits * 2, dtype=torch.float32, device=qkv.device)
-            self._check(self._lib.nib_attention_decode_mma(
-                _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(bt_stride),
-                c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_dec), c_int(heads),
-                c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits), _ptr(part_o),
-                _ptr(part_ml), _ptr(counters), self._stream()), "attention decode")
+            common = (_ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(bt_stride),
+                      c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_dec), c_int(heads),
+                      c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits))
+            if tma:
+                self._check(self._lib.nib_attention_decode_tma(*common, _ptr(part_o), _ptr(part_ml), self._stream()),
+                            "attention decode (TMA)")
+                counters = None
+            else:
+                self._check(self._lib.nib_attention_decode_mma(*common, _ptr(part_o), _ptr(part_ml), _ptr(counters),
+                                                               self._stream()), "attention decode")
             if splits > 1 and counters is None:
                 self.launches += 1
         if n_dec < n_req:
@@ -296,15 +303,26 @@ class Kernels:
         """The error word of the tcgen05 attention's bounded waits (0 = none); synchronises and clears it."""
         return self._lib.nib_attention_tc_error()
 
-    def can_fuse_decode(self, dtype, heads, kv_heads, head_dim, rotary) -> bool:
-        """True if ``attention_decode_fused`` takes this shape (bfloat16, a tensor-core head size, at most
-        16 query heads per kv head, a rotated width that is a multiple of 4)."""
+    def can_fuse_decode(self, dtype, heads, kv_heads, head_dim, rotary, page_size=0) -> bool:
+        """True if ``attention_decode_fused`` should take this shape (bfloat16, a tensor-core head size, at
+        most 16 query heads per kv head, a rotated width that is a multiple of 4), and the faster decode
+        kernel with TMA page loads (which wants rotation and cache write done before it) does not."""
         if dtype != torch.bfloat16 or self.force_general_attention or not self.fuse_decode:
+            return False
+        if self._decode_tma_ok(heads, kv_heads, head_dim, page_size):
             return False
         if self._lib.nib_attention_mma_supported(c_int(heads), c_int(kv_heads), c_int(head_dim)) != 1:
             return False
         rot = 0 if rotary is None else rotary[2]
         return heads // kv_heads <= 16 and rot % 4 == 0
+
+    def _decode_tma_ok(self, heads, kv_heads, head_dim, page_size) -> bool:
+        return self.decode_tma and page_size > 0 and self._lib.nib_attention_decode_tma_supported(
+            c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(page_size)) == 1
+
+    def attention_decode_tma_error(self) -> int:
+        """The error word of the TMA decode kernel's bounded waits (0 = none); synchronises and clears it."""
+        return self._lib.nib_attention_decode_tma_error()
 
     def attention_decode_fused(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
                                page_size, k_pages, v_pages, rotary):
@@ -335,14 +353,19 @@ class Kernels:
         if splits > 1:
             self.launches += 1
 
-    def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int) -> int:
-        """Into how many CTAs the keys of a decoding token are split: two key tiles per CTA (both are in
-        flight at once, so a CTA waits for memory once), as long as that does not make more CTAs than
-        fill the GPU about eight times."""
+    def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int, tma: bool = False) -> int:
+        """Into how many CTAs the keys of a decoding token are split. The kernel with TMA page loads keeps
+        several tiles in flight per CTA: about 256 CTAs in all (measured best from 1 to 64 requests), at
+        least four tiles each. The cp.async kernel: two key tiles per CTA (both are in flight at once, so a
+        CTA waits for memory once), as long as that does not make more CTAs than fill the GPU about eight
+        times."""
         if self.fixed_decode_splits:
             return self.fixed_decode_splits
         keys = min(max_ctx, window) if window > 0 else max_ctx
         tiles = -(-keys // 64) + 1
+        if tma:
+            want = max(1, round(256 / max(1, n_tokens * kv_heads)))
+            return max(1, min(want, tiles // 4, 64))
         most = max(1, (8 * self.sm_count) // max(1, n_tokens * kv_heads))
         return max(1, min(-(-tiles // 2), most, 64))
 

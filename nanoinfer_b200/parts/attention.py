@@ -82,7 +82,7 @@ class GroupedQueryAttention(Mixer):
         attn = torch.empty((m, self.heads * self.head_dim), dtype=self.rt.dtype, device=h.device)
         fused = getattr(self.ops, "can_fuse_decode", None)
         if cache.writes and ctx.host.max_q_len == 1 and fused is not None and \
-                fused(self.rt.dtype, self.heads, self.kv_heads, self.head_dim, self._rotary):
+                fused(self.rt.dtype, self.heads, self.kv_heads, self.head_dim, self._rotary, cache.page_size):
             # a pure decode step: rotation, cache write and attention in one kernel
             self.ops.attention_decode_fused(qkv, attn, self.heads, self.kv_heads, self.head_dim, self.scale,
                                             self.window, ctx, cache.block_table, cache.page_size, cache.k_pages,

@@ -199,21 +199,28 @@ def test_argmax_first_maximum(K, vocab):
     assert out[2].item() == 3 and out[3].item() == vocab - 1
 
 
+@pytest.mark.parametrize("tma", [True, False])
 @pytest.mark.parametrize("splits", [0, 1, 3, 8])
-@pytest.mark.parametrize("heads,kv_heads,hd,window", [(14, 2, 64, 0), (16, 1, 64, 0), (12, 1, 32, 700), (20, 1, 16, 0),
-                                                       (8, 8, 128, 0), (9, 3, 112, 0)])
-def test_attention_decode_long_context_split_over_ctas(K, heads, kv_heads, hd, window, splits):
+@pytest.mark.parametrize("heads,kv_heads,hd,window,page", [
+    (14, 2, 64, 0, 16), (16, 1, 64, 0, 16), (12, 1, 32, 700, 16), (20, 1, 16, 0, 16), (8, 8, 128, 0, 16), (9, 3, 112, 0, 16),
+    (14, 2, 64, 700, 8), (8, 2, 128, 100, 32), (7, 1, 64, 0, 64), (4, 2, 128, 0, 8)])
+def test_attention_decode_long_context_split_over_ctas(K, heads, kv_heads, hd, window, page, splits, tma):
     """Single decoded tokens at contexts from 1 to 3000 keys (tile edges 63, 64, 65), any number of
-    splits, up to 16 query heads per kv head on the decode kernel (20: the prefill kernel takes them)."""
-    dtype, page = torch.bfloat16, 16
+    splits, up to 16 query heads per kv head on the decode kernels (20: the prefill kernel takes them);
+    with the pages fetched by TMA (head sizes 64 and 128, pages of 8..64) and by cp.async."""
+    dtype = torch.bfloat16
     before = [0, 62, 63, 64, 2999, 1500]
     q_lens = [1] * len(before)
-    ctx, bt = make_paged_batch(q_lens, before, page, 400, "cuda", seed=5)
-    kp, vp = _fill_cache(ctx, bt, page, 400, kv_heads, hd, dtype, 50)
+    n_pages = 6 * (3000 // page + 2)
+    ctx, bt = make_paged_batch(q_lens, before, page, n_pages, "cuda", seed=5)
+    if window:      # pages that the window has passed are given back: the table no longer names them
+        for i, b in enumerate(before):
+            bt[i, :max(0, b - window + 1) // page] = -1
+    kp, vp = _fill_cache(ctx, bt, page, n_pages, kv_heads, hd, dtype, 50)
     qkv = rnd((len(before), (heads + 2 * kv_heads) * hd), dtype, 52)
     out, ref = (torch.empty(len(before), heads * hd, dtype=dtype, device="cuda") for _ in range(2))
     scale = 1.0 / math.sqrt(hd)
-    K.fixed_decode_splits = splits
+    K.fixed_decode_splits, K.decode_tma = splits, tma
     two = torch.empty_like(out)
     try:
         K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
@@ -221,7 +228,8 @@ def test_attention_decode_long_context_split_over_ctas(K, heads, kv_heads, hd, w
         K.attention(qkv, two, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     finally:
         K.fixed_decode_splits = 0
-        K.separate_combine = True
+        K.separate_combine = K.decode_tma = True
+    assert K.attention_decode_tma_error() == 0
     REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert_close(out, ref, dtype, "decode attention")
     assert_close(two, ref, dtype, "decode attention, merged by the last CTA")
@@ -444,7 +452,7 @@ def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads
     scale = 1.0 / math.sqrt(hd)
     assert K.can_fuse_decode(dtype, heads, kv_heads, hd, rotary)
     for splits in (0, 1, 5):
-        K.fixed_decode_splits = splits
+        K.fixed_decode_splits, K.decode_tma = splits, False
         try:
             fused = torch.empty(n, heads * hd, dtype=dtype, device="cuda")
             a = kp.clone(), vp.clone()
@@ -455,6 +463,6 @@ def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads
             K.rope_store(q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, b[0], b[1], True)
             K.attention(q2, two, heads, kv_heads, hd, scale, window, ctx, bt, page, b[0], b[1])
         finally:
-            K.fixed_decode_splits = 0
+            K.fixed_decode_splits, K.decode_tma = 0, True
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "pages differ"
         assert torch.equal(fused, two), f"outputs differ with splits={splits}"
