@@ -70,10 +70,88 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int c = threadIdx.x; c < hidden; c += THREADS) Elem<T>::store(o + c, xr[c] * scale * gain[c]);
 }
 
+// One WARP per output row, for widths that are multiples of 4 up to 128 * NV: the row stays in registers
+// (NV float4 per lane) between the sum of squares and the scaling, so it is read once, with 16-byte
+// loads; no shared memory, no block barrier. Which kernel runs depends on the width alone, so a row's
+// result still does not depend on the batch.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain, const int* __restrict__ rows,
+                    T* __restrict__ out, int n_rows, int hidden, float eps) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int n4 = hidden >> 2;
+    float4 g[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {       // the gains are weights: fetched before the wait
+        const int c = lane + 32 * i;
+        g[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(gain) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    if (r >= n_rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    T* o = out + (size_t)r * hidden;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < n4) {
+            const float a = v[i].x * scale * g[i].x, b = v[i].y * scale * g[i].y;
+            const float cc = v[i].z * scale * g[i].z, d = v[i].w * scale * g[i].w;
+            if constexpr (sizeof(T) == 4) {
+                reinterpret_cast<float4*>(o)[c] = make_float4(a, b, cc, d);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(cc, d);
+                uint2 pk;
+                pk.x = *reinterpret_cast<unsigned*>(&lo);
+                pk.y = *reinterpret_cast<unsigned*>(&hi);
+                reinterpret_cast<uint2*>(o)[c] = pk;
+            }
+        }
+    }
+}
+
+template <typename T>
+int launch_rmsnorm_rows(const float* x, const float* gain, const int* rows, T* out, int n_rows, int hidden, float eps,
+                        cudaStream_t stream) {
+    const int warps = n_rows >= 8 ? 8 : n_rows;           // rows per block
+    const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
+    if (hidden <= 128 * 8)
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 8>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps));
+    else if (hidden <= 128 * 16)
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 16>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps));
+    else
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 32>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps));
+    return 0;
+}
+
 NIB_API int nib_rmsnorm(const float* x, const float* gain, const int* rows, void* out, int n_rows,
                         int hidden, float eps, int dtype, cudaStream_t stream) {
     NIB_REQUIRE(n_rows >= 0 && hidden > 0, "rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
     if (n_rows == 0) return 0;
+    // rows of 16-byte multiples up to 4096 wide: a warp per row
+    if (hidden % 4 == 0 && hidden <= 4096 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0 &&
+        (dtype == NIB_F32 || dtype == NIB_BF16)) {
+        const int rc = dtype == NIB_F32 ? launch_rmsnorm_rows<float>(x, gain, rows, (float*)out, n_rows, hidden, eps, stream)
+                                        : launch_rmsnorm_rows<__nv_bfloat16>(x, gain, rows, (__nv_bfloat16*)out, n_rows, hidden, eps, stream);
+        if (rc) return rc;
+        NIB_LAUNCH_CHECK();
+        return 0;
+    }
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(rmsnorm_kernel<float, 256>, dim3(n_rows), dim3(256), (size_t)0, stream, x, gain, rows, (float*)out, hidden, eps));
     else if (dtype == NIB_BF16)
@@ -141,6 +219,88 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
 }
 
+// The same for bfloat16 with 16-byte accesses: one thread per chunk of 8 elements. A token has
+// (heads + kv_heads) * rot/16 rotation items (8 pairs each: two loads, two stores, and two more into the
+// page for a key), kv_heads * (head_dim - rot)/8 items of keys beyond the rotated width and kv_heads *
+// head_dim/8 items of values. The arithmetic per element is that of the kernel above, so are the bits.
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(h[i]); f[2 * i + 1] = __high2float(h[i]); }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+}
+
+__global__ void __launch_bounds__(256)
+rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ req_index,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                      const int* __restrict__ block_table, int bt_stride, int page_size, __nv_bfloat16* __restrict__ k_pages,
+                      __nv_bfloat16* __restrict__ v_pages, int m_tokens, int heads, int kv_heads, int head_dim, int num_pages,
+                      int write_kv) {
+    pdl_launch_dependents();
+    const int half = rot >> 1;
+    const int rot_items = (heads + kv_heads) * (half >> 3);
+    const int tail_items = write_kv ? kv_heads * ((head_dim - rot) >> 3) : 0;
+    const int v_items = write_kv ? kv_heads * (head_dim >> 3) : 0;
+    const int per_token = rot_items + tail_items + v_items;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (per_token == 0 || idx >= (long long)m_tokens * per_token) return;
+    const int m = (int)(idx / per_token);
+    int item = (int)(idx - (long long)m * per_token);
+    const int pos = positions[m];
+    long long page = -1;
+    int off = 0;
+    if (write_kv) {
+        page = block_table[(size_t)req_index[m] * bt_stride + pos / page_size];
+        off = pos % page_size;
+        if (page < 0 || page >= num_pages) page = -1;  // never write outside the pool
+    }
+    __nv_bfloat16* row = qkv + (size_t)m * (heads + 2 * kv_heads) * head_dim;
+    pdl_wait();     // positions and block tables are the step's inputs; qkv is the previous kernel's output
+    if (item < rot_items) {
+        const int per_head = half >> 3;
+        const int h = item / per_head, d = (item - h * per_head) << 3;
+        __nv_bfloat16* p = row + (size_t)h * head_dim;
+        float x1[8], x2[8], c[8], sn[8], o1[8], o2[8];
+        unpack8(*reinterpret_cast<const uint4*>(p + d), x1);
+        unpack8(*reinterpret_cast<const uint4*>(p + d + half), x2);
+        const float4* cp = reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + d);
+        const float4* sp = reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + d);
+        *reinterpret_cast<float4*>(&c[0]) = __ldg(cp); *reinterpret_cast<float4*>(&c[4]) = __ldg(cp + 1);
+        *reinterpret_cast<float4*>(&sn[0]) = __ldg(sp); *reinterpret_cast<float4*>(&sn[4]) = __ldg(sp + 1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { o1[i] = x1[i] * c[i] - x2[i] * sn[i]; o2[i] = x2[i] * c[i] + x1[i] * sn[i]; }
+        const uint4 u1 = pack8(o1), u2 = pack8(o2);
+        *reinterpret_cast<uint4*>(p + d) = u1;
+        *reinterpret_cast<uint4*>(p + d + half) = u2;
+        if (h >= heads && page >= 0) {
+            __nv_bfloat16* dst = k_pages + (((size_t)page * kv_heads + (h - heads)) * page_size + off) * head_dim;
+            *reinterpret_cast<uint4*>(dst + d) = u1;
+            *reinterpret_cast<uint4*>(dst + d + half) = u2;
+        }
+        return;
+    }
+    if (page < 0) return;
+    item -= rot_items;
+    if (item < tail_items) {
+        const int per_head = (head_dim - rot) >> 3;
+        const int h = item / per_head, d = rot + ((item - h * per_head) << 3);
+        *reinterpret_cast<uint4*>(k_pages + (((size_t)page * kv_heads + h) * page_size + off) * head_dim + d) =
+            *reinterpret_cast<const uint4*>(row + (size_t)(heads + h) * head_dim + d);
+        return;
+    }
+    item -= tail_items;
+    const int per_head = head_dim >> 3;
+    const int h = item / per_head, d = (item - h * per_head) << 3;
+    *reinterpret_cast<uint4*>(v_pages + (((size_t)page * kv_heads + h) * page_size + off) * head_dim + d) =
+        *reinterpret_cast<const uint4*>(row + (size_t)(heads + kv_heads + h) * head_dim + d);
+}
+
 NIB_API int nib_rope_store(void* qkv, const int* positions, const int* req_index, const float* cos_t,
                            const float* sin_t, int rot, const int* block_table, int bt_stride, int page_size,
                            void* k_pages, void* v_pages, int m, int heads, int kv_heads, int head_dim,
@@ -151,6 +311,21 @@ NIB_API int nib_rope_store(void* qkv, const int* positions, const int* req_index
                 "rope_store: write asked for without pages");
     if (m == 0) return 0;
     const int threads = 128;
+    const bool aligned = ((((uintptr_t)qkv | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0) &&
+                         (!write_kv || (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0);
+    if (dtype == NIB_BF16 && head_dim % 8 == 0 && rot % 16 == 0 && aligned) {
+        const int half = rot / 2;
+        const long long per_token = (long long)(heads + kv_heads) * (half / 8) +
+                                    (write_kv ? (long long)kv_heads * ((head_dim - rot) / 8 + head_dim / 8) : 0);
+        if (per_token == 0) return 0;
+        const long long total = per_token * m;
+        NIB_REQUIRE(total < (1LL << 31) * 256, "rope_store: too many elements for one launch");
+        NIB_CUDA(launch_pdl(rope_store_vec_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), (size_t)0, stream,
+                            (__nv_bfloat16*)qkv, positions, req_index, cos_t, sin_t, rot, block_table, bt_stride, page_size,
+                            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, m, heads, kv_heads, head_dim, num_pages, write_kv));
+        NIB_LAUNCH_CHECK();
+        return 0;
+    }
     if (dtype == NIB_F32)
         NIB_CUDA(launch_pdl(rope_store_kernel<float>, dim3(m), dim3(threads), (size_t)0, stream, (float*)qkv, positions, req_index,
                             cos_t, sin_t, rot, block_table, bt_stride, page_size, (float*)k_pages, (float*)v_pages, heads,

@@ -147,18 +147,13 @@ template <int EPI>
 __device__ __forceinline__ void emit16(void* __restrict__ out, const float (&v)[16], const float (&u)[16], float b, int f,
                                        int first_token, int tokens, int ldo) {
     if (EPI == EPI_ADD) {
-        // read-modify-write of the residual stream: all 16 loads first, so that they are in flight
-        // together instead of each waiting behind the previous store
-        float r[16];
+        // The sum into the residual stream is a reduction in memory (red.global.add.f32): nothing is
+        // read back, so the epilogue does not wait a memory round trip per batch of tokens. Each element
+        // has one writer here (one add, the same bits as load-add-store); with K split several items add.
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int t = first_token + j;
-            r[j] = t < tokens ? __ldcg((const float*)out + (size_t)t * ldo + f) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int t = first_token + j;
-            if (t < tokens) ((float*)out)[(size_t)t * ldo + f] = r[j] + v[j] + b;
+            if (t < tokens) atomicAdd((float*)out + (size_t)t * ldo + f, v[j] + b);
         }
     } else {
 #pragma unroll
