@@ -340,20 +340,31 @@ def test_decode_graphs_rows_change_hands(model_dirs, name, dtype):
     eng.cache.check()
 
 
+REAL_WIDTHS = {
+    # name: layers, hidden, heads, kv heads, head dim, intermediate, vocabulary, tied head
+    "0.5b": (2, 896, 14, 2, 64, 4864, 151936, True),
+    "1.5b": (1, 1536, 12, 2, 128, 8960, 30011, True),       # the family's widths with a smaller, odd vocabulary
+    "7b": (1, 3584, 28, 4, 128, 18944, 30011, False),
+}
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_real_layer_widths(tmp_path, dtype):
-    """Two layers with the widths of the 0.5B model (hidden 896, 14/2 heads of 64, intermediate 4864,
-    vocabulary 151936, theta 1e6): a prompt in one step, then cut into portions and single tokens."""
+@pytest.mark.parametrize("shape", sorted(REAL_WIDTHS))
+def test_real_layer_widths(tmp_path, dtype, shape):
+    """Layers with the widths of the 0.5B, 1.5B and 7B models (theta 1e6): a prompt in one step, then cut
+    into portions and single tokens, so that the prefill and the decode kernels both run at these sizes."""
     from nanoinfer_b200.engine import StepEntry
     from nanoinfer_b200.registry import config_from_json_dict
     from nanoinfer_b200.weights import write_random_model
-    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 2, "hidden_size": 896,
-           "num_attention_heads": 14, "num_key_value_heads": 2, "intermediate_size": 4864, "vocab_size": 151936,
-           "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 4096}
+    layers, hidden, heads, kv_heads, hd, inter, vocab, tied = REAL_WIDTHS[shape]
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers, "hidden_size": hidden,
+           "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": hd, "intermediate_size": inter,
+           "vocab_size": vocab, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": tied,
+           "max_position_embeddings": 4096}
     d = str(tmp_path / "m")
     write_random_model(config_from_json_dict(cfg), d, seed=11)
     plain = PlainModel(d, torch.float32 if dtype == "bfloat16" else torch.float64)
-    ids = torch.randint(0, 151936, (150,), generator=torch.Generator().manual_seed(12)).tolist()
+    ids = torch.randint(0, vocab, (150,), generator=torch.Generator().manual_seed(12)).tolist()
     want = plain.logits(ids)[[0, 63, 64, 100, 149]]
     eng = engine_for(d, 16, dtype, num_pages=32)
     rc = eng.open("whole")
