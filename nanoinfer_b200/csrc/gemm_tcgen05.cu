@@ -387,6 +387,221 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------------------------- two SMs on one tile
+// The same product with tcgen05.mma.cta_group::2: a cluster of two CTAs owns a tile of 256 output
+// features x TOK tokens. Each CTA loads its own 128 weight rows and HALF of the token tile; the
+// instruction, issued by one thread of the even CTA, reads the token operand from both CTAs' shared
+// memory and accumulates 128 features in each CTA's tensor memory. Per CTA and step of K that is 16 KB of
+// weights + TOK/2 x 128 bytes of tokens for 128 x TOK x 64 multiply-adds: half the token traffic of the
+// one-CTA kernel from L2 and from shared memory, which is what bounds the wide products of a prefill.
+//
+// Who signals whom: both CTAs' TMA copies complete on the EVEN CTA's full barrier (it expects the bytes of
+// both); tcgen05.commit multicasts to the empty barrier of the stage and to the accumulator-full barrier in
+// both CTAs; the epilogue warps of both CTAs arrive on the even CTA's accumulator-empty barrier. No TMA
+// multicast. The cluster meets at a hardware barrier twice, after the barriers are initialised and before
+// tensor memory is freed; every other wait is bounded as above, so every thread reaches those two.
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ unsigned map_to_cta(unsigned smem_addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, unsigned bar_cluster_addr, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(unsigned* dst_smem, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned addr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                            unsigned idesc, bool accumulate) {
+    const unsigned acc = accumulate ? 1u : 0u;
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair when the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__host__ __device__ constexpr unsigned instr_desc_pair(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+}
+
+template <int TOK, bool DUAL> struct PairCfg {
+    static constexpr int W_BYTES = BLOCK_F * BLOCK_K * 2;                 // this CTA's 128 weight rows
+    static constexpr int A_BYTES = (TOK / 2) * BLOCK_K * 2;               // this CTA's half of the token tile
+    static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * W_BYTES + A_BYTES;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int ACC_COLS = (DUAL ? 2 : 1) * TOK;
+    static constexpr int NBUF = 2 * ACC_COLS <= 512 ? 2 : 1;              // accumulator buffers in the 512 columns
+    static constexpr int TMEM_COLS = tmem_cols(NBUF * ACC_COLS);
+    static_assert(ACC_COLS <= 512, "the accumulators must fit the 512 TMEM columns");
+};
+
+template <int TOK, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                 const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo) {
+    constexpr bool DUAL = (EPI == EPI_SWIGLU);
+    using C = PairCfg<TOK, DUAL>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + C::STAGES * C::STAGE_BYTES);
+    unsigned long long* empty_bar = full_bar + C::STAGES;
+    unsigned long long* acc_full_bar = empty_bar + C::STAGES;     // [2]
+    unsigned long long* acc_empty_bar = acc_full_bar + 2;         // [2], used in the even CTA
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty_bar + 2);
+    __shared__ volatile int s_failed;
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_ctarank();                       // 0: issues the MMAs and owns the shared barriers
+    const int f_tiles = (n_out + 2 * BLOCK_F - 1) / (2 * BLOCK_F), t_tiles = (tokens + TOK - 1) / TOK;
+    const int tiles = f_tiles * t_tiles;
+    const int k_blocks = (k_dim + BLOCK_K - 1) / BLOCK_K;
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        s_failed = 0;
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_a) : "memory");
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full_bar[b], 1); mbar_init(&acc_empty_bar[b], 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- producer (in both CTAs): this CTA's weight rows and its half of the tokens
+        int it = 0, issued = 0;
+        for (int tile = cluster_id; tile < tiles && !s_failed; tile += n_clusters) {
+            const int f0 = (tile % f_tiles) * (2 * BLOCK_F) + (int)rank * BLOCK_F;
+            const int t0 = (tile / f_tiles) * TOK + (int)rank * (TOK / 2);
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % C::STAGES;
+                if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1)) {
+                    atomicCAS(&g_tc_error, 0, (5 << 16) | (int)blockIdx.x);
+                    s_failed = 1;
+                    break;
+                }
+                unsigned char* st = smem + s * C::STAGE_BYTES;
+                const unsigned bar0 = map_to_cta(smem_u32(&full_bar[s]), 0);
+                if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
+                tma_load_2d_pair(st, &map_w, bar0, kb * BLOCK_K, f0);
+                if (DUAL) tma_load_2d_pair(st + C::W_BYTES, &map_w, bar0, kb * BLOCK_K, n_out + f0);
+                tma_load_2d_pair(st + (DUAL ? 2 : 1) * C::W_BYTES, &map_a, bar0, kb * BLOCK_K, t0);
+                issued = it + 1;
+            }
+        }
+        (void)issued;
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------- MMA issuer: one thread of the even CTA, for both
+        constexpr unsigned idesc = instr_desc_pair(TOK);
+        int it = 0, local = 0;
+        for (int tile = cluster_id; tile < tiles && !s_failed; tile += n_clusters, ++local) {
+            const int buf = local % C::NBUF;
+            if (!mbar_wait(&acc_empty_bar[buf], ((local / C::NBUF) & 1) ^ 1)) {
+                atomicCAS(&g_tc_error, 0, (6 << 16) | (int)blockIdx.x);
+                s_failed = 1;
+                break;
+            }
+            tc_fence_after();
+            const unsigned acc = tmem_base + buf * C::ACC_COLS;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % C::STAGES;
+                if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1)) {
+                    atomicCAS(&g_tc_error, 0, (7 << 16) | (int)blockIdx.x);
+                    s_failed = 1;
+                    break;
+                }
+                tc_fence_after();
+                const unsigned st = smem_u32(smem + s * C::STAGE_BYTES);
+                const unsigned long long w_desc = smem_desc(st);
+                const unsigned long long u_desc = smem_desc(st + C::W_BYTES);
+                const unsigned long long a_desc = smem_desc(st + (DUAL ? 2 : 1) * C::W_BYTES);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);
+                    const bool accumulate = (kb > 0) || (k > 0);
+                    tc_mma_pair(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
+                    if (DUAL) tc_mma_pair(acc + TOK, u_desc + adv, a_desc + adv, idesc, accumulate);
+                }
+                tc_commit_pair(&empty_bar[s]);       // frees the stage in both CTAs
+            }
+            if (s_failed) break;
+            tc_commit_pair(&acc_full_bar[buf]);      // the accumulators of both CTAs are complete
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue (in both CTAs): this CTA's 128 features
+        const int quad = warp & 3;
+        const unsigned acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
+        int local = 0;
+        for (int tile = cluster_id; tile < tiles; tile += n_clusters, ++local) {
+            const int buf = local % C::NBUF;
+            const int f0 = (tile % f_tiles) * (2 * BLOCK_F) + (int)rank * BLOCK_F, t0 = (tile / f_tiles) * TOK;
+            const int f = f0 + quad * 32 + lane;
+            bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local / C::NBUF) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0 && !s_failed) { atomicCAS(&g_tc_error, 0, (8 << 16) | (int)blockIdx.x); s_failed = 1; }
+                break;
+            }
+            tc_fence_after();
+            const float b = (bias != nullptr && f < n_out) ? bias[f] : 0.f;
+            const unsigned lane_addr = tmem_base + buf * C::ACC_COLS + ((unsigned)(quad * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < TOK; c += 16) {
+                if (t0 + c >= tokens) break;
+                float v[16], u[16];
+                tmem_ld16(lane_addr + c, v);
+                if (DUAL) tmem_ld16(lane_addr + TOK + c, u);
+                if (f < n_out) emit16<EPI>(out, v, u, b, f, t0 + c, tokens, ldo);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty0 + buf * 8);    // to the even CTA, from both
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // the peer no longer reads this CTA's shared memory or signals its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    }
+}
+
 // ---------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -493,6 +708,36 @@ int launch_tc_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const f
     return 1;
 }
 
+template <int TOK, int EPI>
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens, int n_out,
+                int k, int ldo, cudaStream_t stream) {
+    using C = PairCfg<TOK, EPI == EPI_SWIGLU>;
+    static bool configured = false;
+    if (!configured) {
+        NIB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<TOK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured = true;
+    }
+    const int tiles = ceil_div(n_out, 2 * BLOCK_F) * ceil_div(tokens, TOK);
+    int ctas = 2 * tiles, most = sm_count() & ~1;
+    if (ctas > most) ctas = most;
+    NIB_CUDA(launch_pdl(gemm_pair_kernel<TOK, EPI>, dim3(ctas), dim3(THREADS), (size_t)C::SMEM, stream, mw, ma, bias, out,
+                        tokens, n_out, k, ldo));
+    return 0;
+}
+
+template <int TOK>
+int launch_pair_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens,
+                    int n_out, int k, int ldo, cudaStream_t stream) {
+    switch (epi) {
+        case EPI_STORE: return launch_pair<TOK, EPI_STORE>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_ADD: return launch_pair<TOK, EPI_ADD>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_F32: return launch_pair<TOK, EPI_F32>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_SWIGLU: return launch_pair<TOK, EPI_SWIGLU>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+    }
+    nib_set_error("gemm (tensor cores, two SMs per tile): unknown epilogue %d", epi);
+    return 1;
+}
+
 }  // namespace
 
 // 1 if the tensor-core kernel takes these operands: K a multiple of 8 (16-byte rows) and 16-byte aligned bases.
@@ -584,4 +829,33 @@ NIB_API int nib_gemm_tc_splitk(const void* A, const void* W, const float* bias, 
 NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
                         int lda, int ldo, int epi, int tok_tile, cudaStream_t stream) {
     return nib_gemm_tc_splitk(A, W, bias, out, tokens, N, K, lda, ldo, epi, tok_tile, 1, nullptr, nullptr, 0, 0, stream);
+}
+
+// The same product by pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 features x tok_tile tokens
+// (128 or 256; 0 = chosen here). Meant for many tokens and wide outputs; no split of K.
+NIB_API int nib_gemm_tc_pair(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
+                             int lda, int ldo, int epi, int tok_tile, cudaStream_t stream) {
+    NIB_REQUIRE(tokens >= 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm (two SMs per tile): bad sizes tokens=%d N=%d K=%d", tokens, N, K);
+    NIB_REQUIRE(nib_gemm_tc_supported(A, W, K, lda), "gemm (two SMs per tile): K=%d / lda=%d must be multiples of 8 and bases 16-byte aligned", K, lda);
+    NIB_REQUIRE(epi != EPI_SWIGLU || bias == nullptr, "gemm (two SMs per tile): the swiglu epilogue takes no bias");
+    if (tokens == 0) return 0;
+    if (tok_tile == 0) tok_tile = tokens > 128 ? 256 : 128;
+    NIB_REQUIRE(tok_tile == 128 || tok_tile == 256, "gemm (two SMs per tile): token tile %d is not 128 or 256", tok_tile);
+    const long long w_rows = (epi == EPI_SWIGLU) ? 2LL * N : N;
+    CUtensorMap mw, ma;
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        MapKey key{W, w_rows, K, BLOCK_F};
+        auto it = g_weight_maps.find(key);
+        if (it == g_weight_maps.end()) {
+            if (make_map(&mw, W, w_rows, K, K, BLOCK_F)) return 1;
+            if (g_weight_maps.size() > 4096) g_weight_maps.clear();
+            g_weight_maps.emplace(key, mw);
+        } else {
+            mw = it->second;
+        }
+    }
+    if (make_map(&ma, A, tokens, K, lda, tok_tile / 2)) return 1;
+    if (tok_tile == 128) return launch_pair_epi<128>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+    return launch_pair_epi<256>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
 }

@@ -51,6 +51,7 @@ class Kernels:
         self.sm_count = 148
         self.smallm_cross = 0                  # tests: CTAs that split K in the small-M GEMM (0 = chosen)
         self.gemm_route = None                 # tests: "smallm" | "smallm_fused" | "tc" instead of the measured choice
+        self.pair_token_tile = 0               # tests: token tile of the two-SM GEMM (0 = chosen, 128, 256)
         self.tc_splits = 0                     # tests: work items along K per tile of the tcgen05 GEMM (0 = chosen, 1 = none)
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
@@ -64,7 +65,7 @@ class Kernels:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
-                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
+                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
                      "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
@@ -133,7 +134,7 @@ class Kernels:
         by reductions in memory, for every sum into the residual stream with a long K. The fused norm
         re-reads the 32-bit activations in every CTA, which pays only for few tokens and narrow outputs."""
         if self.gemm_route is not None:
-            return ("tc", False) if self.gemm_route == "tc" else ("smallm", has_norm and self.gemm_route == "smallm_fused")
+            return ("tc", False) if self.gemm_route in ("tc", "tc_pair") else ("smallm", has_norm and self.gemm_route == "smallm_fused")
         if self.smallm_ksplit or self.smallm_cross:
             return "smallm", has_norm
         weight_bytes = 2 * rows * k
@@ -147,6 +148,21 @@ class Kernels:
             small = m <= 16 and weight_bytes <= 32e6
         fuse = has_norm and small and epi != _EPI["swiglu"] and (m <= 8 or (m <= 16 and k <= 1024))
         return ("smallm" if small else "tc"), fuse
+
+    def _use_pair(self, m: int, rows: int, k: int, epi: int) -> bool:
+        """Whether pairs of SMs (cta_group::2, tiles of 256 features) take this product."""
+        if self.gemm_route is not None:
+            return self.gemm_route == "tc_pair"
+        if self.tc_token_tile or self.tc_splits or m < 256:
+            return False
+        # measured on B200 at the projection sizes of the 0.5B, 1.5B and 7B models, 512..4096 tokens: tiles
+        # of 256 features x 256 tokens on two SMs win once there are enough of them to fill the GPU; the
+        # fused gate/up form keeps both accumulators of 256 tokens in tensor memory without a second
+        # buffer, which pays only when K is long enough to hide the epilogue
+        if epi == _EPI["swiglu"]:
+            return k >= 2048
+        tiles = -(-rows // 256) * -(-m // 256)
+        return tiles >= 40
 
     def _gemm(self, a, w, bias32, out, m, n, k, epi):
         """bfloat16 goes to the small-M kernel or to the tcgen05 kernel (see ``_route``); shapes neither
@@ -172,6 +188,12 @@ class Kernels:
         if deferred is not None:
             a = deferred.materialize()
         if bf16 and self._lib.nib_gemm_tc_supported(_ptr(a), _ptr(w), c_int(k), c_int(a.stride(0))) == 1:
+            if self._use_pair(m, w.shape[0], k, epi):
+                self._check(self._lib.nib_gemm_tc_pair(
+                    _ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
+                    c_int(out.stride(0)), c_int(epi), c_int(self.pair_token_tile), self._stream()),
+                    "linear (tensor cores, two SMs per tile)")
+                return
             self.ensure_workspace(a.device)
             self._check(self._lib.nib_gemm_tc_splitk(
                 _ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),

@@ -323,6 +323,37 @@ def test_tensor_core_gemm_split_k(K, m, n, k, splits):
     assert K.gemm_tc_error() == 0
 
 
+@pytest.mark.parametrize("tile", [0, 128, 256])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 128), (300, 896, 896), (130, 1000, 344), (1, 256, 64), (700, 130, 72),
+                                   (2048, 1152, 896)])
+def test_tensor_core_gemm_on_pairs_of_sms(K, m, n, k, tile):
+    """tcgen05.mma.cta_group::2: tiles of 256 features on two SMs, each CTA holding half of the token tile;
+    features, tokens and K that do not fill a tile; all four epilogues; several tiles per cluster."""
+    dtype = torch.bfloat16
+    a, w = rnd((m, k), dtype, 170), rnd((n, k), dtype, 171, scale=0.05)
+    bias = rnd((n,), torch.float32, 172)
+    K.gemm_route, K.pair_token_tile = "tc_pair", tile
+    try:
+        out = torch.empty(m, n, dtype=dtype, device="cuda")
+        K.linear(a, w, bias, out, "store")
+        assert_close(out, _ref_linear_f64(a, w, bias), dtype, "pair store")
+        out32 = torch.empty(m, n, device="cuda")
+        K.linear(a, w, None, out32, "f32")
+        assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "pair f32")
+        res = rnd((m, n), torch.float32, 173)
+        acc = res.clone()
+        K.linear(a, w, bias, acc, "add")
+        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "pair add")
+        inter = n // 2
+        sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+        K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+        REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+        assert_close(sw, ref, dtype, "pair swiglu")
+    finally:
+        K.gemm_route, K.pair_token_tile = None, 0
+    assert K.gemm_tc_error() == 0
+
+
 def test_tensor_core_gemm_refuses_what_it_cannot_take(K):
     from nanoinfer_b200.csrc.lib import KernelError
     a, w = rnd((4, 20), torch.bfloat16, 80), rnd((6, 20), torch.bfloat16, 81)      # K = 20: rows are not 16-byte multiples
