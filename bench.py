@@ -15,6 +15,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import shutil
 import statistics
 import subprocess
 import sys
@@ -148,8 +149,11 @@ def run_ours(args) -> dict:
     max_batch = max(batch, 64)
     page = 16
     num_pages = max_batch * (-(-ctx // page) + 1) + 8
-    model = load_model(tmp, dtype="bfloat16", page_size=page, num_pages=num_pages, max_batch=max_batch,
-                       max_tokens_per_step=4096, cuda_graphs=not args.no_graphs)
+    try:
+        model = load_model(tmp, dtype="bfloat16", page_size=page, num_pages=num_pages, max_batch=max_batch,
+                           max_tokens_per_step=4096, cuda_graphs=not args.no_graphs)
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)      # the weights are on the device now; the folder can be gigabytes
     engine, ops = model.engine, model.engine.rt.ops
     print(f"[bench] model ready in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
 

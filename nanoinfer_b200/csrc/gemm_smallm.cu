@@ -276,7 +276,7 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
             if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
             else if (EPI == EPI_ADD) ((float*)out)[o] = res[n][e] + x;
             else if (EPI == EPI_F32) ((float*)out)[o] = x;
-            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * (acc[ACCS - 1][n][e] * scale));
+            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(__fdividef(x, 1.0f + __expf(-x)) * (acc[ACCS - 1][n][e] * scale));
         }
 }
 

@@ -164,7 +164,7 @@ __device__ __forceinline__ void emit16(void* __restrict__ out, const float (&v)[
             const float x = v[j] + b;
             if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
             else if (EPI == EPI_F32) ((float*)out)[o] = x;
-            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x / (1.0f + __expf(-x)) * u[j]);
+            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(__fdividef(x, 1.0f + __expf(-x)) * u[j]);
         }
     }
 }
@@ -388,12 +388,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------- two SMs on one tile
-// The same product with tcgen05.mma.cta_group::2: a cluster of two CTAs owns a tile of 256 output
-// features x TOK tokens. Each CTA loads its own 128 weight rows and HALF of the token tile; the
-// instruction, issued by one thread of the even CTA, reads the token operand from both CTAs' shared
-// memory and accumulates 128 features in each CTA's tensor memory. Per CTA and step of K that is 16 KB of
-// weights + TOK/2 x 128 bytes of tokens for 128 x TOK x 64 multiply-adds: half the token traffic of the
-// one-CTA kernel from L2 and from shared memory, which is what bounds the wide products of a prefill.
+// The product for many tokens (a prefill) with tcgen05.mma.cta_group::2, in the other orientation: the
+// TOKENS are the M side (a cluster of two CTAs owns 256 of them, 128 TMEM lanes in each CTA), the output
+// FEATURES are the N side (NT = 128 or 256 per tile). Each CTA loads its own 128 token rows and HALF of
+// the weight rows of the tile; the instruction, issued by one thread of the even CTA, reads the weight
+// operand from both CTAs' shared memory. Per CTA and step of K that is 16 KB of activations + NT/2 x 128
+// bytes of weights for 128 x NT x 64 multiply-adds: half the traffic per flop of the one-CTA kernel, from
+// L2 and from shared memory. A thread of the epilogue owns one token row and reads consecutive features
+// from its TMEM lane, so it stores 32 contiguous bytes at a time (bfloat16), adds into the residual stream
+// with 16-byte reductions, and takes the bias from broadcast loads.
+//
+// Fused SiLU(gate)*up: the 256 columns of a tile are the gate rows (loaded by the even CTA) and the up
+// rows (loaded by the odd CTA) of the same 128 features, so every thread finds both values of a feature in
+// its own lane.
 //
 // Who signals whom: both CTAs' TMA copies complete on the EVEN CTA's full barrier (it expects the bytes of
 // both); tcgen05.commit multicasts to the empty barrier of the stage and to the accumulator-full barrier in
@@ -442,28 +449,90 @@ __device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __host__ __device__ constexpr unsigned instr_desc_pair(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
 }
 
-template <int TOK, bool DUAL> struct PairCfg {
-    static constexpr int W_BYTES = BLOCK_F * BLOCK_K * 2;                 // this CTA's 128 weight rows
-    static constexpr int A_BYTES = (TOK / 2) * BLOCK_K * 2;               // this CTA's half of the token tile
-    static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * W_BYTES + A_BYTES;
+constexpr int PAIR_M = 256;      // tokens per cluster tile
+constexpr int PAIR_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps: two per TMEM lane quadrant, half of the columns each
+
+template <int NT> struct PairCfg {
+    static constexpr int M_BYTES = BLOCK_F * BLOCK_K * 2;                 // this CTA's 128 token rows
+    static constexpr int N_BYTES = (NT / 2) * BLOCK_K * 2;                // this CTA's half of the weight rows
+    static constexpr int STAGE_BYTES = M_BYTES + N_BYTES;
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
-    static constexpr int ACC_COLS = (DUAL ? 2 : 1) * TOK;
-    static constexpr int NBUF = 2 * ACC_COLS <= 512 ? 2 : 1;              // accumulator buffers in the 512 columns
-    static constexpr int TMEM_COLS = tmem_cols(NBUF * ACC_COLS);
-    static_assert(ACC_COLS <= 512, "the accumulators must fit the 512 TMEM columns");
+    static constexpr int TMEM_COLS = tmem_cols(2 * NT);                   // two accumulator buffers
+    static_assert(2 * NT <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 };
 
-template <int TOK, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                 const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo) {
-    constexpr bool DUAL = (EPI == EPI_SWIGLU);
-    using C = PairCfg<TOK, DUAL>;
+// 16 consecutive features (first .. first+15) of one token row. v: accumulators (for SWIGLU the gate), u: the up values.
+template <int EPI>
+__device__ __forceinline__ void emit_row16(void* __restrict__ out, const float (&v)[16], const float (&u)[16],
+                                           const float* __restrict__ bias, size_t row_off, int first, int n_out, bool vec_ok) {
+    float x[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) x[j] = v[j];
+    if (bias != nullptr) {
+        if (first + 16 <= n_out) {          // 16 features start on a 64-byte boundary of the bias
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(bias + first) + j);
+                x[4 * j] += b.x; x[4 * j + 1] += b.y; x[4 * j + 2] += b.z; x[4 * j + 3] += b.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (first + j < n_out) x[j] += __ldg(bias + first + j);
+        }
+    }
+    if (EPI == EPI_SWIGLU) {
+        // silu(g) * u with the fast exponential and division (2 ulp): the result is rounded to bfloat16
+#pragma unroll
+        for (int j = 0; j < 16; ++j) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j])) * u[j];
+    }
+    if (vec_ok && first + 16 <= n_out) {
+        if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
+            uint4 p0, p1;
+            __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&p0);
+            __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&p1);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { h0[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]); h1[j] = __floats2bfloat162_rn(x[8 + 2 * j], x[9 + 2 * j]); }
+            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)out + row_off + first);
+            dst[0] = p0;
+            dst[1] = p1;
+        } else if (EPI == EPI_F32) {
+            float4* dst = reinterpret_cast<float4*>((float*)out + row_off + first);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        } else {
+            float* dst = (float*)out + row_off + first;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red_add_v4(dst + 4 * j, x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (first + j >= n_out) break;
+        const size_t o = row_off + first + j;
+        if (EPI == EPI_STORE || EPI == EPI_SWIGLU) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x[j]);
+        else if (EPI == EPI_F32) ((float*)out)[o] = x[j];
+        else atomicAdd((float*)out + o, x[j]);
+    }
+}
+
+// map_m: activations [tokens, K], box 64 x 128 rows; map_n: weights [rows, K], box 64 x NT/2 rows.
+template <int NT, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
+                 const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo, int vec_ok) {
+    constexpr bool GU = (EPI == EPI_SWIGLU);                       // the tile's columns: gate rows | up rows of NT/2 features
+    constexpr int FEAT = GU ? NT / 2 : NT;                         // output features per tile
+    using C = PairCfg<NT>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -476,17 +545,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_ctarank();                       // 0: issues the MMAs and owns the shared barriers
-    const int f_tiles = (n_out + 2 * BLOCK_F - 1) / (2 * BLOCK_F), t_tiles = (tokens + TOK - 1) / TOK;
-    const int tiles = f_tiles * t_tiles;
+    const int n_tiles = (n_out + FEAT - 1) / FEAT, m_tiles = (tokens + PAIR_M - 1) / PAIR_M;
+    const int tiles = n_tiles * m_tiles;                           // feature tiles fastest
     const int k_blocks = (k_dim + BLOCK_K - 1) / BLOCK_K;
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
         s_failed = 0;
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_m) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_n) : "memory");
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full_bar[b], 1); mbar_init(&acc_empty_bar[b], 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full_bar[b], 1); mbar_init(&acc_empty_bar[b], 16); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -503,11 +572,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     pdl_wait();
 
     if (warp == 0 && lane == 0) {
-        // ---------------- producer (in both CTAs): this CTA's weight rows and its half of the tokens
-        int it = 0, issued = 0;
+        // ---------------- producer (in both CTAs): this CTA's 128 token rows and its half of the weight rows
+        int it = 0;
         for (int tile = cluster_id; tile < tiles && !s_failed; tile += n_clusters) {
-            const int f0 = (tile % f_tiles) * (2 * BLOCK_F) + (int)rank * BLOCK_F;
-            const int t0 = (tile / f_tiles) * TOK + (int)rank * (TOK / 2);
+            const int f0 = (tile % n_tiles) * FEAT, t0 = (tile / n_tiles) * PAIR_M + (int)rank * BLOCK_F;
+            // weight rows: half of the tile's features, or (gate/up) the gate rows here and the up rows in the peer
+            const int w0 = GU ? f0 + (int)rank * n_out : f0 + (int)rank * (NT / 2);
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1)) {
@@ -518,26 +588,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 unsigned char* st = smem + s * C::STAGE_BYTES;
                 const unsigned bar0 = map_to_cta(smem_u32(&full_bar[s]), 0);
                 if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
-                tma_load_2d_pair(st, &map_w, bar0, kb * BLOCK_K, f0);
-                if (DUAL) tma_load_2d_pair(st + C::W_BYTES, &map_w, bar0, kb * BLOCK_K, n_out + f0);
-                tma_load_2d_pair(st + (DUAL ? 2 : 1) * C::W_BYTES, &map_a, bar0, kb * BLOCK_K, t0);
-                issued = it + 1;
+                tma_load_2d_pair(st, &map_m, bar0, kb * BLOCK_K, t0);
+                tma_load_2d_pair(st + C::M_BYTES, &map_n, bar0, kb * BLOCK_K, w0);
             }
         }
-        (void)issued;
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ---------------- MMA issuer: one thread of the even CTA, for both
-        constexpr unsigned idesc = instr_desc_pair(TOK);
+        constexpr unsigned idesc = instr_desc_pair(NT);
         int it = 0, local = 0;
         for (int tile = cluster_id; tile < tiles && !s_failed; tile += n_clusters, ++local) {
-            const int buf = local % C::NBUF;
-            if (!mbar_wait(&acc_empty_bar[buf], ((local / C::NBUF) & 1) ^ 1)) {
+            const int buf = local & 1;
+            if (!mbar_wait(&acc_empty_bar[buf], ((local >> 1) & 1) ^ 1)) {
                 atomicCAS(&g_tc_error, 0, (6 << 16) | (int)blockIdx.x);
                 s_failed = 1;
                 break;
             }
             tc_fence_after();
-            const unsigned acc = tmem_base + buf * C::ACC_COLS;
+            const unsigned acc = tmem_base + buf * NT;
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1)) {
@@ -547,15 +614,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 }
                 tc_fence_after();
                 const unsigned st = smem_u32(smem + s * C::STAGE_BYTES);
-                const unsigned long long w_desc = smem_desc(st);
-                const unsigned long long u_desc = smem_desc(st + C::W_BYTES);
-                const unsigned long long a_desc = smem_desc(st + (DUAL ? 2 : 1) * C::W_BYTES);
+                const unsigned long long m_desc = smem_desc(st);
+                const unsigned long long n_desc = smem_desc(st + C::M_BYTES);
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);
-                    const bool accumulate = (kb > 0) || (k > 0);
-                    tc_mma_pair(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
-                    if (DUAL) tc_mma_pair(acc + TOK, u_desc + adv, a_desc + adv, idesc, accumulate);
+                    tc_mma_pair(acc, m_desc + adv, n_desc + adv, idesc, (kb > 0) || (k > 0));
                 }
                 tc_commit_pair(&empty_bar[s]);       // frees the stage in both CTAs
             }
@@ -563,30 +627,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             tc_commit_pair(&acc_full_bar[buf]);      // the accumulators of both CTAs are complete
         }
     } else if (warp >= 2) {
-        // ---------------- epilogue (in both CTAs): this CTA's 128 features
+        // ---------------- epilogue (in both CTAs): one token row per thread, half of the tile's features per warp
         const int quad = warp & 3;
+        const int c_begin = ((warp - 2) >> 2) * (FEAT / 2), c_end = c_begin + FEAT / 2;
         const unsigned acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
         int local = 0;
         for (int tile = cluster_id; tile < tiles; tile += n_clusters, ++local) {
-            const int buf = local % C::NBUF;
-            const int f0 = (tile % f_tiles) * (2 * BLOCK_F) + (int)rank * BLOCK_F, t0 = (tile / f_tiles) * TOK;
-            const int f = f0 + quad * 32 + lane;
-            bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local / C::NBUF) & 1);
+            const int buf = local & 1;
+            const int f0 = (tile % n_tiles) * FEAT;
+            const int t = (tile / n_tiles) * PAIR_M + (int)rank * BLOCK_F + quad * 32 + lane;
+            bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 if (lane == 0 && !s_failed) { atomicCAS(&g_tc_error, 0, (8 << 16) | (int)blockIdx.x); s_failed = 1; }
                 break;
             }
             tc_fence_after();
-            const float b = (bias != nullptr && f < n_out) ? bias[f] : 0.f;
-            const unsigned lane_addr = tmem_base + buf * C::ACC_COLS + ((unsigned)(quad * 32) << 16);
+            const unsigned lane_addr = tmem_base + buf * NT + ((unsigned)(quad * 32) << 16);
+            const size_t row_off = (size_t)t * ldo;
 #pragma unroll 1
-            for (int c = 0; c < TOK; c += 16) {
-                if (t0 + c >= tokens) break;
+            for (int c = c_begin; c < c_end; c += 16) {
+                if (f0 + c >= n_out) break;
                 float v[16], u[16];
                 tmem_ld16(lane_addr + c, v);
-                if (DUAL) tmem_ld16(lane_addr + TOK + c, u);
-                if (f < n_out) emit16<EPI>(out, v, u, b, f, t0 + c, tokens, ldo);
+                if (GU) tmem_ld16(lane_addr + FEAT + c, u);
+                if (t < tokens) emit_row16<EPI>(out, v, u, bias, row_off, f0 + c, n_out, vec_ok != 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -708,31 +773,32 @@ int launch_tc_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const f
     return 1;
 }
 
-template <int TOK, int EPI>
-int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens, int n_out,
-                int k, int ldo, cudaStream_t stream) {
-    using C = PairCfg<TOK, EPI == EPI_SWIGLU>;
+template <int NT, int EPI>
+int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, const float* bias, void* out, int tokens, int n_out,
+                int k, int ldo, int vec_ok, cudaStream_t stream) {
+    using C = PairCfg<NT>;
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<TOK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
-    const int tiles = ceil_div(n_out, 2 * BLOCK_F) * ceil_div(tokens, TOK);
+    const int feat = EPI == EPI_SWIGLU ? NT / 2 : NT;
+    const int tiles = ceil_div(n_out, feat) * ceil_div(tokens, PAIR_M);
     int ctas = 2 * tiles, most = sm_count() & ~1;
     if (ctas > most) ctas = most;
-    NIB_CUDA(launch_pdl(gemm_pair_kernel<TOK, EPI>, dim3(ctas), dim3(THREADS), (size_t)C::SMEM, stream, mw, ma, bias, out,
-                        tokens, n_out, k, ldo));
+    NIB_CUDA(launch_pdl(gemm_pair_kernel<NT, EPI>, dim3(ctas), dim3(PAIR_THREADS), (size_t)C::SMEM, stream, mm, mn, bias, out,
+                        tokens, n_out, k, ldo, vec_ok));
     return 0;
 }
 
-template <int TOK>
-int launch_pair_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens,
-                    int n_out, int k, int ldo, cudaStream_t stream) {
+template <int NT>
+int launch_pair_epi(int epi, const CUtensorMap& mm, const CUtensorMap& mn, const float* bias, void* out, int tokens,
+                    int n_out, int k, int ldo, int vec_ok, cudaStream_t stream) {
     switch (epi) {
-        case EPI_STORE: return launch_pair<TOK, EPI_STORE>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
-        case EPI_ADD: return launch_pair<TOK, EPI_ADD>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
-        case EPI_F32: return launch_pair<TOK, EPI_F32>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
-        case EPI_SWIGLU: return launch_pair<TOK, EPI_SWIGLU>(mw, ma, bias, out, tokens, n_out, k, ldo, stream);
+        case EPI_STORE: return launch_pair<NT, EPI_STORE>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
+        case EPI_ADD: return launch_pair<NT, EPI_ADD>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
+        case EPI_F32: return launch_pair<NT, EPI_F32>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
+        case EPI_SWIGLU: return launch_pair<NT, EPI_SWIGLU>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
     }
     nib_set_error("gemm (tensor cores, two SMs per tile): unknown epilogue %d", epi);
     return 1;
@@ -831,31 +897,36 @@ NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* o
     return nib_gemm_tc_splitk(A, W, bias, out, tokens, N, K, lda, ldo, epi, tok_tile, 1, nullptr, nullptr, 0, 0, stream);
 }
 
-// The same product by pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 features x tok_tile tokens
-// (128 or 256; 0 = chosen here). Meant for many tokens and wide outputs; no split of K.
+// The product for many tokens by pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 tokens x n_tile
+// output features (128 or 256; 0 = 256). No split of K.
 NIB_API int nib_gemm_tc_pair(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
-                             int lda, int ldo, int epi, int tok_tile, cudaStream_t stream) {
+                             int lda, int ldo, int epi, int n_tile, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm (two SMs per tile): bad sizes tokens=%d N=%d K=%d", tokens, N, K);
     NIB_REQUIRE(nib_gemm_tc_supported(A, W, K, lda), "gemm (two SMs per tile): K=%d / lda=%d must be multiples of 8 and bases 16-byte aligned", K, lda);
     NIB_REQUIRE(epi != EPI_SWIGLU || bias == nullptr, "gemm (two SMs per tile): the swiglu epilogue takes no bias");
+    NIB_REQUIRE(epi >= EPI_STORE && epi <= EPI_SWIGLU, "gemm (two SMs per tile): unknown epilogue %d", epi);
+    NIB_REQUIRE(((uintptr_t)bias & 15) == 0, "gemm (two SMs per tile): the bias must be 16-byte aligned");
     if (tokens == 0) return 0;
-    if (tok_tile == 0) tok_tile = tokens > 128 ? 256 : 128;
-    NIB_REQUIRE(tok_tile == 128 || tok_tile == 256, "gemm (two SMs per tile): token tile %d is not 128 or 256", tok_tile);
+    if (n_tile == 0) n_tile = 256;      // measured: the instruction of 128 columns runs at about half the rate, whatever the grid
+    NIB_REQUIRE(n_tile == 128 || n_tile == 256, "gemm (two SMs per tile): feature tile %d is not 128 or 256", n_tile);
+    // 16-byte stores and reductions need rows of the output that start on 16 bytes
+    const int elem = (epi == EPI_STORE || epi == EPI_SWIGLU) ? 2 : 4;
+    const int vec_ok = (((uintptr_t)out & 15) == 0 && ((long long)ldo * elem) % 16 == 0) ? 1 : 0;
     const long long w_rows = (epi == EPI_SWIGLU) ? 2LL * N : N;
-    CUtensorMap mw, ma;
+    CUtensorMap mm, mn;
     {
         std::lock_guard<std::mutex> lock(g_map_mutex);
-        MapKey key{W, w_rows, K, BLOCK_F};
+        MapKey key{W, w_rows, K, n_tile / 2};
         auto it = g_weight_maps.find(key);
         if (it == g_weight_maps.end()) {
-            if (make_map(&mw, W, w_rows, K, K, BLOCK_F)) return 1;
+            if (make_map(&mn, W, w_rows, K, K, n_tile / 2)) return 1;
             if (g_weight_maps.size() > 4096) g_weight_maps.clear();
-            g_weight_maps.emplace(key, mw);
+            g_weight_maps.emplace(key, mn);
         } else {
-            mw = it->second;
+            mn = it->second;
         }
     }
-    if (make_map(&ma, A, tokens, K, lda, tok_tile / 2)) return 1;
-    if (tok_tile == 128) return launch_pair_epi<128>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
-    return launch_pair_epi<256>(epi, mw, ma, bias, out, tokens, N, K, ldo, stream);
+    if (make_map(&mm, A, tokens, K, lda, BLOCK_F)) return 1;
+    if (n_tile == 128) return launch_pair_epi<128>(epi, mm, mn, bias, out, tokens, N, K, ldo, vec_ok, stream);
+    return launch_pair_epi<256>(epi, mm, mn, bias, out, tokens, N, K, ldo, vec_ok, stream);
 }

@@ -51,7 +51,7 @@ class Kernels:
         self.sm_count = 148
         self.smallm_cross = 0                  # tests: CTAs that split K in the small-M GEMM (0 = chosen)
         self.gemm_route = None                 # tests: "smallm" | "smallm_fused" | "tc" instead of the measured choice
-        self.pair_token_tile = 0               # tests: token tile of the two-SM GEMM (0 = chosen, 128, 256)
+        self.pair_n_tile = 0               # tests: feature tile of the two-SM GEMM (0 = chosen, 128, 256)
         self.tc_splits = 0                     # tests: work items along K per tile of the tcgen05 GEMM (0 = chosen, 1 = none)
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
@@ -156,13 +156,12 @@ class Kernels:
         if self.tc_token_tile or self.tc_splits or m < 256:
             return False
         # measured on B200 at the projection sizes of the 0.5B, 1.5B and 7B models, 512..4096 tokens: tiles
-        # of 256 features x 256 tokens on two SMs win once there are enough of them to fill the GPU; the
-        # fused gate/up form keeps both accumulators of 256 tokens in tensor memory without a second
-        # buffer, which pays only when K is long enough to hide the epilogue
+        # of 256 tokens x 256 features on two SMs win once there are enough of them to fill the GPU; the
+        # fused gate/up form (gate rows in one CTA, up rows in the other) wins from 256 tokens on
         if epi == _EPI["swiglu"]:
-            return k >= 2048
+            return True
         tiles = -(-rows // 256) * -(-m // 256)
-        return tiles >= 40
+        return tiles >= 48
 
     def _gemm(self, a, w, bias32, out, m, n, k, epi):
         """bfloat16 goes to the small-M kernel or to the tcgen05 kernel (see ``_route``); shapes neither
@@ -191,7 +190,7 @@ class Kernels:
             if self._use_pair(m, w.shape[0], k, epi):
                 self._check(self._lib.nib_gemm_tc_pair(
                     _ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
-                    c_int(out.stride(0)), c_int(epi), c_int(self.pair_token_tile), self._stream()),
+                    c_int(out.stride(0)), c_int(epi), c_int(self.pair_n_tile), self._stream()),
                     "linear (tensor cores, two SMs per tile)")
                 return
             self.ensure_workspace(a.device)

@@ -325,14 +325,15 @@ def test_tensor_core_gemm_split_k(K, m, n, k, splits):
 
 @pytest.mark.parametrize("tile", [0, 128, 256])
 @pytest.mark.parametrize("m,n,k", [(256, 512, 128), (300, 896, 896), (130, 1000, 344), (1, 256, 64), (700, 130, 72),
-                                   (2048, 1152, 896)])
+                                   (2048, 1152, 896), (515, 311, 200), (4096, 4864, 896)])
 def test_tensor_core_gemm_on_pairs_of_sms(K, m, n, k, tile):
-    """tcgen05.mma.cta_group::2: tiles of 256 features on two SMs, each CTA holding half of the token tile;
-    features, tokens and K that do not fill a tile; all four epilogues; several tiles per cluster."""
+    """tcgen05.mma.cta_group::2: tiles of 256 tokens on two SMs, each CTA holding half of the tile's weight
+    rows; features, tokens and K that do not fill a tile (and rows of the output that rule out 16-byte
+    stores); all four epilogues; several tiles per cluster."""
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 170), rnd((n, k), dtype, 171, scale=0.05)
     bias = rnd((n,), torch.float32, 172)
-    K.gemm_route, K.pair_token_tile = "tc_pair", tile
+    K.gemm_route, K.pair_n_tile = "tc_pair", tile
     try:
         out = torch.empty(m, n, dtype=dtype, device="cuda")
         K.linear(a, w, bias, out, "store")
@@ -350,7 +351,7 @@ def test_tensor_core_gemm_on_pairs_of_sms(K, m, n, k, tile):
         REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
         assert_close(sw, ref, dtype, "pair swiglu")
     finally:
-        K.gemm_route, K.pair_token_tile = None, 0
+        K.gemm_route, K.pair_n_tile = None, 0
     assert K.gemm_tc_error() == 0
 
 
