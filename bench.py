@@ -201,7 +201,7 @@ def run_ours(args) -> dict:
     # ---- prefill of 2,048 tokens ----------------------------------------------------------
     t_pre = args.prefill_tokens
     pre_ms = []
-    for i in range((3 + 3) if args.only != "decode" else 0):
+    for i in range((3 + 7) if args.only != "decode" else 0):
         rc = engine.open(f"p{i}")
         ids = rng.integers(0, vocab, t_pre).tolist()
         torch.cuda.synchronize()

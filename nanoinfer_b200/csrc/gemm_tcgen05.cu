@@ -529,7 +529,8 @@ __device__ __forceinline__ void emit_row16(void* __restrict__ out, const float (
 template <int NT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
-                 const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo, int vec_ok) {
+                 const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo, int vec_ok,
+                 int splits, int kb_per_split) {
     constexpr bool GU = (EPI == EPI_SWIGLU);                       // the tile's columns: gate rows | up rows of NT/2 features
     constexpr int FEAT = GU ? NT / 2 : NT;                         // output features per tile
     using C = PairCfg<NT>;
@@ -546,7 +547,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_ctarank();                       // 0: issues the MMAs and owns the shared barriers
     const int n_tiles = (n_out + FEAT - 1) / FEAT, m_tiles = (tokens + PAIR_M - 1) / PAIR_M;
-    const int tiles = n_tiles * m_tiles;                           // feature tiles fastest
+    // work item = (tile, split of K); splits fastest, feature tiles next. More than one split only with the
+    // ADD epilogue: every item adds its partial sums into the output (reductions in memory).
+    const int items = n_tiles * m_tiles * splits;
     const int k_blocks = (k_dim + BLOCK_K - 1) / BLOCK_K;
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
@@ -574,11 +577,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
     if (warp == 0 && lane == 0) {
         // ---------------- producer (in both CTAs): this CTA's 128 token rows and its half of the weight rows
         int it = 0;
-        for (int tile = cluster_id; tile < tiles && !s_failed; tile += n_clusters) {
+        for (int item = cluster_id; item < items && !s_failed; item += n_clusters) {
+            const int tile = item / splits, split = item - tile * splits;
             const int f0 = (tile % n_tiles) * FEAT, t0 = (tile / n_tiles) * PAIR_M + (int)rank * BLOCK_F;
             // weight rows: half of the tile's features, or (gate/up) the gate rows here and the up rows in the peer
             const int w0 = GU ? f0 + (int)rank * n_out : f0 + (int)rank * (NT / 2);
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int kb_end = min(k_blocks, (split + 1) * kb_per_split);
+            for (int kb = split * kb_per_split; kb < kb_end; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&empty_bar[s], ((it / C::STAGES) & 1) ^ 1)) {
                     atomicCAS(&g_tc_error, 0, (5 << 16) | (int)blockIdx.x);
@@ -596,8 +601,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
         // ---------------- MMA issuer: one thread of the even CTA, for both
         constexpr unsigned idesc = instr_desc_pair(NT);
         int it = 0, local = 0;
-        for (int tile = cluster_id; tile < tiles && !s_failed; tile += n_clusters, ++local) {
+        for (int item = cluster_id; item < items && !s_failed; item += n_clusters, ++local) {
             const int buf = local & 1;
+            const int split = item % splits;
+            const int kb_begin = split * kb_per_split, kb_end = min(k_blocks, kb_begin + kb_per_split);
             if (!mbar_wait(&acc_empty_bar[buf], ((local >> 1) & 1) ^ 1)) {
                 atomicCAS(&g_tc_error, 0, (6 << 16) | (int)blockIdx.x);
                 s_failed = 1;
@@ -605,7 +612,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
             }
             tc_fence_after();
             const unsigned acc = tmem_base + buf * NT;
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                 const int s = it % C::STAGES;
                 if (!mbar_wait(&full_bar[s], (it / C::STAGES) & 1)) {
                     atomicCAS(&g_tc_error, 0, (7 << 16) | (int)blockIdx.x);
@@ -619,7 +626,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);
-                    tc_mma_pair(acc, m_desc + adv, n_desc + adv, idesc, (kb > 0) || (k > 0));
+                    tc_mma_pair(acc, m_desc + adv, n_desc + adv, idesc, (kb > kb_begin) || (k > 0));
                 }
                 tc_commit_pair(&empty_bar[s]);       // frees the stage in both CTAs
             }
@@ -632,8 +639,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
         const int c_begin = ((warp - 2) >> 2) * (FEAT / 2), c_end = c_begin + FEAT / 2;
         const unsigned acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
         int local = 0;
-        for (int tile = cluster_id; tile < tiles; tile += n_clusters, ++local) {
+        for (int item = cluster_id; item < items; item += n_clusters, ++local) {
             const int buf = local & 1;
+            const int tile = item / splits;
+            const float* item_bias = (item - tile * splits == 0) ? bias : nullptr;     // the bias is added once
             const int f0 = (tile % n_tiles) * FEAT;
             const int t = (tile / n_tiles) * PAIR_M + (int)rank * BLOCK_F + quad * 32 + lane;
             bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
@@ -651,7 +660,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
                 float v[16], u[16];
                 tmem_ld16(lane_addr + c, v);
                 if (GU) tmem_ld16(lane_addr + FEAT + c, u);
-                if (t < tokens) emit_row16<EPI>(out, v, u, bias, row_off, f0 + c, n_out, vec_ok != 0);
+                if (t < tokens) emit_row16<EPI>(out, v, u, item_bias, row_off, f0 + c, n_out, vec_ok != 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -775,7 +784,7 @@ int launch_tc_epi(int epi, const CUtensorMap& mw, const CUtensorMap& ma, const f
 
 template <int NT, int EPI>
 int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, const float* bias, void* out, int tokens, int n_out,
-                int k, int ldo, int vec_ok, cudaStream_t stream) {
+                int k, int ldo, int vec_ok, int splits, cudaStream_t stream) {
     using C = PairCfg<NT>;
     static bool configured = false;
     if (!configured) {
@@ -784,21 +793,26 @@ int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, const float* bias,
     }
     const int feat = EPI == EPI_SWIGLU ? NT / 2 : NT;
     const int tiles = ceil_div(n_out, feat) * ceil_div(tokens, PAIR_M);
-    int ctas = 2 * tiles, most = sm_count() & ~1;
+    const int k_blocks = ceil_div(k, BLOCK_K);
+    if (EPI != EPI_ADD || splits < 1) splits = 1;
+    if (splits > k_blocks) splits = k_blocks;
+    const int kb_per_split = ceil_div(k_blocks, splits);
+    splits = ceil_div(k_blocks, kb_per_split);
+    int ctas = 2 * tiles * splits, most = sm_count() & ~1;
     if (ctas > most) ctas = most;
     NIB_CUDA(launch_pdl(gemm_pair_kernel<NT, EPI>, dim3(ctas), dim3(PAIR_THREADS), (size_t)C::SMEM, stream, mm, mn, bias, out,
-                        tokens, n_out, k, ldo, vec_ok));
+                        tokens, n_out, k, ldo, vec_ok, splits, kb_per_split));
     return 0;
 }
 
 template <int NT>
 int launch_pair_epi(int epi, const CUtensorMap& mm, const CUtensorMap& mn, const float* bias, void* out, int tokens,
-                    int n_out, int k, int ldo, int vec_ok, cudaStream_t stream) {
+                    int n_out, int k, int ldo, int vec_ok, int splits, cudaStream_t stream) {
     switch (epi) {
-        case EPI_STORE: return launch_pair<NT, EPI_STORE>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
-        case EPI_ADD: return launch_pair<NT, EPI_ADD>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
-        case EPI_F32: return launch_pair<NT, EPI_F32>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
-        case EPI_SWIGLU: return launch_pair<NT, EPI_SWIGLU>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, stream);
+        case EPI_STORE: return launch_pair<NT, EPI_STORE>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, splits, stream);
+        case EPI_ADD: return launch_pair<NT, EPI_ADD>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, splits, stream);
+        case EPI_F32: return launch_pair<NT, EPI_F32>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, splits, stream);
+        case EPI_SWIGLU: return launch_pair<NT, EPI_SWIGLU>(mm, mn, bias, out, tokens, n_out, k, ldo, vec_ok, splits, stream);
     }
     nib_set_error("gemm (tensor cores, two SMs per tile): unknown epilogue %d", epi);
     return 1;
@@ -898,9 +912,10 @@ NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* o
 }
 
 // The product for many tokens by pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 tokens x n_tile
-// output features (128 or 256; 0 = 256). No split of K.
+// output features (128 or 256; 0 = 256). splits: work items along K per tile, for the ADD epilogue only
+// (0 = chosen here: enough to give every pair of SMs an item, at least 8 blocks of K each; 1 = none).
 NIB_API int nib_gemm_tc_pair(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
-                             int lda, int ldo, int epi, int n_tile, cudaStream_t stream) {
+                             int lda, int ldo, int epi, int n_tile, int splits, cudaStream_t stream) {
     NIB_REQUIRE(tokens >= 0 && N > 0 && K > 0 && lda >= K && ldo >= N, "gemm (two SMs per tile): bad sizes tokens=%d N=%d K=%d", tokens, N, K);
     NIB_REQUIRE(nib_gemm_tc_supported(A, W, K, lda), "gemm (two SMs per tile): K=%d / lda=%d must be multiples of 8 and bases 16-byte aligned", K, lda);
     NIB_REQUIRE(epi != EPI_SWIGLU || bias == nullptr, "gemm (two SMs per tile): the swiglu epilogue takes no bias");
@@ -927,6 +942,17 @@ NIB_API int nib_gemm_tc_pair(const void* A, const void* W, const float* bias, vo
         }
     }
     if (make_map(&mm, A, tokens, K, lda, BLOCK_F)) return 1;
-    if (n_tile == 128) return launch_pair_epi<128>(epi, mm, mn, bias, out, tokens, N, K, ldo, vec_ok, stream);
-    return launch_pair_epi<256>(epi, mm, mn, bias, out, tokens, N, K, ldo, vec_ok, stream);
+    NIB_REQUIRE(splits >= 0, "gemm (two SMs per tile): splits=%d", splits);
+    if (splits == 0) {
+        const int tiles = ceil_div(N, n_tile) * ceil_div(tokens, PAIR_M), clusters = sm_count() / 2;
+        splits = 1;
+        if (epi == EPI_ADD && tiles < clusters) {
+            splits = clusters / tiles;
+            const int most = ceil_div(K, BLOCK_K) / 8;
+            if (splits > most) splits = most;
+            if (splits < 1) splits = 1;
+        }
+    }
+    if (n_tile == 128) return launch_pair_epi<128>(epi, mm, mn, bias, out, tokens, N, K, ldo, vec_ok, splits, stream);
+    return launch_pair_epi<256>(epi, mm, mn, bias, out, tokens, N, K, ldo, vec_ok, splits, stream);
 }

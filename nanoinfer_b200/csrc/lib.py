@@ -155,6 +155,10 @@ class Kernels:
             return self.gemm_route == "tc_pair"
         if self.tc_token_tile or self.tc_splits or m < 256:
             return False
+        if epi == _EPI["add"]:      # with K split over pairs of SMs (at least 8 blocks of 64 per item)
+            tiles = -(-rows // 256) * -(-m // 256)
+            splits = max(1, min(74 // tiles, (k // 64) // 8)) if tiles < 74 else 1
+            return tiles * splits >= 48
         # measured on B200 at the projection sizes of the 0.5B, 1.5B and 7B models, 512..4096 tokens: tiles
         # of 256 tokens x 256 features on two SMs win once there are enough of them to fill the GPU; the
         # fused gate/up form (gate rows in one CTA, up rows in the other) wins from 256 tokens on
@@ -190,7 +194,7 @@ class Kernels:
             if self._use_pair(m, w.shape[0], k, epi):
                 self._check(self._lib.nib_gemm_tc_pair(
                     _ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
-                    c_int(out.stride(0)), c_int(epi), c_int(self.pair_n_tile), self._stream()),
+                    c_int(out.stride(0)), c_int(epi), c_int(self.pair_n_tile), c_int(self.tc_splits), self._stream()),
                     "linear (tensor cores, two SMs per tile)")
                 return
             self.ensure_workspace(a.device)

@@ -90,9 +90,10 @@ class Engine:
                 raise ValueError(
                     f"request {e.request.request_id!r}: position {e.request.length + n} exceeds the "
                     f"model's context length {self.max_positions} (max_position_embeddings)")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab_size):
-                    raise ValueError(f"token id {t} outside the vocabulary 0..{self.vocab_size - 1}")
+            ids = np.asarray(e.tokens, dtype=np.int64)      # one pass in numpy: a prompt portion has thousands of ids
+            if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
+                bad = next(int(t) for t in ids if not (0 <= int(t) < self.vocab_size))
+                raise ValueError(f"token id {bad} outside the vocabulary 0..{self.vocab_size - 1}")
             for w in e.want:
                 if not (0 <= int(w) < n):
                     raise ValueError(f"wanted place {w} outside the entry's {n} tokens")

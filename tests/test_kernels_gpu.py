@@ -335,6 +335,13 @@ def test_tensor_core_gemm_on_pairs_of_sms(K, m, n, k, tile):
     bias = rnd((n,), torch.float32, 172)
     K.gemm_route, K.pair_n_tile = "tc_pair", tile
     try:
+        for splits in (2, 5):       # K split over clusters, partial sums added in memory
+            K.tc_splits = splits
+            res = rnd((m, n), torch.float32, 174)
+            acc = res.clone()
+            K.linear(a, w, bias, acc, "add")
+            assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, f"pair add, {splits} splits")
+        K.tc_splits = 0
         out = torch.empty(m, n, dtype=dtype, device="cuda")
         K.linear(a, w, bias, out, "store")
         assert_close(out, _ref_linear_f64(a, w, bias), dtype, "pair store")
@@ -351,7 +358,7 @@ def test_tensor_core_gemm_on_pairs_of_sms(K, m, n, k, tile):
         REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
         assert_close(sw, ref, dtype, "pair swiglu")
     finally:
-        K.gemm_route, K.pair_n_tile = None, 0
+        K.gemm_route, K.pair_n_tile, K.tc_splits = None, 0, 0
     assert K.gemm_tc_error() == 0
 
 
