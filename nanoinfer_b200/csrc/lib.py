@@ -66,7 +66,7 @@ class Kernels:
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
                      "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
-                     "nib_argmax", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
+                     "nib_argmax", "nib_argmax_chunked", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -105,6 +105,8 @@ class Kernels:
             self._ws_scratch = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=device)
             self._ws_counters = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
             self._ws_attn_counters = torch.zeros(64 * 1024, dtype=torch.int32, device=device)
+            self._ws_argmax = torch.zeros(4096 * 64, dtype=torch.int64, device=device)
+            self._ws_argmax_counters = torch.zeros(4096, dtype=torch.int32, device=device)
 
     def linear(self, a, w, bias32, out, mode):
         """out[M,N] (=, +=) a[M,K] . w[N,K]^T (+ bias). mode: 'store' | 'add' (float out) | 'f32' (float out).
@@ -395,8 +397,16 @@ class Kernels:
         return max(1, min(-(-tiles // 2), most, 64))
 
     def argmax(self, logits, out):
+        """First index of each row's maximum. Few rows of a large vocabulary are cut into pieces for many CTAs."""
         _need(logits, torch.float32, "argmax logits"); _need(out, torch.int32, "argmax out")
         rows, vocab = logits.shape
+        chunks = min(64, max(1, (2 * self.sm_count) // max(1, rows)), vocab // 2048)
+        if chunks > 1 and rows <= 4096:
+            self.ensure_workspace(logits.device)
+            self._check(self._lib.nib_argmax_chunked(_ptr(logits), c_int(rows), c_int(vocab), _ptr(out), c_int(chunks),
+                                                     _ptr(self._ws_argmax), _ptr(self._ws_argmax_counters), self._stream()),
+                        "argmax")
+            return
         self._check(self._lib.nib_argmax(_ptr(logits), c_int(rows), c_int(vocab), _ptr(out), self._stream()), "argmax")
 
     def repetition_penalty(self, logits, seen, seen_start, penalty):

@@ -79,6 +79,68 @@ NIB_API int nib_argmax(const float* logits, int rows, int vocab, int* out, cudaS
     return 0;
 }
 
+// The same with every row cut into `chunks` pieces that different CTAs scan: a few rows of a large
+// vocabulary otherwise keep a few SMs busy and the rest idle. A piece's best (value, index) is packed
+// into 64 bits (order-preserving bits of the value above the complement of the index), so the maximum
+// of the packed words is the largest value at its first index, in whatever order they are compared. The
+// CTA that finishes a row's last piece (a counter per row, left at zero) writes the result.
+__device__ __forceinline__ unsigned long long argmax_pack(float x, int i) {
+    if (x != x) return 0ull;                                   // NaN never wins
+    const unsigned b = __float_as_uint(x);
+    const unsigned key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
+}
+
+__global__ void __launch_bounds__(256)
+argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunk, int chunks, unsigned long long* __restrict__ part,
+                    int* __restrict__ counters, int* __restrict__ out) {
+    __shared__ unsigned long long s_best[8];
+    __shared__ int s_last;
+    const int row = blockIdx.y, cid = blockIdx.x;
+    const float* l = logits + (size_t)row * vocab;
+    const int begin = cid * chunk, end = min(vocab, begin + chunk);
+    unsigned long long best = 0ull;
+    for (int i = begin + threadIdx.x; i < end; i += 256) best = max(best, argmax_pack(l[i], i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if ((threadIdx.x & 31) == 0) s_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 1; w < 8; ++w) best = max(best, s_best[w]);
+        part[(size_t)row * chunks + cid] = best;
+        __threadfence();
+        s_last = (atomicAdd(&counters[row], 1) == chunks - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    best = 0ull;
+    for (int c = threadIdx.x; c < chunks; c += 256) best = max(best, __ldcg(part + (size_t)row * chunks + c));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if ((threadIdx.x & 31) == 0) s_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 1; w < 8; ++w) best = max(best, s_best[w]);
+        out[row] = best == 0ull ? 0 : (int)(0xffffffffu - (unsigned)(best & 0xffffffffull));
+        counters[row] = 0;                                      // ready for the next launch
+    }
+}
+
+// scratch: rows * chunks 64-bit words; counters: rows ints that are zero between launches.
+NIB_API int nib_argmax_chunked(const float* logits, int rows, int vocab, int* out, int chunks, unsigned long long* scratch,
+                               int* counters, cudaStream_t stream) {
+    NIB_REQUIRE(rows >= 0 && vocab > 0 && chunks >= 1 && chunks <= 65535 && rows <= 65535, "argmax: bad sizes");
+    NIB_REQUIRE(scratch != nullptr && counters != nullptr, "argmax (chunked): scratch and counters are needed");
+    if (rows == 0) return 0;
+    const int chunk = ceil_div(vocab, chunks);
+    argmax_chunk_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, chunk, chunks, scratch, counters, out);
+    NIB_LAUNCH_CHECK();
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------- sampling
 // Order-preserving map from float to unsigned: larger float <-> larger key.
 __device__ __forceinline__ unsigned key_of(float x) {

@@ -186,17 +186,28 @@ def test_attention_finds_one_far_key(K, dtype, window):
         assert seen == (spot >= lo), f"key at {spot}: seen={seen}, window starts at {lo}"
 
 
-@pytest.mark.parametrize("vocab", [11, 503, 151936])
-def test_argmax_first_maximum(K, vocab):
-    logits = rnd((5, vocab), torch.float32, 40)
+@pytest.mark.parametrize("rows", [5, 200])
+@pytest.mark.parametrize("vocab", [11, 503, 4099, 151936])
+def test_argmax_first_maximum(K, vocab, rows):
+    """One CTA per row, or (few rows of a large vocabulary) many CTAs per row with the pieces' results
+    merged by the last one: ties across pieces go to the first index, NaN never wins, an all-negative
+    row works, and two calls in a row agree (the counters are left ready)."""
+    logits = rnd((rows, vocab), torch.float32, 40)
     logits[1, vocab // 2] = 50.0
     logits[2, 3] = 60.0
     logits[2, vocab - 1] = 60.0      # a tie: the first wins
     logits[3, vocab - 1] = 70.0
-    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    logits[4] = -logits[4].abs() - 1.0
+    logits[4, vocab // 3] = float("nan")
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
     K.argmax(logits, out)
-    assert out.tolist() == torch.argmax(logits.cpu(), dim=-1).tolist()
+    ref = logits.cpu().clone()
+    ref[4, vocab // 3] = -float("inf")
+    assert out.tolist() == torch.argmax(ref, dim=-1).tolist()
     assert out[2].item() == 3 and out[3].item() == vocab - 1
+    again = torch.empty_like(out)
+    K.argmax(logits, again)
+    assert torch.equal(out, again)
 
 
 @pytest.mark.parametrize("tma", [True, False])
