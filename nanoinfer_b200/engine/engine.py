@@ -90,9 +90,13 @@ class Engine:
                 raise ValueError(
                     f"request {e.request.request_id!r}: position {e.request.length + n} exceeds the "
                     f"model's context length {self.max_positions} (max_position_embeddings)")
-            ids = np.asarray(e.tokens, dtype=np.int64)      # one pass in numpy: a prompt portion has thousands of ids
-            if int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size:
-                bad = next(int(t) for t in ids if not (0 <= int(t) < self.vocab_size))
+            if n > 32:      # a prompt portion has thousands of ids: one pass in numpy
+                ids = np.asarray(e.tokens, dtype=np.int64)
+                in_range = int(ids.min()) >= 0 and int(ids.max()) < self.vocab_size
+            else:
+                in_range = all(0 <= int(t) < self.vocab_size for t in e.tokens)
+            if not in_range:
+                bad = next(int(t) for t in e.tokens if not (0 <= int(t) < self.vocab_size))
                 raise ValueError(f"token id {bad} outside the vocabulary 0..{self.vocab_size - 1}")
             for w in e.want:
                 if not (0 <= int(w) < n):
