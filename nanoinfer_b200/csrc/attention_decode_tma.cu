@@ -74,13 +74,19 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
                  ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
-template <int HD>
+// FUSED: qkv is the raw projection. The queries are rotated as they are loaded; the warp whose 16 keys
+// include the token's own position rotates the new key, puts key and value into its rows of the tile (the
+// page's slot still holds old data there) and into the page for the steps to come. Nothing of this step is
+// read from the pages then, so every tile may be fetched before the wait for the step's earlier kernels.
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ qkv, int q_stride, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
                             int page_size, int page_shift, int num_pages, int heads, int kv_heads, int n_rep, float scale,
-                            int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                            int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                            __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot) {
     using C = Cfg<HD>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -136,7 +142,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             const int st = j % C::STAGES;
             const int z = z_next;
             z_next = plane_of(j + 1);
-            if (t_begin + j == t_last && !waited) { pdl_wait(); waited = true; }
+            if (!FUSED && t_begin + j == t_last && !waited) { pdl_wait(); waited = true; }
             int ok = 1;
             if (lane == 0) {
                 if (j >= C::STAGES) ok = !s_failed && mbar_wait(&empty[st], ((j / C::STAGES) - 1) & 1);
@@ -167,7 +173,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         if (g < n_rep) q_ptr[0] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g) * HD;
         if (g + 8 < n_rep) { q_ptr[1] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g + 8) * HD; vis_hi[1] = p; }
         unsigned q[HD / 16][4];
-        load_q<HD>(q, q_ptr, lane);
+        const float* cos_row = FUSED ? cos_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;      // p < 0: a padding row
+        const float* sin_row = FUSED ? sin_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;
+        if (FUSED) load_q_rotated<HD>(q, q_ptr, lane, cos_row, sin_row, rot);
+        else load_q<HD>(q, q_ptr, lane);
 #pragma unroll
         for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
         const float scale2 = scale * LOG2E;
@@ -188,6 +197,31 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 break;
             }
             const unsigned kt = smem_u32(smem + st * C::STAGE), vt = kt + C::TILE;
+            if (FUSED && t_begin + j == t_last && p >= 0 && ((p & (KEYS - 1)) >> 4) == warp) {
+                // this step's own key (rotated) and value: into this warp's rows of the tile and into the page
+                const __nv_bfloat16* k_new = qkv + (size_t)token * q_stride + (size_t)(heads + kvh) * HD;
+                const __nv_bfloat16* v_new = qkv + (size_t)token * q_stride + (size_t)(heads + kv_heads + kvh) * HD;
+                const int r = p & (KEYS - 1);
+                const int page = __ldg(bt + (p >> page_shift));
+                const int slot = p & (page_size - 1);
+                const bool has_page = page >= 0 && page < num_pages;
+                const size_t off = has_page ? (((size_t)page * kv_heads + kvh) * page_size + slot) * HD : 0;
+                unsigned char* k_tile = smem + st * C::STAGE;
+                for (int d = 2 * lane; d < HD; d += 64) {
+                    const unsigned kr = rotated_pair(k_new, d, cos_row, sin_row, rot);
+                    const unsigned vr = *reinterpret_cast<const unsigned*>(v_new + d);
+                    // element d of row r in a swizzled tile: column block d/64, 16-byte chunk (d%64)/8 at ((chunk ^ (r&7)) << 4)
+                    const unsigned byte = (unsigned)(d >> 6) * SUBTILE + (unsigned)r * 128u +
+                                          (((unsigned)((d & 63) >> 3) ^ (unsigned)(r & 7)) << 4) + (unsigned)(d & 7) * 2u;
+                    *reinterpret_cast<unsigned*>(k_tile + byte) = kr;
+                    *reinterpret_cast<unsigned*>(k_tile + C::TILE + byte) = vr;
+                    if (has_page) {
+                        *reinterpret_cast<unsigned*>(k_pages + off + d) = kr;
+                        *reinterpret_cast<unsigned*>(v_pages + off + d) = vr;
+                    }
+                }
+                __syncwarp();
+            }
             float s[2][4];
             s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
             s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
@@ -302,21 +336,22 @@ int make_pool_map(CUtensorMap* map, const void* ptr, int head_dim, int page_size
     return 0;
 }
 
-template <int HD>
+template <int HD, bool FUSED>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const void* qkv, int q_stride, void* out, const int* ctx_lens,
            const int* block_table, int bt_stride, int page_size, int num_pages, int n_tokens, int heads, int kv_heads,
-           float scale, int window, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+           float scale, int window, int splits, float* part_o, float* part_ml, void* k_pages, void* v_pages,
+           const float* cos_t, const float* sin_t, int rot, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
         configured = true;
     }
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
-    NIB_CUDA(launch_pdl(attention_decode_tma_kernel<HD>, dim3(splits, n_tokens, kv_heads), dim3(THREADS), (size_t)Cfg<HD>::SMEM,
+    NIB_CUDA(launch_pdl(attention_decode_tma_kernel<HD, FUSED>, dim3(splits, n_tokens, kv_heads), dim3(THREADS), (size_t)Cfg<HD>::SMEM,
                         stream, mk, mv, (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table,
                         bt_stride, page_size, shift, num_pages, heads, kv_heads, heads / kv_heads, scale, window, splits,
-                        part_o, part_ml));
+                        part_o, part_ml, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, cos_t, sin_t, rot));
     if (splits > 1) return nib_attention_combine(part_o, part_ml, out, n_tokens * heads, splits, HD, stream);
     return 0;
 }
@@ -340,12 +375,11 @@ NIB_API int nib_attention_decode_tma_error() {
     return v;
 }
 
-// Arguments as nib_attention_decode_mma (without counters: the splits are merged by the combine kernel).
-NIB_API int nib_attention_decode_tma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
-                                     const int* block_table, int bt_stride, int page_size, const void* k_pages,
-                                     const void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
-                                     int head_dim, float scale, int window, int splits, float* part_o,
-                                     float* part_ml, cudaStream_t stream) {
+namespace {
+int decode_tma(const void* qkv, int q_stride, void* out, const int* ctx_lens, const int* block_table, int bt_stride,
+               int page_size, void* k_pages, void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
+               int head_dim, float scale, int window, int splits, float* part_o, float* part_ml, bool fused,
+               const float* cos_t, const float* sin_t, int rot, cudaStream_t stream) {
     NIB_REQUIRE(nib_attention_decode_tma_supported(heads, kv_heads, head_dim, page_size),
                 "attention decode (TMA): head_dim %d, %d/%d heads, page size %d are not supported", head_dim, heads, kv_heads, page_size);
     NIB_REQUIRE(n_tokens >= 0 && num_pages > 0 && window >= 0 && splits >= 1 && splits <= 64, "attention decode (TMA): bad sizes (1..64 splits)");
@@ -353,14 +387,41 @@ NIB_API int nib_attention_decode_tma(const void* qkv, int q_stride, void* out, c
     NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode (TMA): too many tokens or kv heads for one launch");
     NIB_REQUIRE((((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0 && q_stride % 2 == 0, "attention decode (TMA): the pools must be 16-byte aligned, rows 4-byte aligned");
     NIB_REQUIRE((long long)num_pages * kv_heads < (1LL << 31) - 1, "attention decode (TMA): too many pages");
+    NIB_REQUIRE(!fused || (rot >= 0 && rot <= head_dim && rot % 4 == 0 && (rot == 0 || (cos_t && sin_t))),
+                "attention decode (TMA, fused): rotated width %d must be a multiple of 4 and at most head_dim", rot);
     if (n_tokens == 0) return 0;
     CUtensorMap mk, mv;
     const long long planes = (long long)num_pages * kv_heads;
     if (make_pool_map(&mk, k_pages, head_dim, page_size, planes)) return 1;
     if (make_pool_map(&mv, v_pages, head_dim, page_size, planes)) return 1;
-    if (head_dim == 64)
-        return launch<64>(mk, mv, qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, num_pages, n_tokens, heads,
-                          kv_heads, scale, window, splits, part_o, part_ml, stream);
-    return launch<128>(mk, mv, qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, num_pages, n_tokens, heads,
-                       kv_heads, scale, window, splits, part_o, part_ml, stream);
+#define CALL(HD, F) launch<HD, F>(mk, mv, qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, num_pages, n_tokens, heads, \
+                                  kv_heads, scale, window, splits, part_o, part_ml, k_pages, v_pages, cos_t, sin_t, rot, stream)
+    if (fused) return head_dim == 64 ? CALL(64, true) : CALL(128, true);
+    return head_dim == 64 ? CALL(64, false) : CALL(128, false);
+#undef CALL
+}
+}  // namespace
+
+// Arguments as nib_attention_decode_mma (without counters: the splits are merged by the combine kernel).
+NIB_API int nib_attention_decode_tma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
+                                     const int* block_table, int bt_stride, int page_size, const void* k_pages,
+                                     const void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
+                                     int head_dim, float scale, int window, int splits, float* part_o, float* part_ml,
+                                     cudaStream_t stream) {
+    return decode_tma(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, const_cast<void*>(k_pages),
+                      const_cast<void*>(v_pages), num_pages, n_tokens, heads, kv_heads, head_dim, scale, window, splits, part_o,
+                      part_ml, false, nullptr, nullptr, 0, stream);
+}
+
+// The same fused with what precedes it in a decode step: qkv is the raw projection; queries and the new key
+// are rotated with the tables' row of the token's position (ctx_len - 1), the new key and value are written
+// into the token's page and used at once. Arguments as nib_attention_decode_fused_mma.
+NIB_API int nib_attention_decode_tma_fused(const void* qkv, int q_stride, void* out, const int* ctx_lens,
+                                           const int* block_table, int bt_stride, int page_size, void* k_pages,
+                                           void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
+                                           int head_dim, float scale, int window, int splits, float* part_o,
+                                           float* part_ml, const float* cos_t, const float* sin_t, int rot,
+                                           cudaStream_t stream) {
+    return decode_tma(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens,
+                      heads, kv_heads, head_dim, scale, window, splits, part_o, part_ml, true, cos_t, sin_t, rot, stream);
 }

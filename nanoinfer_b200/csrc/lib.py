@@ -65,7 +65,7 @@ class Kernels:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
-                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
+                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_fused", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
                      "nib_argmax", "nib_argmax_chunked", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
@@ -331,12 +331,9 @@ class Kernels:
         return self._lib.nib_attention_tc_error()
 
     def can_fuse_decode(self, dtype, heads, kv_heads, head_dim, rotary, page_size=0) -> bool:
-        """True if ``attention_decode_fused`` should take this shape (bfloat16, a tensor-core head size, at
-        most 16 query heads per kv head, a rotated width that is a multiple of 4), and the faster decode
-        kernel with TMA page loads (which wants rotation and cache write done before it) does not."""
+        """True if ``attention_decode_fused`` takes this shape (bfloat16, a tensor-core head size, at most
+        16 query heads per kv head, a rotated width that is a multiple of 4)."""
         if dtype != torch.bfloat16 or self.force_general_attention or not self.fuse_decode:
-            return False
-        if self._decode_tma_ok(heads, kv_heads, head_dim, page_size):
             return False
         if self._lib.nib_attention_mma_supported(c_int(heads), c_int(kv_heads), c_int(head_dim)) != 1:
             return False
@@ -367,16 +364,21 @@ class Kernels:
         rot = 0
         if rotary is not None:
             cos, sin, rot = rotary
-        splits = self.decode_splits(n, kv_heads, max(ctx.host.ctx_lens), window)
+        tma = self._decode_tma_ok(heads, kv_heads, head_dim, page_size)
+        splits = self.decode_splits(n, kv_heads, max(ctx.host.ctx_lens), window, tma)
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty(n * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty(n * heads * splits * 2, dtype=torch.float32, device=qkv.device)
-        self._check(self._lib.nib_attention_decode_fused_mma(
-            _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(block_table.stride(0)),
-            c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(n), c_int(heads),
-            c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits), _ptr(part_o), _ptr(part_ml),
-            c_void_p(0), _ptr(cos), _ptr(sin), c_int(rot), self._stream()), "attention decode (fused)")
+        common = (_ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(block_table.stride(0)),
+                  c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(n), c_int(heads),
+                  c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits), _ptr(part_o), _ptr(part_ml))
+        if tma:
+            self._check(self._lib.nib_attention_decode_tma_fused(*common, _ptr(cos), _ptr(sin), c_int(rot), self._stream()),
+                        "attention decode (TMA, fused)")
+        else:
+            self._check(self._lib.nib_attention_decode_fused_mma(*common, c_void_p(0), _ptr(cos), _ptr(sin), c_int(rot),
+                                                                 self._stream()), "attention decode (fused)")
         if splits > 1:
             self.launches += 1
 

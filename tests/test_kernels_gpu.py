@@ -135,7 +135,8 @@ def _fill_cache(ctx, bt, page, num_pages, kv_heads, hd, dtype, seed):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,hd,page,window", [
     (4, 2, 16, 16, 0), (6, 1, 32, 8, 0), (3, 3, 48, 8, 24), (14, 2, 64, 16, 0), (7, 7, 80, 4, 0),
-    (8, 2, 128, 16, 100), (2, 1, 256, 16, 0), (5, 1, 96, 32, 7)])
+    (8, 2, 128, 16, 100), (2, 1, 256, 16, 0), (5, 1, 96, 32, 7), (4, 4, 64, 16, 0), (2, 2, 128, 8, 30), (1, 1, 64, 32, 0),
+    (32, 2, 64, 16, 0)])
 def test_attention_mixed_batch(K, dtype, heads, kv_heads, hd, page, window):
     q_lens, before = [1, 33, 2, 1], [130, 0, 77, 0]
     num_pages = 64
@@ -483,11 +484,14 @@ def test_attention_tcgen05_prefill(K, heads, kv_heads, hd, page, window):
     assert_close(fast, ref, dtype, "tcgen05 attention")
 
 
+@pytest.mark.parametrize("tma", [True, False])
 @pytest.mark.parametrize("heads,kv_heads,hd,rot,page,window", [(14, 2, 64, 64, 16, 0), (6, 1, 32, 32, 8, 0), (3, 3, 48, 48, 8, 24),
-                                                               (16, 1, 128, 64, 16, 0), (4, 2, 16, 16, 16, 0)])
-def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads, hd, rot, page, window):
-    """The fused decode kernel (rotate q and the new k, write k and v into the page, attend) against the
-    separate rotation kernel followed by the decode kernel: same output, same pages."""
+                                                               (16, 1, 128, 64, 16, 0), (4, 2, 16, 16, 16, 0), (8, 2, 128, 128, 32, 0),
+                                                               (14, 2, 64, 32, 8, 200)])
+def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads, hd, rot, page, window, tma):
+    """The fused decode kernels (rotate q and the new k, write k and v into the page, attend), with TMA page
+    loads and with cp.async, against the separate rotation kernel followed by the decode kernel: same
+    output, same pages."""
     from nanoinfer_b200.parts.position import rotary_tables
     dtype = torch.bfloat16
     before = [0, 63, 64, 300, 1000, 17]
@@ -502,7 +506,7 @@ def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads
     scale = 1.0 / math.sqrt(hd)
     assert K.can_fuse_decode(dtype, heads, kv_heads, hd, rotary)
     for splits in (0, 1, 5):
-        K.fixed_decode_splits, K.decode_tma = splits, False
+        K.fixed_decode_splits, K.decode_tma = splits, tma
         try:
             fused = torch.empty(n, heads * hd, dtype=dtype, device="cuda")
             a = kp.clone(), vp.clone()
@@ -516,3 +520,4 @@ def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads
             K.fixed_decode_splits, K.decode_tma = 0, True
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "pages differ"
         assert torch.equal(fused, two), f"outputs differ with splits={splits}"
+    assert K.attention_decode_tma_error() == 0
