@@ -243,7 +243,7 @@ def run_ours(args) -> dict:
                 "gpu_launches": launches, "config": {"layers": layers, "global_batch": batch, "seq_len": ctx}}
 
     # ---- end to end through the Python entry point (scheduler) -----------------------------
-    sched = Scheduler(model, max_batch=batch, max_tokens_per_step=4096)
+    sched = Scheduler(model, max_batch=batch, max_tokens_per_step=4096, lookahead=True)
     # Requests admitted first decode while the later prompts are still being prefilled (about one step per
     # prompt), so they are ahead by up to `batch` tokens when timing starts; nobody may finish, and nobody may
     # leave the context (and with it the captured graph's bucket), before the timed steps end.

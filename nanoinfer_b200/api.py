@@ -33,7 +33,7 @@ class Model:
         params = params or SamplingParams()
         if params.seed is not None:
             seed = params.seed
-        sched = Scheduler(self)
+        sched = Scheduler(self, lookahead=True)      # run() to the end: the one-step lag of the host is not seen
         sched.add(Request("generate", list(prompt_ids), max_tokens=max_tokens, temperature=params.temperature,
                           top_k=params.k, top_p=params.p, repetition_penalty=params.repetition_penalty,
                           seed=seed, eos_id=eos_id))

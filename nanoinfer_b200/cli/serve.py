@@ -28,7 +28,7 @@ def main(argv=None) -> int:
     model = load_model(model_dir, dtype=args.dtype, page_size=args.page_size, num_pages=args.num_pages,
                        max_batch=args.max_batch, max_tokens_per_step=args.max_tokens_per_step)
     tok = load_tokenizer(model_dir, model.eos_token_id)
-    sched = Scheduler(model, max_batch=args.max_batch)
+    sched = Scheduler(model, max_batch=args.max_batch, lookahead=True)
     prompts = {}
     for i, text in enumerate(args.prompts):
         rid = f"req{i}"

@@ -171,12 +171,21 @@ class Engine:
         return dev
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry], borrow_logits: bool = False) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], borrow_logits: bool = False,
+             device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch. Returns logits ``[wanted, vocab]`` (float32, on the device) in the order of the
         entries and of each entry's ``want``; None if nothing is wanted. Raises ``OutOfPages`` before
         changing anything if the pools cannot hold the new tokens. With ``borrow_logits`` the result may be
-        a view of a buffer that the next step overwrites (for callers that consume it at once)."""
+        a view of a buffer that the next step overwrites (for callers that consume it at once).
+
+        ``device_tokens`` (int32 on the device, one per entry, every entry of one token): the token ids are
+        taken from there instead of from the entries, whose ids are placeholders. A caller that has sampled
+        the previous step's tokens on the device can so launch the next step before it has read them."""
         self._check(entries)
+        if device_tokens is not None:
+            if any(len(e.tokens) != 1 for e in entries) or device_tokens.numel() < len(entries) \
+                    or device_tokens.dtype != torch.int32 or device_tokens.device != self.device:
+                raise ValueError("device_tokens: one int32 token on the engine's device per entry of one token")
         demands = [(e.request, len(e.tokens)) for e in entries]
         if not self.cache.fits(demands):
             raise OutOfPages("the step's new tokens do not fit the free cache pages")
@@ -184,10 +193,12 @@ class Engine:
             self.cache.extend(rc, n)
         self.storage.zero_slots(self.cache.take_fresh_slots())
         if self._graphs is not None and all(n == 1 for _, n in demands) and len(entries) <= self._graphs.max_batch:
-            logits = self._graphs.step(entries, borrow=borrow_logits)
+            logits = self._graphs.step(entries, borrow=borrow_logits, device_tokens=device_tokens)
             m_tokens = len(entries)
         else:
             ctx, want_rows, _ = self.build_context(entries)
+            if device_tokens is not None:
+                ctx.token_ids[:len(entries)].copy_(device_tokens[:len(entries)], non_blocking=True)
             caches = self.storage.layer_caches(ctx.block_tables)
             logits = self.model.forward(ctx, caches, want_rows)
             m_tokens = ctx.num_tokens

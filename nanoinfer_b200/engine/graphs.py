@@ -118,7 +118,7 @@ class DecodeGraphs:
         widths = [max(1, -(-cb // page)) for _ in eng.cache.groups]
         return rb, cb, widths
 
-    def step(self, entries, borrow: bool = False) -> Optional[torch.Tensor]:
+    def step(self, entries, borrow: bool = False, device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         eng = self.engine
         rb, cb, widths = self._key(entries)
         key = (rb, cb)
@@ -128,10 +128,14 @@ class DecodeGraphs:
                 # the first step of a shape runs eagerly: it sets up whatever the kernels set up on first use
                 self.seen.add(key)
                 ctx, want_rows, _ = eng.build_context(entries)
+                if device_tokens is not None:
+                    ctx.token_ids[:len(entries)].copy_(device_tokens[:len(entries)], non_blocking=True)
                 return eng.model.forward(ctx, eng.storage.layer_caches(ctx.block_tables), want_rows)
             cap = self._capture(key, entries, rb, cb, widths)
         cap.mirror.fill(entries)
         eng.last_h2d_bytes = cap.mirror.send(cap.inputs)
+        if device_tokens is not None:       # the ids sampled on the device replace the placeholders (after the copy above, in stream order)
+            cap.inputs[:len(entries)].copy_(device_tokens[:len(entries)], non_blocking=True)
         want_list = [i for i, e in enumerate(entries) for _ in e.want]
         cap.graph.replay()
         eng.graph_launches += cap.launches

@@ -100,8 +100,16 @@ class Scheduler:
     ``model`` offers ``engine`` (with ``cache``, ``open``, ``close``, ``step``), ``sampler`` and
     ``eos_token_id``."""
 
-    def __init__(self, model, max_batch: Optional[int] = None, max_tokens_per_step: Optional[int] = None):
+    def __init__(self, model, max_batch: Optional[int] = None, max_tokens_per_step: Optional[int] = None,
+                 lookahead: bool = False):
+        """``lookahead``: greedy decoding steps are launched with the previous step's tokens still on the
+        device; the host reads them while the new step runs, so ``finished`` and the sequences' outputs lag
+        one step behind the device, and a request that stops at EOS has run one step too many (its result is
+        dropped). What is generated is the same."""
         self.model = model
+        self.lookahead = lookahead
+        self._inflight = None      # (sequences, PendingTokens) of a step whose tokens the host has not read yet
+        self.steps_ahead = 0       # steps launched before the host had read the previous one's tokens
         self.engine = model.engine
         ec = self.engine.engine_config
         self.max_batch = min(max_batch or ec.max_batch, ec.max_batch)
@@ -222,7 +230,63 @@ class Scheduler:
         self.waiting.appendleft(seq)
 
     # ---- one step -------------------------------------------------------------------------
+    def _resolve_inflight(self) -> None:
+        """Read the tokens of the step in flight and apply the stop rules."""
+        if self._inflight is None:
+            return
+        seqs, pending = self._inflight
+        self._inflight = None
+        for seq, tok in zip(seqs, pending.wait()):
+            if seq.state is not State.RUNNING:
+                continue            # stopped meanwhile (EOS one step earlier, cancelled): the extra token is dropped
+            if self._accept(seq, int(tok)):
+                self._finish(seq)
+        self.running = [s for s in self.running if s.state is State.RUNNING]
+
+    def _continuation(self):
+        """The sequences of the step in flight, if the next step is exactly one more token for each of them:
+        nobody waits to be admitted, nobody's token in flight is its last by count, every one decodes greedily
+        without a penalty, and the pages for one more token each are there."""
+        if self._inflight is None or self.waiting:
+            return None
+        seqs, _ = self._inflight
+        if len(seqs) != len(self.running) or len(seqs) > self.max_tokens_per_step:
+            return None
+        for a, b in zip(seqs, sorted(self.running, key=lambda s: s.order)):
+            if a is not b or a.state is not State.RUNNING:
+                return None
+            if not a.params.greedy or a.params.repetition_penalty != 1.0:
+                return None
+            if len(a.output_ids) + 1 >= a.req.max_tokens or len(a.ids) + 2 >= self.engine.max_positions:
+                return None
+        if not self.engine.cache.fits([(s.cache, 1) for s in seqs]):
+            return None
+        return seqs
+
+    def _step_ahead(self, seqs) -> StepPlan:
+        """Launch the next decode step from the device's copy of the tokens in flight, then read those."""
+        _, pending = self._inflight
+        entries = [StepEntry(s.cache, [0], [0]) for s in seqs]       # the ids are placeholders
+        rows = [SampleRow(s.params, None, len(s.output_ids) + 1, s.req.seed) for s in seqs]
+        logits = self.engine.step(entries, borrow_logits=True, device_tokens=pending.device)
+        nxt = self.model.sampler.sample_async(logits, rows)
+        plan = StepPlan(entries=[PlannedEntry(s, s.fed, 1, True) for s in seqs])
+        for s in seqs:
+            s.fed += 1              # the token in flight is in the cache now; ``ids`` gets it below
+        self._resolve_inflight()
+        self._inflight = (list(seqs), nxt)
+        self.tokens_run += len(seqs)
+        self.peak_batch = max(self.peak_batch, len(seqs))
+        self.steps += 1
+        self.steps_ahead += 1
+        return plan
+
     def step(self) -> StepPlan:
+        if self.lookahead:
+            seqs = self._continuation()
+            if seqs is not None:
+                return self._step_ahead(seqs)
+            self._resolve_inflight()
         plan = self.plan()
         if plan.entries:
             entries, rows, samplers = [], [], []
@@ -237,7 +301,13 @@ class Scheduler:
             logits = self.engine.step(entries, borrow_logits=True)
             for e in plan.entries:
                 e.seq.fed += e.count
-            toks = self.model.sampler.sample(logits, rows) if rows else []
+            if self.lookahead and rows and len(samplers) == len(plan.entries) and \
+                    all(e.count == 1 for e in plan.entries) and self.model.sampler.can_sample_async(rows):
+                # a pure greedy decode step: leave its tokens on the device for the next step to start from
+                self._inflight = (samplers, self.model.sampler.sample_async(logits, rows))
+                toks = []
+            else:
+                toks = self.model.sampler.sample(logits, rows) if rows else []
             for seq, tok in zip(samplers, toks):
                 if self._accept(seq, int(tok)):
                     self._finish(seq)
@@ -252,6 +322,7 @@ class Scheduler:
 
     def cancel(self, request_id: str) -> bool:
         """Queued: dropped with an empty output. Running: finished with what it has; pages are freed."""
+        self._resolve_inflight()
         for seq in self.waiting:
             if seq.req.request_id == request_id:
                 self.waiting.remove(seq)

@@ -39,9 +39,48 @@ class SampleRow:
     seed: int = 0
 
 
+class PendingTokens:
+    """Tokens sampled on the device whose copy to the host is under way: ``device`` can feed the next
+    step at once, ``wait()`` returns the ids."""
+
+    def __init__(self, device: torch.Tensor, host: torch.Tensor, event, n: int):
+        self.device, self._host, self._event, self._n = device, host, event, n
+
+    def wait(self) -> List[int]:
+        if self._event is not None:
+            self._event.synchronize()
+        return self._host[:self._n].tolist()
+
+
 class Sampler:
     def __init__(self, ops, device):
         self.ops, self.device = ops, torch.device(device)
+        self._pinned: List[torch.Tensor] = []       # host buffers of the asynchronous reads, used in turn
+        self._turn = 0
+
+    @staticmethod
+    def can_sample_async(rows: Sequence[SampleRow]) -> bool:
+        """Greedy rows without a penalty need nothing from the host but the result."""
+        return bool(rows) and all(r.params.greedy and r.params.repetition_penalty == 1.0 for r in rows)
+
+    def sample_async(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> PendingTokens:
+        """As ``sample`` for rows that ``can_sample_async`` accepts, without waiting for the device."""
+        n = len(rows)
+        assert logits.shape[0] == n and self.can_sample_async(rows)
+        out = torch.empty(n, dtype=torch.int32, device=logits.device)
+        self.ops.argmax(logits, out)
+        if out.device.type != "cuda":       # a host backend (tests): nothing is asynchronous
+            return PendingTokens(out, out, None, n)
+        if len(self._pinned) < 4:
+            self._pinned.append(torch.empty(max(256, n), dtype=torch.int32).pin_memory())
+        self._turn = (self._turn + 1) % len(self._pinned)
+        host = self._pinned[self._turn]
+        if host.numel() < n:
+            host = self._pinned[self._turn] = torch.empty(n, dtype=torch.int32).pin_memory()
+        host[:n].copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(out, host, event, n)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> List[int]:
         """One token per row of ``logits [len(rows), vocab]`` (float32, on the device; penalised in place)."""

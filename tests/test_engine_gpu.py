@@ -126,6 +126,48 @@ def test_scheduler_equals_alone_with_few_pages(model_dirs, dtype):
     assert model.engine.cache.num_free() == 14
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_lookahead_scheduling_generates_the_same(model_dirs, dtype):
+    """With ``lookahead`` the next decode step starts from the tokens on the device while the host still
+    reads the previous ones. Requests of different lengths, one that stops at an EOS token in the middle
+    (it has run one step too many by then: that token is dropped), a late arrival that interrupts the
+    pipeline, few pages: the outputs equal those of the plain scheduler."""
+    from nanoinfer_b200 import Request, Scheduler, load_model
+    d, page = model_dirs["B"]
+    g = torch.Generator().manual_seed(13)
+    prompts = [torch.randint(0, 503, (n,), generator=g).tolist() for n in (20, 5, 33, 9)]
+    limits = [25, 12, 30, 18]
+    model = load_model(d, dtype=dtype, page_size=page, num_pages=40, max_batch=4, max_tokens_per_step=64)
+
+    def run(lookahead, eos):
+        sched = Scheduler(model, lookahead=lookahead)
+        for i in range(3):
+            sched.add(Request(f"r{i}", prompts[i], max_tokens=limits[i], eos_id=eos if i == 0 else -1))
+        for _ in range(6):
+            sched.step()
+        sched.add(Request("r3", prompts[3], max_tokens=limits[3]))
+        out = sched.run()
+        assert sched._inflight is None and not sched.running and (sched.steps_ahead > 0) == lookahead
+        model.engine.cache.check()
+        assert model.engine.cache.num_free() == 40
+        return [out[f"r{i}"] for i in range(4)]
+
+    plain = run(False, -1)
+    assert [len(o) for o in plain] == limits
+    eos = plain[0][10]                       # the first request will stop where this token first appears
+    stop = plain[0].index(eos)
+    for look in (True,):
+        got = run(look, -1)
+        with_eos = run(look, eos)
+        if dtype == "float32":
+            assert got == plain
+            assert with_eos[0] == plain[0][:stop] and with_eos[1:] == plain[1:]
+        else:   # bfloat16: another batch may round a near tie the other way; lengths and stop rules must hold
+            assert [len(o) for o in got] == limits
+            assert eos not in with_eos[0] and len(with_eos[0]) <= limits[0]
+            assert sum(a == b for a, b in zip(got, plain)) >= 3
+
+
 # ------------------------------------------------------------------------------- parts alone
 def _runtime(dtype):
     from nanoinfer_b200.csrc.lib import load_kernels

@@ -106,6 +106,38 @@ def test_admission_errors_and_edge_cases(model_dirs):
     assert model.engine.cache.num_free() == 4
 
 
+def test_lookahead_equals_alone_under_every_interruption(model_dirs):
+    """Lookahead decoding (the next step starts from the device's copy of the last tokens): requests of
+    different lengths that finish by count at different steps, one that stops at EOS, a tight pool that
+    preempts, late arrivals, a cancel: the outputs equal generation alone, and nothing is left held."""
+    d, page = model_dirs["B"]
+    plain = PlainModel(d)
+    ps = prompts(503, [2, 9, 17, 30, 5], seed=6)
+    limits = [9, 4, 12, 7, 10]
+    alone = [plain.greedy(p, n) for p, n in zip(ps, limits)]
+    eos = alone[2][5]
+    stop = alone[2].index(eos)
+    for budget, max_batch, num_pages in ((64, 5, 40), (13, 3, 40), (16, 4, 12)):
+        model = make_model(d, page, num_pages=num_pages, max_batch=max_batch, budget=budget)
+        s = Scheduler(model, lookahead=True)
+        for i in range(3):
+            s.add(Request(f"r{i}", ps[i], max_tokens=limits[i], eos_id=eos if i == 2 else -1))
+        for _ in range(5):
+            s.step()
+        for i in range(3, 5):
+            s.add(Request(f"r{i}", ps[i], max_tokens=limits[i]))
+        for _ in range(4):
+            s.step()
+        assert s.cancel("r4")
+        out = s.run()
+        assert s._inflight is None and s.steps_ahead > 0
+        assert out["r0"] == alone[0] and out["r1"] == alone[1] and out["r3"] == alone[3], (budget, max_batch)
+        assert out["r2"] == alone[2][:stop]
+        assert out["r4"] == alone[4][:len(out["r4"])] and len(out["r4"]) < limits[4]
+        model.engine.cache.check()
+        assert model.engine.cache.num_free() == num_pages and not model.engine.cache.live
+
+
 def test_eos_ends_generation_and_is_not_emitted(model_dirs):
     d, page = model_dirs["B"]
     model = make_model(d, page)
