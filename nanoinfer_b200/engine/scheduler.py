@@ -102,7 +102,7 @@ class Scheduler:
 
     def __init__(self, model, max_batch: Optional[int] = None, max_tokens_per_step: Optional[int] = None,
                  lookahead: bool = False):
-        """``lookahead``: greedy decoding steps are launched with the previous step's tokens still on the
+        """``lookahead``: decoding steps (greedy or sampled, without a repetition penalty) are launched with the previous step's tokens still on the
         device; the host reads them while the new step runs, so ``finished`` and the sequences' outputs lag
         one step behind the device, and a request that stops at EOS has run one step too many (its result is
         dropped). What is generated is the same."""
@@ -245,8 +245,9 @@ class Scheduler:
 
     def _continuation(self):
         """The sequences of the step in flight, if the next step is exactly one more token for each of them:
-        nobody waits to be admitted, nobody's token in flight is its last by count, every one decodes greedily
-        without a penalty, and the pages for one more token each are there."""
+        nobody waits to be admitted, nobody's token in flight is its last by count, nobody has a repetition
+        penalty (it needs the ids on the host), all are greedy or all are sampled, and the pages for one more
+        token each are there."""
         if self._inflight is None or self.waiting:
             return None
         seqs, _ = self._inflight
@@ -255,10 +256,12 @@ class Scheduler:
         for a, b in zip(seqs, sorted(self.running, key=lambda s: s.order)):
             if a is not b or a.state is not State.RUNNING:
                 return None
-            if not a.params.greedy or a.params.repetition_penalty != 1.0:
+            if a.params.repetition_penalty != 1.0:
                 return None
             if len(a.output_ids) + 1 >= a.req.max_tokens or len(a.ids) + 2 >= self.engine.max_positions:
                 return None
+        if len({s.params.greedy for s in seqs}) != 1:
+            return None             # greedy and sampled rows in one batch are merged on the host
         if not self.engine.cache.fits([(s.cache, 1) for s in seqs]):
             return None
         return seqs

@@ -56,27 +56,53 @@ class Sampler:
     def __init__(self, ops, device):
         self.ops, self.device = ops, torch.device(device)
         self._pinned: List[torch.Tensor] = []       # host buffers of the asynchronous reads, used in turn
+        self._pinned_par: List[torch.Tensor] = []   # and of the sampling parameters on their way to the device
         self._turn = 0
 
     @staticmethod
     def can_sample_async(rows: Sequence[SampleRow]) -> bool:
-        """Greedy rows without a penalty need nothing from the host but the result."""
-        return bool(rows) and all(r.params.greedy and r.params.repetition_penalty == 1.0 for r in rows)
+        """Rows without a penalty that are all greedy or all sampled: nothing the host must wait for."""
+        if not rows or any(r.params.repetition_penalty != 1.0 for r in rows):
+            return False
+        greedy = [r.params.greedy for r in rows]
+        return all(greedy) or not any(greedy)
+
+    _RING = 4       # pinned buffers in rotation: one is reused only after three more steps have been launched
+
+    def _pinned_pair(self, n: int):
+        """This call's pinned buffers (tokens out, sampling parameters in), large enough for ``n`` rows."""
+        if not self._pinned or self._pinned[0].numel() < n:
+            size = max(256, 2 * n)
+            self._pinned = [torch.empty(size, dtype=torch.int32).pin_memory() for _ in range(self._RING)]
+            self._pinned_par = [torch.empty(4 * size, dtype=torch.float32).pin_memory() for _ in range(self._RING)]
+        self._turn = (self._turn + 1) % self._RING
+        return self._pinned[self._turn], self._pinned_par[self._turn]
 
     def sample_async(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> PendingTokens:
         """As ``sample`` for rows that ``can_sample_async`` accepts, without waiting for the device."""
         n = len(rows)
         assert logits.shape[0] == n and self.can_sample_async(rows)
         out = torch.empty(n, dtype=torch.int32, device=logits.device)
-        self.ops.argmax(logits, out)
-        if out.device.type != "cuda":       # a host backend (tests): nothing is asynchronous
+        on_gpu = out.device.type == "cuda"
+        host, stage = self._pinned_pair(n) if on_gpu else (None, None)
+        if rows[0].params.greedy:
+            self.ops.argmax(logits, out)
+        else:
+            # temperature, top-k, top-p and the uniform numbers travel as one array (top-k as integer bits)
+            par = np.empty((4, n), dtype=np.float32)
+            par[0] = [r.params.temperature for r in rows]
+            par[1].view(np.int32)[:] = [r.params.k for r in rows]
+            par[2] = [r.params.p for r in rows]
+            par[3] = [uniform_for(r.seed, r.generated) for r in rows]
+            if on_gpu:
+                stage[:4 * n].numpy()[:] = par.reshape(-1)
+                dev = torch.empty(4 * n, dtype=torch.float32, device=out.device)
+                dev.copy_(stage[:4 * n], non_blocking=True)
+            else:
+                dev = torch.from_numpy(par.reshape(-1).copy())
+            self.ops.sample(logits, dev[:n], dev[n:2 * n].view(torch.int32), dev[2 * n:3 * n], dev[3 * n:], out)
+        if not on_gpu:       # a host backend (tests): nothing is asynchronous
             return PendingTokens(out, out, None, n)
-        if len(self._pinned) < 4:
-            self._pinned.append(torch.empty(max(256, n), dtype=torch.int32).pin_memory())
-        self._turn = (self._turn + 1) % len(self._pinned)
-        host = self._pinned[self._turn]
-        if host.numel() < n:
-            host = self._pinned[self._turn] = torch.empty(n, dtype=torch.int32).pin_memory()
         host[:n].copy_(out, non_blocking=True)
         event = torch.cuda.Event()
         event.record()

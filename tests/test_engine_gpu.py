@@ -139,13 +139,14 @@ def test_lookahead_scheduling_generates_the_same(model_dirs, dtype):
     limits = [25, 12, 30, 18]
     model = load_model(d, dtype=dtype, page_size=page, num_pages=40, max_batch=4, max_tokens_per_step=64)
 
-    def run(lookahead, eos):
+    def run(lookahead, eos, temperature=0.0):
         sched = Scheduler(model, lookahead=lookahead)
         for i in range(3):
-            sched.add(Request(f"r{i}", prompts[i], max_tokens=limits[i], eos_id=eos if i == 0 else -1))
+            sched.add(Request(f"r{i}", prompts[i], max_tokens=limits[i], eos_id=eos if i == 0 else -1,
+                              temperature=temperature, top_k=40, top_p=0.95, seed=100 + i))
         for _ in range(6):
             sched.step()
-        sched.add(Request("r3", prompts[3], max_tokens=limits[3]))
+        sched.add(Request("r3", prompts[3], max_tokens=limits[3], temperature=temperature, seed=7))
         out = sched.run()
         assert sched._inflight is None and not sched.running and (sched.steps_ahead > 0) == lookahead
         model.engine.cache.check()
@@ -162,6 +163,7 @@ def test_lookahead_scheduling_generates_the_same(model_dirs, dtype):
         if dtype == "float32":
             assert got == plain
             assert with_eos[0] == plain[0][:stop] and with_eos[1:] == plain[1:]
+            assert run(True, -1, temperature=0.8) == run(False, -1, temperature=0.8)      # sampled rows start early too
         else:   # bfloat16: another batch may round a near tie the other way; lengths and stop rules must hold
             assert [len(o) for o in got] == limits
             assert eos not in with_eos[0] and len(with_eos[0]) <= limits[0]

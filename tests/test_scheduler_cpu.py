@@ -165,14 +165,17 @@ def test_cancel(model_dirs):
 def test_sampling_is_reproducible_and_independent_of_the_batch(model_dirs):
     d, page = model_dirs["B"]
     ps = prompts(503, [9, 17, 40], seed=5)
-    def run(max_batch, budget):
+    def run(max_batch, budget, lookahead=False):
         model = make_model(d, page, max_batch=max_batch, budget=budget)
-        s = Scheduler(model)
+        s = Scheduler(model, lookahead=lookahead)
         for i, p in enumerate(ps):
             s.add(Request(f"r{i}", p, max_tokens=12, temperature=0.7, seed=11 + i, top_k=50, top_p=0.9))
-        return s.run()
+        out = s.run()
+        assert (s.steps_ahead > 0) == (lookahead and max_batch > 1)
+        return out
     a, b = run(1, 64), run(3, 7)
     assert a == b
+    assert run(3, 64, lookahead=True) == a       # the draw's counter is the same when the step starts early
     model = make_model(d, page)
     alone = model.generate(ps[1], max_tokens=12, params=SamplingParams(temperature=0.7, top_k=50, top_p=0.9, seed=12))
     assert alone == a["r1"]
