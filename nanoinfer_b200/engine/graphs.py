@@ -104,6 +104,7 @@ class DecodeGraphs:
         self.captured: Dict[Tuple[int, int], _Captured] = {}
         self.seen = set()
         self.pool = None
+        self.stream = None         # the side stream that captures
 
     @property
     def engine(self):
@@ -167,15 +168,25 @@ class DecodeGraphs:
         before = ops.launches
         # Freeing device memory or another graph while a stream captures invalidates the capture, and the
         # cyclic collector may free such objects at any allocation: keep it off until the capture ends.
-        gc.collect()
+        # The capture is begun and ended by hand on a side stream: the ``torch.cuda.graph`` context would
+        # collect garbage and empty the allocator's cache first, ~0.1 s per capture, which a short run with
+        # a dozen (batch, context) buckets notices.
         gc_was_on = gc.isenabled()
         gc.disable()
+        if self.stream is None:
+            self.stream = torch.cuda.Stream()
+        self.stream.wait_stream(torch.cuda.current_stream())
         try:
-            with torch.cuda.graph(graph, pool=self.pool):
-                logits = eng.model.forward(ctx, caches, want_rows)
+            with torch.cuda.stream(self.stream):
+                graph.capture_begin(pool=self.pool)
+                try:
+                    logits = eng.model.forward(ctx, caches, want_rows)
+                finally:
+                    graph.capture_end()
         finally:
             if gc_was_on:
                 gc.enable()
+        torch.cuda.current_stream().wait_stream(self.stream)
         cap = _Captured(graph, static, logits, ops.launches - before, _InputMirror(rb, widths, eng.device))
         assert cap.mirror.size == size
         self.captured[key] = cap
