@@ -24,7 +24,7 @@ def tdt(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "C"])
 def test_long_decoding_token_by_token(model_dirs, name, dtype):
     from nanoinfer_b200.engine import StepEntry
     d, page = model_dirs[name]

@@ -12,16 +12,17 @@ from replay_util import Trace, add_decode_tail, add_mixed, add_portions, add_who
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [1, 7, 33, 90, 200, 61], "B": [2, 9, 17, 64, 100, 150], "W": [3, 40, 77, 130, 58, 101]}
+LENGTHS = {"A": [1, 7, 33, 90, 200, 61], "B": [2, 9, 17, 64, 100, 150], "W": [3, 40, 77, 130, 58, 101],
+           "C": [5, 70, 300, 129, 260, 33]}      # C: heads of 64, prompts beyond 256 tokens (the kernels of the large models)
 
 
 def prompts_for(name, vocab):
-    g = torch.Generator().manual_seed({"A": 11, "B": 22, "W": 33}[name])
+    g = torch.Generator().manual_seed({"A": 11, "B": 22, "W": 33, "C": 44}[name])
     return {f"{name}{i}": torch.randint(0, vocab, (n,), generator=g).tolist() for i, n in enumerate(LENGTHS[name])}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "W"])
+@pytest.mark.parametrize("name", ["A", "B", "W", "C"])
 def test_replay_all_cuts(model_dirs, tmp_path, name, dtype):
     d, page = model_dirs[name]
     plain = PlainModel(d)

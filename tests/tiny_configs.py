@@ -27,4 +27,11 @@ TINY_W = dict(TINY_B, num_hidden_layers=3, hidden_size=144, num_attention_heads=
               sliding_window=24, max_window_layers=1, rms_norm_eps=3e-6, rope_theta=50000.0)
 TINY_W_PAGE = 8
 
-ALL = {"A": (TINY_A, TINY_A_PAGE), "B": (TINY_B, TINY_B_PAGE), "W": (TINY_W, TINY_W_PAGE)}
+# Heads of 64 and a prompt of a few hundred tokens reach the kernels that the large models run on: tcgen05
+# GEMMs (also on pairs of SMs), tcgen05 prefill attention, TMA decode attention.
+TINY_C = dict(TINY_A, num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=64, intermediate_size=640, vocab_size=1000, rope_theta=1000000.0, tie_word_embeddings=False,
+              max_position_embeddings=1024)
+TINY_C_PAGE = 16
+
+ALL = {"A": (TINY_A, TINY_A_PAGE), "B": (TINY_B, TINY_B_PAGE), "W": (TINY_W, TINY_W_PAGE), "C": (TINY_C, TINY_C_PAGE)}
