@@ -7,8 +7,8 @@
 // outside the pool and arrives as zeros. Slots of a held page beyond the context hold finite values
 // (the pool starts zeroed and only finite values are written), and their scores are masked.
 //
-// grid (splits, tokens, kv heads), 160 threads. A CTA walks over its tiles of 64 keys (aligned to
-// absolute multiples of 64) with STAGES tiles in flight: a producer warp issues the copies and runs
+// grid (splits, tokens, kv heads), 160 threads. A CTA walks over its tiles of 64 or 128 keys (aligned to
+// absolute multiples of the tile) with STAGES tiles in flight: a producer warp issues the copies and runs
 // ahead, a full and an empty mbarrier per stage hand the tiles back and forth, and no barrier of the
 // whole CTA stands in the loop. Four consumer warps take 16 keys of every tile each, keep their own
 // running (max, sum, output) and merge at the end. The rows of the mma tile are the query heads of
@@ -28,19 +28,23 @@ extern "C" int nib_attention_combine(const float* part_o, const float* part_ml, 
 
 namespace {
 
-constexpr int KEYS = 64;          // keys per tile
 constexpr int WARPS = 4;          // consumer warps: 16 keys of every tile each; one more warp fetches
 constexpr int THREADS = (WARPS + 1) * 32;
-constexpr int SUBTILE = KEYS * 128;   // 64 rows of 128 bytes (64 elements of a head), swizzled
+// Keys per tile: 128 for heads of 64 (a tile of 64 keys is only 16 KB there, and the fixed work per tile,
+// barrier waits and the softmax's shuffles, bounded the kernel at large batches), 64 for heads of 128.
+template <int HD> constexpr int keys_of() { return HD == 64 ? 128 : 64; }
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_dec_error = 0;   // 0, or (code << 16 | blockIdx.x) of the first wait that ran out
 
 template <int HD> struct Cfg {
+    static constexpr int KEYS = keys_of<HD>();
+    static constexpr int WKEYS = KEYS / WARPS;                // keys of a tile per consumer warp: 32 or 16
     static constexpr int SUB = HD / 64;                       // 64-element column blocks of a head
-    static constexpr int TILE = SUB * SUBTILE;                // K (or V) of 64 keys
+    static constexpr int SUBTILE = KEYS * 128;                // KEYS rows of 128 bytes (64 elements of a head), swizzled
+    static constexpr int TILE = SUB * SUBTILE;                // K (or V) of one tile
     static constexpr int STAGE = 2 * TILE;
-    static constexpr int STAGES = HD == 64 ? 4 : 3;
+    static constexpr int STAGES = 3;                          // 96 KB in flight, two CTAs per SM
     static constexpr int MERGE = WARPS * 16 * (HD + 4 + 2) * 4 + WARPS * 16 * 4;
     static constexpr int DATA = STAGES * STAGE > MERGE ? STAGES * STAGE : MERGE;
     static constexpr int SMEM = DATA + 1024 /* alignment */ + 64 /* barriers */;
@@ -88,6 +92,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot) {
     using C = Cfg<HD>;
+    constexpr int KEYS = C::KEYS, SUBTILE = C::SUBTILE, WKEYS = C::WKEYS, NT = WKEYS / 8;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + C::DATA);
@@ -183,9 +188,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
         // ldmatrix addresses inside a swizzled tile: row r (128 bytes), 16-byte chunk c at ((c ^ (r & 7)) << 4)
         const int mat = lane >> 3, rr = lane & 7;
-        const unsigned k_row = (unsigned)(warp * 16 + (mat >> 1) * 8 + rr) * 128u;   // keys 0-7 / 8-15, dims 0-7 / 8-15
+        const unsigned k_row = (unsigned)(warp * WKEYS + (mat >> 1) * 8 + rr) * 128u;   // keys 0-7 / 8-15, dims 0-7 / 8-15
         const unsigned k_half = mat & 1;
-        const unsigned v_row = (unsigned)(warp * 16 + (mat & 1) * 8 + rr) * 128u;    // transposed: keys 0-7 / 8-15 first
+        const unsigned v_row = (unsigned)(warp * WKEYS + (mat & 1) * 8 + rr) * 128u;    // transposed: keys 0-7 / 8-15 first
         const unsigned v_half = mat >> 1;
 
         for (int j = 0; j < n_mine; ++j) {
@@ -197,7 +202,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 break;
             }
             const unsigned kt = smem_u32(smem + st * C::STAGE), vt = kt + C::TILE;
-            if (FUSED && t_begin + j == t_last && p >= 0 && ((p & (KEYS - 1)) >> 4) == warp) {
+            if (FUSED && t_begin + j == t_last && p >= 0 && (p & (KEYS - 1)) / WKEYS == warp) {
                 // this step's own key (rotated) and value: into this warp's rows of the tile and into the page
                 const __nv_bfloat16* k_new = qkv + (size_t)token * q_stride + (size_t)(heads + kvh) * HD;
                 const __nv_bfloat16* v_new = qkv + (size_t)token * q_stride + (size_t)(heads + kv_heads + kvh) * HD;
@@ -222,26 +227,32 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 }
                 __syncwarp();
             }
-            float s[2][4];
-            s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
-            s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+            float s[NT][4];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk) {
-                unsigned b[4];
                 const unsigned chunk = (unsigned)((kk & 3) * 2) + k_half;
-                ldmatrix_x4_addr(b, kt + (kk >> 2) * SUBTILE + k_row + ((chunk ^ (unsigned)rr) << 4));
-                mma_bf16(s[0], q[kk], b[0], b[1]);
-                mma_bf16(s[1], q[kk], b[2], b[3]);
-            }
-            unsigned pfrag[1][4];
-            softmax_block<HD, 2>(s, pfrag, o, m_run, l_run, scale2, (t_begin + j) * KEYS + warp * 16, vis_lo, vis_hi, lane);
 #pragma unroll
-            for (int dp = 0; dp < HD / 16; ++dp) {
-                unsigned b[4];
-                const unsigned chunk = (unsigned)((dp & 3) * 2) + v_half;
-                ldmatrix_x4_trans_addr(b, vt + (dp >> 2) * SUBTILE + v_row + ((chunk ^ (unsigned)rr) << 4));
-                mma_bf16(o[2 * dp], pfrag[0], b[0], b[1]);
-                mma_bf16(o[2 * dp + 1], pfrag[0], b[2], b[3]);
+                for (int np = 0; np < NT / 2; ++np) {                    // 16 keys per ldmatrix.x4
+                    unsigned b[4];
+                    ldmatrix_x4_addr(b, kt + (kk >> 2) * SUBTILE + k_row + np * 16 * 128 + ((chunk ^ (unsigned)rr) << 4));
+                    mma_bf16(s[2 * np], q[kk], b[0], b[1]);
+                    mma_bf16(s[2 * np + 1], q[kk], b[2], b[3]);
+                }
+            }
+            unsigned pfrag[NT / 2][4];
+            softmax_block<HD, NT>(s, pfrag, o, m_run, l_run, scale2, (t_begin + j) * KEYS + warp * WKEYS, vis_lo, vis_hi, lane);
+#pragma unroll
+            for (int kb = 0; kb < NT / 2; ++kb) {
+#pragma unroll
+                for (int dp = 0; dp < HD / 16; ++dp) {
+                    unsigned b[4];
+                    const unsigned chunk = (unsigned)((dp & 3) * 2) + v_half;
+                    ldmatrix_x4_trans_addr(b, vt + (dp >> 2) * SUBTILE + v_row + kb * 16 * 128 + ((chunk ^ (unsigned)rr) << 4));
+                    mma_bf16(o[2 * dp], pfrag[kb], b[0], b[1]);
+                    mma_bf16(o[2 * dp + 1], pfrag[kb], b[2], b[3]);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[st]);            // this warp has read the stage

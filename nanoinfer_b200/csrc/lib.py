@@ -34,6 +34,20 @@ def _need(t: torch.Tensor, dtype, what: str, contiguous: bool = True):
         raise KernelError(f"{what}: tensor must be contiguous")
 
 
+class _StreamScope:
+    def __init__(self, ops):
+        self.ops = ops
+
+    def __enter__(self):
+        self.prev = self.ops._bound_stream
+        self.ops._bound_stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        self.ops._bound_stream = self.prev
+        return False
+
+
 class Kernels:
     """One instance per process; stateless apart from the loaded library."""
 
@@ -42,6 +56,7 @@ class Kernels:
     def __init__(self, lib_path: str):
         self.lib_path = lib_path
         self.launches = 0           # kernel launches issued through this object (graph replays add theirs)
+        self._bound_stream = None   # the stream of the enclosing stream_scope(), if any
         self.force_general_attention = False   # tests: run the general attention kernel for bfloat16 too
         self.fixed_decode_splits = 0           # tests: a fixed split count for the decode kernel
         self.force_mma_prefill = False         # tests: prompt portions on the mma.sync kernel instead of tcgen05
@@ -75,9 +90,16 @@ class Kernels:
         if rc != 0:
             raise KernelError(f"{what}: {self._lib.nib_last_error().decode()}")
 
-    @staticmethod
-    def _stream() -> c_void_p:
+    def _stream(self) -> c_void_p:
+        if self._bound_stream is not None:
+            return self._bound_stream
         return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def stream_scope(self):
+        """Within the scope the kernels launch on the stream that is current at its start, looked up once: a
+        forward pass issues some two hundred launches, and asking torch for the current stream costs about
+        as much as a launch. The caller must not switch streams inside the scope."""
+        return _StreamScope(self)
 
     def device_arch(self) -> int:
         return self._lib.nib_device_arch()
@@ -288,7 +310,7 @@ class Kernels:
                 n_dec += 1
         if n_dec:
             tma = self._decode_tma_ok(heads, kv_heads, head_dim, page_size)
-            splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window, tma)
+            splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window, tma, head_dim)
             part_o = part_ml = counters = None
             if splits > 1 and not self.separate_combine and n_dec * kv_heads <= 64 * 1024:
                 self.ensure_workspace(qkv.device)
@@ -365,7 +387,7 @@ class Kernels:
         if rotary is not None:
             cos, sin, rot = rotary
         tma = self._decode_tma_ok(heads, kv_heads, head_dim, page_size)
-        splits = self.decode_splits(n, kv_heads, max(ctx.host.ctx_lens), window, tma)
+        splits = self.decode_splits(n, kv_heads, max(ctx.host.ctx_lens), window, tma, head_dim)
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty(n * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
@@ -382,10 +404,11 @@ class Kernels:
         if splits > 1:
             self.launches += 1
 
-    def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int, tma: bool = False) -> int:
+    def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int, tma: bool = False,
+                      head_dim: int = 128) -> int:
         """Into how many CTAs the keys of a decoding token are split. The kernel with TMA page loads keeps
         several tiles in flight per CTA: about 256 CTAs in all (measured best from 1 to 64 requests), at
-        least four tiles each. The cp.async kernel: two key tiles per CTA (both are in flight at once, so a
+        least four of its tiles (128 keys for heads of 64, else 64) each. The cp.async kernel: two key tiles per CTA (both are in flight at once, so a
         CTA waits for memory once), as long as that does not make more CTAs than fill the GPU about eight
         times."""
         if self.fixed_decode_splits:
@@ -394,7 +417,8 @@ class Kernels:
         tiles = -(-keys // 64) + 1
         if tma:
             want = max(1, round(256 / max(1, n_tokens * kv_heads)))
-            return max(1, min(want, tiles // 4, 64))
+            tile_keys = 128 if head_dim == 64 else 64           # the kernel's tile
+            return max(1, min(want, -(-keys // tile_keys) // 4, 64))
         most = max(1, (8 * self.sm_count) // max(1, n_tokens * kv_heads))
         return max(1, min(-(-tiles // 2), most, 64))
 

@@ -70,6 +70,14 @@ class DecoderModel:
     def forward(self, ctx: StepContext, caches: List[LayerCache],
                 want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Runs ``ctx``'s tokens; returns 32-bit logits ``[len(want_rows), vocab]`` (None if nothing is wanted)."""
+        scope = getattr(self.rt.ops, "stream_scope", None)
+        if scope is None:
+            return self._forward(ctx, caches, want_rows)
+        with scope():       # one look-up of the current stream for the whole pass
+            return self._forward(ctx, caches, want_rows)
+
+    def _forward(self, ctx: StepContext, caches: List[LayerCache],
+                 want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         x32 = self.embedding.forward(ctx.token_ids, ctx)
         for pos in self.positions.values():
             pos.add_to_embedding(x32, ctx)
