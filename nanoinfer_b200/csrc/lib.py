@@ -72,6 +72,8 @@ class Kernels:
         self._ws_counters = None
         self._ws_attn_counters = None
         self.fuse_decode = True                # pure decode steps: rotation and cache write inside the attention kernel
+        self.fuse_ffn = False                  # norm + gate/up + down of a decode step in one cooperative kernel: measured slower
+                                               # (18.6 us against 13.2 us for the three kernels chained by dependent launch), so off
         self.decode_tma = True                 # decode attention with TMA page loads where the shape allows (else mma.sync + cp.async)
         self.separate_combine = True           # merge the decode splits in a second kernel (measured faster than letting the last CTA do it)
         try:
@@ -81,7 +83,7 @@ class Kernels:
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
                      "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_fused", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
-                     "nib_argmax", "nib_argmax_chunked", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
+                     "nib_argmax", "nib_argmax_chunked", "nib_ffn_decode", "nib_ffn_decode_supported", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -127,6 +129,7 @@ class Kernels:
             self._ws_scratch = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=device)
             self._ws_counters = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
             self._ws_attn_counters = torch.zeros(64 * 1024, dtype=torch.int32, device=device)
+            self._ws_ffn = torch.zeros(4, dtype=torch.int32, device=device)      # two barrier counters, an error word
             self._ws_argmax = torch.zeros(4096 * 64, dtype=torch.int64, device=device)
             self._ws_argmax_counters = torch.zeros(4096, dtype=torch.int32, device=device)
 
@@ -231,6 +234,36 @@ class Kernels:
         self._check(self._lib.nib_gemm_simt(_ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k),
                                             c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi), c_int(_DT[a.dtype]),
                                             self._stream()), "linear")
+
+    def can_fuse_ffn(self, dtype, tokens: int, hidden: int, inter: int, ldx: int) -> bool:
+        """True if ``ffn_decode`` takes this shape (bfloat16, up to 8 tokens, at most 64 rows of either matrix
+        per SM)."""
+        return self.fuse_ffn and dtype == torch.bfloat16 and not self.force_simt_gemm and self.gemm_route is None and \
+            self._lib.nib_ffn_decode_supported(c_int(tokens), c_int(hidden), c_int(inter), c_int(ldx)) == 1
+
+    def ffn_decode(self, x32, gain32, eps, w_gate_up, w_down):
+        """x32 += down(silu(gate(n)) * up(n)) with n = rmsnorm(x32) * gain, in one kernel (a decode step)."""
+        _need(x32, torch.float32, "ffn x", contiguous=False); _need(gain32, torch.float32, "ffn gain")
+        _need(w_gate_up, torch.bfloat16, "ffn gate/up"); _need(w_down, torch.bfloat16, "ffn down")
+        m, hidden = x32.shape
+        inter = w_down.shape[1]
+        if tuple(w_gate_up.shape) != (2 * inter, hidden) or w_down.shape[0] != hidden or x32.stride(1) != 1:
+            raise KernelError("ffn_decode: shapes do not fit")
+        self.ensure_workspace(x32.device)
+        act = torch.empty(m * inter, dtype=torch.bfloat16, device=x32.device)
+        self._check(self._lib.nib_ffn_decode(_ptr(x32), c_int(x32.stride(0)), _ptr(gain32), c_float(eps), _ptr(w_gate_up),
+                                             _ptr(w_down), _ptr(act), c_int(m), c_int(hidden), c_int(inter),
+                                             c_void_p(self._ws_ffn.data_ptr()), c_void_p(self._ws_ffn.data_ptr() + 8),
+                                             self._stream()), "ffn (fused decode)")
+
+    def ffn_decode_error(self) -> int:
+        """1 if the fused feed-forward kernel's grid barrier ran out of its bounded wait; synchronises and clears."""
+        if self._ws_scratch is None:
+            return 0
+        v = int(self._ws_ffn[2].item())
+        if v:
+            self._ws_ffn[2] = 0
+        return v
 
     def gemm_tc_error(self) -> int:
         """The error word of the tensor-core GEMM's bounded waits (0 = none); synchronises and clears it."""

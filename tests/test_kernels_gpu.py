@@ -420,6 +420,44 @@ def test_small_m_gemm(K, m, n, k, ksplit, cross):
         K.gemm_route = None
 
 
+@pytest.mark.parametrize("tokens", [1, 5, 8])
+@pytest.mark.parametrize("hidden,inter,eps", [(896, 4864, 1e-6), (192, 320, 1e-5), (1536, 8960, 1e-6), (64, 9472, 1e-3)])
+def test_fused_feed_forward_of_a_decode_step(K, tokens, hidden, inter, eps):
+    """RMSNorm + gate/up with SiLU*up + down + residual sum in one cooperative kernel (a barrier over the grid
+    between the two products), against the three separate kernels and against float64; twice in a row (the
+    barrier's counters are left ready); inside a row of a wider tensor."""
+    dtype = torch.bfloat16
+    x = rnd((tokens, hidden + 32), torch.float32, 300, scale=2.0)[:, :hidden]          # rows with a stride
+    gain = 1 + 0.1 * rnd((hidden,), torch.float32, 301)
+    w_gu = rnd((2 * inter, hidden), dtype, 302, scale=0.05)
+    w_d = rnd((hidden, inter), dtype, 303, scale=0.05)
+    K.fuse_ffn = True
+    try:
+        assert K.can_fuse_ffn(dtype, tokens, hidden, inter, x.stride(0))
+    finally:
+        K.fuse_ffn = False
+    xd = x.double()
+    n = (xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps) * gain.double()).to(dtype).double()
+    g, u = n @ w_gu[:inter].double().t(), n @ w_gu[inter:].double().t()
+    act = (g / (1 + torch.exp(-g)) * u).to(dtype).double()
+    want = xd + act @ w_d.double().t()
+    for _ in range(2):
+        got = x.clone()
+        got = torch.cat([got, torch.zeros(tokens, 32, device="cuda")], dim=1)[:, :hidden]
+        got.copy_(x)
+        K.ffn_decode(got, gain, eps, w_gu, w_d)
+        assert_close(got, want, torch.bfloat16, "fused feed-forward")
+    # the three kernels give the same within rounding
+    h = torch.empty(tokens, hidden, dtype=dtype, device="cuda")
+    K.rmsnorm(x.contiguous(), gain, eps, h)
+    a = torch.empty(tokens, inter, dtype=dtype, device="cuda")
+    K.linear_swiglu(h, w_gu, a)
+    sep = x.contiguous().clone()
+    K.linear(a, w_d, None, sep, "add")
+    assert_close(got, sep.double(), torch.bfloat16, "fused vs separate feed-forward")
+    assert K.ffn_decode_error() == 0
+
+
 @pytest.mark.parametrize("m,n,k,eps", [(1, 1152, 896, 1e-6), (8, 320, 192, 1e-5), (20, 200, 64, 1e-3), (64, 503, 320, 1e-6)])
 def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     """The decode GEMM that reads the 32-bit residual stream and applies RMSNorm on the fly, against the
