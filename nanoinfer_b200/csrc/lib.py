@@ -71,7 +71,8 @@ class Kernels:
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
         self._ws_attn_counters = None
-        self.fuse_decode = True                # pure decode steps: rotation and cache write inside the attention kernel
+        self.fuse_decode = False               # rotation and cache write inside the decode attention kernel: one launch fewer per layer, but
+                                               # measured equal (0.5B, batch 8) or 3-7 % slower (batch 1 and 64, heads of 128) than the separate kernel
         self.fuse_ffn = False                  # norm + gate/up + down of a decode step in one cooperative kernel: measured slower
                                                # (18.6 us against 13.2 us for the three kernels chained by dependent launch), so off
         self.decode_tma = True                 # decode attention with TMA page loads where the shape allows (else mma.sync + cp.async)

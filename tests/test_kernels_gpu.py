@@ -542,7 +542,11 @@ def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads
     rotary = (cos.cuda(), sin.cuda(), rot)
     raw = rnd((n, (heads + 2 * kv_heads) * hd), dtype, 122)
     scale = 1.0 / math.sqrt(hd)
-    assert K.can_fuse_decode(dtype, heads, kv_heads, hd, rotary)
+    K.fuse_decode = True
+    try:
+        assert K.can_fuse_decode(dtype, heads, kv_heads, hd, rotary)
+    finally:
+        K.fuse_decode = False
     for splits in (0, 1, 5):
         K.fixed_decode_splits, K.decode_tma = splits, tma
         try:
