@@ -3,11 +3,13 @@
 batch of 8 and a context of 4,096 tokens on ONE B200, with prefill of 2,048 tokens, the decode
 roofline and batch 1 / 64 points on the same JSON line.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 0.5b|1.5b|7b]
 
 A "step" is one decode step of the whole batch. ``value`` is decoded tokens per second over K steps
 timed with CUDA events on the launching stream; ``e2e`` is the same through the Python entry point
-(the scheduler: host token ids in, sampled ids out, every step). Inputs larger than L2: every step
+(the scheduler with lookahead, as ``Model.generate`` and the serve command run it: host token ids in,
+sampled ids out, every step; each step's inputs go up from pinned memory and each step's tokens come
+back, the latter while the next step already runs). Inputs larger than L2: every step
 reads all weights (~1 GB) and the live requests' cache, several times the 126 MB L2.
 """
 from __future__ import annotations
