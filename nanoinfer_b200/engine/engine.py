@@ -157,6 +157,9 @@ class Engine:
         """One host-to-device copy of the step's inputs, from pinned memory when the device is a GPU."""
         self.last_h2d_bytes = int(flat.nbytes)
         if self.device.type != "cuda":
+            if static is not None:
+                static.copy_(torch.from_numpy(flat))
+                return static
             return torch.from_numpy(flat).to(self.device)
         if self._stage is None or self._stage.numel() < flat.size:
             self._stage = torch.empty(max(4096, 2 * flat.size), dtype=torch.int32).pin_memory()

@@ -48,9 +48,13 @@ class _InputMirror:
     def __init__(self, rb: int, widths: List[int], device: torch.device):
         sizes = [rb, rb, rb, rb + 1, rb, rb, rb] + [rb * w for w in widths]
         self.size = sum(sizes)
-        self.host = torch.empty(self.size, dtype=torch.int32).pin_memory()
-        self.event = torch.cuda.Event()
-        self.event.record()
+        on_gpu = torch.device(device).type == "cuda"
+        self.host = torch.empty(self.size, dtype=torch.int32)
+        self.event = None                   # on a host backend (tests of the layout) nothing is asynchronous
+        if on_gpu:
+            self.host = self.host.pin_memory()
+            self.event = torch.cuda.Event()
+            self.event.record()
         h = self.host.numpy()
         offs = np.concatenate([[0], np.cumsum(sizes)])
         cut = [h[offs[i]:offs[i + 1]] for i in range(len(sizes))]
@@ -67,7 +71,8 @@ class _InputMirror:
         self.row_ver = [-1] * rb
 
     def fill(self, entries) -> None:
-        self.event.synchronize()            # the previous copy has left the buffer
+        if self.event is not None:
+            self.event.synchronize()        # the previous copy has left the buffer
         n = len(entries)
         self.tok[:n] = [e.tokens[0] for e in entries]
         lens = np.fromiter((e.request.length for e in entries), dtype=np.int32, count=n)
@@ -92,7 +97,8 @@ class _InputMirror:
 
     def send(self, device_buffer: torch.Tensor) -> int:
         device_buffer.copy_(self.host, non_blocking=True)
-        self.event.record()
+        if self.event is not None:
+            self.event.record()
         return self.size * 4
 
 

@@ -109,3 +109,47 @@ def test_step_errors(model_dirs):
         eng.step([StepEntry(rc, [1], [0])])
     eng.close(rc)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("name", ["B", "W"])
+def test_graph_input_mirror_equals_the_built_context(model_dirs, name):
+    """A captured decode graph reads its inputs from a buffer that a host mirror refreshes row by row. Whatever
+    happens to the rows (requests decode on, one ends and the others move up, a new one takes the first
+    row, the batch shrinks and grows, a window gives pages back), the mirror must hold exactly what
+    ``Engine.build_context`` builds for the same padded batch."""
+    from nanoinfer_b200.engine.graphs import _InputMirror
+    d, page = model_dirs[name]
+    eng = make_engine(d, page, num_pages=96)
+    vocab = PlainModel(d).cfg["vocab"]
+    rng = np.random.default_rng(5)
+    rb, widths = 4, [16 for _ in eng.cache.groups]
+    mirror = _InputMirror(rb, widths, torch.device("cpu"))
+    static = torch.empty(mirror.size, dtype=torch.int32)
+    live = {}
+
+    def prompt(k, n):
+        live[k] = eng.open(k)
+        eng.step([StepEntry(live[k], rng.integers(0, vocab, n).tolist(), [])])
+
+    def decode(order, steps):
+        for _ in range(steps):
+            entries = [StepEntry(live[k], [int(rng.integers(0, vocab))], [0]) for k in order]
+            for e in entries:                        # what Engine.step does before it builds the inputs
+                eng.cache.extend(e.request, 1)
+            eng.build_context(entries, pad_to=rb, widths=widths, static=static)
+            mirror.fill(entries)
+            assert torch.equal(mirror.host, static), f"{name}: rows {order}"
+            for e in entries:
+                eng.cache.commit(e.request, 1)
+
+    prompt("a", 30); prompt("b", 7); prompt("c", 19)
+    decode("abc", 20)
+    eng.close(live.pop("a"))
+    decode("bc", 6)
+    prompt("d", 3)
+    decode("dbc", 30)               # W: the window passes whole pages here and their entries become -1
+    decode("c", 5)
+    decode("cbd", 10)
+    for rc in live.values():
+        eng.close(rc)
+    eng.cache.check()
