@@ -14,8 +14,10 @@ from .tokenizer import load_tokenizer
 
 
 def add_model_args(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--model-dir", "--weights-dir", dest="model_dir", default=None,
-                   help="folder with config.json and model.safetensors")
+    p.add_argument("--model-dir", "--weights-dir", "--model", dest="model_dir", default=None,
+                   help="folder with config.json and model.safetensors (the reference's --model takes a hub id; "
+                        "there is no network here, so this takes a local folder)")
+    p.add_argument("--device", default="cuda", help="the reference's option; this engine runs on a CUDA device only")
     p.add_argument("--random-weights", metavar="CONFIG_JSON", default=None,
                    help="write a random-weights model folder from this config.json file and use it")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
@@ -36,7 +38,13 @@ def add_sampling_args(p: argparse.ArgumentParser) -> None:
 
 
 def resolve_model_dir(args) -> str:
+    import os
+    if not str(getattr(args, "device", "cuda")).startswith("cuda"):
+        raise SystemExit(f"--device {args.device}: this engine has no CPU path; give a CUDA device")
     if args.model_dir:
+        if not os.path.isdir(args.model_dir):
+            raise SystemExit(f"{args.model_dir} is not a folder; models are read from a local folder with "
+                             f"config.json and model.safetensors (nothing is downloaded)")
         return args.model_dir
     if args.random_weights:
         import json
