@@ -28,7 +28,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Layer sizes of the benchmark model: BASELINE.json configs[2], the Qwen2.5-0.5B shape.
+# Layer sizes of the benchmark model: the Qwen2.5-0.5B shape, the reference's headline configuration.
 MODEL = {
     "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 24, "hidden_size": 896,
     "num_attention_heads": 14, "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 4864,

@@ -181,3 +181,52 @@ def test_sampling_is_reproducible_and_independent_of_the_batch(model_dirs):
     assert alone == a["r1"]
     other = model.generate(ps[1], max_tokens=12, params=SamplingParams(temperature=0.7, top_k=50, top_p=0.9, seed=13))
     assert other != alone
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_arrivals_cancels_and_tight_pools(model_dirs, seed):
+    """A seeded random run: requests arrive at random steps, some are cancelled at random steps, the pool,
+    the batch and the token budget are drawn small enough that prompts are cut and requests preempted,
+    with and without lookahead. Whatever happens, every output is generation alone (cut short where the
+    request was cancelled), the manager's books balance after every step and nothing stays held."""
+    import random
+    rnd = random.Random(1000 + seed)
+    name = "B" if seed % 2 else "A"
+    d, page = model_dirs[name]
+    vocab = 503 if name == "B" else 256
+    plain = PlainModel(d)
+    n_req = rnd.randint(5, 8)
+    lengths = [rnd.choice([1, 2, 3, 5, 9, 17, 26, 33]) for _ in range(n_req)]
+    limits = [rnd.randint(1, 12) for _ in range(n_req)]
+    ps = prompts(vocab, lengths, seed=50 + seed)
+    alone = [plain.greedy(p, n) for p, n in zip(ps, limits)]
+    largest = max(-(-(l + n) // page) for l, n in zip(lengths, limits))
+    num_pages = largest + rnd.randint(1, 2 * largest)          # the largest request fits; not all of them
+    max_batch = rnd.randint(1, 4)
+    budget = max(max_batch, rnd.choice([2, 5, 13, 64]))      # at least one token for each decoding request
+    model = make_model(d, page, num_pages=num_pages, max_batch=max_batch, budget=budget)
+    s = Scheduler(model, lookahead=bool(seed & 2))
+    arrive = sorted((rnd.randint(0, 25), i) for i in range(n_req))
+    cancel_at = {i: rnd.randint(1, 40) for i in range(n_req) if rnd.random() < 0.3}
+    cancelled = set()
+    step = 0
+    while arrive or s.has_work():
+        while arrive and arrive[0][0] <= step:
+            _, i = arrive.pop(0)
+            s.add(Request(f"r{i}", ps[i], max_tokens=limits[i]))
+        for i, at in cancel_at.items():
+            if at == step and s.cancel(f"r{i}"):
+                cancelled.add(i)
+        if s.has_work():
+            s.step()
+        model.engine.cache.check()
+        step += 1
+        assert step < 2000, "the scheduler makes no progress"
+    for i in range(n_req):
+        out = s.finished[f"r{i}"]
+        if i in cancelled:
+            assert out == alone[i][:len(out)], (seed, i)
+        else:
+            assert out == alone[i], (seed, i, name, num_pages, max_batch, budget)
+    assert s._inflight is None
+    assert model.engine.cache.num_free() == num_pages and not model.engine.cache.live
