@@ -153,3 +153,57 @@ def test_graph_input_mirror_equals_the_built_context(model_dirs, name):
     for rc in live.values():
         eng.close(rc)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("name,seed", [("A", 0), ("B", 1), ("W", 2), ("B", 3), ("W", 4), ("A", 5)])
+def test_random_traces_equal_plain(model_dirs, name, seed):
+    """Seeded random traces: up to four live requests, each step a random subset of them (a request may sit
+    a step out) with random portions from one token up, random wanted places, and a pool that only just
+    holds the live requests so that pages change hands. Every wanted row equals the plain model's."""
+    import random
+    rnd = random.Random(77 + seed)
+    d, page = model_dirs[name]
+    plain = PlainModel(d)
+    eng_probe = make_engine(d, page, num_pages=4)
+    vocab = eng_probe.vocab_size
+    g = torch.Generator().manual_seed(100 + seed)
+    lengths = [rnd.randint(1, 70) for _ in range(7)]
+    prompts = {f"q{i}": torch.randint(0, vocab, (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+    want = {k: plain.logits(v) for k, v in prompts.items()}
+    pages_of = {k: -(-len(v) // page) for k, v in prompts.items()}
+    top4 = sum(sorted(pages_of.values())[-4:])
+    num_pages = max(max(pages_of.values()), top4 - rnd.randint(0, top4 // 3))
+    eng = make_engine(d, page, num_pages=num_pages)
+    fed = {k: 0 for k in prompts}
+    live, waiting = {}, list(prompts)
+    worst = 0.0
+    steps = 0
+    while waiting or live:
+        steps += 1
+        assert steps < 5000
+        while waiting and len(live) < 4:
+            k = waiting[0]
+            if sum(pages_of[j] for j in live) + pages_of[k] > num_pages:
+                break
+            live[waiting.pop(0)] = eng.open(k)
+        chosen = [k for k in live if rnd.random() < 0.8] or [next(iter(live))]
+        entries, keys = [], []
+        for k in chosen:
+            left = len(prompts[k]) - fed[k]
+            n = min(left, rnd.choice([1, 1, 2, 3, 7, 16, 29]))
+            places = sorted(rnd.sample(range(n), rnd.randint(0, n)))
+            entries.append(StepEntry(live[k], prompts[k][fed[k]:fed[k] + n], places))
+            keys.append((k, fed[k], places))
+            fed[k] += n
+        logits = eng.step(entries)
+        row = 0
+        for k, start, places in keys:
+            for p in places:
+                worst = max(worst, (logits[row].double().cpu() - want[k][start + p]).abs().max().item())
+                row += 1
+        assert (0 if logits is None else logits.shape[0]) == row
+        for k in [k for k in live if fed[k] == len(prompts[k])]:
+            eng.close(live.pop(k))
+        eng.cache.check()
+    assert worst < 1e-4, worst
+    assert eng.cache.num_free(0) == num_pages
