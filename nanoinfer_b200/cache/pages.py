@@ -3,7 +3,8 @@
 A page holds ``page_size`` consecutive positions of one request; one page id addresses the same
 page in every layer of its cache group. Groups of layers with different needs (all keys; a window
 of them) have pools and block tables of their own. Pages go back to the pool when a request
-ends and when a window has passed them, and are handed out again.
+ends and when a window has passed them, and are handed out again. The pool's books (free stack,
+reference counts) are kept in native code (``csrc/host/page_pool.cpp``); tables and slots here.
 
 Reference: cpp/src/paged.cpp:17-71 (free list as a stack handing out 0,1,2,...; reference counts;
 allocate throws when empty; double free throws), cpp/src/paged.cpp:93-127 (block table grown
@@ -12,6 +13,7 @@ and no windows (cpp/src/config.hpp:55-57 holds the fields unused).
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -24,48 +26,109 @@ class OutOfSlots(RuntimeError):
     """Every per-request state slot is taken."""
 
 
+_host_lib = None
+
+
+def _host():
+    """The host runtime library (built with the host compiler at first use), with its signatures set."""
+    global _host_lib
+    if _host_lib is None:
+        from ..csrc.build import build_host
+        lib = ctypes.CDLL(build_host())
+        i32, ptr, i32p = ctypes.c_int32, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)
+        if lib.nibh_abi_version() != 1:
+            raise RuntimeError("the host runtime library is of another version than this package")
+        lib.nibh_pool_create.restype, lib.nibh_pool_create.argtypes = ptr, [i32]
+        lib.nibh_pool_destroy.restype, lib.nibh_pool_destroy.argtypes = None, [ptr]
+        lib.nibh_pool_num_free.restype, lib.nibh_pool_num_free.argtypes = i32, [ptr]
+        lib.nibh_pool_allocate.restype, lib.nibh_pool_allocate.argtypes = i32, [ptr, i32, i32p]
+        lib.nibh_pool_incref.restype, lib.nibh_pool_incref.argtypes = i32, [ptr, i32]
+        lib.nibh_pool_free.restype, lib.nibh_pool_free.argtypes = i32, [ptr, i32p, i32, i32p]
+        lib.nibh_pool_refcount.restype, lib.nibh_pool_refcount.argtypes = i32, [ptr, i32]
+        lib.nibh_pool_free_list.restype, lib.nibh_pool_free_list.argtypes = i32, [ptr, i32p, i32]
+        _host_lib = lib
+    return _host_lib
+
+
+_EMPTY, _BAD_PAGE, _NOT_HELD = -1, -2, -3
+
+
 class PagePool:
-    """Page ids ``0..num_pages-1`` of one cache group, with reference counts."""
+    """Page ids ``0..num_pages-1`` of one cache group, with reference counts. The books are kept by the
+    native allocator (``csrc/host/page_pool.cpp``); this class turns its status codes into exceptions."""
 
     def __init__(self, num_pages: int):
         if num_pages <= 0:
             raise ValueError("num_pages must be > 0")
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))  # pop() hands out 0, 1, 2, ...
-        self._ref = [0] * num_pages
+        self._lib = _host()
+        self._pool = ctypes.c_void_p(self._lib.nibh_pool_create(num_pages))
+        if not self._pool:
+            raise MemoryError(f"no memory for a pool of {num_pages} pages")
+        self._one = (ctypes.c_int32 * 1)()
+
+    def __del__(self):
+        pool, self._pool = getattr(self, "_pool", None), None
+        if pool:
+            self._lib.nibh_pool_destroy(pool)
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.nibh_pool_num_free(self._pool)
 
     def allocate(self) -> int:
-        if not self._free:
+        if self._lib.nibh_pool_allocate(self._pool, 1, self._one) != 0:
             raise OutOfPages("page pool is empty")
-        p = self._free.pop()
-        self._ref[p] = 1
-        return p
+        return self._one[0]
+
+    def allocate_many(self, n: int) -> List[int]:
+        """``n`` pages, all of them or none (``OutOfPages``), in the order a loop of ``allocate`` gives."""
+        out = (ctypes.c_int32 * max(n, 1))()
+        if self._lib.nibh_pool_allocate(self._pool, n, out) != 0:
+            raise OutOfPages(f"{n} pages asked for, {self.num_free} are free")
+        return out[:n]
 
     def incref(self, page: int) -> None:
-        self._check(page)
-        if self._ref[page] <= 0:
-            raise RuntimeError(f"incref of free page {page}")
-        self._ref[page] += 1
+        self._raise(self._lib.nibh_pool_incref(self._pool, page), page, "incref of free page {}")
 
     def free(self, page: int) -> None:
         self._check(page)
-        if self._ref[page] <= 0:
-            raise RuntimeError(f"page {page} freed twice")
-        self._ref[page] -= 1
-        if self._ref[page] == 0:
-            self._free.append(page)
+        self._one[0] = page
+        self._raise(self._lib.nibh_pool_free(self._pool, self._one, 1, None), page, "page {} freed twice")
+
+    def free_many(self, pages: Sequence[int]) -> None:
+        """Drops one reference of every page in ``pages``; entries below zero (no page) are skipped."""
+        n = len(pages)
+        arr = (ctypes.c_int32 * max(n, 1))(*pages)
+        done = ctypes.c_int32(0)
+        status = self._lib.nibh_pool_free(self._pool, arr, n, ctypes.byref(done))
+        if status != 0:
+            self._raise(status, pages[done.value], "page {} freed twice")
 
     def refcount(self, page: int) -> int:
-        self._check(page)
-        return self._ref[page]
+        r = self._lib.nibh_pool_refcount(self._pool, page)
+        if r < 0:
+            self._raise(r, page, "")
+        return r
+
+    def free_pages(self) -> List[int]:
+        """The free list, bottom of the stack first (the last one is handed out next)."""
+        out = (ctypes.c_int32 * self.num_pages)()
+        n = self._lib.nibh_pool_free_list(self._pool, out, self.num_pages)
+        return out[:n]
 
     def _check(self, page: int) -> None:
         if not (0 <= page < self.num_pages):
             raise IndexError(f"page id {page} outside 0..{self.num_pages - 1}")
+
+    def _raise(self, status: int, page: int, not_held: str) -> None:
+        if status == 0:
+            return
+        if status == _BAD_PAGE:
+            raise IndexError(f"page id {page} outside 0..{self.num_pages - 1}")
+        if status == _NOT_HELD:
+            raise RuntimeError(not_held.format(page))
+        raise RuntimeError(f"page allocator: status {status}")
 
 
 @dataclass(frozen=True)
@@ -103,6 +166,7 @@ class CacheManager:
         self.page_size = page_size
         self.num_pages = num_pages
         self.pools = [PagePool(num_pages) for _ in self.groups]
+        self._window_groups = [g for g, spec in enumerate(self.groups) if spec.window]   # the others never return pages early
         self.max_requests = max_requests
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.live: Dict[object, RequestCache] = {}
@@ -124,9 +188,7 @@ class CacheManager:
         if rc.closed:
             raise RuntimeError(f"request {rc.request_id!r} closed twice")
         for g, table in enumerate(rc.tables):
-            for p in table:
-                if p >= 0:
-                    self.pools[g].free(p)
+            self.pools[g].free_many(table)
             table.clear()
         rc.closed = True
         self._free_slots.append(rc.slot)
@@ -158,15 +220,21 @@ class CacheManager:
 
     def extend(self, rc: RequestCache, n_new: int) -> None:
         """Allocate the pages for the next ``n_new`` positions (all of them, or none and OutOfPages)."""
+        end = rc.length + n_new
+        ps = self.page_size
+        for table in rc.tables:
+            if end > len(table) * ps:
+                break
+        else:
+            return                      # the usual decode step: the last page still has room
         need = self.pages_needed(rc, n_new)
         for g, k in enumerate(need):
             if k > self.pools[g].num_free:
                 raise OutOfPages(
                     f"request {rc.request_id!r} needs {k} pages of group {g}, {self.pools[g].num_free} are free")
         for g, k in enumerate(need):
-            for _ in range(k):
-                rc.tables[g].append(self.pools[g].allocate())
             if k:
+                rc.tables[g].extend(self.pools[g].allocate_many(k))
                 rc.version += 1
 
     def commit(self, rc: RequestCache, n_new: int) -> None:
@@ -175,7 +243,7 @@ class CacheManager:
         for table in rc.tables:
             if rc.length > len(table) * self.page_size:
                 raise RuntimeError("commit beyond the pages held")
-        for g in range(len(self.groups)):
+        for g in self._window_groups:
             first = self._first_needed_page(g, rc.length)
             table = rc.tables[g]
             for lp in range(rc.first_live[g], min(first, len(table))):
@@ -208,8 +276,9 @@ class CacheManager:
                 for p in rc.tables[g]:
                     if p >= 0:
                         held[p] = held.get(p, 0) + 1
-            free = set(pool._free)
-            if len(free) != len(pool._free):
+            free_list = pool.free_pages()
+            free = set(free_list)
+            if len(free) != len(free_list):
                 raise AssertionError(f"group {g}: a page is on the free list twice")
             for p in range(pool.num_pages):
                 n = held.get(p, 0)

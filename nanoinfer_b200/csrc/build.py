@@ -1,5 +1,7 @@
 """Builds the kernel library (``libnanoinfer_b200.so``) from the ``.cu`` files of this folder with nvcc,
-for sm_100a, into ``_build/`` beside them (or, when that is not writable, a per-user temp folder).
+for sm_100a, into ``_build/`` beside them (or, when that is not writable, a per-user temp folder), and the
+host runtime library (``libnanoinfer_b200_host.so``: the page allocator) from ``host/*.cpp`` with the host
+compiler alone.
 
 Nothing but the CUDA toolkit is needed: the sources include no framework header, so a cold build
 takes well under a minute. It happens at the first call that needs a kernel, prints a line per
@@ -135,5 +137,63 @@ def build(force: bool = False, verbose: bool = True) -> str:
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
+HOST_LIB_NAME = "libnanoinfer_b200_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    raise BuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++); "
+                     "the cache manager's page allocator is native code")
+
+
+def host_sources() -> List[str]:
+    d = os.path.join(HERE, "host")
+    return sorted(os.path.join("host", f) for f in os.listdir(d) if f.endswith((".cpp", ".h")))
+
+
+def build_host(force: bool = False, verbose: bool = True) -> str:
+    """Returns the path of the host runtime library, building it (a second or two) if its sources changed."""
+    d = build_dir()
+    lib = os.path.join(d, HOST_LIB_NAME)
+    stamp = os.path.join(d, "build_host.json")
+    h = hashlib.sha256(" ".join(HOST_FLAGS).encode())
+    srcs = host_sources()
+    for f in srcs:
+        h.update(f.encode())
+        with open(os.path.join(HERE, f), "rb") as fh:
+            h.update(fh.read())
+    digest = h.hexdigest()
+    with open(os.path.join(d, ".lock_host"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and os.path.isfile(lib) and os.path.isfile(stamp):
+                try:
+                    with open(stamp) as f:
+                        if json.load(f).get("digest") == digest:
+                            return lib
+                except (OSError, ValueError):
+                    pass
+            cxx = find_cxx()
+            if verbose:
+                _say(f"building {HOST_LIB_NAME} in {d} ...")
+            tmp = lib + f".tmp{os.getpid()}"
+            cpp = [os.path.join(HERE, f) for f in srcs if f.endswith(".cpp")]
+            r = subprocess.run([cxx] + HOST_FLAGS + ["-o", tmp] + cpp, stdout=subprocess.PIPE,
+                               stderr=subprocess.STDOUT, text=True)
+            if r.returncode != 0:
+                raise BuildError(f"{cxx} failed on {HOST_LIB_NAME}:\n{r.stdout}")
+            os.replace(tmp, lib)
+            with open(stamp, "w") as f:
+                json.dump({"digest": digest, "flags": HOST_FLAGS, "sources": srcs}, f)
+            return lib
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
 if __name__ == "__main__":
+    print(build_host(force="--force" in sys.argv))
     print(build(force="--force" in sys.argv))

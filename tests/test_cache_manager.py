@@ -27,6 +27,67 @@ def test_pool_hands_out_in_order_and_refuses_double_free():
     assert pool.num_free == 1
 
 
+def test_pool_takes_and_returns_many_pages_at_once():
+    pool = PagePool(6)
+    assert pool.allocate_many(4) == [0, 1, 2, 3]
+    with pytest.raises(OutOfPages):
+        pool.allocate_many(3)                       # all or none: the two free pages stay free
+    assert pool.num_free == 2 and pool.free_pages() == [5, 4]
+    assert pool.allocate_many(0) == []
+    pool.incref(2)
+    pool.free_many([1, -1, 2, 3])                   # -1 marks "no page" in a block table
+    assert [pool.refcount(p) for p in range(6)] == [1, 0, 1, 0, 0, 0]
+    assert pool.free_pages() == [5, 4, 1, 3]        # the page given back last is handed out next
+    assert pool.allocate_many(2) == [3, 1]
+    with pytest.raises(RuntimeError, match="page 4 freed twice"):
+        pool.free_many([0, 4, 2])                   # stops at the page that is not held
+    assert pool.refcount(0) == 0 and pool.refcount(2) == 1
+    with pytest.raises(IndexError):
+        pool.free_many([9])
+    with pytest.raises(IndexError):
+        pool.refcount(-1)
+    with pytest.raises(ValueError):
+        PagePool(0)
+
+
+def test_pool_under_random_orders_agrees_with_a_plain_model_of_it():
+    """The native allocator against a few lines of Python that keep the same books."""
+    rnd = random.Random(5)
+    n = 17
+    pool = PagePool(n)
+    free, ref = list(range(n - 1, -1, -1)), [0] * n
+    held = []
+    for _ in range(3000):
+        op = rnd.random()
+        if op < 0.45:
+            k = rnd.randint(0, 4)
+            if k > len(free):
+                with pytest.raises(OutOfPages):
+                    pool.allocate_many(k)
+            else:
+                want = [free.pop() for _ in range(k)]
+                for p in want:
+                    ref[p] = 1
+                assert pool.allocate_many(k) == want
+                held += want
+        elif op < 0.55 and held:
+            p = rnd.choice(held)
+            pool.incref(p)
+            ref[p] += 1
+            held.append(p)
+        elif held:
+            rnd.shuffle(held)
+            k = rnd.randint(1, min(5, len(held)))
+            give, held = held[:k], held[k:]
+            pool.free_many(give)
+            for p in give:
+                ref[p] -= 1
+                if ref[p] == 0:
+                    free.append(p)
+        assert pool.num_free == len(free) and pool.free_pages() == free
+        assert [pool.refcount(p) for p in range(n)] == ref
+
+
 def groups(window=0):
     g = [GroupSpec(2, 16, 0, (0, 1))]
     if window:
