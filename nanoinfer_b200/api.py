@@ -4,7 +4,8 @@
   cpp/bindings/nicpp.cpp:207-217; ``nanoinfer.weights.load_model``, nanoinfer/weights.py:25-71).
 * ``Model.generate(prompt_ids, max_tokens=20, params=SamplingParams(), seed=0, eos_id=-1) -> list[int]``
   (cpp/bindings/nicpp.cpp:296-316; loop: cpp/src/generate.cpp:10-42).
-* ``generate(model, tokenizer, prompt, max_tokens=32, sampling=None) -> str`` (nanoinfer/generate.py:33-85).
+* ``generate(model, tokenizer, prompt, max_tokens=32, use_cache=True, sampling=None) -> str``
+  (nanoinfer/generate.py:33-85).
 * ``Request`` and ``Scheduler`` for many requests (cpp/python/ni/scheduler.py).
 """
 from __future__ import annotations
@@ -28,16 +29,49 @@ class Model:
         self.eos_token_id = self.engine.plan.eos_token_id
 
     def generate(self, prompt_ids: List[int], max_tokens: int = 20, params: Optional[SamplingParams] = None,
-                 seed: int = 0, eos_id: int = -1) -> List[int]:
-        """Continue ``prompt_ids`` by up to ``max_tokens`` tokens; EOS ends generation and is not returned."""
+                 seed: int = 0, eos_id: int = -1, use_cache: bool = True) -> List[int]:
+        """Continue ``prompt_ids`` by up to ``max_tokens`` tokens; EOS ends generation and is not returned.
+
+        ``use_cache=False`` is the reference's ``--no-cache`` (nanoinfer/generate.py:44-60, 94-98): every
+        token is computed from the whole sequence so far with nothing kept between tokens. It is slow and
+        exists to check the cache: both ways give the same tokens."""
         params = params or SamplingParams()
         if params.seed is not None:
             seed = params.seed
+        if not use_cache:
+            return self._generate_recomputing(list(prompt_ids), max_tokens, params, seed, eos_id)
         sched = Scheduler(self, lookahead=True)      # run() to the end: the one-step lag of the host is not seen
         sched.add(Request("generate", list(prompt_ids), max_tokens=max_tokens, temperature=params.temperature,
                           top_k=params.k, top_p=params.p, repetition_penalty=params.repetition_penalty,
                           seed=seed, eos_id=eos_id))
         return sched.run()["generate"]
+
+
+    def _generate_recomputing(self, ids: List[int], max_tokens: int, params: SamplingParams, seed: int,
+                              eos_id: int) -> List[int]:
+        from .engine.engine import StepEntry
+        from .sampling.sampler import SampleRow
+        eos = eos_id if eos_id >= 0 else self.eos_token_id
+        out: List[int] = []
+        if not ids:
+            return out
+        budget = self.engine.engine_config.max_tokens_per_step
+        while len(out) < max_tokens:
+            rc = self.engine.open("generate-no-cache")
+            try:
+                for start in range(0, len(ids), budget):        # the whole sequence again, in portions
+                    part = ids[start:start + budget]
+                    last = start + len(part) == len(ids)
+                    logits = self.engine.step([StepEntry(rc, part, [len(part) - 1] if last else [])])
+            finally:
+                self.engine.close(rc)
+            context = ids if params.repetition_penalty != 1.0 else None
+            token = self.sampler.sample(logits, [SampleRow(params, context, len(out), seed)])[0]
+            if token == eos:
+                break
+            out.append(token)
+            ids = ids + [token]
+        return out
 
 
 def load_model(model_dir: str, dtype: str = "bfloat16", page_size: int = 16, num_pages: int = 0,
@@ -51,12 +85,13 @@ def load_model(model_dir: str, dtype: str = "bfloat16", page_size: int = 16, num
     return Model(model_dir, cfg)
 
 
-def generate(model: Model, tokenizer, prompt: str, max_tokens: int = 32,
+def generate(model: Model, tokenizer, prompt: str, max_tokens: int = 32, use_cache: bool = True,
              sampling: Optional[SamplingParams] = None) -> str:
-    """Text in, text out. ``tokenizer`` needs ``encode(str) -> ids`` and ``decode(ids) -> str``."""
+    """Text in, text out. ``tokenizer`` needs ``encode(str) -> ids`` and ``decode(ids) -> str``.
+    ``use_cache=False`` recomputes the whole sequence for every token (see ``Model.generate``)."""
     enc = tokenizer.encode(prompt)
     ids = list(getattr(enc, "ids", enc))
     eos = getattr(tokenizer, "eos_token_id", None)
     out = model.generate(ids, max_tokens=max_tokens, params=sampling or SamplingParams(),
-                         eos_id=eos if eos is not None else -1)
+                         eos_id=eos if eos is not None else -1, use_cache=use_cache)
     return tokenizer.decode(out)

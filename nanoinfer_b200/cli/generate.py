@@ -64,6 +64,8 @@ def main(argv=None) -> int:
     p.add_argument("--prompt", required=True, help="text (with tokenizer.json in the model folder) or token ids")
     add_model_args(p)
     add_sampling_args(p)
+    p.add_argument("--no-cache", dest="use_cache", action="store_false",
+                   help="recompute the whole sequence for every token (slow; checks the cache: same output)")
     args = p.parse_args(argv)
 
     from ..api import generate, load_model
@@ -75,7 +77,7 @@ def main(argv=None) -> int:
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             repetition_penalty=args.repetition_penalty, seed=args.seed)
     print(f"Prompt: {args.prompt}")
-    print(f"Completion: {generate(model, tok, args.prompt, max_tokens=args.max_tokens, sampling=params)}")
+    print(f"Completion: {generate(model, tok, args.prompt, max_tokens=args.max_tokens, use_cache=args.use_cache, sampling=params)}")
     return 0
 
 

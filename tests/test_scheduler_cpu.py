@@ -230,3 +230,22 @@ def test_random_arrivals_cancels_and_tight_pools(model_dirs, seed):
             assert out == alone[i], (seed, i, name, num_pages, max_batch, budget)
     assert s._inflight is None
     assert model.engine.cache.num_free() == num_pages and not model.engine.cache.live
+
+
+def test_generation_without_the_cache_gives_the_same_tokens(model_dirs):
+    """``use_cache=False`` (the reference's --no-cache) recomputes the whole sequence for every token, in
+    portions under the token budget; greedy, sampled and penalised generation equal the cached way, and
+    no page stays held."""
+    d, page = model_dirs["B"]
+    model = make_model(d, page, num_pages=40, budget=16)
+    p = prompts(503, [23], seed=9)[0]
+    for params in (SamplingParams(), SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=5),
+                   SamplingParams(repetition_penalty=1.3)):
+        cached = model.generate(p, max_tokens=7, params=params)
+        assert len(cached) == 7
+        assert model.generate(p, max_tokens=7, params=params, use_cache=False) == cached
+    eos = model.generate(p, max_tokens=7)[3]
+    stop = model.generate(p, max_tokens=7).index(eos)
+    assert model.generate(p, max_tokens=7, eos_id=eos, use_cache=False) == model.generate(p, max_tokens=7)[:stop]
+    assert model.generate([], max_tokens=3, use_cache=False) == []
+    assert model.engine.cache.num_free() == 40 and not model.engine.cache.live
