@@ -14,8 +14,8 @@ and no windows (cpp/src/config.hpp:55-57 holds the fields unused).
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Dict, List, Sequence, Tuple
 
 
 class OutOfPages(RuntimeError):

@@ -2,7 +2,6 @@
 ``tokenizers`` package) when both exist; otherwise prompts are given as token ids."""
 from __future__ import annotations
 
-import json
 import os
 from typing import List, Optional
 

@@ -11,8 +11,8 @@ a ragged batch: cpp/src/model.cpp:347-561); the ragged one is the shape generali
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch

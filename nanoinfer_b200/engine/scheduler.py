@@ -16,7 +16,7 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 from enum import Enum
-from typing import Deque, Dict, List, Optional, Sequence as Seq, Tuple
+from typing import Deque, Dict, List, Optional
 
 from ..cache.pages import OutOfPages
 from ..sampling.params import SamplingParams

@@ -13,7 +13,7 @@ from __future__ import annotations
 import json
 import os
 import struct
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, List, Tuple
 
 import numpy as np
 import torch

@@ -1,5 +1,4 @@
 """Helpers of the GPU tests: tolerances, paged-cache fixtures, comparison with NaN awareness."""
-import math
 from types import SimpleNamespace
 
 import torch

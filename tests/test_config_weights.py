@@ -1,9 +1,7 @@
 """Configuration reading, the registry, safetensors I/O, the loader's one error, random weights."""
-import json
 import os
 import struct
 
-import numpy as np
 import pytest
 import torch
 

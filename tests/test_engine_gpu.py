@@ -1,7 +1,6 @@
 """The engine on the GPU, in-process: long decoding, the first tokens of a sequence, greedy generation
 through the entry point, continuous batching against generation alone, and each part alone against the
 plain implementation's function for it. In 32-bit and in bfloat16."""
-import math
 
 import pytest
 import torch

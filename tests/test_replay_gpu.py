@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import assert_close, F32_REL
+from gpu_util import assert_close
 from plain_qwen2 import PlainModel
 from replay_util import Trace, add_decode_tail, add_mixed, add_portions, add_whole, run_trace
 

@@ -2,8 +2,6 @@
 state of its own (a running mean of its inputs) is registered, built and stepped beside attention
 layers in one model, without a change to the framework's files; the run order names a layer twice and
 lets a layer read another layer's cache. Compared with a plain computation of whole sequences."""
-import json
-import os
 from dataclasses import dataclass
 
 import pytest

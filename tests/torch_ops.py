@@ -5,7 +5,6 @@ Math is done in float64 and rounded once to the output's dtype.
 """
 from __future__ import annotations
 
-import math
 
 import torch
 
