@@ -83,8 +83,13 @@ class Kernels:
             raise KernelError(f"cannot load the kernel library {lib_path}: {e}") from e
         self._lib.nib_last_error.restype = ctypes.c_char_p
         for name in ("nib_embed", "nib_rmsnorm", "nib_rope_store", "nib_gemm_simt", "nib_attention_generic",
-                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk", "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported", "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma", "nib_attention_decode_tma_fused", "nib_attention_decode_tma_supported", "nib_attention_decode_tma_error",
-                     "nib_argmax", "nib_argmax_chunked", "nib_ffn_decode", "nib_ffn_decode_supported", "nib_sample", "nib_repetition_penalty", "nib_device_arch", "nib_sm_count"):
+                     "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk",
+                     "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported",
+                     "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma",
+                     "nib_attention_decode_tma_fused", "nib_attention_decode_tma_supported",
+                     "nib_attention_decode_tma_error", "nib_argmax", "nib_argmax_chunked", "nib_ffn_decode",
+                     "nib_ffn_decode_supported", "nib_sample", "nib_repetition_penalty", "nib_device_arch",
+                     "nib_sm_count"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
