@@ -205,18 +205,21 @@ class CacheManager:
     def pages_needed(self, rc: RequestCache, n_new: int) -> List[int]:
         """New pages per group so that positions ``[length, length + n_new)`` have a page."""
         end_page = -(-(rc.length + n_new) // self.page_size)
-        need = []
-        for g, table in enumerate(rc.tables):
-            have = len(table)
-            need.append(max(0, end_page - max(have, 0)))
-        return need
+        return [max(0, end_page - len(table)) for table in rc.tables]
+
+    def demand(self, demands: Sequence[Tuple[RequestCache, int]]) -> List[int]:
+        """Pages per group that the given (request, new positions) pairs need together."""
+        total = [0] * len(self.groups)
+        ps = self.page_size
+        for rc, n in demands:
+            end_page = -(-(rc.length + n) // ps)
+            for g, table in enumerate(rc.tables):
+                if end_page > len(table):
+                    total[g] += end_page - len(table)
+        return total
 
     def fits(self, demands: Sequence[Tuple[RequestCache, int]]) -> bool:
-        total = [0] * len(self.groups)
-        for rc, n in demands:
-            for g, k in enumerate(self.pages_needed(rc, n)):
-                total[g] += k
-        return all(total[g] <= self.pools[g].num_free for g in range(len(self.groups)))
+        return all(k <= pool.num_free for k, pool in zip(self.demand(demands), self.pools))
 
     def extend(self, rc: RequestCache, n_new: int) -> None:
         """Allocate the pages for the next ``n_new`` positions (all of them, or none and OutOfPages)."""

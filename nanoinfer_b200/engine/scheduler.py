@@ -181,21 +181,21 @@ class Scheduler:
             budget -= n
 
         # 2. pages for them; preempt the request admitted last until the step fits
-        def fits() -> bool:
-            return cache.fits([(e.seq.cache, e.count) for e in plan.entries])
-        while plan.entries and not fits():
+        free = [cache.num_free(g) for g in range(len(cache.groups))]
+        while plan.entries:
+            need = cache.demand([(e.seq.cache, e.count) for e in plan.entries])
+            if all(k <= f for k, f in zip(need, free)):
+                free = [f - k for f, k in zip(free, need)]
+                break
             victim = max((e.seq for e in plan.entries), key=lambda s: s.order)
             if len(self.running) == 1:
                 raise OutOfPages(f"request {victim.req.request_id} alone does not fit the cache pool")
             plan.entries = [e for e in plan.entries if e.seq is not victim]
             plan.preempted.append(victim)
             self._preempt(victim)
+            free = [cache.num_free(g) for g in range(len(cache.groups))]     # the victim's pages came back
 
         # 3. admit waiting requests, first come first served, while places, budget and pages last
-        free = [cache.num_free(g) for g in range(len(cache.groups))]
-        for e in plan.entries:
-            for g, k in enumerate(cache.pages_needed(e.seq.cache, e.count)):
-                free[g] -= k
         while self.waiting and len(self.running) < self.max_batch and budget > 0 and not plan.preempted:
             seq = self.waiting[0]
             if not seq.req.prompt_ids:
