@@ -167,3 +167,40 @@ def test_random_weights_are_reproducible_and_distributed_as_stated(tmp_path):
     assert abs(g.mean().item() - 1.0) < 0.03 and abs(g.std().item() - 0.1) < 0.03
     assert abs(a.tensor("model.layers.0.self_attn.q_proj.bias").std().item() - 0.02) < 0.005
     assert config_from_json_dict(read_config_json(d1)) == cfg
+
+
+def test_loader_reads_a_checkpoint_in_shards(tmp_path):
+    """A folder with ``model.safetensors.index.json`` and several files gives the same tensors as one file;
+    a tensor that no shard holds is reported with the others; a shard the index names but the folder
+    lacks is an error that names the file."""
+    import json
+    from nanoinfer_b200.weights.safetensors_io import SafetensorsError
+    cfg = config_from_json_dict(TINY_B)
+    whole = write_random_model(cfg, str(tmp_path / "whole"), seed=4)
+    plan = plan_for(cfg)
+    want = load_tensors(whole, plan)
+    f = open_model_files(whole)[0]
+    names = sorted(f.names())
+    parts = {"model-00001-of-00003.safetensors": names[0::3], "model-00002-of-00003.safetensors": names[1::3],
+             "model-00003-of-00003.safetensors": names[2::3]}
+    d = tmp_path / "sharded"
+    d.mkdir()
+    (d / "config.json").write_text((tmp_path / "whole" / "config.json").read_text())
+    weight_map = {}
+    for fn, ns in parts.items():
+        save_safetensors(str(d / fn), {n: f.tensor(n) for n in ns})
+        weight_map.update({n: fn for n in ns})
+    (d / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    got = load_tensors(str(d), plan)
+    assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+    # one tensor gone from its shard
+    gone = parts["model-00002-of-00003.safetensors"][0]
+    save_safetensors(str(d / "model-00002-of-00003.safetensors"),
+                     {n: f.tensor(n) for n in parts["model-00002-of-00003.safetensors"][1:]})
+    with pytest.raises(WeightError) as e:
+        load_tensors(str(d), plan)
+    assert e.value.missing == [gone] and not e.value.unexpected
+    # a shard gone from the folder
+    os.remove(d / "model-00003-of-00003.safetensors")
+    with pytest.raises((SafetensorsError, OSError), match="model-00003-of-00003"):
+        load_tensors(str(d), plan)
