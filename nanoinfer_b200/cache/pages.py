@@ -70,7 +70,10 @@ class PagePool:
     def __del__(self):
         pool, self._pool = getattr(self, "_pool", None), None
         if pool:
-            self._lib.nibh_pool_destroy(pool)
+            try:
+                self._lib.nibh_pool_destroy(pool)
+            except Exception:       # the interpreter is shutting down and the library is gone already
+                pass
 
     @property
     def num_free(self) -> int:
