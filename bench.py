@@ -158,6 +158,8 @@ def run_ours(args) -> dict:
         shutil.rmtree(tmp, ignore_errors=True)      # the weights are on the device now; the folder can be gigabytes
     engine, ops = model.engine, model.engine.rt.ops
     print(f"[bench] model ready in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+    if args.only == "serve":
+        return serve_workload(model, args, rng, vocab, layers)
 
     def fill(n_req: int, length: int):
         """n_req live requests holding ``length`` random tokens each."""
@@ -290,6 +292,46 @@ def run_ours(args) -> dict:
     }
 
 
+def serve_workload(model, args, rng, vocab: int, layers: int) -> dict:
+    """A mixed continuous batch through the scheduler: 64 requests with prompts of 128 to 2,048 random ids
+    and 256 decoded tokens each, all queued at once; prompts are cut under a budget of 2,048 tokens a step
+    and run beside the decoding requests. Wall-clock time from the first step to the last token, host ids in
+    and sampled ids out; the first run warms up (it captures the decode graphs), the second is timed."""
+    import torch
+    from nanoinfer_b200 import Request, Scheduler
+    n_req, new_tokens, budget = 64, 256, 2048
+    lens = rng.integers(128, 2049, n_req)
+
+    def run():
+        sched = Scheduler(model, max_batch=n_req, max_tokens_per_step=budget, lookahead=True)
+        for i, n in enumerate(lens):
+            sched.add(Request(f"r{i}", rng.integers(0, vocab, int(n)).tolist(), max_tokens=new_tokens))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        t_prompts, steps_prompts = None, 0
+        while sched.has_work():
+            plan = sched.step()
+            if t_prompts is None and not sched.waiting and all(e.count == 1 for e in plan.entries):
+                torch.cuda.synchronize()            # every prompt is in the cache: the rest is decoding
+                t_prompts, steps_prompts = time.perf_counter() - t0, sched.steps
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        generated = sum(len(v) for v in sched.finished.values())
+        return dt, generated, sched.steps, t_prompts, steps_prompts, sched.preemptions
+
+    run()
+    dt, generated, steps, t_prompts, steps_prompts, preemptions = run()
+    return {"impl": "ours", "only": "serve", "metric": "generated tok/s of a continuous batch (64 requests, prompts 128-2048, 256 new tokens each)",
+            "value": round(generated / dt, 1), "unit": "tokens/s", "ms_total": round(dt * 1e3, 1), "steps": steps,
+            "total_tokens_per_s": round((generated + int(lens.sum())) / dt, 1),
+            "prompt_phase_ms": round(t_prompts * 1e3, 1), "prompt_phase_steps": steps_prompts,
+            "decode_ms_per_step": round((dt - t_prompts) * 1e3 / max(1, steps - steps_prompts), 4),
+            "preemptions": preemptions,
+            "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers, "requests": n_req,
+                       "prompt_tokens": int(lens.sum()), "new_tokens": new_tokens, "max_tokens_per_step": budget,
+                       "page_size": 16}}
+
+
 def run_reference(args) -> dict:
     """The unmodified reference (its Python model, installed under baseline/_ref) on the same workload:
     random weights of the same shape, batch 8 decode at context 4096 through ``Model.forward`` with its
@@ -373,8 +415,9 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel (for profilers that filter by kernel name)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
-                    help="measure one part only (for profiling small cases); the JSON line then lacks the rest")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "serve"],
+                    help="measure one part only (for profiling small cases); the JSON line then lacks the rest. "
+                         "'serve' runs the continuous-batching workload (64 requests through the scheduler) instead")
     ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes: the family's 0.5B (default), 1.5B or 7B")
     args = ap.parse_args()
     MODEL.update(SHAPES[args.shape])
