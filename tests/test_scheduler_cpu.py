@@ -249,3 +249,36 @@ def test_generation_without_the_cache_gives_the_same_tokens(model_dirs):
     assert model.generate(p, max_tokens=7, eos_id=eos, use_cache=False) == model.generate(p, max_tokens=7)[:stop]
     assert model.generate([], max_tokens=3, use_cache=False) == []
     assert model.engine.cache.num_free() == 40 and not model.engine.cache.live
+
+
+def test_sampled_workload_of_the_second_tiny_configuration(model_dirs):
+    """Five prompts of 2, 9, 17, 64 and 100 ids, 24 tokens each at temperature 0.7 with a fixed seed, prompts
+    cut into portions of 13 beside the other requests' decoded tokens: every request's tokens equal a plain
+    loop of its own (whole-sequence logits, the sampling distribution of the plain implementation, the
+    draw's uniform number from (seed, tokens generated), inverse CDF in vocabulary order)."""
+    import numpy as np
+    from plain_qwen2 import sampling_distribution
+    from nanoinfer_b200.sampling.sampler import uniform_for
+    d, page = model_dirs["B"]
+    plain = PlainModel(d)
+    ps = prompts(503, [2, 9, 17, 64, 100], seed=21)
+
+    def plain_sampled(prompt, n, seed):
+        ids, out = list(prompt), []
+        for step in range(n):
+            probs = sampling_distribution(plain.logits(ids)[-1].numpy(), ids, 0.7)
+            cdf = np.cumsum(probs)
+            tok = int(np.searchsorted(cdf, uniform_for(seed, step) * cdf[-1], side="right"))
+            out.append(tok)
+            ids.append(tok)
+        return out
+
+    want = [plain_sampled(p, 24, 100 + i) for i, p in enumerate(ps)]
+    for lookahead in (False, True):
+        model = make_model(d, page, num_pages=80, max_batch=5, budget=13)
+        s = Scheduler(model, lookahead=lookahead)
+        for i, p in enumerate(ps):
+            s.add(Request(f"r{i}", p, max_tokens=24, temperature=0.7, seed=100 + i))
+        out = s.run()
+        assert [out[f"r{i}"] for i in range(5)] == want, lookahead
+        assert model.engine.cache.num_free() == 80
