@@ -1,0 +1,79 @@
+"""The command-line tools (options with the reference's names, what they print, what they refuse), run
+in-process on the CPU: the engine they build is given the host backend of the tests instead of the CUDA
+kernels. Prompts are token ids, as they are for a model folder without a tokenizer."""
+import dataclasses
+import json
+
+import pytest
+
+from plain_qwen2 import PlainModel
+from tiny_configs import TINY_A
+from torch_ops import TorchOps
+
+
+@pytest.fixture()
+def host_engine(monkeypatch):
+    import nanoinfer_b200.engine.engine as engine_module
+    real_init = engine_module.Engine.__init__
+
+    def init_on_host(self, model_dir, cfg, ops=None):
+        real_init(self, model_dir, dataclasses.replace(cfg, device="cpu", dtype="float32"), ops=TorchOps())
+    monkeypatch.setattr(engine_module.Engine, "__init__", init_on_host)
+
+
+def completions(text):
+    return [line.split("Completion: ", 1)[1] for line in text.splitlines() if line.startswith("Completion: ")]
+
+
+def test_generate_cli(model_dirs, host_engine, capsys):
+    from nanoinfer_b200.cli import generate
+    d, page = model_dirs["A"]
+    plain = PlainModel(d)
+    want = " ".join(map(str, plain.greedy([5, 17, 3], 9)))
+    for extra in ([], ["--no-cache"], ["--weights-dir", d], ["--model", d]):
+        argv = ["--prompt", "5 17 3", "--max-tokens", "9", "--block-size", str(page), "--num-blocks", "16"]
+        argv += extra if extra and extra[0] != "--no-cache" else ["--model-dir", d] + extra
+        assert generate.main(argv) == 0
+        out = capsys.readouterr().out
+        assert "Prompt: 5 17 3" in out and completions(out) == [want], extra
+    # sampling options are taken and reproducible under a seed
+    argv = ["--model-dir", d, "--prompt", "5,17,3", "--max-tokens", "9", "--temperature", "0.9", "--top-k", "40",
+            "--top-p", "0.95", "--repetition-penalty", "1.1", "--seed", "7", "--num-blocks", "16"]
+    generate.main(argv)
+    first = completions(capsys.readouterr().out)
+    generate.main(argv)
+    assert completions(capsys.readouterr().out) == first and len(first[0].split()) == 9
+
+
+def test_generate_cli_writes_random_weights_and_refuses_what_it_cannot_do(tmp_path, host_engine, capsys, monkeypatch):
+    import tempfile
+    from nanoinfer_b200.cli import generate
+    monkeypatch.setattr(tempfile, "tempdir", str(tmp_path))      # the model folder it writes goes away with the test
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(TINY_A))
+    assert generate.main(["--random-weights", str(cfg), "--prompt", "1 2", "--max-tokens", "3", "--seed", "3",
+                          "--num-blocks", "8"]) == 0
+    captured = capsys.readouterr()
+    assert len(completions(captured.out)[0].split()) == 3 and "random-weights model" in captured.err
+    with pytest.raises(SystemExit, match="no CPU path"):
+        generate.main(["--model-dir", str(tmp_path), "--device", "cpu", "--prompt", "1"])
+    with pytest.raises(SystemExit, match="not a folder"):
+        generate.main(["--model", "Qwen/Qwen2.5-0.5B", "--prompt", "1"])
+    with pytest.raises(SystemExit, match="--model-dir DIR or --random-weights"):
+        generate.main(["--prompt", "1"])
+
+
+def test_serve_cli(model_dirs, host_engine, capsys):
+    from nanoinfer_b200.cli import serve
+    d, page = model_dirs["A"]
+    plain = PlainModel(d)
+    prompts = ["5 17 3", "9", "200 100 50 25 12 6 3"]
+    argv = ["--model-dir", d, "--max-batch", "2", "--max-tokens", "6", "--block-size", str(page), "--num-blocks", "12"]
+    for p in prompts:
+        argv += ["--prompt", p]
+    assert serve.main(argv) == 0
+    out = capsys.readouterr().out
+    assert "served 3 prompts, max_batch=2" in out and "peak_batch=2" in out and "18 tokens" in out
+    want = [" ".join(map(str, plain.greedy([int(t) for t in p.split()], 6))) for p in prompts]
+    assert completions(out) == want
+    assert [line for line in out.splitlines() if line.startswith("Prompt: ")] == [f"Prompt: {p}" for p in prompts]
