@@ -54,12 +54,20 @@ def peaks() -> dict:
             with open(path) as f:
                 d = json.load(f)
             out = dict(FALLBACK_PEAKS)
+            found = 0
             for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
-                if isinstance(d.get(k), (int, float)) and d[k] > 0:
-                    out[k] = float(d[k])
-            out["source"] = "measured"
-            return out
-        except (OSError, ValueError):
+                v = d.get(k)
+                if isinstance(v, dict):             # {"value": ...} is read as well as a bare number
+                    v = v.get("value")
+                if isinstance(v, str):
+                    v = float(v)
+                if isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+                    out[k] = float(v)
+                    found += 1
+            if found:
+                out["source"] = "measured" if found == 3 else "measured (partly fallback)"
+                return out
+        except (OSError, ValueError, AttributeError):
             pass
     return dict(FALLBACK_PEAKS)
 
