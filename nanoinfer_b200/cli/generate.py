@@ -74,6 +74,10 @@ def main(argv=None) -> int:
     model = load_model(model_dir, dtype=args.dtype, page_size=args.page_size, num_pages=args.num_pages,
                        max_batch=1, max_tokens_per_step=args.max_tokens_per_step)
     tok = load_tokenizer(model_dir, model.eos_token_id)
+    try:
+        tok.encode(args.prompt)
+    except ValueError as e:
+        raise SystemExit(str(e)) from None
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                             repetition_penalty=args.repetition_penalty, seed=args.seed)
     print(f"Prompt: {args.prompt}")

@@ -33,7 +33,11 @@ def main(argv=None) -> int:
     for i, text in enumerate(args.prompts):
         rid = f"req{i}"
         prompts[rid] = text
-        sched.add(Request(rid, tok.encode(text), max_tokens=args.max_tokens, temperature=args.temperature,
+        try:
+            ids = tok.encode(text)
+        except ValueError as e:
+            raise SystemExit(str(e)) from None
+        sched.add(Request(rid, ids, max_tokens=args.max_tokens, temperature=args.temperature,
                           top_k=args.top_k, top_p=args.top_p, repetition_penalty=args.repetition_penalty,
                           seed=args.seed, eos_id=model.eos_token_id))
     t0 = time.perf_counter()

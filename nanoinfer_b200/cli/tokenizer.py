@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import os
+import sys
 from typing import List, Optional
 
 
@@ -11,7 +12,11 @@ class IdTokenizer:
     eos_token_id = None
 
     def encode(self, text: str) -> List[int]:
-        return [int(t) for t in text.replace(",", " ").split()]
+        try:
+            return [int(t) for t in text.replace(",", " ").split()]
+        except ValueError:
+            raise ValueError(f"the model folder has no usable tokenizer.json, so a prompt is a list of token ids "
+                             f"(\"5 17 3\"); got {text!r}") from None
 
     def decode(self, ids) -> str:
         return " ".join(str(int(i)) for i in ids)
@@ -36,5 +41,6 @@ def load_tokenizer(model_dir: str, eos_token_id: int = -1):
         try:
             return JsonTokenizer(path, eos_token_id if eos_token_id >= 0 else None)
         except ImportError:
-            pass
+            print(f"{path} is there but the 'tokenizers' package is not: prompts are read as token ids",
+                  file=sys.stderr)
     return IdTokenizer()

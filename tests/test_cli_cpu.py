@@ -77,3 +77,30 @@ def test_serve_cli(model_dirs, host_engine, capsys):
     want = [" ".join(map(str, plain.greedy([int(t) for t in p.split()], 6))) for p in prompts]
     assert completions(out) == want
     assert [line for line in out.splitlines() if line.startswith("Prompt: ")] == [f"Prompt: {p}" for p in prompts]
+
+
+def test_text_prompts_with_a_tokenizer_file_and_ids_without(model_dirs, host_engine, capsys, tmp_path):
+    """With ``tokenizer.json`` in the model folder prompts and completions are text; without it a prompt that
+    is no list of ids is refused in one line."""
+    import shutil
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from nanoinfer_b200.cli import generate, serve
+    d, page = model_dirs["A"]
+    with pytest.raises(SystemExit, match="list of token ids"):
+        generate.main(["--model-dir", d, "--prompt", "the cat", "--num-blocks", "8"])
+    with pytest.raises(SystemExit, match="list of token ids"):
+        serve.main(["--model-dir", d, "--prompt", "1 2", "--prompt", "the cat", "--num-blocks", "8"])
+    capsys.readouterr()
+    folder = tmp_path / "with_tokenizer"
+    shutil.copytree(d, folder)
+    vocab = {f"w{i}": i for i in range(256)}
+    vocab.update({"the": 5, "cat": 17, "sat": 3})
+    del vocab["w5"], vocab["w17"], vocab["w3"]
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(str(folder / "tokenizer.json"))
+    assert generate.main(["--model-dir", str(folder), "--prompt", "the cat sat", "--max-tokens", "5",
+                          "--block-size", str(page), "--num-blocks", "8"]) == 0
+    words = completions(capsys.readouterr().out)[0].split()
+    by_id = {i: w for w, i in vocab.items()}
+    assert words == [by_id[t] for t in PlainModel(d).greedy([5, 17, 3], 5)]
