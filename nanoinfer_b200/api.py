@@ -44,7 +44,7 @@ class Model:
         sched.add(Request("generate", list(prompt_ids), max_tokens=max_tokens, temperature=params.temperature,
                           top_k=params.k, top_p=params.p, repetition_penalty=params.repetition_penalty,
                           seed=seed, eos_id=eos_id))
-        return sched.run()["generate"]
+        return sched.run()["generate"]      # run() gives back what the request holds if a step raises
 
 
     def _generate_recomputing(self, ids: List[int], max_tokens: int, params: SamplingParams, seed: int,
@@ -71,6 +71,9 @@ class Model:
                 break
             out.append(token)
             ids = ids + [token]
+            if len(ids) >= self.engine.max_positions:
+                break       # the cached way's stop rule (Scheduler._accept): no position is left for another token
+        self.engine.check_device()
         return out
 
 

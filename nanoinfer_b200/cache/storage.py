@@ -54,9 +54,12 @@ class CacheStorage:
                 shape = (num_pages, g.kv_heads, page_size, g.head_dim)
                 self.k[e] = torch.zeros(shape, dtype=dtype, device=device)
                 self.v[e] = torch.zeros(shape, dtype=dtype, device=device)
+        # One slot more than there can be requests: the padding rows of a captured decode step read and write
+        # the spare slot, never a live request's state.
+        self.pad_slot = max_requests
         for i, (_need, state, _reads) in enumerate(self.needs):
             if state is not None:
-                self.state[i] = torch.zeros((max_requests,) + tuple(state.shape), dtype=state.dtype, device=device)
+                self.state[i] = torch.zeros((max_requests + 1,) + tuple(state.shape), dtype=state.dtype, device=device)
 
     def make_manager(self, max_requests: int) -> CacheManager:
         return CacheManager(self.groups, self.num_pages, self.page_size, max_requests)

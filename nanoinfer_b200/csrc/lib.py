@@ -409,6 +409,18 @@ class Kernels:
         """The error word of the TMA decode kernel's bounded waits (0 = none); synchronises and clears it."""
         return self._lib.nib_attention_decode_tma_error()
 
+    def check_device_errors(self) -> None:
+        """Raises ``KernelError`` if a bounded wait of a tcgen05 or TMA kernel has run out since the last check.
+
+        Such a kernel returns instead of hanging, and what it wrote is not to be trusted. The words are read
+        with a 4-byte copy each, which waits for the device: call it where the host waits anyway (a request
+        finishes, a run ends, results are about to be written out)."""
+        raise_device_errors([
+            ("tensor-core GEMM (gemm_tcgen05.cu)", self.gemm_tc_error(), _GEMM_TC_ROLES),
+            ("tcgen05 prefill attention (attention_tcgen05.cu)", self.attention_tc_error(), _ATTN_TC_ROLES),
+            ("TMA decode attention (attention_decode_tma.cu)", self.attention_decode_tma_error(), _DECODE_TMA_ROLES),
+        ])
+
     def attention_decode_fused(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
                                page_size, k_pages, v_pages, rotary):
         """A pure decode step's rotation, cache write and attention in one kernel: ``qkv`` is the raw
@@ -488,6 +500,32 @@ class Kernels:
         rows, vocab = logits.shape
         self._check(self._lib.nib_sample(_ptr(logits), c_int(rows), c_int(vocab), _ptr(temperature), _ptr(top_k),
                                          _ptr(top_p), _ptr(uniform), _ptr(out), self._stream()), "sample")
+
+
+# what the code in the upper half of an error word says about the wait that ran out
+_GEMM_TC_ROLES = {1: "copy warp: a stage was never freed", 2: "MMA warp: a stage was never filled",
+                  3: "epilogue: the accumulator never arrived", 4: "MMA warp: the accumulator buffer was never drained",
+                  5: "pair kernel, copy warp: a stage was never freed", 6: "pair kernel, MMA warp: the accumulator buffer was never drained",
+                  7: "pair kernel, MMA warp: a stage was never filled", 8: "pair kernel, epilogue: the accumulator never arrived"}
+_ATTN_TC_ROLES = {1: "copy warp: a key/value stage was never freed", 2: "MMA warp: the queries never arrived",
+                  3: "MMA warp: keys, values or probabilities never arrived", 4: "softmax warps: scores or outputs never arrived"}
+_DECODE_TMA_ROLES = {1: "consumer warps: a page tile never arrived", 2: "copy warp: a stage was never freed"}
+
+
+def raise_device_errors(words) -> None:
+    """``words``: (kernel name, error word, {code: role}) triples; raises one ``KernelError`` naming every
+    kernel whose word is not zero, with the role of the wait that ran out and the block it ran in."""
+    bad = []
+    for name, word, roles in words:
+        if word == 0:
+            continue
+        if word < 0:
+            bad.append(f"{name}: the error word could not be read")
+            continue
+        code, block = word >> 16, word & 0xFFFF
+        bad.append(f"{name}: a bounded wait ran out in block {block} ({roles.get(code, f'code {code}')})")
+    if bad:
+        raise KernelError("a kernel gave up waiting; the results of this run are not to be trusted: " + "; ".join(bad))
 
 
 _KERNELS: Optional[Kernels] = None

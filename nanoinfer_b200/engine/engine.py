@@ -72,6 +72,14 @@ class Engine:
     def close(self, rc: RequestCache) -> None:
         self.cache.close(rc)
 
+    def check_device(self) -> None:
+        """Raises if a kernel's bounded wait ran out since the last check (the kernel then returned without
+        finishing its work, and the run's results are wrong). Waits for the device: the scheduler calls it
+        when a request finishes and when a run ends, trace replay before it writes logits out."""
+        check = getattr(self.rt.ops, "check_device_errors", None)
+        if check is not None:
+            check()
+
     # ---- the step -------------------------------------------------------------------------
     def _check(self, entries: Sequence[StepEntry]) -> None:
         if not entries:
@@ -108,7 +116,7 @@ class Engine:
 
         With ``pad_to`` the batch is padded to that many requests of one token each; a padding row holds
         no pages (its block-table row is -1, its context length 0), so kernels write nothing for it and
-        its attention is empty. ``widths`` fixes the block-table widths; ``static`` is a device buffer of
+        its attention is empty; its state slot is the spare one that no request is ever given. ``widths`` fixes the block-table widths; ``static`` is a device buffer of
         the right size that is reused (a captured graph reads its inputs there)."""
         q_lens = [len(e.tokens) for e in entries]
         r_real = len(entries)
@@ -123,7 +131,7 @@ class Engine:
         positions = np.concatenate([np.arange(e.request.length, e.request.length + n, dtype=np.int32)
                                     for e, n in zip(entries, q_lens)] + [np.zeros(pad, np.int32)])
         req_index = np.repeat(np.arange(r, dtype=np.int32), q_lens_p)
-        slots = np.asarray([e.request.slot for e in entries] + [0] * pad, dtype=np.int32)
+        slots = np.asarray([e.request.slot for e in entries] + [self.storage.pad_slot] * pad, dtype=np.int32)
         want_list = [q_start[i] + int(w) for i, e in enumerate(entries) for w in e.want]
         want = np.asarray(want_list, dtype=np.int32)
         if pad_to:      # a graph computes the logits of every row

@@ -45,7 +45,7 @@ class _InputMirror:
     only when the request in that row, or the version of its tables, differs from what the row holds.
     The layout is the one ``Engine.build_context`` produces for a padded batch of one-token requests."""
 
-    def __init__(self, rb: int, widths: List[int], device: torch.device):
+    def __init__(self, rb: int, widths: List[int], device: torch.device, pad_slot: int = 0):
         sizes = [rb, rb, rb, rb + 1, rb, rb, rb] + [rb * w for w in widths]
         self.size = sum(sizes)
         on_gpu = torch.device(device).type == "cuda"
@@ -66,6 +66,8 @@ class _InputMirror:
         want[:] = np.arange(rb)
         for t in self.tables:
             t[:] = -1
+        self.pad_slot = pad_slot            # the state slot of rows without a request
+        self.slots[:] = pad_slot
         self.rb = rb
         self.row_req = [None] * rb          # the request whose pages a row's block tables list
         self.row_ver = [-1] * rb
@@ -90,7 +92,8 @@ class _InputMirror:
         for i in range(n, self.rb):         # rows that a request has left become padding again
             if row_req[i] is None:
                 continue
-            self.tok[i] = self.pos[i] = self.ctx[i] = self.slots[i] = 0
+            self.tok[i] = self.pos[i] = self.ctx[i] = 0
+            self.slots[i] = self.pad_slot
             for t in self.tables:
                 t[i, :] = -1
             row_req[i], row_ver[i] = None, -1
@@ -193,7 +196,7 @@ class DecodeGraphs:
             if gc_was_on:
                 gc.enable()
         torch.cuda.current_stream().wait_stream(self.stream)
-        cap = _Captured(graph, static, logits, ops.launches - before, _InputMirror(rb, widths, eng.device))
+        cap = _Captured(graph, static, logits, ops.launches - before, _InputMirror(rb, widths, eng.device, eng.storage.pad_slot))
         assert cap.mirror.size == size
         self.captured[key] = cap
         return cap

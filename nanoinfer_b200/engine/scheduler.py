@@ -134,7 +134,7 @@ class Scheduler:
         if cache.groups and need > cache.num_pages:
             raise ValueError(f"request {req.request_id} needs {need} pages; the pool has {cache.num_pages} "
                              f"(raise num_pages or page_size)")
-        if worst > self.engine.max_positions + 1 and len(req.prompt_ids) >= self.engine.max_positions:
+        if len(req.prompt_ids) > self.engine.max_positions:
             raise ValueError(f"request {req.request_id}: prompt of {len(req.prompt_ids)} tokens exceeds the "
                              f"model's context length {self.engine.max_positions}")
         req.sampling()  # validates
@@ -150,6 +150,7 @@ class Scheduler:
         if seq.cache is not None:
             self.engine.close(seq.cache)
             seq.cache = None
+        self.engine.check_device()      # what is handed out as finished was computed by kernels that all completed
 
     def _accept(self, seq: Sequence, tok: int) -> bool:
         """Stop rules, in the reference's order (cpp/python/ni/scheduler.py:250-259): EOS is checked before
@@ -340,6 +341,21 @@ class Scheduler:
         return False
 
     def run(self) -> Dict[str, List[int]]:
-        while self.has_work():
-            self.step()
+        try:
+            while self.has_work():
+                self.step()
+        except BaseException:
+            self.abort()
+            raise
+        self.engine.check_device()
         return self.finished
+
+    def abort(self) -> None:
+        """Give back what running requests hold (after an error in a step): the engine stays usable."""
+        self._inflight = None
+        for seq in list(self.running):
+            if seq.cache is not None and not seq.cache.closed:
+                self.engine.close(seq.cache)
+            seq.cache = None
+            seq.state = State.FINISHED
+        self.running = []

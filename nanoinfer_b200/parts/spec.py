@@ -19,6 +19,7 @@ class TensorSpec:
     name: str                 # tensor name in the safetensors file
     shape: Tuple[int, ...]
     init: str = "matrix"      # random-weights rule: "matrix" | "gain" | "bias" | "embedding"
+    integer: bool = False     # an integer table (kept as int32); everything else must be stored as floats
 
 
 @dataclass(frozen=True)

@@ -148,7 +148,59 @@ def test_loader_keeps_dtypes_and_tolerates_a_stored_tied_head(tmp_path):
     got = load_tensors(d, plan)
     assert "lm_head.weight" not in got
     assert got["model.norm.weight"].dtype == torch.bfloat16
-    assert got["model.layers.0.input_layernorm.weight"].dtype == torch.bfloat16   # float16 -> bfloat16
+    # float16 -> float32: nothing is lost, whatever the engine's dtype is (bfloat16 would drop mantissa bits)
+    assert got["model.layers.0.input_layernorm.weight"].dtype == torch.float32
+    assert torch.equal(got["model.layers.0.input_layernorm.weight"],
+                       t["model.layers.0.input_layernorm.weight"].float())
+
+
+def test_loader_lists_wrong_element_types_with_the_other_faults(tmp_path):
+    """A matrix, gain or bias stored as integers or booleans is an error of the checkpoint, listed in the
+    one WeightError beside what is missing (nanoinfer/weights.py:56-68, cpp/src/serialize.cpp:18-64)."""
+    cfg = config_from_json_dict(TINY_B)
+    d = write_random_model(cfg, str(tmp_path / "m"), seed=1)
+    plan = plan_for(cfg)
+    f = open_model_files(d)[0]
+    t = {n: f.tensor(n) for n in f.names()}
+    t["model.layers.0.self_attn.k_proj.weight"] = t["model.layers.0.self_attn.k_proj.weight"].float().mul(100).to(torch.int8)
+    t["model.layers.1.post_attention_layernorm.weight"] = torch.ones_like(
+        t["model.layers.1.post_attention_layernorm.weight"], dtype=torch.bool)
+    t["model.layers.2.self_attn.v_proj.bias"] = t["model.layers.2.self_attn.v_proj.bias"].to(torch.int32)
+    del t["model.norm.weight"]
+    save_safetensors(os.path.join(d, "model.safetensors"), t)
+    with pytest.raises(WeightError) as e:
+        load_tensors(d, plan)
+    err = e.value
+    assert err.missing == ["model.norm.weight"]
+    assert len(err.wrong_dtype) == 3
+    joined = " ".join(err.wrong_dtype)
+    for name, tag in (("k_proj.weight", "I8"), ("post_attention_layernorm.weight", "BOOL"), ("v_proj.bias", "I32")):
+        assert name in joined and tag in joined
+    assert "wrong element types (3)" in str(err) and "missing tensors (1)" in str(err)
+
+
+def test_loader_wants_integers_for_an_integer_table(tmp_path):
+    """A plan may declare an integer table (TensorSpec.integer): it is kept as int32, and floats in its place
+    are refused."""
+    import dataclasses
+    cfg = config_from_json_dict(TINY_A)
+    d = write_random_model(cfg, str(tmp_path / "m"), seed=3)
+    plan = plan_for(cfg)
+    from nanoinfer_b200.parts.spec import PartSpec, TensorSpec
+    table = TensorSpec("toy.table", (5,), "bias", integer=True)
+    plan2 = dataclasses.replace(plan, final_norm=PartSpec(plan.final_norm.kind, plan.final_norm.params,
+                                                         {**plan.final_norm.tensors, "table": table}))
+    f = open_model_files(d)[0]
+    t = {n: f.tensor(n) for n in f.names()}
+    t["toy.table"] = torch.arange(5, dtype=torch.int64)
+    save_safetensors(os.path.join(d, "model.safetensors"), t)
+    got = load_tensors(d, plan2)
+    assert got["toy.table"].dtype == torch.int32 and got["toy.table"].tolist() == [0, 1, 2, 3, 4]
+    t["toy.table"] = torch.arange(5, dtype=torch.float32)
+    save_safetensors(os.path.join(d, "model.safetensors"), t)
+    with pytest.raises(WeightError) as e:
+        load_tensors(d, plan2)
+    assert e.value.wrong_dtype and "integer table" in e.value.wrong_dtype[0]
 
 
 def test_random_weights_are_reproducible_and_distributed_as_stated(tmp_path):

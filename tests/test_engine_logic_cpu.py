@@ -123,7 +123,8 @@ def test_graph_input_mirror_equals_the_built_context(model_dirs, name):
     vocab = PlainModel(d).cfg["vocab"]
     rng = np.random.default_rng(5)
     rb, widths = 4, [16 for _ in eng.cache.groups]
-    mirror = _InputMirror(rb, widths, torch.device("cpu"))
+    mirror = _InputMirror(rb, widths, torch.device("cpu"), eng.storage.pad_slot)
+    assert eng.storage.pad_slot == eng.cache.max_requests      # the spare slot that no request is ever given
     static = torch.empty(mirror.size, dtype=torch.int32)
     live = {}
 
