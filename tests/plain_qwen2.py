@@ -87,7 +87,7 @@ def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
     """cos, sin [T, head_dim]: inv_freq_i = theta^(-2i/head_dim), angle = position * inv_freq_i, each
     frequency repeated in both halves, angles in float64   (cpp/src/ops.cpp:121-144)."""
     half = head_dim // 2
-    inv_freq = 1.0 / (float(theta) ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim))
+    inv_freq = 1.0 / (float(theta) ** (torch.arange(0, half, dtype=torch.float64, device=positions.device) * 2.0 / head_dim))
     ang = positions.to(torch.float64)[:, None] * inv_freq[None, :]
     ang = torch.cat([ang, ang], dim=-1)
     return ang.cos(), ang.sin()
@@ -130,8 +130,8 @@ def causal_attention_fast(q, k, v, window: int = 0, scale: Optional[float] = Non
     kk = k.repeat_interleave(n_rep, dim=1)   # out head j*n_rep + r <- kv head j
     vv = v.repeat_interleave(n_rep, dim=1)
     s = torch.einsum("ihd,jhd->hij", q, kk) * scale
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
+    i = torch.arange(T, device=q.device)[:, None]
+    j = torch.arange(T, device=q.device)[None, :]
     visible = j <= i
     if window:
         visible &= j > i - window
@@ -177,8 +177,8 @@ def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], ids: List[int], fast: 
     """Logits [T, vocab] of one whole sequence: embedding, blocks, final norm, head (tied: the
     embedding table)   (cpp/src/model.cpp:347-410; nanoinfer/model.py:33-89)."""
     table = w["model.embed_tokens.weight"]
-    x = table[torch.tensor(ids, dtype=torch.long)]
-    positions = torch.arange(len(ids))
+    x = table[torch.tensor(ids, dtype=torch.long, device=table.device)]
+    positions = torch.arange(len(ids), device=table.device)
     for i in range(cfg["layers"]):
         x = block(x, w, i, cfg, positions, fast)
     x = rms_norm(x, w["model.norm.weight"], cfg["eps"])
@@ -189,9 +189,10 @@ def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], ids: List[int], fast: 
 class PlainModel:
     """A folder's model, for whole sequences."""
 
-    def __init__(self, model_dir: str, dtype=torch.float64):
+    def __init__(self, model_dir: str, dtype=torch.float64, device="cpu"):
+        """``device``: where torch computes (long test sequences may run the same plain formulas on a GPU)."""
         self.cfg = read_config(model_dir)
-        self.w = read_weights(model_dir, dtype)
+        self.w = {k: v.to(device) for k, v in read_weights(model_dir, dtype).items()}
 
     def logits(self, ids: List[int], fast: bool = True) -> torch.Tensor:
         return forward_logits(self.cfg, self.w, list(ids), fast)

@@ -522,6 +522,75 @@ def test_attention_tcgen05_prefill(K, heads, kv_heads, hd, page, window):
     assert_close(fast, ref, dtype, "tcgen05 attention")
 
 
+def _ref_attention_masked(qkv, heads, kv_heads, hd, scale, window, q_lens, before, bt, page, kp, vp):
+    """The same formula as ``TorchOps.attention`` (float64, keys lo..own position), one masked softmax per
+    request instead of a loop over tokens: for portions of thousands of tokens."""
+    m = qkv.shape[0]
+    q_all = qkv.view(m, heads + 2 * kv_heads, hd)[:, :heads].double()
+    out = torch.empty(m, heads, hd, dtype=torch.float64, device=qkv.device)
+    n_rep = heads // kv_heads
+    row = 0
+    for r, (ql, b) in enumerate(zip(q_lens, before)):
+        n = b + ql
+        idx = torch.arange(n, device=qkv.device)
+        pages = bt[r, idx // page].long()
+        held = pages >= 0
+        k = kp[pages.clamp(min=0), :, idx % page, :].double()      # [n, kv_heads, hd]
+        v = vp[pages.clamp(min=0), :, idx % page, :].double()
+        pos = torch.arange(b, n, device=qkv.device)[:, None]
+        visible = idx[None, :] <= pos
+        if window:
+            visible &= idx[None, :] > pos - window
+        assert bool((held[None, :] | ~visible).all()), "read of a position without a page"
+        q = q_all[row:row + ql]
+        s = torch.einsum("thd,nhd->htn", q, k.repeat_interleave(n_rep, dim=1)) * scale
+        s = s.masked_fill(~visible[None], float("-inf"))
+        out[row:row + ql] = torch.einsum("htn,nhd->thd", torch.softmax(s, dim=-1), v.repeat_interleave(n_rep, dim=1))
+        row += ql
+    return out.view(m, heads * hd)
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page,window,q_lens,before", [
+    (14, 2, 64, 16, 0, [2048], [0]), (14, 2, 64, 16, 0, [2048, 1000], [2048, 3096]), (12, 2, 128, 16, 0, [4096], [0]),
+    (12, 2, 128, 16, 0, [2048, 2], [2048, 4094]), (4, 1, 64, 32, 1500, [2048], [2048]), (28, 4, 128, 16, 0, [2048], [0])])
+def test_attention_prefill_at_benchmark_lengths(K, heads, kv_heads, hd, page, window, q_lens, before):
+    """Prompt portions of 2,048 and 4,096 tokens, from position 0 and behind 2,048 cached keys: the tcgen05
+    kernel walks 16 to 32 key blocks per tile."""
+    dtype = torch.bfloat16
+    total = sum(a + b for a, b in zip(q_lens, before))
+    pages = total // page + 8
+    ctx, bt = make_paged_batch(q_lens, before, page, pages, "cuda", seed=17)
+    kp, vp = _fill_cache(ctx, bt, page, pages, kv_heads, hd, dtype, 210)
+    m = sum(q_lens)
+    qkv = rnd((m, (heads + 2 * kv_heads) * hd), dtype, 212)
+    got = torch.empty(m, heads * hd, dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    K.attention(qkv, got, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    assert K.attention_tc_error() == 0
+    ref = _ref_attention_masked(qkv, heads, kv_heads, hd, scale, window, q_lens, before, bt, page, kp, vp)
+    assert_close(got, ref, dtype, "prefill attention at benchmark lengths")
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,page", [(14, 2, 64, 16), (12, 2, 128, 16), (28, 4, 128, 64)])
+@pytest.mark.parametrize("n_req", [1, 8, 64])
+def test_attention_decode_at_benchmark_lengths(K, heads, kv_heads, hd, page, n_req):
+    """Single decoded tokens over 4,096 and 8,192 cached keys (and shorter neighbours in the same batch), with
+    the number of splits that the engine chooses for the batch size."""
+    dtype = torch.bfloat16
+    before = [(8191 if i % 4 == 0 else 4095 if i % 4 == 1 else 4096 if i % 4 == 2 else 3000 + 7 * i) for i in range(n_req)]
+    q_lens = [1] * n_req
+    pages = sum(-(-(b + 1) // page) for b in before) + 8
+    ctx, bt = make_paged_batch(q_lens, before, page, pages, "cuda", seed=18)
+    kp, vp = _fill_cache(ctx, bt, page, pages, kv_heads, hd, dtype, 220)
+    qkv = rnd((n_req, (heads + 2 * kv_heads) * hd), dtype, 222)
+    got = torch.empty(n_req, heads * hd, dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    K.attention(qkv, got, heads, kv_heads, hd, scale, 0, ctx, bt, page, kp, vp)
+    assert K.attention_decode_tma_error() == 0
+    ref = _ref_attention_masked(qkv, heads, kv_heads, hd, scale, 0, q_lens, before, bt, page, kp, vp)
+    assert_close(got, ref, dtype, "decode attention at benchmark lengths")
+
+
 @pytest.mark.parametrize("tma", [True, False])
 @pytest.mark.parametrize("heads,kv_heads,hd,rot,page,window", [(14, 2, 64, 64, 16, 0), (6, 1, 32, 32, 8, 0), (3, 3, 48, 48, 8, 24),
                                                                (16, 1, 128, 64, 16, 0), (4, 2, 16, 16, 16, 0), (8, 2, 128, 128, 32, 0),
