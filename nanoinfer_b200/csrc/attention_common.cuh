@@ -116,42 +116,4 @@ __device__ __forceinline__ void load_q(unsigned (&q)[HD / 16][4], const __nv_bfl
     }
 }
 
-// Rotation of one even/odd pair (d, d+1) of a head for the token's position: cos/sin rows hold rot/2 values;
-// d < rot/2 pairs with d + rot/2 (x*c - partner*s), rot/2 <= d < rot with d - rot/2 (x*c + partner*s),
-// d >= rot is left as it is. rot/2 is even, so a pair never straddles the halves. The result is rounded to
-// bfloat16 exactly as the separate rotation kernel rounds it.
-__device__ __forceinline__ unsigned rotated_pair(const __nv_bfloat16* x, int d, const float* cos_row, const float* sin_row, int rot) {
-    const int half = rot >> 1;
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + d);
-    if (d >= rot) return *reinterpret_cast<const unsigned*>(&v);
-    const bool low = d < half;
-    const int f = low ? d : d - half;
-    const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(x + (low ? d + half : d - half));
-    const float2 c = *reinterpret_cast<const float2*>(cos_row + f), sn = *reinterpret_cast<const float2*>(sin_row + f);
-    const float a0 = __low2float(v), a1 = __high2float(v), b0 = __low2float(w), b1 = __high2float(w);
-    const float r0 = low ? a0 * c.x - b0 * sn.x : a0 * c.x + b0 * sn.x;
-    const float r1 = low ? a1 * c.y - b1 * sn.y : a1 * c.y + b1 * sn.y;
-    return pack_bf16(r0, r1);
-}
-
-// As load_q, with the rotation applied on the way (the fused decode path: q comes straight from the projection).
-template <int HD>
-__device__ __forceinline__ void load_q_rotated(unsigned (&q)[HD / 16][4], const __nv_bfloat16* const (&row_ptr)[2], int lane,
-                                               const float* cos_row, const float* sin_row, int rot) {
-    const int t = lane & 3;
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            unsigned lo = 0u, hi = 0u;
-            if (row_ptr[r]) {
-                lo = rotated_pair(row_ptr[r], kk * 16 + 2 * t, cos_row, sin_row, rot);
-                hi = rotated_pair(row_ptr[r], kk * 16 + 8 + 2 * t, cos_row, sin_row, rot);
-            }
-            q[kk][r] = lo;
-            q[kk][2 + r] = hi;
-        }
-    }
-}
-
 }  // namespace

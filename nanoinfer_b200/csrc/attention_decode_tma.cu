@@ -12,8 +12,15 @@
 // ahead, a full and an empty mbarrier per stage hand the tiles back and forth, and no barrier of the
 // whole CTA stands in the loop. Four consumer warps take 16 keys of every tile each, keep their own
 // running (max, sum, output) and merge at the end. The rows of the mma tile are the query heads of
-// the kv group (at most 16). With more than one split the partial triples go to scratch and a second kernel merges them in split order
-// (nib_attention_combine).
+// the kv group (at most 16).
+//
+// The CTAs that split one (token, kv head) form a thread-block cluster of up to eight. Each leaves its
+// partial (max, sum, output) in its own shared memory; after a cluster barrier every CTA of the cluster
+// merges a slice of the output columns from all its peers' shared memory (distributed shared memory, in
+// rank order) and stores the finished bfloat16 values: no scratch in global memory, no second kernel, no
+// extra round trip in a decode layer's chain. Only a context so long that eight CTAs per (token, kv head)
+// are too few is cut further: then each cluster writes one partial triple to scratch and
+// nib_attention_combine merges the clusters' triples in order.
 //
 // Every wait has an iteration limit; a wait that runs out sets an error word, the CTA stops, waits
 // (bounded) for its copies in flight and returns.
@@ -21,87 +28,59 @@
 // Formula as in attention_generic.cu (cpp/src/ops.cpp:206-270). The reference's decode attention is a
 // SIMT split-KV kernel with a combine pass (cpp/src/cuda/cuda_backend.cu:578-640, :331-352).
 #include "attention_common.cuh"
-#include <cuda.h>
+#include "pipeline.cuh"
+
+using namespace nibp;
 
 extern "C" int nib_attention_combine(const float* part_o, const float* part_ml, void* out, int rows, int splits,
                                      int head_dim, cudaStream_t stream);
 
 namespace {
 
-constexpr int WARPS = 4;          // consumer warps: 16 keys of every tile each; one more warp fetches
-constexpr int THREADS = (WARPS + 1) * 32;
+constexpr int GW = 4;             // consumer warps of a group: a quarter of a tile's keys each
+constexpr int GROUPS = 1;         // groups that would take alternate tiles need rings of their own (a warp must see every phase of a barrier it waits on)
+constexpr int WARPS = GW * GROUPS;
+constexpr int THREADS = (WARPS + 1) * 32;      // one more warp fetches
 // Keys per tile: 128 for heads of 64 (a tile of 64 keys is only 16 KB there, and the fixed work per tile,
 // barrier waits and the softmax's shuffles, bounded the kernel at large batches), 64 for heads of 128.
 template <int HD> constexpr int keys_of() { return HD == 64 ? 128 : 64; }
-constexpr unsigned WAIT_LIMIT = 1u << 22;
 
+int g_dec_stages = 3;             // tiles in flight per CTA (2..4): 32 KB each
 __device__ int g_dec_error = 0;   // 0, or (code << 16 | blockIdx.x) of the first wait that ran out
 
 template <int HD> struct Cfg {
     static constexpr int KEYS = keys_of<HD>();
-    static constexpr int WKEYS = KEYS / WARPS;                // keys of a tile per consumer warp: 32 or 16
+    static constexpr int WKEYS = KEYS / GW;                   // keys of a tile per consumer warp: 32 or 16
     static constexpr int SUB = HD / 64;                       // 64-element column blocks of a head
     static constexpr int SUBTILE = KEYS * 128;                // KEYS rows of 128 bytes (64 elements of a head), swizzled
     static constexpr int TILE = SUB * SUBTILE;                // K (or V) of one tile
     static constexpr int STAGE = 2 * TILE;
-    static constexpr int STAGES = 3;                          // 96 KB in flight, two CTAs per SM
-    static constexpr int MERGE = WARPS * 16 * (HD + 4 + 2) * 4 + WARPS * 16 * 4;
-    static constexpr int DATA = STAGES * STAGE > MERGE ? STAGES * STAGE : MERGE;
-    static constexpr int SMEM = DATA + 1024 /* alignment */ + 64 /* barriers */;
+    static constexpr int MAX_STAGES = 4;
+    static constexpr int MERGE = WARPS * 16 * (HD + 4 + 2) * 4 + WARPS * 16 * 4 + 16 * HD * 4 + 16 * 2 * 4;
+    static constexpr int data_bytes(int stages) { return stages * STAGE > MERGE ? stages * STAGE : MERGE; }
+    static constexpr int smem_bytes(int stages) { return data_bytes(stages) + 1024 /* alignment */ + 64 /* barriers */; }
 };
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if (i > 256) __nanosleep(64);
-    }
-    return false;
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, unsigned long long* bar, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
-// FUSED: qkv is the raw projection. The queries are rotated as they are loaded; the warp whose 16 keys
-// include the token's own position rotates the new key, puts key and value into its rows of the tile (the
-// page's slot still holds old data there) and into the page for the steps to come. Nothing of this step is
-// read from the pages then, so every tile may be fetched before the wait for the step's earlier kernels.
-template <int HD, bool FUSED>
+template <int HD>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ qkv, int q_stride, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
                             int page_size, int page_shift, int num_pages, int heads, int kv_heads, int n_rep, float scale,
-                            int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                            __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
-                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot) {
+                            int window, int splits, int csize, int stages, int data_bytes, int own_kv, float* __restrict__ part_o, float* __restrict__ part_ml,
+                            unsigned long long* trace, int trace_cap) {
     using C = Cfg<HD>;
     constexpr int KEYS = C::KEYS, SUBTILE = C::SUBTILE, WKEYS = C::WKEYS, NT = WKEYS / 8;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + C::DATA);
-    unsigned long long* empty = full + C::STAGES;
+    unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + data_bytes);
+    unsigned long long* empty = full + stages;
     __shared__ volatile int s_failed;
 
     pdl_launch_dependents();
     const int split = blockIdx.x, token = blockIdx.y, kvh = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if (tid == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ATTN_DECODE, 0, 0);
     const int p = ctx_lens[token] - 1;                     // the token's own position; -1: a padding row
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int* bt = block_table + (size_t)token * bt_stride;
@@ -116,11 +95,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     if (tid == 0) {
         s_failed = 0;
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_k) : "memory");
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_v) : "memory");
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], WARPS); }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+        for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], GW); }
+        mbar_fence_init();
     }
     __syncthreads();
 
@@ -130,8 +108,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // ---------------- producer warp: lane i fetches page i of every tile (K and V), lane 0 arms the
         // stage's barrier. The block-table entry of the next tile is read while this one waits for its
         // stage. Keys and values of earlier positions were written by earlier steps, so their tiles are
-        // fetched at once; the tile that holds p (this step's own key and value) waits for this step's
-        // kernels.
+        // fetched at once, before the step's earlier kernels have finished. The tile that holds p holds this
+        // step's own key and value, written by the kernel before this one: with own_kv the consumers take
+        // them from the activation buffer instead (below) and no fetch waits; without, that tile's does.
         const int pages_per_tile = KEYS >> page_shift;
         const int oob = num_pages * kv_heads;
         auto plane_of = [&](int j) -> int {
@@ -144,15 +123,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         bool waited = false;
         int issued = 0;
         for (int j = 0; j < n_mine; ++j) {
-            const int st = j % C::STAGES;
+            const int st = j % stages;
             const int z = z_next;
             z_next = plane_of(j + 1);
-            if (!FUSED && t_begin + j == t_last && !waited) { pdl_wait(); waited = true; }
+            if (!own_kv && t_begin + j == t_last && !waited) { pdl_wait(); waited = true; }
             int ok = 1;
             if (lane == 0) {
-                if (j >= C::STAGES) ok = !s_failed && mbar_wait(&empty[st], ((j / C::STAGES) - 1) & 1);
+                if (j >= stages) ok = !s_failed && mbar_wait(&empty[st], ((j / stages) - 1) & 1);
                 if (ok) mbar_expect_tx(&full[st], C::STAGE);
-                else if (!s_failed) { atomicCAS(&g_dec_error, 0, (2 << 16) | (int)blockIdx.x); s_failed = 1; }
+                else if (!s_failed) { atomicCAS(&g_dec_error, 0, (2 << 16) | (int)(blockIdx.x & 0xffff)); s_failed = 1; }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
@@ -168,62 +147,52 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
         if (s_failed && lane == 0) {
             // copies already issued still target this CTA's shared memory: wait for them, bounded
-            for (int j = max(0, issued - C::STAGES); j < issued; ++j) mbar_wait(&full[j % C::STAGES], (j / C::STAGES) & 1);
+            for (int j = max(0, issued - stages); j < issued; ++j) mbar_wait(&full[j % stages], (j / stages) & 1);
         }
     } else {
-        // ---------------- four consumer warps: 16 keys of every tile each
+        // ---------------- four consumer warps: a quarter of every tile's keys each
+        const int grp = warp / GW, wg = warp % GW;
         pdl_wait();
+        if (tid == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ATTN_DECODE, 0, 1);
         int vis_lo[2] = {lo, lo}, vis_hi[2] = {g < n_rep ? p : -1, -1};      // rows g+8 exist only if n_rep > 8
         const __nv_bfloat16* q_ptr[2] = {nullptr, nullptr};
         if (g < n_rep) q_ptr[0] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g) * HD;
         if (g + 8 < n_rep) { q_ptr[1] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g + 8) * HD; vis_hi[1] = p; }
         unsigned q[HD / 16][4];
-        const float* cos_row = FUSED ? cos_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;      // p < 0: a padding row
-        const float* sin_row = FUSED ? sin_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;
-        if (FUSED) load_q_rotated<HD>(q, q_ptr, lane, cos_row, sin_row, rot);
-        else load_q<HD>(q, q_ptr, lane);
+        load_q<HD>(q, q_ptr, lane);
 #pragma unroll
         for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
         const float scale2 = scale * LOG2E;
 
         // ldmatrix addresses inside a swizzled tile: row r (128 bytes), 16-byte chunk c at ((c ^ (r & 7)) << 4)
         const int mat = lane >> 3, rr = lane & 7;
-        const unsigned k_row = (unsigned)(warp * WKEYS + (mat >> 1) * 8 + rr) * 128u;   // keys 0-7 / 8-15, dims 0-7 / 8-15
+        const unsigned k_row = (unsigned)(wg * WKEYS + (mat >> 1) * 8 + rr) * 128u;   // keys 0-7 / 8-15, dims 0-7 / 8-15
         const unsigned k_half = mat & 1;
-        const unsigned v_row = (unsigned)(warp * WKEYS + (mat & 1) * 8 + rr) * 128u;    // transposed: keys 0-7 / 8-15 first
+        const unsigned v_row = (unsigned)(wg * WKEYS + (mat & 1) * 8 + rr) * 128u;    // transposed: keys 0-7 / 8-15 first
         const unsigned v_half = mat >> 1;
 
-        for (int j = 0; j < n_mine; ++j) {
-            const int st = j % C::STAGES;
-            bool ok = !s_failed && mbar_wait(&full[st], (j / C::STAGES) & 1);
+        for (int j = grp; j < n_mine; j += GROUPS) {
+            const int st = j % stages;
+            bool ok = !s_failed && mbar_wait(&full[st], (j / stages) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
-                if (lane == 0 && !s_failed) { atomicCAS(&g_dec_error, 0, (1 << 16) | (int)blockIdx.x); s_failed = 1; }
+                if (lane == 0 && !s_failed) { atomicCAS(&g_dec_error, 0, (1 << 16) | (int)(blockIdx.x & 0xffff)); s_failed = 1; }
                 break;
             }
             const unsigned kt = smem_u32(smem + st * C::STAGE), vt = kt + C::TILE;
-            if (FUSED && t_begin + j == t_last && p >= 0 && (p & (KEYS - 1)) / WKEYS == warp) {
-                // this step's own key (rotated) and value: into this warp's rows of the tile and into the page
+            if (own_kv && t_begin + j == t_last && p >= 0 && (p & (KEYS - 1)) / WKEYS == wg) {
+                // this step's own key (rotated) and value, from the token's row of the activation buffer into this
+                // warp's rows of the tile: the copy of the page may have been taken before they were written there
                 const __nv_bfloat16* k_new = qkv + (size_t)token * q_stride + (size_t)(heads + kvh) * HD;
                 const __nv_bfloat16* v_new = qkv + (size_t)token * q_stride + (size_t)(heads + kv_heads + kvh) * HD;
                 const int r = p & (KEYS - 1);
-                const int page = __ldg(bt + (p >> page_shift));
-                const int slot = p & (page_size - 1);
-                const bool has_page = page >= 0 && page < num_pages;
-                const size_t off = has_page ? (((size_t)page * kv_heads + kvh) * page_size + slot) * HD : 0;
                 unsigned char* k_tile = smem + st * C::STAGE;
                 for (int d = 2 * lane; d < HD; d += 64) {
-                    const unsigned kr = rotated_pair(k_new, d, cos_row, sin_row, rot);
-                    const unsigned vr = *reinterpret_cast<const unsigned*>(v_new + d);
                     // element d of row r in a swizzled tile: column block d/64, 16-byte chunk (d%64)/8 at ((chunk ^ (r&7)) << 4)
                     const unsigned byte = (unsigned)(d >> 6) * SUBTILE + (unsigned)r * 128u +
                                           (((unsigned)((d & 63) >> 3) ^ (unsigned)(r & 7)) << 4) + (unsigned)(d & 7) * 2u;
-                    *reinterpret_cast<unsigned*>(k_tile + byte) = kr;
-                    *reinterpret_cast<unsigned*>(k_tile + C::TILE + byte) = vr;
-                    if (has_page) {
-                        *reinterpret_cast<unsigned*>(k_pages + off + d) = kr;
-                        *reinterpret_cast<unsigned*>(v_pages + off + d) = vr;
-                    }
+                    *reinterpret_cast<unsigned*>(k_tile + byte) = *reinterpret_cast<const unsigned*>(k_new + d);
+                    *reinterpret_cast<unsigned*>(k_tile + C::TILE + byte) = *reinterpret_cast<const unsigned*>(v_new + d);
                 }
                 __syncwarp();
             }
@@ -242,7 +211,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 }
             }
             unsigned pfrag[NT / 2][4];
-            softmax_block<HD, NT>(s, pfrag, o, m_run, l_run, scale2, (t_begin + j) * KEYS + warp * WKEYS, vis_lo, vis_hi, lane);
+            softmax_block<HD, NT>(s, pfrag, o, m_run, l_run, scale2, (t_begin + j) * KEYS + wg * WKEYS, vis_lo, vis_hi, lane);
 #pragma unroll
             for (int kb = 0; kb < NT / 2; ++kb) {
 #pragma unroll
@@ -259,27 +228,32 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
     }
     __syncthreads();        // every tile is consumed (or the CTA failed): no copy is in flight any more
-    if (s_failed || warp == WARPS) return;
 
-    // merge the four warps through shared memory (no copy is in flight any more)
+    // ---- merge the consumer warps through shared memory. A CTA that failed, and the rows of a padding token,
+    // contribute (max -inf, sum 0); every thread goes on to the cluster's barriers.
     constexpr int MS = HD + 4;                                    // padded row: conflict-free float2 stores
     float* sm_o = reinterpret_cast<float*>(smem);                 // [WARPS][16][MS]
     float* sm_ml = sm_o + WARPS * 16 * MS;                        // [WARPS][16][2]
     float* sm_f = sm_ml + WARPS * 16 * 2;                         // [WARPS][16] factors
+    float* cta_o = sm_f + WARPS * 16;                             // [16][HD]  this CTA's output, relative to its own maximum
+    float* cta_ml = cta_o + 16 * HD;                              // [16][2]   its (max, sum)
+    const bool failed = s_failed != 0;
+    if (warp < WARPS) {
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = g + 8 * r;
+        for (int r = 0; r < 2; ++r) {
+            const int row = g + 8 * r;
 #pragma unroll
-        for (int d = 0; d < HD / 8; ++d)
-            *reinterpret_cast<float2*>(&sm_o[(warp * 16 + row) * MS + d * 8 + 2 * t]) = make_float2(o[d][2 * r], o[d][2 * r + 1]);
-        if (t == 0) {
-            sm_ml[(warp * 16 + row) * 2] = m_run[r];
-            sm_ml[(warp * 16 + row) * 2 + 1] = l_run[r];
+            for (int d = 0; d < HD / 8; ++d)
+                *reinterpret_cast<float2*>(&sm_o[(warp * 16 + row) * MS + d * 8 + 2 * t]) = make_float2(o[d][2 * r], o[d][2 * r + 1]);
+            if (t == 0) {
+                sm_ml[(warp * 16 + row) * 2] = failed ? -INFINITY : m_run[r];
+                sm_ml[(warp * 16 + row) * 2 + 1] = failed ? 0.f : l_run[r];
+            }
         }
     }
     __syncthreads();
-    float m_row = -INFINITY, l_row = 0.f;
-    if (tid < n_rep) {
+    if (tid < 16) {
+        float m_row = -INFINITY, l_row = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) m_row = fmaxf(m_row, sm_ml[(w * 16 + tid) * 2]);
 #pragma unroll
@@ -289,52 +263,70 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             l_row += sm_ml[(w * 16 + tid) * 2 + 1] * f;
             sm_f[w * 16 + tid] = f;
         }
-        if (splits > 1) {
-            const size_t slot = ((size_t)token * heads + kvh * n_rep + tid) * splits + split;
-            part_ml[slot * 2] = m_row;
-            part_ml[slot * 2 + 1] = l_row;
-        } else {
-            sm_ml[tid * 2 + 1] = l_row;                         // warp 0's slot of the row: the total for the division below
-        }
+        cta_ml[tid * 2] = m_row;
+        cta_ml[tid * 2 + 1] = l_row;
     }
     __syncthreads();
-    for (int i = tid; i < n_rep * HD; i += WARPS * 32) {
+    for (int i = tid; i < n_rep * HD; i += THREADS) {
         const int row = i / HD, d = i - row * HD;
         float acc = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) acc += sm_o[(w * 16 + row) * MS + d] * sm_f[w * 16 + row];
-        const size_t th = (size_t)token * heads + kvh * n_rep + row;
-        if (splits == 1) {
-            const float l = sm_ml[row * 2 + 1];
-            out[th * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        cta_o[row * HD + d] = acc;
+    }
+    if (csize > 1) cluster_sync(); else __syncthreads();
+
+    // ---- merge the CTAs of the cluster: this CTA finishes its slice of the group's n_rep x HD outputs from
+    // every peer's (max, sum, output), in rank order
+    const int rank = csize > 1 ? (int)cluster_rank() : 0;
+    const int outer = splits / csize, oidx = split / csize;
+    const int total = n_rep * HD;
+    const int slice = (total + csize - 1) / csize;
+    const int i_end = min(total, (rank + 1) * slice);
+    for (int i = rank * slice + tid; i < i_end; i += THREADS) {
+        const int row = i / HD, d = i - row * HD;
+        float m_all = -INFINITY, l_all = 0.f, acc = 0.f;
+        if (csize > 1) {
+            float mr[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                mr[r] = -INFINITY;
+                if (r < csize) mr[r] = ld_peer_f32(peer_smem(&cta_ml[row * 2], r));
+                m_all = fmaxf(m_all, mr[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < csize) {
+                    const float f = (mr[r] == -INFINITY) ? 0.f : exp2f(mr[r] - m_all);
+                    l_all += ld_peer_f32(peer_smem(&cta_ml[row * 2 + 1], r)) * f;
+                    acc += ld_peer_f32(peer_smem(&cta_o[row * HD + d], r)) * f;
+                }
+            }
         } else {
-            part_o[(th * splits + split) * HD + d] = acc;
+            m_all = cta_ml[row * 2];
+            l_all = cta_ml[row * 2 + 1];
+            acc = cta_o[row * HD + d];
+        }
+        const size_t th = (size_t)token * heads + kvh * n_rep + row;
+        if (outer == 1) {
+            out[th * HD + d] = __float2bfloat16_rn(l_all > 0.f ? acc / l_all : 0.f);
+        } else {
+            part_o[(th * outer + oidx) * HD + d] = acc;
+            if (d == 0) {
+                part_ml[(th * outer + oidx) * 2] = m_all;
+                part_ml[(th * outer + oidx) * 2 + 1] = l_all;
+            }
         }
     }
+    if (tid == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ATTN_DECODE, 0, 2);
+    if (csize > 1) cluster_sync();      // nobody leaves while a peer may still read its shared memory
 }
 
 // ---------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
 
 // Map over the pool: (head dim, slot in page, page * kv_heads + kv head); a box is 64 elements of one page of one kv head.
 int make_pool_map(CUtensorMap* map, const void* ptr, int head_dim, int page_size, long long planes) {
-    EncodeTiledFn enc = get_encode();
+    NibEncodeTiledFn enc = nib_tensor_map_encoder();
     NIB_REQUIRE(enc != nullptr, "attention decode (TMA): cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)page_size, (cuuint64_t)planes};
     cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)page_size * head_dim * 2};
@@ -347,23 +339,46 @@ int make_pool_map(CUtensorMap* map, const void* ptr, int head_dim, int page_size
     return 0;
 }
 
-template <int HD, bool FUSED>
+template <int HD>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const void* qkv, int q_stride, void* out, const int* ctx_lens,
            const int* block_table, int bt_stride, int page_size, int num_pages, int n_tokens, int heads, int kv_heads,
-           float scale, int window, int splits, float* part_o, float* part_ml, void* k_pages, void* v_pages,
-           const float* cos_t, const float* sin_t, int rot, cudaStream_t stream) {
+           float scale, int window, int splits, int csize, int own_kv, float* part_o, float* part_ml, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<HD>::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg<HD>::smem_bytes(Cfg<HD>::MAX_STAGES)));
         configured = true;
     }
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
-    NIB_CUDA(launch_pdl(attention_decode_tma_kernel<HD, FUSED>, dim3(splits, n_tokens, kv_heads), dim3(THREADS), (size_t)Cfg<HD>::SMEM,
-                        stream, mk, mv, (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table,
-                        bt_stride, page_size, shift, num_pages, heads, kv_heads, heads / kv_heads, scale, window, splits,
-                        part_o, part_ml, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, cos_t, sin_t, rot));
-    if (splits > 1) return nib_attention_combine(part_o, part_ml, out, n_tokens * heads, splits, HD, stream);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, n_tokens, kv_heads);
+    cfg.blockDim = dim3(THREADS);
+    const int stages = g_dec_stages;
+    cfg.dynamicSmemBytes = (size_t)Cfg<HD>::smem_bytes(stages);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (csize > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = csize;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    if (nib_pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    NIB_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<HD>, mk, mv, (const __nv_bfloat16*)qkv, q_stride,
+                                (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size, shift, num_pages, heads,
+                                kv_heads, heads / kv_heads, scale, window, splits, csize, stages, Cfg<HD>::data_bytes(stages), own_kv, part_o, part_ml,
+                                nib_trace_buffer(), nib_trace_capacity()));
+    const int outer = splits / csize;
+    if (outer > 1) return nib_attention_combine(part_o, part_ml, out, n_tokens * heads, outer, HD, stream);
     return 0;
 }
 
@@ -375,8 +390,11 @@ NIB_API int nib_attention_decode_tma_supported(int heads, int kv_heads, int head
     if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16) return 0;
     if (head_dim != 64 && head_dim != 128) return 0;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return 0;
-    return get_encode() != nullptr;
+    return nib_tensor_map_encoder() != nullptr;
 }
+
+// Tiles in flight per CTA (2..4, 32 KB of shared memory each); for measurements.
+NIB_API void nib_attention_decode_tma_stages(int stages) { g_dec_stages = stages < 2 ? 2 : (stages > 4 ? 4 : stages); }
 
 // The error word of the kernel's bounded waits (0 = none); synchronises with the device and clears it.
 NIB_API int nib_attention_decode_tma_error() {
@@ -386,53 +404,35 @@ NIB_API int nib_attention_decode_tma_error() {
     return v;
 }
 
-namespace {
-int decode_tma(const void* qkv, int q_stride, void* out, const int* ctx_lens, const int* block_table, int bt_stride,
-               int page_size, void* k_pages, void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
-               int head_dim, float scale, int window, int splits, float* part_o, float* part_ml, bool fused,
-               const float* cos_t, const float* sin_t, int rot, cudaStream_t stream) {
+// Attention of n_tokens single decoded tokens (token i is request i) over their cached keys; ``qkv`` holds the
+// rotated queries, and the token's own key and value are in its page already; with ``own_kv`` the row also holds the
+// token's rotated key and its value behind the queries ([q heads | k heads | v heads]) and they are taken from there, so
+// that no page has to be read after the kernel that wrote them. ``splits`` CTAs share the keys
+// of a (token, kv head): 1, 2, 4 or 8 (one cluster merges them in shared memory), or a multiple of 8 (clusters
+// of eight, whose partial results go to ``part_o`` [tokens*heads*splits/8*head_dim] and ``part_ml``
+// [tokens*heads*splits/8*2] floats and are merged by a second kernel).
+NIB_API int nib_attention_decode_tma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
+                                     const int* block_table, int bt_stride, int page_size, const void* k_pages,
+                                     const void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
+                                     int head_dim, float scale, int window, int splits, int own_kv, float* part_o,
+                                     float* part_ml, cudaStream_t stream) {
     NIB_REQUIRE(nib_attention_decode_tma_supported(heads, kv_heads, head_dim, page_size),
                 "attention decode (TMA): head_dim %d, %d/%d heads, page size %d are not supported", head_dim, heads, kv_heads, page_size);
     NIB_REQUIRE(n_tokens >= 0 && num_pages > 0 && window >= 0 && splits >= 1 && splits <= 64, "attention decode (TMA): bad sizes (1..64 splits)");
-    NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode (TMA): splits > 1 need scratch memory");
+    const int csize = splits >= 8 ? 8 : splits;
+    NIB_REQUIRE((csize & (csize - 1)) == 0 && splits % csize == 0,
+                "attention decode (TMA): %d splits; 1, 2, 4, 8 or a multiple of 8 are possible", splits);
+    NIB_REQUIRE(splits == csize || (part_o && part_ml), "attention decode (TMA): more than 8 splits need scratch memory");
     NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode (TMA): too many tokens or kv heads for one launch");
     NIB_REQUIRE((((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0 && q_stride % 2 == 0, "attention decode (TMA): the pools must be 16-byte aligned, rows 4-byte aligned");
     NIB_REQUIRE((long long)num_pages * kv_heads < (1LL << 31) - 1, "attention decode (TMA): too many pages");
-    NIB_REQUIRE(!fused || (rot >= 0 && rot <= head_dim && rot % 4 == 0 && (rot == 0 || (cos_t && sin_t))),
-                "attention decode (TMA, fused): rotated width %d must be a multiple of 4 and at most head_dim", rot);
     if (n_tokens == 0) return 0;
     CUtensorMap mk, mv;
     const long long planes = (long long)num_pages * kv_heads;
     if (make_pool_map(&mk, k_pages, head_dim, page_size, planes)) return 1;
     if (make_pool_map(&mv, v_pages, head_dim, page_size, planes)) return 1;
-#define CALL(HD, F) launch<HD, F>(mk, mv, qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, num_pages, n_tokens, heads, \
-                                  kv_heads, scale, window, splits, part_o, part_ml, k_pages, v_pages, cos_t, sin_t, rot, stream)
-    if (fused) return head_dim == 64 ? CALL(64, true) : CALL(128, true);
-    return head_dim == 64 ? CALL(64, false) : CALL(128, false);
+#define CALL(HD) launch<HD>(mk, mv, qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, num_pages, n_tokens, heads, \
+                            kv_heads, scale, window, splits, csize, own_kv, part_o, part_ml, stream)
+    return head_dim == 64 ? CALL(64) : CALL(128);
 #undef CALL
-}
-}  // namespace
-
-// Arguments as nib_attention_decode_mma (without counters: the splits are merged by the combine kernel).
-NIB_API int nib_attention_decode_tma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
-                                     const int* block_table, int bt_stride, int page_size, const void* k_pages,
-                                     const void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
-                                     int head_dim, float scale, int window, int splits, float* part_o, float* part_ml,
-                                     cudaStream_t stream) {
-    return decode_tma(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, const_cast<void*>(k_pages),
-                      const_cast<void*>(v_pages), num_pages, n_tokens, heads, kv_heads, head_dim, scale, window, splits, part_o,
-                      part_ml, false, nullptr, nullptr, 0, stream);
-}
-
-// The same fused with what precedes it in a decode step: qkv is the raw projection; queries and the new key
-// are rotated with the tables' row of the token's position (ctx_len - 1), the new key and value are written
-// into the token's page and used at once. Arguments as nib_attention_decode_fused_mma.
-NIB_API int nib_attention_decode_tma_fused(const void* qkv, int q_stride, void* out, const int* ctx_lens,
-                                           const int* block_table, int bt_stride, int page_size, void* k_pages,
-                                           void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
-                                           int head_dim, float scale, int window, int splits, float* part_o,
-                                           float* part_ml, const float* cos_t, const float* sin_t, int rot,
-                                           cudaStream_t stream) {
-    return decode_tma(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens,
-                      heads, kv_heads, head_dim, scale, window, splits, part_o, part_ml, true, cos_t, sin_t, rot, stream);
 }

@@ -200,15 +200,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __
 // ------------------------------------------------------------------------------------------ decode
 // grid: (splits, tokens, kv heads). Every token has q_len 1; its position is ctx_len - 1.
 // part_o: [tokens, heads, splits, HD] float, part_ml: [tokens, heads, splits, 2] (max in log2 units, sum).
-// FUSED: qkv is the raw projection; the kernel rotates the queries as it loads them, and the CTA whose keys
-// include the token's own position rotates the new key, puts key and value into its tiles and into the page.
-template <int HD, bool FUSED>
+template <int HD>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
-                        int page_size, __nv_bfloat16* k_pages, __nv_bfloat16* v_pages, int num_pages, int heads, int kv_heads,
+                        int page_size, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, int num_pages, int heads, int kv_heads,
                         float scale, int window, int splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int* __restrict__ counters, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot) {
+                        int* __restrict__ counters) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_last;
     pdl_launch_dependents();
@@ -255,10 +253,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
     cp_async_commit();
     pdl_wait();
     unsigned q[HD / 16][4];
-    const float* cos_row = FUSED ? cos_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;      // p < 0: a padding row
-    const float* sin_row = FUSED ? sin_t + (size_t)max(p, 0) * (rot >> 1) : nullptr;
-    if (FUSED) load_q_rotated<HD>(q, q_ptr, lane, cos_row, sin_row, rot);
-    else load_q<HD>(q, q_ptr, lane);
+    load_q<HD>(q, q_ptr, lane);
     if (!issued0) {
         if (t_begin <= t_end) issue(t_begin, 0);
         cp_async_commit();
@@ -272,27 +267,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, int q_stride, __n
         const int cur = (tile - t_begin) & 1;
         cp_async_wait<1>();                        // everything but the newest group: tile `tile` has landed
         __syncthreads();
-        if (FUSED && tile == own && p >= 0) {
-            // this step's own key (rotated) and value: into the tiles, and into the page for the steps to come
-            const __nv_bfloat16* k_new = qkv + (size_t)token * q_stride + (size_t)(heads + kvh) * HD;
-            const __nv_bfloat16* v_new = qkv + (size_t)token * q_stride + (size_t)(heads + kv_heads + kvh) * HD;
-            const int r = p - own * BLOCK_N;
-            const int page = bt[shift >= 0 ? (p >> shift) : (p / page_size)];
-            const int slot = shift >= 0 ? (p & (page_size - 1)) : (p % page_size);
-            const bool has_page = page >= 0 && page < num_pages;
-            const size_t off = has_page ? (((size_t)page * kv_heads + kvh) * page_size + slot) * HD : 0;
-            for (int d = 2 * tid; d < HD; d += 2 * WARPS * 32) {
-                const unsigned kr = rotated_pair(k_new, d, cos_row, sin_row, rot);
-                const unsigned vr = *reinterpret_cast<const unsigned*>(v_new + d);
-                *reinterpret_cast<unsigned*>(k_buf[cur] + r * Tile<HD>::ROW_BYTES + d * 2) = kr;
-                *reinterpret_cast<unsigned*>(v_buf[cur] + r * Tile<HD>::ROW_BYTES + d * 2) = vr;
-                if (has_page) {
-                    *reinterpret_cast<unsigned*>(k_pages + off + d) = kr;
-                    *reinterpret_cast<unsigned*>(v_pages + off + d) = vr;
-                }
-            }
-            __syncthreads();
-        }
         // each warp takes 16 keys of the tile
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
@@ -470,28 +444,20 @@ int launch_prefill(const void* qkv, int q_stride, void* out, const int* q_start,
 
 template <int HD>
 int launch_decode(const void* qkv, int q_stride, void* out, const int* ctx_lens, const int* block_table,
-                  int bt_stride, int page_size, void* k_pages, void* v_pages, int num_pages,
+                  int bt_stride, int page_size, const void* k_pages, const void* v_pages, int num_pages,
                   int n_tokens, int heads, int kv_heads, float scale, int window, int splits, float* part_o,
-                  float* part_ml, int* counters, const float* cos_t, const float* sin_t, int rot, bool fused,
-                  cudaStream_t stream) {
+                  float* part_ml, int* counters, cudaStream_t stream) {
     static bool configured = false;
     const int smem = decode_smem<HD>();
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        NIB_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        NIB_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
     dim3 grid(splits, n_tokens, kv_heads);
-    if (fused)
-        NIB_CUDA(launch_pdl(attention_decode_kernel<HD, true>, grid, dim3(WARPS * 32), (size_t)smem, stream,
-                            (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
-                            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
-                            window, splits, part_o, part_ml, counters, cos_t, sin_t, rot));
-    else
-        NIB_CUDA(launch_pdl(attention_decode_kernel<HD, false>, grid, dim3(WARPS * 32), (size_t)smem, stream,
-                            (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
-                            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
-                            window, splits, part_o, part_ml, counters, cos_t, sin_t, rot));
+    NIB_CUDA(launch_pdl(attention_decode_kernel<HD>, grid, dim3(WARPS * 32), (size_t)smem, stream,
+                        (const __nv_bfloat16*)qkv, q_stride, (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size,
+                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, num_pages, heads, kv_heads, scale,
+                        window, splits, part_o, part_ml, counters));
     if (splits > 1 && counters == nullptr)
         NIB_CUDA(launch_pdl(attention_combine_kernel, dim3(n_tokens * heads), dim3(128), (size_t)0, stream,
                             (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, HD));
@@ -561,31 +527,7 @@ NIB_API int nib_attention_decode_mma(const void* qkv, int q_stride, void* out, c
     NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode: splits > 1 need scratch memory");
     NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode: too many tokens or kv heads for one launch");
     if (n_tokens == 0) return 0;
-#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, const_cast<void*>(k_pages), const_cast<void*>(v_pages), num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, counters, nullptr, nullptr, 0, false, stream)
-    NIB_HD_SWITCH(head_dim, CALL)
-#undef CALL
-    NIB_REQUIRE(false, "attention decode: unreachable head_dim %d", head_dim);
-}
-
-// The decode attention fused with what precedes it in a decode step: qkv is the raw projection [n_tokens,
-// (heads + 2 kv_heads) * head_dim]; queries and the new key are rotated with the tables' row of the token's
-// position (ctx_len - 1), the new key and value are written into the token's page and used at once. The
-// rotated width must be a multiple of 4 and at most head_dim. Otherwise as nib_attention_decode_mma.
-NIB_API int nib_attention_decode_fused_mma(const void* qkv, int q_stride, void* out, const int* ctx_lens,
-                                           const int* block_table, int bt_stride, int page_size, void* k_pages,
-                                           void* v_pages, int num_pages, int n_tokens, int heads, int kv_heads,
-                                           int head_dim, float scale, int window, int splits, float* part_o,
-                                           float* part_ml, int* counters, const float* cos_t, const float* sin_t, int rot,
-                                           cudaStream_t stream) {
-    NIB_REQUIRE(nib_attention_mma_supported(heads, kv_heads, head_dim), "attention (tensor cores): head_dim %d with %d/%d heads is not supported", head_dim, heads, kv_heads);
-    NIB_REQUIRE(heads / kv_heads <= 16, "attention decode: at most 16 query heads per kv head, got %d", heads / kv_heads);
-    NIB_REQUIRE(n_tokens >= 0 && page_size > 0 && num_pages > 0 && window >= 0 && splits >= 1 && splits <= 64, "attention decode: bad sizes (1..64 splits)");
-    NIB_REQUIRE(splits == 1 || (part_o && part_ml), "attention decode: splits > 1 need scratch memory");
-    NIB_REQUIRE(rot >= 0 && rot <= head_dim && rot % 4 == 0 && (rot == 0 || (cos_t && sin_t)), "attention decode (fused): rotated width %d must be a multiple of 4 and at most head_dim", rot);
-    NIB_REQUIRE(q_stride % 2 == 0, "attention decode (fused): rows must be 4-byte aligned");
-    NIB_REQUIRE(n_tokens <= 65535 && kv_heads <= 65535, "attention decode: too many tokens or kv heads for one launch");
-    if (n_tokens == 0) return 0;
-#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, counters, cos_t, sin_t, rot, true, stream)
+#define CALL(HD) launch_decode<HD>(qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, k_pages, v_pages, num_pages, n_tokens, heads, kv_heads, scale, window, splits, part_o, part_ml, counters, stream)
     NIB_HD_SWITCH(head_dim, CALL)
 #undef CALL
     NIB_REQUIRE(false, "attention decode: unreachable head_dim %d", head_dim);

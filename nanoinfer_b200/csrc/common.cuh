@@ -83,3 +83,27 @@ static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 b
     cfg.numAttrs = nib_pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// ---- timeline of a step -------------------------------------------------------------------------------
+// Kernels that overlap through programmatic dependent launch cannot be timed from outside (an event between two
+// of them would end the overlap). When a trace buffer is set (nib_trace_set), thread 0 of the first CTA of a
+// kernel notes the GPU's nanosecond timer at a few points of its life: 0 entry, 1 after the wait for the
+// earlier kernels, 2 its results written. buf[0] counts the notes; note i is buf[1 + 2i] = kernel id << 8 | phase
+// and buf[2 + 2i] = time. Without a buffer a launch passes nullptr and the kernel does one predictable branch.
+enum NibTraceKernel : int {
+    NIB_TK_EMBED = 1, NIB_TK_RMSNORM = 2, NIB_TK_ROPE = 3, NIB_TK_GEMM_SMALLM = 4, NIB_TK_GEMM_STREAM = 5,
+    NIB_TK_GEMM_TC = 6, NIB_TK_ATTN_DECODE = 7, NIB_TK_ATTN_COMBINE = 8, NIB_TK_ARGMAX = 9, NIB_TK_ATTN_DECODE_MMA = 10,
+};
+unsigned long long* nib_trace_buffer();      // nullptr unless a trace is being taken
+int nib_trace_capacity();
+
+__device__ __forceinline__ void nib_trace_mark(unsigned long long* buf, int cap, int kernel, int tag, int phase) {
+    if (buf == nullptr || (blockIdx.x | blockIdx.y | blockIdx.z) != 0) return;
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+    const unsigned long long i = atomicAdd(buf, 1ULL);
+    if ((int)i < cap) {
+        buf[1 + 2 * i] = ((unsigned long long)kernel << 16) | ((unsigned long long)(tag & 0xff) << 8) | (unsigned long long)phase;
+        buf[2 + 2 * i] = now;
+    }
+}

@@ -77,9 +77,10 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain, const int* __restrict__ rows,
-                    T* __restrict__ out, int n_rows, int hidden, float eps) {
+                    T* __restrict__ out, int n_rows, int hidden, float eps, unsigned long long* trace, int trace_cap) {
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_RMSNORM, 0, 0);
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int n4 = hidden >> 2;
     float4 g[NV];
@@ -89,6 +90,7 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain,
         g[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(gain) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     pdl_wait();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_RMSNORM, 0, 1);
     if (r >= n_rows) return;
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
     float4 v[NV];
@@ -123,6 +125,7 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain,
             }
         }
     }
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_RMSNORM, 0, 2);
 }
 
 template <typename T>
@@ -131,11 +134,11 @@ int launch_rmsnorm_rows(const float* x, const float* gain, const int* rows, T* o
     const int warps = n_rows >= 8 ? 8 : n_rows;           // rows per block
     const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
     if (hidden <= 128 * 8)
-        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 8>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps));
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 8>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, nib_trace_buffer(), nib_trace_capacity()));
     else if (hidden <= 128 * 16)
-        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 16>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps));
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 16>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, nib_trace_buffer(), nib_trace_capacity()));
     else
-        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 32>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps));
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 32>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, nib_trace_buffer(), nib_trace_capacity()));
     return 0;
 }
 

@@ -29,7 +29,7 @@
 
 namespace {
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
 constexpr int WARPS = 8;
 constexpr int MAX_TOKENS = 64;
 
@@ -51,13 +51,35 @@ __device__ __forceinline__ unsigned pack2(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// The q/k/v epilogue (EPI_QKV): the product's rows are [q heads | k heads | v heads] of head_dim each. A group of 16
+// rows is cut so that the rotated dimension d of a query or key head (rows g of the group) and its partner d + rot/2
+// (rows g + 8) are the two halves of one thread's accumulator: the rotation needs no exchange between threads.
+// After bias and rotation the whole row goes to the activation buffer, and (writes) the rotated key and the value
+// into the slot of the token's position in its request's page.
+struct QkvEpi {
+    int heads, kv_heads, head_dim, rot;
+    const int* positions; const int* req_index; const float* cos_t; const float* sin_t;
+    const int* block_table; int bt_stride, page_size, num_pages;
+    __nv_bfloat16* k_pages; __nv_bfloat16* v_pages; int writes;
+};
+
+// First rows of the two halves of row group `group` in the q/k/v form.
+__device__ __forceinline__ void qkv_group_rows(const QkvEpi& q, int group, int& a, int& b) {
+    const int per_head = q.head_dim >> 4;
+    const int hs = group / per_head, i = group - hs * per_head;
+    const int base = hs * q.head_dim;
+    if (hs < q.heads + q.kv_heads && i < (q.rot >> 4)) { a = base + i * 8; b = a + (q.rot >> 1); }
+    else { a = base + i * 16; b = a + 8; }
+}
+
 // NT: token tiles of 8. KSPLIT: 1 (each warp its own 16 rows, whole K) or WARPS (the warps of a CTA
 // share 16 rows and split K; gridDim.y CTAs split K further). grid.x: CTAs over the row groups.
 template <int NT, int KSPLIT, int EPI, bool NORM>
 __global__ void __launch_bounds__(WARPS * 32, 2)      // two CTAs per SM: a projection's 300 row groups fit one wave
 gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
                    void* __restrict__ out, int tokens, int n_out, int k_dim, int lda, int ldo,
-                   const float* __restrict__ gain, float eps, float* __restrict__ scratch, int* __restrict__ counters) {
+                   const float* __restrict__ gain, float eps, float* __restrict__ scratch, int* __restrict__ counters,
+                   const QkvEpi qe, unsigned long long* trace, int trace_cap) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     constexpr int ACCS = DUAL ? 2 : 1;
     constexpr int GROUPS = WARPS / KSPLIT;
@@ -68,6 +90,7 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
     pdl_launch_dependents();
     bool waited = false;          // pdl_wait() comes after the first batch of weight loads has been issued
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_SMALLM, EPI, 0);
     const int group = blockIdx.x * GROUPS + (KSPLIT > 1 ? 0 : warp);
     const int f0 = group * 16;
     const int cross = gridDim.y;
@@ -88,9 +111,42 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
 #pragma unroll
             for (int e = 0; e < E; ++e) acc[a][n][e] = 0.f;
 
+    // The q/k/v epilogue's view of the thread's tokens (2t, 2t+1 of every tile): position, page, cos and sin of the
+    // thread's rotated dimension. They are inputs of the step, not results of its kernels: read before the wait.
+    constexpr int QN = (EPI == EPI_QKV) ? NT : 1;
+    int q_ra = 0, q_rb = 0, q_pos[QN][2], q_page[QN][2];
+    float q_cs[QN][2], q_sn[QN][2], q_bias[2] = {0.f, 0.f};
+    bool q_rot = false;
+    if (EPI == EPI_QKV && f0 < n_out) {
+        qkv_group_rows(qe, group, q_ra, q_rb);
+        const int hs = q_ra / qe.head_dim, d = q_ra - hs * qe.head_dim + g;
+        q_rot = hs < qe.heads + qe.kv_heads && q_rb - q_ra == (qe.rot >> 1) && qe.rot > 0 && d < (qe.rot >> 1);
+        if (KSPLIT == 1 || warp == 0) {
+            if (bias) { q_bias[0] = __ldg(bias + q_ra + g); q_bias[1] = __ldg(bias + q_rb + g); }
+#pragma unroll
+            for (int n = 0; n < QN; ++n)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int tok = n * 8 + 2 * t + j;
+                    q_pos[n][j] = 0; q_page[n][j] = -1; q_cs[n][j] = 1.f; q_sn[n][j] = 0.f;
+                    if (tok < tokens) {
+                        const int pos = __ldg(qe.positions + tok);
+                        q_pos[n][j] = pos;
+                        if (hs >= qe.heads && qe.writes)
+                            q_page[n][j] = __ldg(qe.block_table + (size_t)__ldg(qe.req_index + tok) * qe.bt_stride + pos / qe.page_size);
+                        if (q_rot) {
+                            q_cs[n][j] = __ldg(qe.cos_t + (size_t)pos * (qe.rot >> 1) + d);
+                            q_sn[n][j] = __ldg(qe.sin_t + (size_t)pos * (qe.rot >> 1) + d);
+                        }
+                    }
+                }
+        }
+    }
+
     if (f0 < n_out) {
         // rows past the end are clamped (their results are not stored)
-        const int r0 = min(f0 + g, n_out - 1), r1 = min(f0 + g + 8, n_out - 1);
+        int r0 = min(f0 + g, n_out - 1), r1 = min(f0 + g + 8, n_out - 1);
+        if (EPI == EPI_QKV) { r0 = q_ra + g; r1 = q_rb + g; }
         const __nv_bfloat16* w0 = W + (size_t)r0 * k_dim + 8 * t;
         const __nv_bfloat16* w1 = W + (size_t)r1 * k_dim + 8 * t;
         const __nv_bfloat16* u0 = W + (size_t)(n_out + r0) * k_dim + 8 * t;
@@ -123,7 +179,11 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
                     gf[NORM ? u : 0][1] = __ldg(reinterpret_cast<const float4*>(gain + k0 + 8 * t + 4));
                 }
             }
-            if (!waited) { pdl_wait(); waited = true; }     // weights are nobody's output; the activations are
+            if (!waited) {                                  // weights are nobody's output; the activations are
+                pdl_wait();
+                waited = true;
+                if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_SMALLM, EPI, 1);
+            }
 #pragma unroll
             for (int u = 0; u < UN; ++u) {
                 const bool live = base + u < kb_end;
@@ -245,6 +305,45 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
     }
     if (f0 >= n_out) return;
 
+    if (EPI == EPI_QKV) {
+        // the thread's rows q_ra + g (elements 0, 1) and q_rb + g (elements 2, 3) of tokens n*8 + 2t and + 1
+        const int hs = q_ra / qe.head_dim;
+        const int d_lo = q_ra - hs * qe.head_dim + g, d_hi = q_rb - hs * qe.head_dim + g;
+        const bool is_v = hs >= qe.heads + qe.kv_heads;
+        const int kvh = hs - qe.heads - (is_v ? qe.kv_heads : 0);
+        __nv_bfloat16* pages = is_v ? qe.v_pages : qe.k_pages;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int tok = n * 8 + 2 * t + j;
+                float scale = 1.f;
+                if (NORM) {
+                    const float ss = __shfl_sync(0xffffffffu, acc[0][n][E - 1], (2 * t + j) * 4);
+                    scale = 1.0f / sqrtf(ss / (float)k_dim + eps);
+                }
+                if (tok >= tokens) continue;
+                float lo = acc[0][n][j] * scale + q_bias[0], hi = acc[0][n][2 + j] * scale + q_bias[1];
+                if (q_rot) {
+                    const float c = q_cs[EPI == EPI_QKV ? n : 0][j], sn = q_sn[EPI == EPI_QKV ? n : 0][j];
+                    const float a = lo * c - hi * sn, b = hi * c + lo * sn;
+                    lo = a;
+                    hi = b;
+                }
+                const __nv_bfloat16 blo = __float2bfloat16_rn(lo), bhi = __float2bfloat16_rn(hi);
+                __nv_bfloat16* row = (__nv_bfloat16*)out + (size_t)tok * ldo;
+                row[q_ra + g] = blo;
+                row[q_rb + g] = bhi;
+                const int page = q_page[EPI == EPI_QKV ? n : 0][j];
+                if (hs >= qe.heads && qe.writes && page >= 0 && page < qe.num_pages) {
+                    __nv_bfloat16* dst = pages + (((size_t)page * qe.kv_heads + kvh) * qe.page_size + q_pos[EPI == EPI_QKV ? n : 0][j] % qe.page_size) * qe.head_dim;
+                    dst[d_lo] = blo;
+                    dst[d_hi] = bhi;
+                }
+            }
+        if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_SMALLM, EPI, 2);
+        return;
+    }
     // accumulator element e of tile n: feature f0 + g + 8*(e/2), token n*8 + 2t + (e&1);
     // the sum of squares of token n*8 + j sits in the lanes of quad j
     const float bias0 = (bias && f0 + g < n_out) ? bias[f0 + g] : 0.f;
@@ -276,13 +375,15 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
             if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
             else if (EPI == EPI_ADD) ((float*)out)[o] = res[n][e] + x;
             else if (EPI == EPI_F32) ((float*)out)[o] = x;
-            else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(__fdividef(x, 1.0f + __expf(-x)) * (acc[ACCS - 1][n][e] * scale));
+            else if (EPI == EPI_SWIGLU) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(__fdividef(x, 1.0f + __expf(-x)) * (acc[ACCS - 1][n][e] * scale));
         }
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_SMALLM, EPI, 2);
 }
 
 struct Args {
     const void* A; const void* W; const float* bias; void* out; int tokens, N, K, lda, ldo;
     const float* gain; float eps; float* scratch; int* counters; int cross;
+    QkvEpi qe;
 };
 
 template <int NT, int KSPLIT, int EPI, bool NORM>
@@ -298,7 +399,7 @@ int launch_one(const Args& a, cudaStream_t stream) {
     configured = true;
     NIB_CUDA(launch_pdl(gemm_smallm_kernel<NT, KSPLIT, EPI, NORM>, grid, dim3(WARPS * 32), smem, stream,
                         a.A, (const __nv_bfloat16*)a.W, a.bias, a.out, a.tokens, a.N, a.K, a.lda, a.ldo, a.gain, a.eps,
-                        a.scratch, a.counters));
+                        a.scratch, a.counters, a.qe, nib_trace_buffer(), nib_trace_capacity()));
     return 0;
 }
 
@@ -309,6 +410,9 @@ int launch_epi(int epi, const Args& a, cudaStream_t stream) {
         case EPI_ADD: return launch_one<NT, KSPLIT, EPI_ADD, NORM>(a, stream);
         case EPI_F32: return launch_one<NT, KSPLIT, EPI_F32, NORM>(a, stream);
         case EPI_SWIGLU: return launch_one<NT, KSPLIT, EPI_SWIGLU, NORM>(a, stream);
+        case EPI_QKV:
+            if constexpr (KSPLIT > 1 && NT <= 2) return launch_one<NT, KSPLIT, EPI_QKV, NORM>(a, stream);
+            break;
     }
     nib_set_error("gemm (small M): unknown epilogue %d", epi);
     return 1;
@@ -377,7 +481,40 @@ NIB_API int nib_gemm_smallm(const void* A, const void* W, const float* bias, voi
         NIB_REQUIRE(nib_gemm_smallm_scratch_floats(N, cross) <= scratch_floats && groups <= counter_ints,
                     "gemm (small M): workspace too small for N=%d cross=%d", N, cross);
     }
-    Args a{A, W, bias, out, tokens, N, K, lda, ldo, gain, eps, scratch, counters, cross};
+    Args a{A, W, bias, out, tokens, N, K, lda, ldo, gain, eps, scratch, counters, cross, QkvEpi{}};
     if (gain) return launch_tokens<true>(ksplit, epi, a, stream);
     return launch_tokens<false>(ksplit, epi, a, stream);
+}
+
+// 1 if nib_gemm_smallm_qkv takes these sizes: up to 16 tokens, head size and rotated width multiples of 16.
+NIB_API int nib_gemm_smallm_qkv_supported(const void* A, const void* W, int tokens, int K, int lda, int elem_bytes,
+                                          int head_dim, int rot) {
+    if (tokens > 16 || head_dim <= 0 || head_dim % 16 || rot < 0 || rot > head_dim || rot % 16) return 0;
+    return nib_gemm_smallm_supported(A, W, tokens, K, lda, elem_bytes);
+}
+
+// The q/k/v projection of a decode step with what follows it, in one kernel: qkv[tokens, (heads + 2 kv_heads) *
+// head_dim] = A . W^T + bias (A, gain, eps as in nib_gemm_smallm); query and key heads are rotated by
+// positions[token] (tables of rot/2 values per position; the first rot dimensions of a head, halves paired); the whole
+// row is stored to ``qkv``; with ``writes`` the rotated key and the value also go to the slot of the token's position
+// in its request's page (block_table[req_index[token]][position / page_size]; a negative entry is skipped).
+NIB_API int nib_gemm_smallm_qkv(const void* A, const void* W, const float* bias, void* qkv, int tokens, int heads,
+                                int kv_heads, int head_dim, int K, int lda, int ldq, const float* gain, float eps,
+                                const int* positions, const int* req_index, const float* cos_t, const float* sin_t,
+                                int rot, const int* block_table, int bt_stride, int page_size, void* k_pages,
+                                void* v_pages, int num_pages, int writes, cudaStream_t stream) {
+    const int N = (heads + 2 * kv_heads) * head_dim;
+    NIB_REQUIRE(heads > 0 && kv_heads > 0 && lda >= K && ldq >= N, "gemm (small M, q/k/v): bad sizes heads=%d/%d head_dim=%d", heads, kv_heads, head_dim);
+    NIB_REQUIRE(nib_gemm_smallm_qkv_supported(A, W, tokens, K, lda, gain ? 4 : 2, head_dim, rot),
+                "gemm (small M, q/k/v): needs 1..16 tokens, K %% 32 == 0, head_dim and the rotated width multiples of 16 (tokens=%d K=%d head_dim=%d rot=%d)",
+                tokens, K, head_dim, rot);
+    NIB_REQUIRE(rot == 0 || (cos_t && sin_t), "gemm (small M, q/k/v): rotation needs the tables");
+    NIB_REQUIRE(positions && req_index, "gemm (small M, q/k/v): positions and request rows are needed");
+    NIB_REQUIRE(!writes || (block_table && k_pages && v_pages && page_size > 0 && num_pages > 0), "gemm (small M, q/k/v): writing needs pages and a block table");
+    NIB_REQUIRE(gain == nullptr || (((uintptr_t)gain & 15) == 0), "gemm (small M, q/k/v): the gain must be 16-byte aligned");
+    Args a{A, W, bias, qkv, tokens, N, K, lda, ldq, gain, eps, nullptr, nullptr, 1,
+           QkvEpi{heads, kv_heads, head_dim, rot, positions, req_index, cos_t, sin_t, block_table, bt_stride, page_size,
+                  num_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, writes}};
+    if (gain) return launch_tokens<true>(WARPS, EPI_QKV, a, stream);
+    return launch_tokens<false>(WARPS, EPI_QKV, a, stream);
 }

@@ -174,7 +174,8 @@ template <int TOK, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo,
-               int splits, int kb_per_split, float* __restrict__ scratch, int* __restrict__ counters) {
+               int splits, int kb_per_split, float* __restrict__ scratch, int* __restrict__ counters,
+               unsigned long long* trace, int trace_cap) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     using C = Cfg<TOK, DUAL>;
     extern __shared__ unsigned char smem_raw[];
@@ -188,6 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_TC, EPI, 0);
     const int f_tiles = (n_out + BLOCK_F - 1) / BLOCK_F, t_tiles = (tokens + TOK - 1) / TOK;
     const int items = f_tiles * t_tiles * splits;       // work item = (output tile, split of K), splits fastest
     const int k_blocks = (k_dim + BLOCK_K - 1) / BLOCK_K;
@@ -210,6 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_wait();         // from here on the kernel reads what earlier kernels wrote (activations, the residual stream)
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_TC, EPI, 1);
 
     if (warp == 0 && lane == 0) {
         // ---------------- producer: TMA loads of W (and the up rows) and A tiles, stage after stage across tiles
@@ -381,6 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_TC, EPI, 2);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -763,7 +767,8 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, v
     }
     const int items = tiles * splits;
     NIB_CUDA(launch_pdl(gemm_tc_kernel<TOK, EPI>, dim3(items < sms ? items : sms), dim3(THREADS), (size_t)C::SMEM, stream,
-                        mw, ma, bias, out, tokens, n_out, k, ldo, splits, kb_per_split, sk.scratch, sk.counters));
+                        mw, ma, bias, out, tokens, n_out, k, ldo, splits, kb_per_split, sk.scratch, sk.counters,
+                        nib_trace_buffer(), nib_trace_capacity()));
     return 0;
 }
 

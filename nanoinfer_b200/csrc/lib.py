@@ -71,12 +71,10 @@ class Kernels:
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
         self._ws_attn_counters = None
-        self.fuse_decode = False               # rotation and cache write inside the decode attention kernel: one launch fewer per layer, but
-                                               # measured equal (0.5B, batch 8) or 3-7 % slower (batch 1 and 64, heads of 128) than the separate kernel
-        self.fuse_ffn = False                  # norm + gate/up + down of a decode step in one cooperative kernel: measured slower
-                                               # (18.6 us against 13.2 us for the three kernels chained by dependent launch), so off
         self.decode_tma = True                 # decode attention with TMA page loads where the shape allows (else mma.sync + cp.async)
         self.separate_combine = True           # merge the decode splits in a second kernel (measured faster than letting the last CTA do it)
+        self.fuse_norm_swiglu = False          # the norm inside the gate/up product as well (every CTA re-reads the activations)
+        self.fuse_qkv = True                   # up to 16 tokens: bias, rotation and the page write are the q/k/v product's epilogue
         try:
             self._lib = ctypes.CDLL(lib_path)
         except OSError as e:
@@ -86,10 +84,9 @@ class Kernels:
                      "nib_gemm_smallm", "nib_gemm_smallm_supported", "nib_gemm_tc", "nib_gemm_tc_splitk",
                      "nib_gemm_tc_pair", "nib_gemm_tc_supported", "nib_gemm_tc_error", "nib_attention_mma_supported",
                      "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma",
-                     "nib_attention_decode_tma_fused", "nib_attention_decode_tma_supported",
-                     "nib_attention_decode_tma_error", "nib_argmax", "nib_argmax_chunked", "nib_ffn_decode",
-                     "nib_ffn_decode_supported", "nib_sample", "nib_repetition_penalty", "nib_device_arch",
-                     "nib_sm_count"):
+                     "nib_attention_decode_tma_supported",
+                     "nib_attention_decode_tma_error", "nib_argmax", "nib_argmax_chunked", "nib_sample", "nib_repetition_penalty", "nib_device_arch",
+                     "nib_sm_count", "nib_gemm_smallm_qkv", "nib_gemm_smallm_qkv_supported"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -135,7 +132,6 @@ class Kernels:
             self._ws_scratch = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=device)
             self._ws_counters = torch.zeros(16 * 1024, dtype=torch.int32, device=device)
             self._ws_attn_counters = torch.zeros(64 * 1024, dtype=torch.int32, device=device)
-            self._ws_ffn = torch.zeros(4, dtype=torch.int32, device=device)      # two barrier counters, an error word
             self._ws_argmax = torch.zeros(4096 * 64, dtype=torch.int64, device=device)
             self._ws_argmax_counters = torch.zeros(4096, dtype=torch.int32, device=device)
 
@@ -179,7 +175,7 @@ class Kernels:
             small = (m <= 8 and weight_bytes <= 64e6) or (m <= 16 and weight_bytes <= 12e6)
         else:
             small = m <= 16 and weight_bytes <= 32e6
-        fuse = has_norm and small and epi != _EPI["swiglu"] and (m <= 8 or (m <= 16 and k <= 1024))
+        fuse = has_norm and small and (epi != _EPI["swiglu"] or self.fuse_norm_swiglu) and (m <= 8 or (m <= 16 and k <= 1024))
         return ("smallm" if small else "tc"), fuse
 
     def _use_pair(self, m: int, rows: int, k: int, epi: int) -> bool:
@@ -241,36 +237,6 @@ class Kernels:
                                             c_int(a.stride(0)), c_int(out.stride(0)), c_int(epi), c_int(_DT[a.dtype]),
                                             self._stream()), "linear")
 
-    def can_fuse_ffn(self, dtype, tokens: int, hidden: int, inter: int, ldx: int) -> bool:
-        """True if ``ffn_decode`` takes this shape (bfloat16, up to 8 tokens, at most 64 rows of either matrix
-        per SM)."""
-        return self.fuse_ffn and dtype == torch.bfloat16 and not self.force_simt_gemm and self.gemm_route is None and \
-            self._lib.nib_ffn_decode_supported(c_int(tokens), c_int(hidden), c_int(inter), c_int(ldx)) == 1
-
-    def ffn_decode(self, x32, gain32, eps, w_gate_up, w_down):
-        """x32 += down(silu(gate(n)) * up(n)) with n = rmsnorm(x32) * gain, in one kernel (a decode step)."""
-        _need(x32, torch.float32, "ffn x", contiguous=False); _need(gain32, torch.float32, "ffn gain")
-        _need(w_gate_up, torch.bfloat16, "ffn gate/up"); _need(w_down, torch.bfloat16, "ffn down")
-        m, hidden = x32.shape
-        inter = w_down.shape[1]
-        if tuple(w_gate_up.shape) != (2 * inter, hidden) or w_down.shape[0] != hidden or x32.stride(1) != 1:
-            raise KernelError("ffn_decode: shapes do not fit")
-        self.ensure_workspace(x32.device)
-        act = torch.empty(m * inter, dtype=torch.bfloat16, device=x32.device)
-        self._check(self._lib.nib_ffn_decode(_ptr(x32), c_int(x32.stride(0)), _ptr(gain32), c_float(eps), _ptr(w_gate_up),
-                                             _ptr(w_down), _ptr(act), c_int(m), c_int(hidden), c_int(inter),
-                                             c_void_p(self._ws_ffn.data_ptr()), c_void_p(self._ws_ffn.data_ptr() + 8),
-                                             self._stream()), "ffn (fused decode)")
-
-    def ffn_decode_error(self) -> int:
-        """1 if the fused feed-forward kernel's grid barrier ran out of its bounded wait; synchronises and clears."""
-        if self._ws_scratch is None:
-            return 0
-        v = int(self._ws_ffn[2].item())
-        if v:
-            self._ws_ffn[2] = 0
-        return v
-
     def gemm_tc_error(self) -> int:
         """The error word of the tensor-core GEMM's bounded waits (0 = none); synchronises and clears it."""
         return self._lib.nib_gemm_tc_error()
@@ -285,6 +251,60 @@ class Kernels:
         if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != k or tuple(out.shape) != (m, inter):
             raise KernelError("linear_swiglu: shapes do not fit")
         self._gemm(a, w_gate_up, None, out, m, inter, k, _EPI["swiglu"])
+
+    def qkv_project(self, a, w_qkv, bias32, qkv, heads, kv_heads, head_dim, positions, req_index, rotary,
+                    block_table, page_size, k_pages, v_pages, writes):
+        """qkv = a . w_qkv^T + bias with query and key heads rotated by their positions; with ``writes`` the
+        rotated keys and the values also go into the cache pages. ``a`` may be a DeferredNorm.
+
+        Up to 16 tokens of bfloat16 take one kernel for all of it (bias, rotation and the page write are the
+        small-M product's epilogue, the norm its prologue); everything else is the product followed by
+        ``rope_store``."""
+        deferred = a if hasattr(a, "materialize") else None
+        m, k = a.shape
+        n = w_qkv.shape[0]
+        rot = 0 if rotary is None else rotary[2]
+        fused = False
+        if a.dtype == torch.bfloat16 and self.fuse_qkv and not self.force_simt_gemm and self.tc_token_tile == 0 \
+                and self.gemm_route in (None, "smallm", "smallm_fused") and not self.smallm_ksplit and not self.smallm_cross:
+            kernel, with_norm = self._route(m, n, k, _EPI["store"], deferred is not None)
+            if deferred is not None and not with_norm:
+                a, deferred = deferred.materialize(), None
+            src = deferred.x32 if deferred is not None else a
+            fused = kernel == "smallm" and qkv.stride(0) % 2 == 0 and self._lib.nib_gemm_smallm_qkv_supported(
+                _ptr(src), _ptr(w_qkv), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if deferred is not None else 2),
+                c_int(head_dim), c_int(rot)) == 1
+        if not fused:
+            self.linear(a, w_qkv, bias32, qkv, "store")
+            self.rope_store(qkv, heads, kv_heads, head_dim, positions, req_index, rotary, block_table, page_size,
+                            k_pages, v_pages, writes)
+            return
+        _need(w_qkv, torch.bfloat16, "qkv w"); _need(qkv, torch.bfloat16, "qkv out")
+        _need(positions, torch.int32, "positions"); _need(req_index, torch.int32, "req_index")
+        if n != (heads + 2 * kv_heads) * head_dim or tuple(qkv.shape) != (m, n) or w_qkv.shape[1] != k:
+            raise KernelError("qkv_project: shapes do not fit the head counts")
+        if bias32 is not None:
+            _need(bias32, torch.float32, "qkv bias")
+        cos = sin = None
+        if rotary is not None:
+            cos, sin, _ = rotary
+            _need(cos, torch.float32, "cos"); _need(sin, torch.float32, "sin")
+            if cos.shape[1] != rot // 2:
+                raise KernelError("qkv_project: table width must be rot/2")
+        num_pages = bt_stride = 0
+        if writes:
+            _need(block_table, torch.int32, "block_table", contiguous=False)
+            _need(k_pages, torch.bfloat16, "k_pages"); _need(v_pages, torch.bfloat16, "v_pages")
+            if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim) or block_table.stride(1) != 1:
+                raise KernelError("qkv_project: pages or block table do not fit")
+            num_pages, bt_stride = k_pages.shape[0], block_table.stride(0)
+        gain = deferred.gain32 if deferred is not None else None
+        self._check(self._lib.nib_gemm_smallm_qkv(
+            _ptr(src), _ptr(w_qkv), _ptr(bias32), _ptr(qkv), c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim),
+            c_int(k), c_int(src.stride(0)), c_int(qkv.stride(0)), _ptr(gain), c_float(deferred.eps if deferred is not None else 0.0),
+            _ptr(positions), _ptr(req_index), _ptr(cos), _ptr(sin), c_int(rot), _ptr(block_table if writes else None),
+            c_int(bt_stride), c_int(page_size), _ptr(k_pages if writes else None), _ptr(v_pages if writes else None),
+            c_int(num_pages), c_int(1 if writes else 0), self._stream()), "q/k/v projection with rotation and page write")
 
     def rope_store(self, qkv, heads, kv_heads, head_dim, positions, req_index, rotary, block_table,
                    page_size, k_pages, v_pages, writes):
@@ -317,12 +337,14 @@ class Kernels:
             c_int(_DT[qkv.dtype]), self._stream()), "rope_store")
 
     def attention(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
-                  page_size, k_pages, v_pages):
+                  page_size, k_pages, v_pages, own_kv=False):
         """Attention of every token of the step over its request's cached keys (positions lo..own).
 
         bfloat16 with a supported head size runs on the tensor cores: the leading requests that bring one
         token each go to the decode kernel (keys split over CTAs), the others to the prefill kernel.
-        Everything else (32-bit, other head sizes) runs the general kernel."""
+        Everything else (32-bit, other head sizes) runs the general kernel. ``own_kv``: the rows of ``qkv`` also
+        hold each token's own rotated key and its value, the same that its page holds (a decode kernel may then
+        take them from the row instead of waiting for the page write)."""
         _need(qkv, None, "attention qkv"); _need(out, qkv.dtype, "attention out")
         _need(k_pages, qkv.dtype, "k_pages"); _need(v_pages, qkv.dtype, "v_pages")
         _need(block_table, torch.int32, "block_table", contiguous=False)
@@ -351,23 +373,24 @@ class Kernels:
             tma = self._decode_tma_ok(heads, kv_heads, head_dim, page_size)
             splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window, tma, head_dim)
             part_o = part_ml = counters = None
-            if splits > 1 and not self.separate_combine and n_dec * kv_heads <= 64 * 1024:
+            if splits > 1 and not tma and not self.separate_combine and n_dec * kv_heads <= 64 * 1024:
                 self.ensure_workspace(qkv.device)
                 counters = self._ws_attn_counters
-            if splits > 1:
-                part_o = torch.empty(n_dec * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
-                part_ml = torch.empty(n_dec * heads * splits * 2, dtype=torch.float32, device=qkv.device)
+            parts = splits // 8 if tma else splits      # the TMA kernel merges up to eight splits inside a cluster
+            if parts > 1:
+                part_o = torch.empty(n_dec * heads * parts * head_dim, dtype=torch.float32, device=qkv.device)
+                part_ml = torch.empty(n_dec * heads * parts * 2, dtype=torch.float32, device=qkv.device)
             common = (_ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(bt_stride),
                       c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(num_pages), c_int(n_dec), c_int(heads),
                       c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits))
             if tma:
-                self._check(self._lib.nib_attention_decode_tma(*common, _ptr(part_o), _ptr(part_ml), self._stream()),
+                self._check(self._lib.nib_attention_decode_tma(*common, c_int(1 if own_kv else 0), _ptr(part_o), _ptr(part_ml), self._stream()),
                             "attention decode (TMA)")
                 counters = None
             else:
                 self._check(self._lib.nib_attention_decode_mma(*common, _ptr(part_o), _ptr(part_ml), _ptr(counters),
                                                                self._stream()), "attention decode")
-            if splits > 1 and counters is None:
+            if parts > 1 and counters is None:
                 self.launches += 1
         if n_dec < n_req:
             q_start = c_void_p(ctx.q_start.data_ptr() + 4 * n_dec)
@@ -391,16 +414,6 @@ class Kernels:
         """The error word of the tcgen05 attention's bounded waits (0 = none); synchronises and clears it."""
         return self._lib.nib_attention_tc_error()
 
-    def can_fuse_decode(self, dtype, heads, kv_heads, head_dim, rotary, page_size=0) -> bool:
-        """True if ``attention_decode_fused`` takes this shape (bfloat16, a tensor-core head size, at most
-        16 query heads per kv head, a rotated width that is a multiple of 4)."""
-        if dtype != torch.bfloat16 or self.force_general_attention or not self.fuse_decode:
-            return False
-        if self._lib.nib_attention_mma_supported(c_int(heads), c_int(kv_heads), c_int(head_dim)) != 1:
-            return False
-        rot = 0 if rotary is None else rotary[2]
-        return heads // kv_heads <= 16 and rot % 4 == 0
-
     def _decode_tma_ok(self, heads, kv_heads, head_dim, page_size) -> bool:
         return self.decode_tma and page_size > 0 and self._lib.nib_attention_decode_tma_supported(
             c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(page_size)) == 1
@@ -421,40 +434,6 @@ class Kernels:
             ("TMA decode attention (attention_decode_tma.cu)", self.attention_decode_tma_error(), _DECODE_TMA_ROLES),
         ])
 
-    def attention_decode_fused(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
-                               page_size, k_pages, v_pages, rotary):
-        """A pure decode step's rotation, cache write and attention in one kernel: ``qkv`` is the raw
-        projection; every request brings exactly one token."""
-        _need(qkv, torch.bfloat16, "attention qkv"); _need(out, torch.bfloat16, "attention out")
-        _need(k_pages, torch.bfloat16, "k_pages"); _need(v_pages, torch.bfloat16, "v_pages")
-        _need(block_table, torch.int32, "block_table", contiguous=False)
-        if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim) or block_table.stride(1) != 1:
-            raise KernelError("attention_decode_fused: pages or block table do not fit")
-        n = qkv.shape[0]
-        if any(q != 1 for q in ctx.host.q_lens):
-            raise KernelError("attention_decode_fused: every request must bring exactly one token")
-        cos = sin = None
-        rot = 0
-        if rotary is not None:
-            cos, sin, rot = rotary
-        tma = self._decode_tma_ok(heads, kv_heads, head_dim, page_size)
-        splits = self.decode_splits(n, kv_heads, max(ctx.host.ctx_lens), window, tma, head_dim)
-        part_o = part_ml = None
-        if splits > 1:
-            part_o = torch.empty(n * heads * splits * head_dim, dtype=torch.float32, device=qkv.device)
-            part_ml = torch.empty(n * heads * splits * 2, dtype=torch.float32, device=qkv.device)
-        common = (_ptr(qkv), c_int(qkv.stride(0)), _ptr(out), _ptr(ctx.ctx_lens), _ptr(block_table), c_int(block_table.stride(0)),
-                  c_int(page_size), _ptr(k_pages), _ptr(v_pages), c_int(k_pages.shape[0]), c_int(n), c_int(heads),
-                  c_int(kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(splits), _ptr(part_o), _ptr(part_ml))
-        if tma:
-            self._check(self._lib.nib_attention_decode_tma_fused(*common, _ptr(cos), _ptr(sin), c_int(rot), self._stream()),
-                        "attention decode (TMA, fused)")
-        else:
-            self._check(self._lib.nib_attention_decode_fused_mma(*common, c_void_p(0), _ptr(cos), _ptr(sin), c_int(rot),
-                                                                 self._stream()), "attention decode (fused)")
-        if splits > 1:
-            self.launches += 1
-
     def decode_splits(self, n_tokens: int, kv_heads: int, max_ctx: int, window: int, tma: bool = False,
                       head_dim: int = 128) -> int:
         """Into how many CTAs the keys of a decoding token are split. The kernel with TMA page loads keeps
@@ -463,13 +442,14 @@ class Kernels:
         CTA waits for memory once), as long as that does not make more CTAs than fill the GPU about eight
         times."""
         if self.fixed_decode_splits:
-            return self.fixed_decode_splits
+            return _cluster_splits(self.fixed_decode_splits) if tma else self.fixed_decode_splits
         keys = min(max_ctx, window) if window > 0 else max_ctx
         tiles = -(-keys // 64) + 1
         if tma:
             want = max(1, round(256 / max(1, n_tokens * kv_heads)))
             tile_keys = 128 if head_dim == 64 else 64           # the kernel's tile
-            return max(1, min(want, -(-keys // tile_keys) // 4, 64))
+            n = max(1, min(want, -(-keys // tile_keys) // 4, 64))
+            return _cluster_splits(n)
         most = max(1, (8 * self.sm_count) // max(1, n_tokens * kv_heads))
         return max(1, min(-(-tiles // 2), most, 64))
 
@@ -500,6 +480,12 @@ class Kernels:
         rows, vocab = logits.shape
         self._check(self._lib.nib_sample(_ptr(logits), c_int(rows), c_int(vocab), _ptr(temperature), _ptr(top_k),
                                          _ptr(top_p), _ptr(uniform), _ptr(out), self._stream()), "sample")
+
+
+def _cluster_splits(n: int) -> int:
+    """The split count the TMA decode kernel takes, at most ``n``: one cluster of 1, 2, 4 or 8 CTAs merges its
+    splits in shared memory; beyond that whole clusters of 8, whose results a second kernel merges."""
+    return (n // 8) * 8 if n >= 8 else 1 << (max(1, n).bit_length() - 1)
 
 
 # what the code in the upper half of an error word says about the wait that ran out

@@ -35,3 +35,29 @@ NIB_API int nib_sm_count() {
 static int g_pdl = 1;
 bool nib_pdl_enabled() { return g_pdl != 0; }
 NIB_API void nib_set_pdl(int on) { g_pdl = on; }
+
+// cuTensorMapEncodeTiled, looked up once through the runtime; nullptr if this driver does not offer it.
+#include "pipeline.cuh"
+NibEncodeTiledFn nib_tensor_map_encoder() {
+    static NibEncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (NibEncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// The trace buffer of nib_trace_mark: device memory of 1 + 2 * capacity 64-bit words, zeroed by the caller.
+static unsigned long long* g_trace_buf = nullptr;
+static int g_trace_cap = 0;
+unsigned long long* nib_trace_buffer() { return g_trace_buf; }
+int nib_trace_capacity() { return g_trace_cap; }
+NIB_API void nib_trace_set(void* buf, int capacity) {
+    g_trace_buf = static_cast<unsigned long long*>(buf);
+    g_trace_cap = buf ? capacity : 0;
+}

@@ -78,21 +78,13 @@ class GroupedQueryAttention(Mixer):
     def forward(self, h: torch.Tensor, residual32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
         m = h.shape[0]
         qkv = torch.empty((m, self.qkv_width), dtype=self.rt.dtype, device=h.device)
-        self.ops.linear(h, self.w_qkv, self.b_qkv, qkv, "store")
+        # projection, rotation of q and k, keys (rotated) and values into the pages
+        self.ops.qkv_project(h, self.w_qkv, self.b_qkv, qkv, self.heads, self.kv_heads, self.head_dim, ctx.positions,
+                             ctx.req_index, self._rotary, cache.block_table, cache.page_size, cache.k_pages,
+                             cache.v_pages, cache.writes)
         attn = torch.empty((m, self.heads * self.head_dim), dtype=self.rt.dtype, device=h.device)
-        fused = getattr(self.ops, "can_fuse_decode", None)
-        if cache.writes and ctx.host.max_q_len == 1 and fused is not None and \
-                fused(self.rt.dtype, self.heads, self.kv_heads, self.head_dim, self._rotary, cache.page_size):
-            # a pure decode step: rotation, cache write and attention in one kernel
-            self.ops.attention_decode_fused(qkv, attn, self.heads, self.kv_heads, self.head_dim, self.scale,
-                                            self.window, ctx, cache.block_table, cache.page_size, cache.k_pages,
-                                            cache.v_pages, self._rotary)
-        else:
-            self.ops.rope_store(qkv, self.heads, self.kv_heads, self.head_dim, ctx.positions, ctx.req_index,
-                                self._rotary, cache.block_table, cache.page_size, cache.k_pages,
-                                cache.v_pages, cache.writes)
-            self.ops.attention(qkv, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window,
-                               ctx, cache.block_table, cache.page_size, cache.k_pages, cache.v_pages)
+        self.ops.attention(qkv, attn, self.heads, self.kv_heads, self.head_dim, self.scale, self.window,
+                           ctx, cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, own_kv=cache.writes)
         self.ops.linear(attn, self.w_o, None, residual32, "add")
 
 

@@ -38,12 +38,6 @@ class SwiGLU(FeedForward):
         self.w_down = rt.matrix(tensors["down_w"])
 
     def forward(self, h: torch.Tensor, residual32: torch.Tensor, ctx: StepContext) -> None:
-        fused = getattr(self.ops, "can_fuse_ffn", None)
-        if fused is not None and hasattr(h, "materialize") and h.x32.data_ptr() == residual32.data_ptr() and \
-                fused(self.rt.dtype, h.shape[0], self.hidden, self.intermediate, residual32.stride(0)):
-            # a decode step of a few tokens: norm, both projections and the residual sum in one kernel
-            self.ops.ffn_decode(residual32, h.gain32, h.eps, self.w_gate_up, self.w_down)
-            return
         act = torch.empty((h.shape[0], self.intermediate), dtype=self.rt.dtype, device=h.device)
         self.ops.linear_swiglu(h, self.w_gate_up, act)
         self.ops.linear(act, self.w_down, None, residual32, "add")

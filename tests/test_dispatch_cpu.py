@@ -21,6 +21,7 @@ def rules():
     k.smallm_ksplit = k.smallm_cross = 0
     k.tc_token_tile = k.tc_splits = 0
     k.fixed_decode_splits = 0
+    k.stream_gemm = False
     k.sm_count = 148
     return k
 
@@ -82,4 +83,7 @@ def test_decode_attention_splits(rules):
     assert rules.decode_splits(8, 2, 100, 0, True, 64) == 1              # a short context is not split
     assert rules.decode_splits(8, 2, 4096, 512, True, 64) == 1           # nor is a window of 512 keys
     rules.fixed_decode_splits = 5
-    assert rules.decode_splits(8, 2, 4096, 0, True, 64) == 5
+    assert rules.decode_splits(8, 2, 4096, 0, True, 64) == 4             # the TMA kernel's clusters: 1, 2, 4, 8, 16, 24, ...
+    assert rules.decode_splits(8, 2, 4096, 0, False, 64) == 5
+    rules.fixed_decode_splits = 21
+    assert rules.decode_splits(8, 2, 4096, 0, True, 64) == 16

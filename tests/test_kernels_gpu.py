@@ -247,6 +247,39 @@ def test_attention_decode_long_context_split_over_ctas(K, heads, kv_heads, hd, w
     assert_close(two, ref, dtype, "decode attention, merged by the last CTA")
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd,page", [(14, 2, 64, 16), (12, 2, 128, 16), (4, 4, 64, 8), (7, 1, 128, 64)])
+@pytest.mark.parametrize("splits", [0, 1, 4, 8])
+def test_attention_decode_takes_the_own_key_and_value_from_the_row(K, heads, kv_heads, hd, page, splits):
+    """With own_kv the TMA decode kernel reads every page before the step's earlier kernels have finished and takes
+    the token's own key and value from its row of the activation buffer: the page's slot for that position may
+    still hold anything (here: large finite junk). Positions at tile and page edges, first token of a request."""
+    dtype = torch.bfloat16
+    before = [0, 1, 15, 16, 127, 128, 129, 1000, 2047, 2048]
+    n = len(before)
+    ctx, bt = make_paged_batch([1] * n, before, page, sum(b // page + 2 for b in before), "cuda", seed=9)
+    pages = int(bt.max().item()) + 1
+    kp, vp = _fill_cache(ctx, bt, page, pages, kv_heads, hd, dtype, 60)
+    qkv = rnd((n, (heads + 2 * kv_heads) * hd), dtype, 62)
+    rows = qkv.view(n, heads + 2 * kv_heads, hd)
+    pos = ctx.positions.long()
+    phys = bt[torch.arange(n, device="cuda"), pos // page].long()
+    true_k, true_v = kp.clone(), vp.clone()
+    true_k[phys, :, pos % page, :] = rows[:, heads:heads + kv_heads]
+    true_v[phys, :, pos % page, :] = rows[:, heads + kv_heads:]
+    kp[phys, :, pos % page, :] = 77.0            # what a copy taken too early would see
+    vp[phys, :, pos % page, :] = -55.0
+    got, ref = (torch.empty(n, heads * hd, dtype=dtype, device="cuda") for _ in range(2))
+    scale = 1.0 / math.sqrt(hd)
+    K.fixed_decode_splits = splits
+    try:
+        K.attention(qkv, got, heads, kv_heads, hd, scale, 0, ctx, bt, page, kp, vp, own_kv=True)
+    finally:
+        K.fixed_decode_splits = 0
+    assert K.attention_decode_tma_error() == 0
+    REF.attention(qkv, ref, heads, kv_heads, hd, scale, 0, ctx, bt, page, true_k, true_v)
+    assert_close(got, ref, dtype, "decode attention, own key and value from the row")
+
+
 @pytest.mark.parametrize("heads,kv_heads,hd,page,window", [(14, 2, 64, 16, 0), (6, 1, 32, 8, 0), (3, 3, 48, 8, 24), (8, 2, 128, 16, 0)])
 def test_attention_tensor_core_kernels_agree_with_the_general_kernel(K, heads, kv_heads, hd, page, window):
     """bfloat16: the same batch through the tensor-core kernels and through the general kernel."""
@@ -420,44 +453,6 @@ def test_small_m_gemm(K, m, n, k, ksplit, cross):
         K.gemm_route = None
 
 
-@pytest.mark.parametrize("tokens", [1, 5, 8])
-@pytest.mark.parametrize("hidden,inter,eps", [(896, 4864, 1e-6), (192, 320, 1e-5), (1536, 8960, 1e-6), (64, 9472, 1e-3)])
-def test_fused_feed_forward_of_a_decode_step(K, tokens, hidden, inter, eps):
-    """RMSNorm + gate/up with SiLU*up + down + residual sum in one cooperative kernel (a barrier over the grid
-    between the two products), against the three separate kernels and against float64; twice in a row (the
-    barrier's counters are left ready); inside a row of a wider tensor."""
-    dtype = torch.bfloat16
-    x = rnd((tokens, hidden + 32), torch.float32, 300, scale=2.0)[:, :hidden]          # rows with a stride
-    gain = 1 + 0.1 * rnd((hidden,), torch.float32, 301)
-    w_gu = rnd((2 * inter, hidden), dtype, 302, scale=0.05)
-    w_d = rnd((hidden, inter), dtype, 303, scale=0.05)
-    K.fuse_ffn = True
-    try:
-        assert K.can_fuse_ffn(dtype, tokens, hidden, inter, x.stride(0))
-    finally:
-        K.fuse_ffn = False
-    xd = x.double()
-    n = (xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps) * gain.double()).to(dtype).double()
-    g, u = n @ w_gu[:inter].double().t(), n @ w_gu[inter:].double().t()
-    act = (g / (1 + torch.exp(-g)) * u).to(dtype).double()
-    want = xd + act @ w_d.double().t()
-    for _ in range(2):
-        got = x.clone()
-        got = torch.cat([got, torch.zeros(tokens, 32, device="cuda")], dim=1)[:, :hidden]
-        got.copy_(x)
-        K.ffn_decode(got, gain, eps, w_gu, w_d)
-        assert_close(got, want, torch.bfloat16, "fused feed-forward")
-    # the three kernels give the same within rounding
-    h = torch.empty(tokens, hidden, dtype=dtype, device="cuda")
-    K.rmsnorm(x.contiguous(), gain, eps, h)
-    a = torch.empty(tokens, inter, dtype=dtype, device="cuda")
-    K.linear_swiglu(h, w_gu, a)
-    sep = x.contiguous().clone()
-    K.linear(a, w_d, None, sep, "add")
-    assert_close(got, sep.double(), torch.bfloat16, "fused vs separate feed-forward")
-    assert K.ffn_decode_error() == 0
-
-
 @pytest.mark.parametrize("m,n,k,eps", [(1, 1152, 896, 1e-6), (8, 320, 192, 1e-5), (20, 200, 64, 1e-3), (64, 503, 320, 1e-6)])
 def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     """The decode GEMM that reads the 32-bit residual stream and applies RMSNorm on the fly, against the
@@ -591,44 +586,77 @@ def test_attention_decode_at_benchmark_lengths(K, heads, kv_heads, hd, page, n_r
     assert_close(got, ref, dtype, "decode attention at benchmark lengths")
 
 
-@pytest.mark.parametrize("tma", [True, False])
-@pytest.mark.parametrize("heads,kv_heads,hd,rot,page,window", [(14, 2, 64, 64, 16, 0), (6, 1, 32, 32, 8, 0), (3, 3, 48, 48, 8, 24),
-                                                               (16, 1, 128, 64, 16, 0), (4, 2, 16, 16, 16, 0), (8, 2, 128, 128, 32, 0),
-                                                               (14, 2, 64, 32, 8, 200)])
-def test_attention_decode_fused_with_rotation_and_cache_write(K, heads, kv_heads, hd, rot, page, window, tma):
-    """The fused decode kernels (rotate q and the new k, write k and v into the page, attend), with TMA page
-    loads and with cp.async, against the separate rotation kernel followed by the decode kernel: same
-    output, same pages."""
+@pytest.mark.parametrize("with_norm", [False, True])
+@pytest.mark.parametrize("heads,kv_heads,hd,rot,page,hidden", [(14, 2, 64, 64, 16, 896), (6, 1, 32, 32, 8, 192), (3, 3, 48, 48, 8, 160),
+                                                               (16, 1, 128, 64, 16, 1536), (4, 2, 16, 16, 16, 64), (28, 4, 128, 128, 32, 3584),
+                                                               (5, 5, 80, 0, 4, 96), (2, 1, 128, 32, 16, 256)])
+def test_qkv_projection_with_rotation_and_cache_write(K, heads, kv_heads, hd, rot, page, hidden, with_norm):
+    """The decode step's q/k/v product with the norm as its prologue and bias, rotation and the write of keys and
+    values into the pages as its epilogue, in one kernel: against float64 for the whole row, and the pages
+    against the separate rotation kernel's pages (which other tests hold against float64). Tokens of several
+    requests at different positions, one request with two tokens, pages in shuffled order."""
+    from nanoinfer_b200.parts.base import DeferredNorm
     from nanoinfer_b200.parts.position import rotary_tables
     dtype = torch.bfloat16
-    before = [0, 63, 64, 300, 1000, 17]
-    n = len(before)
-    ctx, bt = make_paged_batch([1] * n, before, page, 200 * (16 // min(page, 16)), "cuda", seed=8)
+    q_lens, before = [1, 1, 2, 1, 1], [0, 63, 64, 300, 17]
+    m = sum(q_lens)
+    ctx, bt = make_paged_batch(q_lens, before, page, 100 * (16 // min(page, 16)), "cuda", seed=8)
     pages = int(bt.max().item()) + 1
-    kp, vp = _fill_cache(ctx, bt, page, pages, kv_heads, hd, dtype, 120)
-    kp2, vp2 = kp.clone(), vp.clone()
-    cos, sin = rotary_tables(1100, rot, 10000.0)
-    rotary = (cos.cuda(), sin.cuda(), rot)
-    raw = rnd((n, (heads + 2 * kv_heads) * hd), dtype, 122)
-    scale = 1.0 / math.sqrt(hd)
-    K.fuse_decode = True
-    try:
-        assert K.can_fuse_decode(dtype, heads, kv_heads, hd, rotary)
-    finally:
-        K.fuse_decode = False
-    for splits in (0, 1, 5):
-        K.fixed_decode_splits, K.decode_tma = splits, tma
-        try:
-            fused = torch.empty(n, heads * hd, dtype=dtype, device="cuda")
-            a = kp.clone(), vp.clone()
-            K.attention_decode_fused(raw.clone(), fused, heads, kv_heads, hd, scale, window, ctx, bt, page, a[0], a[1], rotary)
-            two = torch.empty_like(fused)
-            b = kp2.clone(), vp2.clone()
-            q2 = raw.clone()
-            K.rope_store(q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, b[0], b[1], True)
-            K.attention(q2, two, heads, kv_heads, hd, scale, window, ctx, bt, page, b[0], b[1])
-        finally:
-            K.fixed_decode_splits, K.decode_tma = 0, True
-        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]), "pages differ"
-        assert torch.equal(fused, two), f"outputs differ with splits={splits}"
-    assert K.attention_decode_tma_error() == 0
+    shape = (pages, kv_heads, page, hd)
+    rotary = None
+    if rot:
+        cos, sin = rotary_tables(400, rot, 10000.0)
+        rotary = (cos.cuda(), sin.cuda(), rot)
+    n = (heads + 2 * kv_heads) * hd
+    w = rnd((n, hidden), dtype, 121, scale=0.05)
+    bias = rnd((n,), torch.float32, 122)
+    eps = 1e-6
+    gain = 1 + 0.1 * rnd((hidden,), torch.float32, 123)
+    x32 = rnd((m, hidden), torch.float32, 124, scale=2.0)
+
+    class _Norm:
+        def forward(self_, x, rows=None):
+            out = torch.empty(x.shape, dtype=dtype, device="cuda")
+            K.rmsnorm(x, gain, eps, out, rows)
+            return out
+
+    h = _Norm().forward(x32)
+    a = DeferredNorm(_Norm(), x32, gain, eps, dtype) if with_norm else h
+    kp, vp = torch.zeros(shape, dtype=dtype, device="cuda"), torch.zeros(shape, dtype=dtype, device="cuda")
+    qkv = torch.empty(m, n, dtype=dtype, device="cuda")
+    before_launches = K.launches
+    K.qkv_project(a, w, bias, qkv, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, kp, vp, True)
+    assert K.launches == before_launches + 1, "one kernel for the whole of it"
+    # float64: product (+ norm), bias, rotation
+    hh = (x32.double() * torch.rsqrt(x32.double().pow(2).mean(-1, keepdim=True) + eps) * gain.double()) if with_norm else h.double()
+    ref = (hh @ w.double().t() + bias.double()).view(m, heads + 2 * kv_heads, hd)
+    if rot:
+        half = rot // 2
+        c = rotary[0][ctx.positions.long()].double()[:, None, :]
+        sn = rotary[1][ctx.positions.long()].double()[:, None, :]
+        qk = ref[:, :heads + kv_heads]
+        x1, x2 = qk[..., :half].clone(), qk[..., half:rot].clone()
+        qk[..., :half] = x1 * c - x2 * sn
+        qk[..., half:rot] = x2 * c + x1 * sn
+    assert_close(qkv, ref.view(m, n), dtype, "q/k/v row")
+    # the pages hold exactly the row's keys and values, at the tokens' positions, and nothing else
+    kr, vr = torch.zeros_like(kp), torch.zeros_like(vp)
+    pos = ctx.positions.long()
+    page_of = bt[ctx.req_index.long(), pos // page].long()
+    got = qkv.view(m, heads + 2 * kv_heads, hd)
+    kr[page_of, :, pos % page, :] = got[:, heads:heads + kv_heads]
+    vr[page_of, :, pos % page, :] = got[:, heads + kv_heads:]
+    assert torch.equal(kp, kr) and torch.equal(vp, vr)
+    # without writing, pages stay as they are
+    kp2 = torch.zeros_like(kp)
+    q2 = torch.empty_like(qkv)
+    K.qkv_project(a, w, bias, q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, kp2, kp2, False)
+    assert torch.equal(q2, qkv) and not kp2.any()
+    # a row of a padded batch (no page: -1 in the table) writes nothing
+    bt_pad = bt.clone()
+    bt_pad[1] = -1
+    kp3, vp3 = torch.zeros_like(kp), torch.zeros_like(vp)
+    K.qkv_project(a, w, bias, q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt_pad, page, kp3, vp3, True)
+    keep = torch.ones(pages, dtype=torch.bool, device="cuda")
+    keep[page_of[1]] = False
+    assert torch.equal(kp3[keep], kr[keep]) and not kp3[page_of[1]].any()

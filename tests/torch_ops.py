@@ -39,6 +39,12 @@ class TorchOps:
         u = a.double() @ w_gate_up[inter:].double().t()
         out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
+    def qkv_project(self, a, w_qkv, bias32, qkv, heads, kv_heads, head_dim, positions, req_index, rotary,
+                    block_table, page_size, k_pages, v_pages, writes):
+        self.linear(a, w_qkv, bias32, qkv, "store")
+        self.rope_store(qkv, heads, kv_heads, head_dim, positions, req_index, rotary, block_table, page_size,
+                        k_pages, v_pages, writes)
+
     def rope_store(self, qkv, heads, kv_heads, head_dim, positions, req_index, rotary, block_table,
                    page_size, k_pages, v_pages, writes):
         m = qkv.shape[0]
@@ -65,7 +71,7 @@ class TorchOps:
         v_pages[page, :, off, :] = v
 
     def attention(self, qkv, out, heads, kv_heads, head_dim, scale, window, ctx, block_table,
-                  page_size, k_pages, v_pages):
+                  page_size, k_pages, v_pages, own_kv=False):
         m = qkv.shape[0]
         q = qkv.view(m, heads + 2 * kv_heads, head_dim)[:, :heads].double()
         n_rep = heads // kv_heads
