@@ -31,6 +31,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Transposes an 8 x 8 matrix of 16-bit elements that a warp holds in the fragment layout (thread (g, t): row g, columns
+// 2t and 2t+1): afterwards the thread holds row g, columns 2t and 2t+1 of the transposed matrix.
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
+    unsigned r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(r) : "r"(v));
+    return r;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);

@@ -7,12 +7,15 @@
 // outside the pool and arrives as zeros. Slots of a held page beyond the context hold finite values
 // (the pool starts zeroed and only finite values are written), and their scores are masked.
 //
-// grid (splits, tokens, kv heads), 160 threads. A CTA walks over its tiles of 64 or 128 keys (aligned to
-// absolute multiples of the tile) with STAGES tiles in flight: a producer warp issues the copies and runs
-// ahead, a full and an empty mbarrier per stage hand the tiles back and forth, and no barrier of the
-// whole CTA stands in the loop. Four consumer warps take 16 keys of every tile each, keep their own
-// running (max, sum, output) and merge at the end. The rows of the mma tile are the query heads of
-// the kv group (at most 16).
+// grid (splits, tokens, kv heads). A CTA walks over its tiles of 64 or 128 keys (aligned to absolute
+// multiples of the tile) with a few tiles in flight: a producer warp issues the copies and runs ahead, a
+// full and an empty mbarrier per stage hand the tiles back and forth, and no barrier of the whole CTA
+// stands in the loop. The consumer warps take 16 keys of every tile each, keep their own running
+// (max, sum, output) and merge at the end. The 16 keys are the ROWS of the tensor-core tile and the
+// query heads of the kv group (at most 16, usually fewer than 8) its columns: S^T = K Q^T, the
+// probabilities are transposed inside the warp (movmatrix) and O^T = V^T P^T. With the heads as the rows
+// a group of 7 heads would fill 7 of 16 rows and the instruction count, which bounds a decode step's
+// warps, would double.
 //
 // The CTAs that split one (token, kv head) form a thread-block cluster of up to eight. Each leaves its
 // partial (max, sum, output) in its own shared memory; after a cluster barrier every CTA of the cluster
@@ -37,20 +40,23 @@ extern "C" int nib_attention_combine(const float* part_o, const float* part_ml, 
 
 namespace {
 
-constexpr int GW = 4;             // consumer warps of a group: a quarter of a tile's keys each
-constexpr int GROUPS = 1;         // groups that would take alternate tiles need rings of their own (a warp must see every phase of a barrier it waits on)
-constexpr int WARPS = GW * GROUPS;
-constexpr int THREADS = (WARPS + 1) * 32;      // one more warp fetches
 // Keys per tile: 128 for heads of 64 (a tile of 64 keys is only 16 KB there, and the fixed work per tile,
 // barrier waits and the softmax's shuffles, bounded the kernel at large batches), 64 for heads of 128.
 template <int HD> constexpr int keys_of() { return HD == 64 ? 128 : 64; }
+// Consumer warps: 16 keys of every tile each, so eight for tiles of 128 keys and four for tiles of 64; one more
+// warp fetches. A warp's instructions depend on one another (tensor-core results, shuffles, exponentials), and a
+// warp alone on its scheduler waits out every one of those latencies: two warps per scheduler measured faster than
+// one with twice the keys.
+template <int HD> constexpr int warps_of() { return keys_of<HD>() / 16; }
 
 int g_dec_stages = 3;             // tiles in flight per CTA (2..4): 32 KB each
 __device__ int g_dec_error = 0;   // 0, or (code << 16 | blockIdx.x) of the first wait that ran out
 
 template <int HD> struct Cfg {
     static constexpr int KEYS = keys_of<HD>();
-    static constexpr int WKEYS = KEYS / GW;                   // keys of a tile per consumer warp: 32 or 16
+    static constexpr int WARPS = warps_of<HD>();
+    static constexpr int THREADS = (WARPS + 1) * 32;
+    static constexpr int WKEYS = 16;                          // keys of a tile per consumer warp
     static constexpr int SUB = HD / 64;                       // 64-element column blocks of a head
     static constexpr int SUBTILE = KEYS * 128;                // KEYS rows of 128 bytes (64 elements of a head), swizzled
     static constexpr int TILE = SUB * SUBTILE;                // K (or V) of one tile
@@ -61,8 +67,8 @@ template <int HD> struct Cfg {
     static constexpr int smem_bytes(int stages) { return data_bytes(stages) + 1024 /* alignment */ + 64 /* barriers */; }
 };
 
-template <int HD>
-__global__ void __launch_bounds__(THREADS)
+template <int HD, int NH>
+__global__ void __launch_bounds__(Cfg<HD>::THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ qkv, int q_stride, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
@@ -70,7 +76,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             int window, int splits, int csize, int stages, int data_bytes, int own_kv, float* __restrict__ part_o, float* __restrict__ part_ml,
                             unsigned long long* trace, int trace_cap) {
     using C = Cfg<HD>;
-    constexpr int KEYS = C::KEYS, SUBTILE = C::SUBTILE, WKEYS = C::WKEYS, NT = WKEYS / 8;
+    constexpr int KEYS = C::KEYS, SUBTILE = C::SUBTILE, WKEYS = C::WKEYS, MT = WKEYS / 16, WARPS = C::WARPS, THREADS = C::THREADS;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + data_bytes);
@@ -97,13 +103,17 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         s_failed = 0;
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
-        for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], GW); }
+        for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], WARPS); }
         mbar_fence_init();
     }
     __syncthreads();
 
-    float o[HD / 8][4];
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // O^T of this warp's keys: [16 dims of a head][8 query heads of the group] tiles; the running maximum of the
+    // thread's two heads of every tile (the same in the eight lanes that share them) and ITS OWN part of their sums
+    float o[HD / 16][NH][4];
+    float m_run[NH][2], l_part[NH][2];
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) { m_run[nh][0] = m_run[nh][1] = -INFINITY; l_part[nh][0] = l_part[nh][1] = 0.f; }
     if (warp == WARPS) {
         // ---------------- producer warp: lane i fetches page i of every tile (K and V), lane 0 arms the
         // stage's barrier. The block-table entry of the next tile is read while this one waits for its
@@ -150,28 +160,41 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             for (int j = max(0, issued - stages); j < issued; ++j) mbar_wait(&full[j % stages], (j / stages) & 1);
         }
     } else {
-        // ---------------- four consumer warps: a quarter of every tile's keys each
-        const int grp = warp / GW, wg = warp % GW;
+        // ---------------- the consumer warps: 16 keys of every tile each
+        const int wg = warp;
         pdl_wait();
         if (tid == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ATTN_DECODE, 0, 1);
-        int vis_lo[2] = {lo, lo}, vis_hi[2] = {g < n_rep ? p : -1, -1};      // rows g+8 exist only if n_rep > 8
-        const __nv_bfloat16* q_ptr[2] = {nullptr, nullptr};
-        if (g < n_rep) q_ptr[0] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g) * HD;
-        if (g + 8 < n_rep) { q_ptr[1] = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + g + 8) * HD; vis_hi[1] = p; }
-        unsigned q[HD / 16][4];
-        load_q<HD>(q, q_ptr, lane);
+        // The keys are the 16-row operand of the tensor-core instruction and the (at most 8) query heads of the group
+        // its 8 columns: S^T = K Q^T and O^T = V^T P^T. With the heads as the rows, 16 rows would hold 7 heads of a
+        // typical group and the instruction count would double; the warps of a decode step are bound by that count.
+        // Q^T as the column operand: thread (g, t) holds head g, dims 2t, 2t+1 and 2t+8, 2t+9 of every block of 16.
+        unsigned qb[HD / 16][NH][2];
 #pragma unroll
-        for (int d = 0; d < HD / 8; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+        for (int nh = 0; nh < NH; ++nh) {
+            const int head = nh * 8 + g;
+            const __nv_bfloat16* qp = qkv + (size_t)token * q_stride + (size_t)(kvh * n_rep + head) * HD;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                qb[kk][nh][0] = head < n_rep ? *reinterpret_cast<const unsigned*>(qp + kk * 16 + 2 * t) : 0u;
+                qb[kk][nh][1] = head < n_rep ? *reinterpret_cast<const unsigned*>(qp + kk * 16 + 8 + 2 * t) : 0u;
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < HD / 16; ++d)
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) o[d][nh][0] = o[d][nh][1] = o[d][nh][2] = o[d][nh][3] = 0.f;
         const float scale2 = scale * LOG2E;
 
-        // ldmatrix addresses inside a swizzled tile: row r (128 bytes), 16-byte chunk c at ((c ^ (r & 7)) << 4)
+        // ldmatrix addresses inside a swizzled tile: row r (128 bytes), 16-byte chunk c at ((c ^ (r & 7)) << 4).
+        // K as the row operand: matrices (keys 0-7, dims 0-7), (keys 8-15, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15,
+        // dims 8-15). V^T as the row operand, read transposed: (keys 0-7, dims 0-7), (keys 0-7, dims 8-15), (keys 8-15, ...).
         const int mat = lane >> 3, rr = lane & 7;
-        const unsigned k_row = (unsigned)(wg * WKEYS + (mat >> 1) * 8 + rr) * 128u;   // keys 0-7 / 8-15, dims 0-7 / 8-15
-        const unsigned k_half = mat & 1;
-        const unsigned v_row = (unsigned)(wg * WKEYS + (mat & 1) * 8 + rr) * 128u;    // transposed: keys 0-7 / 8-15 first
-        const unsigned v_half = mat >> 1;
+        const unsigned k_row = (unsigned)(wg * WKEYS + (mat & 1) * 8 + rr) * 128u;
+        const unsigned k_half = mat >> 1;
+        const unsigned v_row = (unsigned)(wg * WKEYS + (mat >> 1) * 8 + rr) * 128u;
+        const unsigned v_half = mat & 1;
 
-        for (int j = grp; j < n_mine; j += GROUPS) {
+        for (int j = 0; j < n_mine; ++j) {
             const int st = j % stages;
             bool ok = !s_failed && mbar_wait(&full[st], (j / stages) & 1);
             ok = __all_sync(0xffffffffu, ok);
@@ -196,31 +219,81 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 }
                 __syncwarp();
             }
-            float s[NT][4];
+            float s[MT][NH][4];
 #pragma unroll
-            for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk) {
-                const unsigned chunk = (unsigned)((kk & 3) * 2) + k_half;
+                for (int nh = 0; nh < NH; ++nh) s[mt][nh][0] = s[mt][nh][1] = s[mt][nh][2] = s[mt][nh][3] = 0.f;
 #pragma unroll
-                for (int np = 0; np < NT / 2; ++np) {                    // 16 keys per ldmatrix.x4
-                    unsigned b[4];
-                    ldmatrix_x4_addr(b, kt + (kk >> 2) * SUBTILE + k_row + np * 16 * 128 + ((chunk ^ (unsigned)rr) << 4));
-                    mma_bf16(s[2 * np], q[kk], b[0], b[1]);
-                    mma_bf16(s[2 * np + 1], q[kk], b[2], b[3]);
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    unsigned a[4];
+                    const unsigned chunk = (unsigned)((kk & 3) * 2) + k_half;
+                    ldmatrix_x4_addr(a, kt + (kk >> 2) * SUBTILE + k_row + mt * 16 * 128 + ((chunk ^ (unsigned)rr) << 4));
+#pragma unroll
+                    for (int nh = 0; nh < NH; ++nh) mma_bf16(s[mt][nh], a, qb[kk][nh][0], qb[kk][nh][1]);
                 }
             }
-            unsigned pfrag[NT / 2][4];
-            softmax_block<HD, NT>(s, pfrag, o, m_run, l_run, scale2, (t_begin + j) * KEYS + wg * WKEYS, vis_lo, vis_hi, lane);
+            // element e of a tile: key g + 8*(e/2) of the 16, head 2t + (e&1) of the 8. Scores in log2 units; a key outside
+            // lo..p counts as -inf. The maximum of a head goes over the thread's keys and then over the eight lanes that
+            // hold the head's other keys.
+            const int key0 = (t_begin + j) * KEYS + wg * WKEYS + g;
+            float corr[NH][2], m_use[NH][2];
 #pragma unroll
-            for (int kb = 0; kb < NT / 2; ++kb) {
+            for (int nh = 0; nh < NH; ++nh) {
+                float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int dp = 0; dp < HD / 16; ++dp) {
-                    unsigned b[4];
-                    const unsigned chunk = (unsigned)((dp & 3) * 2) + v_half;
-                    ldmatrix_x4_trans_addr(b, vt + (dp >> 2) * SUBTILE + v_row + kb * 16 * 128 + ((chunk ^ (unsigned)rr) << 4));
-                    mma_bf16(o[2 * dp], pfrag[kb], b[0], b[1]);
-                    mma_bf16(o[2 * dp + 1], pfrag[kb], b[2], b[3]);
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + mt * 16 + 8 * (e >> 1);
+                        const float v = (key >= lo && key <= p) ? s[mt][nh][e] * scale2 : -INFINITY;
+                        s[mt][nh][e] = v;
+                        mx[e & 1] = fmaxf(mx[e & 1], v);
+                    }
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 4));
+                    mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 8));
+                    mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 16));
+                    const float m_new = fmaxf(m_run[nh][q], mx[q]);
+                    m_use[nh][q] = (m_new == -INFINITY) ? 0.f : m_new;           // nothing visible yet: exp2(-inf - 0) = 0
+                    corr[nh][q] = (m_run[nh][q] == -INFINITY) ? 0.f : exp2f(m_run[nh][q] - m_use[nh][q]);
+                    m_run[nh][q] = m_new;
+                    l_part[nh][q] *= corr[nh][q];
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pv = exp2f(s[mt][nh][e] - m_use[nh][e & 1]);
+                        s[mt][nh][e] = pv;
+                        l_part[nh][e & 1] += pv;
+                    }
+#pragma unroll
+                for (int d = 0; d < HD / 16; ++d) {
+                    o[d][nh][0] *= corr[nh][0]; o[d][nh][1] *= corr[nh][1];
+                    o[d][nh][2] *= corr[nh][0]; o[d][nh][3] *= corr[nh][1];
+                }
+            }
+            // O^T += V^T P^T: P^T (keys x heads, what the first product left in the accumulators) becomes the column
+            // operand by transposing its two 8 x 8 blocks inside the warp
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                unsigned pb[NH][2];
+#pragma unroll
+                for (int nh = 0; nh < NH; ++nh) {
+                    pb[nh][0] = movmatrix_trans(pack_bf16(s[mt][nh][0], s[mt][nh][1]));
+                    pb[nh][1] = movmatrix_trans(pack_bf16(s[mt][nh][2], s[mt][nh][3]));
+                }
+#pragma unroll
+                for (int d = 0; d < HD / 16; ++d) {
+                    unsigned a[4];
+                    const unsigned chunk = (unsigned)((d & 3) * 2) + v_half;
+                    ldmatrix_x4_trans_addr(a, vt + (d >> 2) * SUBTILE + v_row + mt * 16 * 128 + ((chunk ^ (unsigned)rr) << 4));
+#pragma unroll
+                    for (int nh = 0; nh < NH; ++nh) mma_bf16(o[d][nh], a, pb[nh][0], pb[nh][1]);
                 }
             }
             __syncwarp();
@@ -234,45 +307,49 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     constexpr int MS = HD + 4;                                    // padded row: conflict-free float2 stores
     float* sm_o = reinterpret_cast<float*>(smem);                 // [WARPS][16][MS]
     float* sm_ml = sm_o + WARPS * 16 * MS;                        // [WARPS][16][2]
-    float* sm_f = sm_ml + WARPS * 16 * 2;                         // [WARPS][16] factors
-    float* cta_o = sm_f + WARPS * 16;                             // [16][HD]  this CTA's output, relative to its own maximum
+    float* cta_o = sm_ml + WARPS * 16 * 2;                            // [16][HD]  this CTA's output, relative to its own maximum
     float* cta_ml = cta_o + 16 * HD;                              // [16][2]   its (max, sum)
     const bool failed = s_failed != 0;
     if (warp < WARPS) {
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const int row = g + 8 * r;
+        for (int nh = 0; nh < NH; ++nh) {
 #pragma unroll
-            for (int d = 0; d < HD / 8; ++d)
-                *reinterpret_cast<float2*>(&sm_o[(warp * 16 + row) * MS + d * 8 + 2 * t]) = make_float2(o[d][2 * r], o[d][2 * r + 1]);
-            if (t == 0) {
-                sm_ml[(warp * 16 + row) * 2] = failed ? -INFINITY : m_run[r];
-                sm_ml[(warp * 16 + row) * 2 + 1] = failed ? 0.f : l_run[r];
+            for (int q = 0; q < 2; ++q) {
+                const int head = nh * 8 + 2 * t + q;
+                float l = l_part[nh][q];            // the sum over the keys of the lanes that share the head
+                l += __shfl_xor_sync(0xffffffffu, l, 4);
+                l += __shfl_xor_sync(0xffffffffu, l, 8);
+                l += __shfl_xor_sync(0xffffffffu, l, 16);
+#pragma unroll
+                for (int d = 0; d < HD / 16; ++d) {
+                    sm_o[(warp * 16 + head) * MS + d * 16 + g] = o[d][nh][q];
+                    sm_o[(warp * 16 + head) * MS + d * 16 + g + 8] = o[d][nh][2 + q];
+                }
+                if (g == 0) {
+                    sm_ml[(warp * 16 + head) * 2] = failed ? -INFINITY : m_run[nh][q];
+                    sm_ml[(warp * 16 + head) * 2 + 1] = failed ? 0.f : l;
+                }
             }
         }
     }
     __syncthreads();
-    if (tid < 16) {
-        float m_row = -INFINITY, l_row = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) m_row = fmaxf(m_row, sm_ml[(w * 16 + tid) * 2]);
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
-            const float mw = sm_ml[(w * 16 + tid) * 2];
-            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m_row);
-            l_row += sm_ml[(w * 16 + tid) * 2 + 1] * f;
-            sm_f[w * 16 + tid] = f;
-        }
-        cta_ml[tid * 2] = m_row;
-        cta_ml[tid * 2 + 1] = l_row;
-    }
-    __syncthreads();
     for (int i = tid; i < n_rep * HD; i += THREADS) {
         const int row = i / HD, d = i - row * HD;
-        float acc = 0.f;
+        float mw[WARPS], m_row = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) acc += sm_o[(w * 16 + row) * MS + d] * sm_f[w * 16 + row];
+        for (int w = 0; w < WARPS; ++w) { mw[w] = sm_ml[(w * 16 + row) * 2]; m_row = fmaxf(m_row, mw[w]); }
+        float acc = 0.f, l_row = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float f = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - m_row);
+            acc += sm_o[(w * 16 + row) * MS + d] * f;
+            l_row += sm_ml[(w * 16 + row) * 2 + 1] * f;
+        }
         cta_o[row * HD + d] = acc;
+        if (d == 0) {
+            cta_ml[row * 2] = m_row;
+            cta_ml[row * 2 + 1] = l_row;
+        }
     }
     if (csize > 1) cluster_sync(); else __syncthreads();
 
@@ -287,20 +364,24 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int row = i / HD, d = i - row * HD;
         float m_all = -INFINITY, l_all = 0.f, acc = 0.f;
         if (csize > 1) {
-            float mr[8];
+            // every peer's (max, sum, output) of this element is asked for before the first is used: one round trip
+            float mr[8], lr[8], orr[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
-                mr[r] = -INFINITY;
-                if (r < csize) mr[r] = ld_peer_f32(peer_smem(&cta_ml[row * 2], r));
-                m_all = fmaxf(m_all, mr[r]);
+                mr[r] = -INFINITY; lr[r] = 0.f; orr[r] = 0.f;
+                if (r < csize) {
+                    mr[r] = ld_peer_f32(peer_smem(&cta_ml[row * 2], r));
+                    lr[r] = ld_peer_f32(peer_smem(&cta_ml[row * 2 + 1], r));
+                    orr[r] = ld_peer_f32(peer_smem(&cta_o[row * HD + d], r));
+                }
             }
 #pragma unroll
+            for (int r = 0; r < 8; ++r) m_all = fmaxf(m_all, mr[r]);
+#pragma unroll
             for (int r = 0; r < 8; ++r) {
-                if (r < csize) {
-                    const float f = (mr[r] == -INFINITY) ? 0.f : exp2f(mr[r] - m_all);
-                    l_all += ld_peer_f32(peer_smem(&cta_ml[row * 2 + 1], r)) * f;
-                    acc += ld_peer_f32(peer_smem(&cta_o[row * HD + d], r)) * f;
-                }
+                const float f = (mr[r] == -INFINITY) ? 0.f : exp2f(mr[r] - m_all);
+                l_all += lr[r] * f;
+                acc += orr[r] * f;
             }
         } else {
             m_all = cta_ml[row * 2];
@@ -339,13 +420,13 @@ int make_pool_map(CUtensorMap* map, const void* ptr, int head_dim, int page_size
     return 0;
 }
 
-template <int HD>
+template <int HD, int NH>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const void* qkv, int q_stride, void* out, const int* ctx_lens,
            const int* block_table, int bt_stride, int page_size, int num_pages, int n_tokens, int heads, int kv_heads,
            float scale, int window, int splits, int csize, int own_kv, float* part_o, float* part_ml, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        NIB_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<HD, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Cfg<HD>::smem_bytes(Cfg<HD>::MAX_STAGES)));
         configured = true;
     }
@@ -353,7 +434,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const void* qkv, int q_
     while ((1 << shift) < page_size) ++shift;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits, n_tokens, kv_heads);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(Cfg<HD>::THREADS);
     const int stages = g_dec_stages;
     cfg.dynamicSmemBytes = (size_t)Cfg<HD>::smem_bytes(stages);
     cfg.stream = stream;
@@ -373,7 +454,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const void* qkv, int q_
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    NIB_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<HD>, mk, mv, (const __nv_bfloat16*)qkv, q_stride,
+    NIB_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<HD, NH>, mk, mv, (const __nv_bfloat16*)qkv, q_stride,
                                 (__nv_bfloat16*)out, ctx_lens, block_table, bt_stride, page_size, shift, num_pages, heads,
                                 kv_heads, heads / kv_heads, scale, window, splits, csize, stages, Cfg<HD>::data_bytes(stages), own_kv, part_o, part_ml,
                                 nib_trace_buffer(), nib_trace_capacity()));
@@ -431,8 +512,9 @@ NIB_API int nib_attention_decode_tma(const void* qkv, int q_stride, void* out, c
     const long long planes = (long long)num_pages * kv_heads;
     if (make_pool_map(&mk, k_pages, head_dim, page_size, planes)) return 1;
     if (make_pool_map(&mv, v_pages, head_dim, page_size, planes)) return 1;
-#define CALL(HD) launch<HD>(mk, mv, qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, num_pages, n_tokens, heads, \
-                            kv_heads, scale, window, splits, csize, own_kv, part_o, part_ml, stream)
-    return head_dim == 64 ? CALL(64) : CALL(128);
+#define CALL(HD, NH) launch<HD, NH>(mk, mv, qkv, q_stride, out, ctx_lens, block_table, bt_stride, page_size, num_pages, n_tokens, heads, \
+                                    kv_heads, scale, window, splits, csize, own_kv, part_o, part_ml, stream)
+    if (heads / kv_heads <= 8) return head_dim == 64 ? CALL(64, 1) : CALL(128, 1);
+    return head_dim == 64 ? CALL(64, 2) : CALL(128, 2);
 #undef CALL
 }

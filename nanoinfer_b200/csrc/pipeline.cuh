@@ -90,7 +90,7 @@ __device__ __forceinline__ unsigned peer_smem(const void* p, unsigned rank) {
 }
 __device__ __forceinline__ float ld_peer_f32(unsigned addr) {
     float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ float4 ld_peer_f32x4(unsigned addr) {
