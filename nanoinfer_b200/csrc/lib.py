@@ -73,7 +73,6 @@ class Kernels:
         self._ws_attn_counters = None
         self.decode_tma = True                 # decode attention with TMA page loads where the shape allows (else mma.sync + cp.async)
         self.separate_combine = True           # merge the decode splits in a second kernel (measured faster than letting the last CTA do it)
-        self.fuse_norm_swiglu = False          # the norm inside the gate/up product as well (every CTA re-reads the activations)
         self.fuse_qkv = True                   # up to 16 tokens: bias, rotation and the page write are the q/k/v product's epilogue
         try:
             self._lib = ctypes.CDLL(lib_path)
@@ -175,7 +174,9 @@ class Kernels:
             small = (m <= 8 and weight_bytes <= 64e6) or (m <= 16 and weight_bytes <= 12e6)
         else:
             small = m <= 16 and weight_bytes <= 32e6
-        fuse = has_norm and small and (epi != _EPI["swiglu"] or self.fuse_norm_swiglu) and (m <= 8 or (m <= 16 and k <= 1024))
+        # (inside the gate/up product the norm measured slower, +2 us a layer at the 0.5B widths: 300 CTAs re-read
+        # the 32-bit activations; the norm kernel before it costs less)
+        fuse = has_norm and small and epi != _EPI["swiglu"] and (m <= 8 or (m <= 16 and k <= 1024))
         return ("smallm" if small else "tc"), fuse
 
     def _use_pair(self, m: int, rows: int, k: int, epi: int) -> bool:

@@ -21,7 +21,6 @@ def rules():
     k.smallm_ksplit = k.smallm_cross = 0
     k.tc_token_tile = k.tc_splits = 0
     k.fixed_decode_splits = 0
-    k.stream_gemm = False
     k.sm_count = 148
     return k
 
