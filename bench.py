@@ -129,12 +129,135 @@ def model_numbers(layers: int) -> dict:
     nq, nkv, hd = m["num_attention_heads"], m["num_key_value_heads"], m["head_dim"]
     per_layer = (nq + 2 * nkv) * hd * h + h * nq * hd + 3 * h * inter
     return {
+        "kinds": {"qkv": (nq + 2 * nkv) * hd * h, "o_proj": h * nq * hd, "gate_up": 2 * h * inter, "down": h * inter,
+                  "lm_head": v * h},
+        "attention_flops": lambda t: 4.0 * nq * hd * t * (t + 1) / 2.0,           # one layer, a prompt of t tokens
+        "kv_bytes_per_token_layer": 2 * nkv * hd * 2,
         "per_layer_params": per_layer,
         "weight_bytes": 2 * (layers * per_layer + v * h),           # every matrix once, head included
         "kv_bytes_per_token": 2 * layers * nkv * hd * 2,
         "prefill_flops": lambda t: 2.0 * t * layers * per_layer + 2.0 * v * h
         + layers * 4.0 * nq * hd * t * (t + 1) / 2.0,
     }
+
+
+def _kind_of(kernel: str, what: str, state: dict) -> str:
+    """Which part of a layer a launch is, from its kernel and its place in the layer's order: norm, q/k/v,
+    (rotation), attention, output projection, norm, gate/up, down."""
+    w = what.lower()
+    if "attention" in kernel or "attention" in w:
+        state["after_attention"] = True
+        return "attention"
+    if "rmsnorm" in kernel or "rmsnorm" in w:
+        return "rmsnorm"
+    if "rope" in kernel or "rope" in w:
+        return "rope_store"
+    if "embed" in kernel or "embed" in w:
+        return "embed"
+    if "argmax" in kernel or "argmax" in w:
+        return "argmax"
+    if "gemm" in kernel or "linear" in w or "q/k/v" in w:
+        tag = state.get("tag")
+        if tag == "swiglu":
+            state["after_gate_up"] = True
+            return "gate_up"
+        if tag == "f32":
+            return "lm_head"
+        if tag in ("qkv", "store"):
+            return "qkv"
+        if state.pop("after_attention", False):
+            return "o_proj"
+        state.pop("after_gate_up", None)
+        return "down"
+    return kernel or what
+
+
+def decode_breakdown(engine, ops, reqs, rng, vocab, batch, mean_ctx, nums, pk) -> dict:
+    """Where the time of ONE decode step goes, from the kernels' own notes of the GPU timer (they keep the overlap
+    of dependent launches inside the captured graph): a kernel's share is the time from the moment its wait for the
+    earlier kernels ended to the moment the next kernel's did. Bytes: the weights of its product once, or the
+    cached keys and values of the live requests; the fraction is of the measured copy bandwidth."""
+    import torch
+    from nanoinfer_b200.engine import StepEntry
+    base = [rc.length for rc in reqs]
+    ops.timeline_start()
+    engine.reset_graphs()
+
+    def one():
+        engine.step([StepEntry(rc, [int(rng.integers(0, vocab))], [0]) for rc in reqs], borrow_logits=True)
+    for _ in range(4):
+        one()
+    ops.timeline_clear()
+    one()
+    notes = ops.timeline()
+    ops.timeline_stop()
+    engine.reset_graphs()
+    for rc, n in zip(reqs, base):
+        engine.truncate(rc, n)
+    epi = {0: "store", 1: "add", 2: "f32", 3: "swiglu", 4: "qkv"}
+    starts = [(t, k, tag) for t, k, tag, phase in notes if phase == 1]
+    ends = [t for t, _, _, phase in notes if phase == 2]
+    if len(starts) < 2 or not ends:
+        return {}
+    state, rows = {}, {}
+    for i, (t, kernel, tag) in enumerate(starts):
+        state["tag"] = epi.get(tag) if kernel.startswith("gemm") else None
+        kind = _kind_of(kernel, "", state)
+        t_next = starts[i + 1][0] if i + 1 < len(starts) else max(ends)
+        rows.setdefault(kind, []).append((t_next - t) / 1e3)
+    step_us = (max(ends) - starts[0][0]) / 1e3
+    bytes_of = {k: 2.0 * v for k, v in nums["kinds"].items()}
+    bytes_of["attention"] = batch * mean_ctx * nums["kv_bytes_per_token_layer"]
+    out = {"step_us": round(step_us, 1)}
+    for kind, us in rows.items():
+        mean = sum(us) / len(us)
+        row = {"n": len(us), "us": round(mean, 2), "share": round(sum(us) / step_us, 3)}
+        if kind in bytes_of:
+            gbs = bytes_of[kind] / (mean * 1e-6) / 1e9
+            row.update({"mb": round(bytes_of[kind] / 1e6, 2), "gbs": round(gbs, 0), "frac": round(gbs / pk["hbm_gbs"], 3)})
+        out[kind] = row
+    return out
+
+
+def prefill_breakdown(engine, ops, rng, vocab, t_pre, nums, pk) -> dict:
+    """Where the time of one prompt portion goes: an event behind every launch (the kernels of a portion run for
+    tens of microseconds, so ending their overlap changes little). FLOPs of a product: 2 x tokens x weights; of
+    the attention: 4 x heads x head size x t(t+1)/2; the fraction is of the measured cuBLAS burst throughput."""
+    import torch
+    from nanoinfer_b200.engine import StepEntry
+    rc = engine.open("breakdown")
+    ids = rng.integers(0, vocab, t_pre).tolist()
+    engine.step([StepEntry(rc, ids, [t_pre - 1])])
+    engine.truncate(rc, 0)
+    ops.time_ops(True)
+    engine.step([StepEntry(rc, ids, [t_pre - 1])])
+    times = ops.op_times()
+    ops.time_ops(False)
+    engine.close(rc)
+    state, rows = {}, {}
+    for what, us in times:
+        w = what.lower()
+        state["tag"] = None
+        if "linear" in w or "q/k/v" in w:
+            # the order of a layer's products: q/k/v, output, gate/up, down; the head comes after the last layer
+            n = state.get("linears", 0)
+            state["linears"] = n + 1
+            state["tag"] = ("qkv", "add", "swiglu", "add")[n % 4] if n < 4 * engine.config.num_hidden_layers else "f32"
+        kind = _kind_of("", what, state)
+        rows.setdefault(kind, []).append(us)
+    total = sum(us for _, us in times)
+    flops_of = {k: 2.0 * t_pre * v for k, v in nums["kinds"].items()}
+    flops_of["lm_head"] = 2.0 * nums["kinds"]["lm_head"]          # one wanted row
+    flops_of["attention"] = nums["attention_flops"](t_pre)
+    out = {"step_us": round(total, 1)}
+    for kind, us in rows.items():
+        mean = sum(us) / len(us)
+        row = {"n": len(us), "us": round(mean, 2), "share": round(sum(us) / total, 3)}
+        if kind in flops_of and kind != "lm_head":
+            tf = flops_of[kind] / (mean * 1e-6) / 1e12
+            row.update({"gflop": round(flops_of[kind] / 1e9, 2), "tflops": round(tf, 0), "frac": round(tf / pk["bf16_tflops"], 3)})
+        out[kind] = row
+    return out
 
 
 def run_ours(args) -> dict:
@@ -180,8 +303,11 @@ def run_ours(args) -> dict:
                 done += n
         return reqs
 
-    def decode_timed(reqs, n_warm: int, n_steps: int, sample_clocks: bool = False):
-        """Device time of n_steps decode steps (one token for every request, greedy pick on the device)."""
+    def decode_timed(reqs, n_warm: int, n_steps: int, min_seconds: float = 0.5, max_repeats: int = 40):
+        """Device time of n_steps decode steps (one token for every request, greedy pick on the device), measured
+        again and again FROM THE SAME CONTEXT (the requests forget the n_steps positions in between) until
+        min_seconds have been timed. Returns (median ms per step, launches of one region, ms per step of every
+        repeat)."""
         out = torch.empty(len(reqs), dtype=torch.int32, device=engine.device)
         toks = [rng.integers(0, vocab, len(reqs)).tolist() for _ in range(n_warm + n_steps)]
 
@@ -191,20 +317,23 @@ def run_ours(args) -> dict:
         for i in range(n_warm):
             one(i)
         torch.cuda.synchronize()
-        l0 = ops.launches + engine.graph_launches
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sampler = ClockSampler()
-        if sample_clocks:
-            sampler.__enter__()
-        start.record()
-        for i in range(n_warm, n_warm + n_steps):
-            one(i)
-        end.record()
-        torch.cuda.synchronize()
-        if sample_clocks:
-            sampler.__exit__()
-        ms = start.elapsed_time(end)
-        return ms / n_steps, ops.launches + engine.graph_launches - l0, (sampler.summary() if sample_clocks else None)
+        base = [rc.length for rc in reqs]
+        per_step, launches, total = [], 0, 0.0
+        while total < min_seconds * 1e3 and len(per_step) < max_repeats:
+            l0 = ops.launches + engine.graph_launches
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(n_warm, n_warm + n_steps):
+                one(i)
+            end.record()
+            torch.cuda.synchronize()
+            ms = start.elapsed_time(end)
+            launches = ops.launches + engine.graph_launches - l0
+            per_step.append(ms / n_steps)
+            total += ms
+            for rc, n in zip(reqs, base):
+                engine.truncate(rc, n)
+        return statistics.median(per_step), launches, per_step
 
     def close_all(reqs):
         for rc in reqs:
@@ -229,30 +358,54 @@ def run_ours(args) -> dict:
     if pre_ms:
         pre = statistics.median(pre_ms)
         prefill = {"value": round(t_pre / (pre / 1e3), 1), "tokens": t_pre, "ms": round(pre, 3),
-                   "frac": round(nums["prefill_flops"](t_pre) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+                   "frac": round(nums["prefill_flops"](t_pre) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "peak": f"{pk['bf16_tflops']:.0f} TFLOP/s, cuBLAS bf16 burst, {pk['source']}"}
+    prefill_kernels = None
+    if pre_ms and args.breakdown:
+        prefill_kernels = prefill_breakdown(engine, ops, rng, vocab, t_pre, nums, pk)
 
     if args.only == "prefill":
-        return {"impl": "ours", "only": "prefill", "prefill": prefill, "config": {"layers": layers}}
+        out = {"impl": "ours", "only": "prefill", "prefill": prefill,
+               "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers}}
+        if prefill_kernels:
+            out["kernels"] = {"prefill": prefill_kernels}
+        return out
 
+    # The clocks are sampled from before the warm-up to the end of the timed regions.
+    sampler = ClockSampler()
+    sampler.__enter__()
     # ---- decode points at batch 1 and 64 --------------------------------------------------
     points = {}
     for b in ((1, 64) if args.only == "all" else ()):
         n_w, n_s = 4, min(steps, 32)
         reqs = fill(b, ctx - n_w - n_s - 1)
-        ms, _, _ = decode_timed(reqs, n_w, n_s)
+        ms, _, _ = decode_timed(reqs, n_w, n_s, min_seconds=0.15)
         points[f"decode_b{b}"] = round(b / (ms / 1e3), 1)
         close_all(reqs)
 
     # ---- the headline: batch 8 (default), device-timed -------------------------------------
     reqs = fill(batch, ctx - warmup - steps - 1)
-    ms_step, launches, clocks = decode_timed(reqs, warmup, steps, sample_clocks=True)
+    ms_step, launches, repeats = decode_timed(reqs, warmup, steps)
+    sampler.__exit__()
+    clocks = sampler.summary()
     mean_ctx = ctx - steps / 2.0
     step_bytes = nums["weight_bytes"] + batch * mean_ctx * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms_step / 1e3) / 1e9
+    kernels = None
+    if args.breakdown:
+        kernels = {"decode": decode_breakdown(engine, ops, reqs, rng, vocab, batch, mean_ctx, nums, pk)}
+        if prefill_kernels is not None:
+            kernels["prefill"] = prefill_kernels
     close_all(reqs)
     if args.only == "decode":
-        return {"impl": "ours", "only": "decode", "value": round(batch / (ms_step / 1e3), 1), "ms_per_step": round(ms_step, 4),
-                "gpu_launches": launches, "config": {"layers": layers, "global_batch": batch, "seq_len": ctx}}
+        out = {"impl": "ours", "only": "decode", "value": round(batch / (ms_step / 1e3), 1), "ms_per_step": round(ms_step, 4),
+               "gpu_launches": launches, "repeats": len(repeats), "clocks": clocks,
+               "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                            "frac": round(achieved / pk["hbm_gbs"], 4)},
+               "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers, "global_batch": batch, "seq_len": ctx}}
+        if kernels:
+            out["kernels"] = kernels
+        return out
 
     # ---- end to end through the Python entry point (scheduler) -----------------------------
     sched = Scheduler(model, max_batch=batch, max_tokens_per_step=4096, lookahead=True)
@@ -280,7 +433,9 @@ def run_ours(args) -> dict:
            "d2h_bytes_per_step": 4 * batch, "ms_per_step": round(dt / steps * 1e3, 4)}
 
     value = batch / (ms_step / 1e3)
+    extra = {"kernels": kernels} if kernels else {}
     return {
+        **extra,
         "metric": f"decode tok/s at batch {batch} (Qwen2.5-{args.shape.upper()} shape, context {ctx})", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -291,7 +446,7 @@ def run_ours(args) -> dict:
                    "intermediate": MODEL["intermediate_size"], "vocab": MODEL["vocab_size"], "tied_head": MODEL["tie_word_embeddings"],
                    "global_batch": batch, "seq_len": ctx, "page_size": page, "prefill_tokens": t_pre,
                    "parallelism": "single-gpu", "l2": f"inputs larger than L2 (weights {nums['weight_bytes'] / 1e9:.1f} GB per step)",
-                   "peaks": pk["source"]},
+                   "peaks": pk["source"], "timed_regions": len(repeats)},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -403,8 +558,12 @@ def run_reference(args) -> dict:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights and random token ids", "impl": "reference",
         "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": layers, "layers_full": m["num_hidden_layers"],
-                   "global_batch": batch, "seq_len": ctx, "parallelism": "single-gpu",
-                   "engine": "reference Python model (torch, CUDA)"},
+                   "hidden": m["hidden_size"], "heads": m["num_attention_heads"], "kv_heads": m["num_key_value_heads"],
+                   "head_dim": m["head_dim"], "intermediate": m["intermediate_size"], "vocab": m["vocab_size"],
+                   "tied_head": m["tie_word_embeddings"], "global_batch": batch, "seq_len": ctx, "page_size": 16,
+                   "prefill_tokens": args.prefill_tokens, "parallelism": "single-gpu",
+                   "l2": "inputs larger than L2 (weights 1.0 GB per step)", "peaks": peaks()["source"], "timed_regions": 1},
+        "engine": "reference Python model (torch, CUDA)",
         "clocks": cs.summary(),
         "e2e": {"value": round(batch * steps / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": 8 * batch,
                 "d2h_bytes_per_step": 8 * batch},
@@ -426,6 +585,9 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "serve"],
                     help="measure one part only (for profiling small cases); the JSON line then lacks the rest. "
                          "'serve' runs the continuous-batching workload (64 requests through the scheduler) instead")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="add a 'kernels' block: where the time of a decode step and of a prompt portion goes, kernel kind by "
+                         "kind, with bytes or FLOPs and the fraction of the measured peak")
     ap.add_argument("--shape", default="0.5b", choices=sorted(SHAPES), help="layer sizes: the family's 0.5B (default), 1.5B or 7B")
     args = ap.parse_args()
     MODEL.update(SHAPES[args.shape])

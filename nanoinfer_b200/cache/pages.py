@@ -259,6 +259,23 @@ class CacheManager:
                     rc.version += 1
             rc.first_live[g] = max(rc.first_live[g], min(first, len(table)))
 
+    def truncate(self, rc: RequestCache, new_length: int) -> None:
+        """Forget the positions from ``new_length`` on: what is fed next overwrites their keys and values. Pages
+        that hold no position any more are returned. A group with a window cannot go back to a position whose
+        window reaches into pages that it has already given back."""
+        if rc.closed or not (0 <= new_length <= rc.length):
+            raise ValueError(f"request {rc.request_id!r}: cannot truncate {rc.length} positions to {new_length}")
+        for g in self._window_groups:
+            if self._first_needed_page(g, new_length) < rc.first_live[g]:
+                raise ValueError(f"request {rc.request_id!r}: the window's pages for position {new_length} were returned")
+        keep = -(-new_length // self.page_size)
+        for g, table in enumerate(rc.tables):
+            if len(table) > keep:
+                self.pools[g].free_many(table[keep:])
+                del table[keep:]
+                rc.version += 1
+        rc.length = new_length
+
     # ---- views ----------------------------------------------------------------------------
     def capacity_tokens(self) -> int:
         """Positions that one request alone could hold (limited by the groups that keep every key)."""

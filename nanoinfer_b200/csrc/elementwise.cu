@@ -11,8 +11,9 @@
 // ---------------------------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, unsigned long long* trace, int trace_cap) {
     const int m = blockIdx.x;
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_EMBED, 0, 1);
     const int id = ids[m];
     float* o = out + (size_t)m * hidden;
     if (id < 0 || id >= vocab) {  // the engine checks ids on the host; never read outside the table
@@ -21,6 +22,7 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     }
     const T* src = table + (size_t)id * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = Elem<T>::load(src + c);
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_EMBED, 0, 2);
 }
 
 NIB_API int nib_embed(const int* ids, const void* table, float* out, int m, int hidden, int vocab,
@@ -29,9 +31,9 @@ NIB_API int nib_embed(const int* ids, const void* table, float* out, int m, int 
     if (m == 0) return 0;
     const int threads = hidden >= 256 ? 256 : 64;
     if (dtype == NIB_F32)
-        embed_kernel<float><<<m, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+        embed_kernel<float><<<m, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, nib_trace_buffer(), nib_trace_capacity());
     else if (dtype == NIB_BF16)
-        embed_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+        embed_kernel<__nv_bfloat16><<<m, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, nib_trace_buffer(), nib_trace_capacity());
     else
         NIB_REQUIRE(false, "embed: unknown dtype %d", dtype);
     NIB_LAUNCH_CHECK();
@@ -244,8 +246,9 @@ rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ p
                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
                       const int* __restrict__ block_table, int bt_stride, int page_size, __nv_bfloat16* __restrict__ k_pages,
                       __nv_bfloat16* __restrict__ v_pages, int m_tokens, int heads, int kv_heads, int head_dim, int num_pages,
-                      int write_kv) {
+                      int write_kv, unsigned long long* trace, int trace_cap) {
     pdl_launch_dependents();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ROPE, 0, 1);
     const int half = rot >> 1;
     const int rot_items = (heads + kv_heads) * (half >> 3);
     const int tail_items = write_kv ? kv_heads * ((head_dim - rot) >> 3) : 0;
@@ -325,7 +328,8 @@ NIB_API int nib_rope_store(void* qkv, const int* positions, const int* req_index
         NIB_REQUIRE(total < (1LL << 31) * 256, "rope_store: too many elements for one launch");
         NIB_CUDA(launch_pdl(rope_store_vec_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), (size_t)0, stream,
                             (__nv_bfloat16*)qkv, positions, req_index, cos_t, sin_t, rot, block_table, bt_stride, page_size,
-                            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, m, heads, kv_heads, head_dim, num_pages, write_kv));
+                            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, m, heads, kv_heads, head_dim, num_pages, write_kv,
+                            nib_trace_buffer(), nib_trace_capacity()));
         NIB_LAUNCH_CHECK();
         return 0;
     }

@@ -57,6 +57,8 @@ class Kernels:
         self.lib_path = lib_path
         self.launches = 0           # kernel launches issued through this object (graph replays add theirs)
         self._bound_stream = None   # the stream of the enclosing stream_scope(), if any
+        self._op_events = None      # time_ops(): (what, event) behind every launch
+        self._timeline = None       # timeline_start(): the device buffer the kernels note their times in
         self.force_general_attention = False   # tests: run the general attention kernel for bfloat16 too
         self.fixed_decode_splits = 0           # tests: a fixed split count for the decode kernel
         self.force_mma_prefill = False         # tests: prompt portions on the mma.sync kernel instead of tcgen05
@@ -93,6 +95,62 @@ class Kernels:
         self.launches += 1
         if rc != 0:
             raise KernelError(f"{what}: {self._lib.nib_last_error().decode()}")
+        if self._op_events is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream())
+            self._op_events.append((what, ev))
+
+    # ---- where the time goes ----------------------------------------------------------------
+    def time_ops(self, on: bool = True):
+        """Eager launches only. While on, an event is recorded behind every launch; ``op_times()`` then gives
+        (what, microseconds) per launch, the time from the launch before it to its own end. Events between
+        kernels end the overlap of programmatic dependent launch, so this suits steps whose kernels run for
+        tens of microseconds (prompt portions); a decode step is read with ``timeline_start`` instead."""
+        if on:
+            start = torch.cuda.Event(enable_timing=True)
+            start.record(torch.cuda.current_stream())
+            self._op_events = [("start", start)]
+        else:
+            self._op_events = None
+
+    def op_times(self):
+        torch.cuda.synchronize()
+        ev = self._op_events or []
+        out = [(what, 1000.0 * ev[i - 1][1].elapsed_time(e)) for i, (what, e) in enumerate(ev) if i > 0]
+        self._op_events = ev[-1:] if ev else None
+        return out
+
+    def timeline_start(self, capacity: int = 8192) -> None:
+        """From now on the kernels launched (and the graphs captured) note the GPU's nanosecond timer at their
+        entry, after their wait for the earlier kernels and at their end (first CTA, first thread):
+        ``timeline()`` returns the notes. Works inside captured graphs and leaves the overlap of dependent
+        launches as it is; the notes cost a few hundred nanoseconds each."""
+        self._timeline = torch.zeros(1 + 2 * capacity, dtype=torch.int64, device="cuda")
+        self._lib.nib_trace_set(c_void_p(self._timeline.data_ptr()), c_int(capacity))
+
+    def timeline_clear(self) -> None:
+        if self._timeline is not None:
+            torch.cuda.synchronize()
+            self._timeline.zero_()
+            torch.cuda.synchronize()
+
+    def timeline(self):
+        """[(t_ns, kernel, tag, phase)] in time order; phase 0 entry, 1 after the wait, 2 done."""
+        if self._timeline is None:
+            return []
+        torch.cuda.synchronize()
+        h = self._timeline.cpu().tolist()
+        n = min(int(h[0]), (len(h) - 1) // 2)
+        notes = []
+        for i in range(n):
+            code, t = h[1 + 2 * i], h[2 + 2 * i]
+            notes.append((t, TIMELINE_KERNELS.get(code >> 16, str(code >> 16)), (code >> 8) & 0xff, code & 0xff))
+        return sorted(notes)
+
+    def timeline_stop(self) -> None:
+        """Kernels launched from now on note nothing. Graphs captured while the timeline was on still write into its
+        buffer, which therefore stays allocated."""
+        self._lib.nib_trace_set(c_void_p(0), c_int(0))
 
     def _stream(self) -> c_void_p:
         if self._bound_stream is not None:
@@ -481,6 +539,11 @@ class Kernels:
         rows, vocab = logits.shape
         self._check(self._lib.nib_sample(_ptr(logits), c_int(rows), c_int(vocab), _ptr(temperature), _ptr(top_k),
                                          _ptr(top_p), _ptr(uniform), _ptr(out), self._stream()), "sample")
+
+
+# kernel ids of the timeline (common.cuh: NibTraceKernel)
+TIMELINE_KERNELS = {1: "embed", 2: "rmsnorm", 3: "rope_store", 4: "gemm_smallm", 5: "gemm_stream", 6: "gemm_tc",
+                    7: "attention_decode", 8: "attention_combine", 9: "argmax", 10: "attention_decode_mma"}
 
 
 def _cluster_splits(n: int) -> int:

@@ -93,9 +93,10 @@ __device__ __forceinline__ unsigned long long argmax_pack(float x, int i) {
 
 __global__ void __launch_bounds__(256)
 argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunk, int chunks, unsigned long long* __restrict__ part,
-                    int* __restrict__ counters, int* __restrict__ out) {
+                    int* __restrict__ counters, int* __restrict__ out, unsigned long long* trace, int trace_cap) {
     __shared__ unsigned long long s_best[8];
     __shared__ int s_last;
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ARGMAX, 0, 1);
     const int row = blockIdx.y, cid = blockIdx.x;
     const float* l = logits + (size_t)row * vocab;
     const int begin = cid * chunk, end = min(vocab, begin + chunk);
@@ -136,7 +137,7 @@ NIB_API int nib_argmax_chunked(const float* logits, int rows, int vocab, int* ou
     NIB_REQUIRE(scratch != nullptr && counters != nullptr, "argmax (chunked): scratch and counters are needed");
     if (rows == 0) return 0;
     const int chunk = ceil_div(vocab, chunks);
-    argmax_chunk_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, chunk, chunks, scratch, counters, out);
+    argmax_chunk_kernel<<<dim3(chunks, rows), 256, 0, stream>>>(logits, vocab, chunk, chunks, scratch, counters, out, nib_trace_buffer(), nib_trace_capacity());
     NIB_LAUNCH_CHECK();
     return 0;
 }

@@ -72,6 +72,20 @@ class Engine:
     def close(self, rc: RequestCache) -> None:
         self.cache.close(rc)
 
+    def truncate(self, rc: RequestCache, new_length: int) -> None:
+        """The request forgets its positions from ``new_length`` on (to recompute them, or to decode from the same
+        context again). A model whose mixers keep per-request state cannot go back."""
+        if self.storage.state:
+            raise ValueError("a model with per-request state cannot be truncated: the state has no history")
+        self.cache.truncate(rc, new_length)
+
+    def reset_graphs(self) -> None:
+        """Forget the captured decode graphs; steps capture them anew (after a change of what kernels do at launch)."""
+        if self._graphs is not None:
+            from .graphs import DecodeGraphs
+            self._old_graphs = getattr(self, "_old_graphs", []) + [self._graphs]     # their memory pool stays alive
+            self._graphs = DecodeGraphs(self)
+
     def check_device(self) -> None:
         """Raises if a kernel's bounded wait ran out since the last check (the kernel then returned without
         finishing its work, and the run's results are wrong). Waits for the device: the scheduler calls it

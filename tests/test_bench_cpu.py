@@ -58,3 +58,22 @@ def test_more_than_one_gpu_is_refused_with_one_line():
     assert r.returncode == 2
     lines = [line for line in r.stdout.splitlines() if line.strip()]
     assert len(lines) == 1 and json.loads(lines[0])["n_gpus"] == 2
+
+
+def test_launches_are_sorted_into_the_parts_of_a_layer():
+    """The breakdown names a launch by its kernel, its epilogue and its place in the layer's order."""
+    epi = {"qkv": "qkv", "o": "add", "gate_up": "swiglu", "down": "add", "head": "f32"}
+    order = [("embed", None), ("gemm_smallm", "qkv"), ("attention_decode", None), ("gemm_smallm", "o"), ("rmsnorm", None),
+             ("gemm_smallm", "gate_up"), ("gemm_tc", "down"), ("rmsnorm", None), ("gemm_tc", "qkv"), ("rope_store", None),
+             ("attention_decode", None), ("gemm_tc", "o"), ("rmsnorm", None), ("gemm_tc", "gate_up"), ("gemm_tc", "down"),
+             ("rmsnorm", None), ("gemm_tc", "head"), ("argmax", None)]
+    state, kinds = {}, []
+    for kernel, what in order:
+        state["tag"] = epi.get(what)
+        kinds.append(bench._kind_of(kernel, "", state))
+    assert kinds == ["embed", "qkv", "attention", "o_proj", "rmsnorm", "gate_up", "down", "rmsnorm", "qkv", "rope_store",
+                     "attention", "o_proj", "rmsnorm", "gate_up", "down", "rmsnorm", "lm_head", "argmax"]
+    n = bench.model_numbers(24)
+    assert n["kinds"]["qkv"] == 1152 * 896 and n["kinds"]["gate_up"] == 2 * 896 * 4864
+    assert sum(n["kinds"][k] for k in ("qkv", "o_proj", "gate_up", "down")) == n["per_layer_params"]
+    assert n["kv_bytes_per_token_layer"] * 24 == n["kv_bytes_per_token"]

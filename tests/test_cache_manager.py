@@ -146,6 +146,35 @@ def test_window_group_returns_pages_while_running():
     m.check()
 
 
+def test_truncate_gives_back_whole_pages_and_refuses_what_a_window_has_dropped():
+    m = CacheManager(groups(), num_pages=8, page_size=8, max_requests=2)
+    a = m.open("a")
+    m.extend(a, 30)
+    m.commit(a, 30)
+    assert len(a.tables[0]) == 4 and m.num_free() == 4
+    v = a.version
+    m.truncate(a, 17)                       # positions 17..29 are forgotten; page 3 holds nothing any more
+    assert a.length == 17 and len(a.tables[0]) == 3 and m.num_free() == 5 and a.version > v
+    m.truncate(a, 17)                       # nothing to do
+    m.extend(a, 20)
+    m.commit(a, 20)
+    assert a.length == 37 and len(a.tables[0]) == 5
+    m.truncate(a, 0)
+    assert a.tables[0] == [] and m.num_free() == 8
+    with pytest.raises(ValueError, match="cannot truncate"):
+        m.truncate(a, 1)
+    m.check()
+    w = CacheManager(groups(window=20), num_pages=16, page_size=8, max_requests=1)
+    r = w.open("r")
+    w.extend(r, 64)
+    w.commit(r, 64)                         # the window group has returned pages 0..4
+    w.truncate(r, 60)                       # position 60 reads keys from 41 on: page 5, still held
+    assert r.length == 60
+    with pytest.raises(ValueError, match="were returned"):
+        w.truncate(r, 30)
+    w.check()
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_keep_every_page_accounted_for(seed):
     rng = random.Random(seed)
