@@ -28,6 +28,28 @@ def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: torch.dtype, what:
         assert excess <= 0, f"{what}: max err {err.max().item():.3e} exceeds {BF16_MAX * rms:.3e} + one ulp by {excess:.3e}"
 
 
+def bf16_slack(row: torch.Tensor) -> float:
+    """How far below the best logit of ``row`` (the plain model's, float64) a token may lie and still be the
+    best one for an engine whose logits carry bfloat16's rounding: twice the element tolerance."""
+    row = row.double()
+    return 2 * (BF16_MAX * row.pow(2).mean().sqrt().item() + BF16_ULP * row.abs().max().item())
+
+
+def assert_diverges_only_at_a_close_call(plain, prompt, a, b, what=""):
+    """Two greedy continuations of one prompt in bfloat16 (another batch, another cut): they are equal, or at
+    the first place where they differ BOTH tokens are within rounding of the plain model's best logit, given
+    the tokens both have read so far. After that place the two runs read different contexts."""
+    for i, (x, y) in enumerate(zip(a, b)):
+        if x != y:
+            row = plain.logits(list(prompt) + list(a[:i]))[-1].double()
+            slack = bf16_slack(row)
+            best = row.max().item()
+            assert best - row[x].item() <= slack and best - row[y].item() <= slack, \
+                f"{what}: token {i}: {x} ({row[x].item():.4f}) against {y} ({row[y].item():.4f}), best {best:.4f}, slack {slack:.4f}"
+            return
+    assert len(a) == len(b), f"{what}: lengths {len(a)} and {len(b)}"
+
+
 def make_paged_batch(q_lens, ctx_before, page_size, num_pages, device, seed=0, shuffle=True):
     """A batch description like the engine builds, with pages handed out in a shuffled order so that
     logical and physical order differ. Returns (ctx, block_table)."""

@@ -109,7 +109,7 @@ def test_scheduler_equals_alone_with_few_pages(model_dirs, dtype):
         # bfloat16 rounds differently in different batches, so a near tie may turn another way and the
         # continuation then differs. What must hold: every token emitted is, under the plain model fed
         # the same tokens, within twice the element tolerance of the best one.
-        from gpu_util import BF16_MAX, BF16_ULP
+        from gpu_util import assert_diverges_only_at_a_close_call, bf16_slack
         plain = PlainModel(d)
         for i, p in enumerate(prompts):
             for got in (out[f"r{i}"], alone[i]):
@@ -117,9 +117,9 @@ def test_scheduler_equals_alone_with_few_pages(model_dirs, dtype):
                 ref = plain.logits(p + got).double()
                 for j, tok in enumerate(got):
                     row = ref[len(p) + j - 1]
-                    slack = 2 * (BF16_MAX * row.pow(2).mean().sqrt().item() + BF16_ULP * row.abs().max().item())
-                    assert row.max().item() - row[tok].item() <= slack, f"request {i} token {j}: not the best within rounding"
-        assert sum(out[f"r{i}"] == alone[i] for i in range(6)) >= 3
+                    assert row.max().item() - row[tok].item() <= bf16_slack(row), f"request {i} token {j}: not the best within rounding"
+            # and the batched run leaves the lone run only where the plain model's best two are within rounding
+            assert_diverges_only_at_a_close_call(plain, p, out[f"r{i}"], alone[i], f"request {i}")
     assert sched.preemptions > 0
     model.engine.cache.check()
     assert model.engine.cache.num_free() == 14
@@ -166,7 +166,10 @@ def test_lookahead_scheduling_generates_the_same(model_dirs, dtype):
         else:   # bfloat16: another batch may round a near tie the other way; lengths and stop rules must hold
             assert [len(o) for o in got] == limits
             assert eos not in with_eos[0] and len(with_eos[0]) <= limits[0]
-            assert sum(a == b for a, b in zip(got, plain)) >= 3
+            from gpu_util import assert_diverges_only_at_a_close_call
+            oracle = PlainModel(d)
+            for i, (a, b) in enumerate(zip(got, plain)):
+                assert_diverges_only_at_a_close_call(oracle, prompts[i], a, b, f"request {i} with lookahead")
 
 
 # ------------------------------------------------------------------------------- parts alone

@@ -56,6 +56,14 @@ def test_no_alloc_decode_attention_matches_the_ordinary_entry_point_twice():
         rc = _call(lib, noalloc, qkv, got, ctx, bt, page, kp, vp, heads, kv_heads, hd, window, splits)
         assert rc == 0, lib.nib_last_error().decode()
         assert torch.cuda.memory_allocated() == before_bytes
+        # the driver's own count of free device memory sees what torch's allocator cannot (a cudaMalloc inside
+        # the library); the call above has loaded the kernels' module, so this one can add nothing
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        rc = _call(lib, noalloc, qkv, got, ctx, bt, page, kp, vp, heads, kv_heads, hd, window, splits)
+        torch.cuda.synchronize()
+        assert rc == 0, lib.nib_last_error().decode()
+        assert torch.cuda.mem_get_info()[0] == free_before, "device memory was taken during the call"
         rc = _call(lib, ordinary, qkv, ref, ctx, bt, page, kp, vp, heads, kv_heads, hd, window, splits, scratch)
         assert rc == 0, lib.nib_last_error().decode()
         torch.cuda.synchronize()
