@@ -13,6 +13,7 @@ from __future__ import annotations
 from typing import List, Optional
 
 from .config.engine_config import EngineConfig
+from .config.kernel_options import KernelOptions
 from .engine.engine import Engine
 from .engine.scheduler import Request, Scheduler
 from .sampling.params import SamplingParams
@@ -79,12 +80,13 @@ class Model:
 
 def load_model(model_dir: str, dtype: str = "bfloat16", page_size: int = 16, num_pages: int = 0,
                max_cache_tokens: int = 0, max_batch: int = 8, max_tokens_per_step: int = 2048,
-               device: str = "cuda:0", cuda_graphs: bool = True) -> Model:
+               device: str = "cuda:0", cuda_graphs: bool = True,
+               kernel_options: Optional[KernelOptions] = None) -> Model:
     if num_pages <= 0 and max_cache_tokens <= 0:
         max_cache_tokens = 16384
     cfg = EngineConfig(dtype=dtype, page_size=page_size, num_pages=num_pages, max_cache_tokens=max_cache_tokens,
                        max_batch=max_batch, max_tokens_per_step=max_tokens_per_step, device=device,
-                       cuda_graphs=cuda_graphs)
+                       cuda_graphs=cuda_graphs, kernel_options=kernel_options or KernelOptions())
     return Model(model_dir, cfg)
 
 

@@ -136,11 +136,12 @@ class PagePool:
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """A cache group: schedule entries whose mixers keep the same kind of pages."""
-    kv_heads: int
-    head_dim: int
+    """A cache group: schedule entries whose mixers keep the same kind of pages. The manager counts pages and
+    positions only; what a page holds (``tensors``: name, heads, width, dtype of each tensor kept per token) matters
+    to the storage alone."""
     window: int                      # 0: every key is kept; w: only the last w keys are ever read
     entries: Tuple[int, ...]         # schedule entries that own a cache in this group
+    tensors: Tuple = ()              # the PagedTensor descriptions of the group's entries
 
 
 class RequestCache:

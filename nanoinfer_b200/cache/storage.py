@@ -1,7 +1,9 @@
-"""Device memory of the cache: key and value pages per group and entry, and the state slots.
+"""Device memory of the cache: the paged tensors of every entry, group by group, and the state slots.
 
-Layout of one entry's keys (values likewise): ``[num_pages, kv_heads, page_size, head_dim]``, so that
-the ``page_size x head_dim`` tile of one kv head of one page is contiguous. The reference keeps
+What an entry keeps per token is a list of tensors (``CacheNeed.tensors``: keys and values for attention; a mixer
+may keep keys alone, one latent, or tensors of different widths and dtypes). Layout of one of them:
+``[num_pages, heads, page_size, width]``, so that the ``page_size x width`` tile of one head of one page is
+contiguous. The reference keeps
 ``[layers, blocks, n_kv, block_size, head_dim]`` in 32-bit (cpp/src/cuda/cuda_backend.cu:852-871);
 here the element type is the engine's compute dtype.
 """
@@ -16,9 +18,9 @@ from .pages import CacheManager, GroupSpec
 
 
 def plan_groups(needs: Sequence[Tuple[Optional[CacheNeed], Optional[StateNeed], Optional[int]]]):
-    """Cache groups from the per-entry needs: entries with the same (kv_heads, head_dim, window)
+    """Cache groups from the per-entry needs: entries that keep the same tensors with the same window
     share a group. Returns (groups, group index of each entry or -1)."""
-    keys: List[Tuple[int, int, int]] = []
+    keys: list = []
     members: List[List[int]] = []
     entry_group = []
     for i, (need, _state, reads) in enumerate(needs):
@@ -36,7 +38,7 @@ def plan_groups(needs: Sequence[Tuple[Optional[CacheNeed], Optional[StateNeed], 
     for i, (need, _state, reads) in enumerate(needs):
         if reads is not None:
             entry_group[i] = entry_group[reads]
-    groups = [GroupSpec(k[0], k[1], k[2], tuple(m)) for k, m in zip(keys, members)]
+    groups = [GroupSpec(k[1], tuple(m), k[0]) for k, m in zip(keys, members)]
     return groups, entry_group
 
 
@@ -46,14 +48,15 @@ class CacheStorage:
         self.needs = list(needs)
         self.groups, self.entry_group = plan_groups(self.needs)
         self.page_size, self.num_pages = page_size, num_pages
-        self.k: Dict[int, torch.Tensor] = {}
-        self.v: Dict[int, torch.Tensor] = {}
+        self.pages: Dict[int, Dict[str, torch.Tensor]] = {}     # entry -> tensor name -> pages
         self.state: Dict[int, torch.Tensor] = {}
         for g in self.groups:
+            if len({t.name for t in g.tensors}) != len(g.tensors):
+                raise ValueError(f"a cache need names a tensor twice: {[t.name for t in g.tensors]}")
             for e in g.entries:
-                shape = (num_pages, g.kv_heads, page_size, g.head_dim)
-                self.k[e] = torch.zeros(shape, dtype=dtype, device=device)
-                self.v[e] = torch.zeros(shape, dtype=dtype, device=device)
+                self.pages[e] = {t.name: torch.zeros((num_pages, t.heads, page_size, t.width),
+                                                     dtype=t.dtype if t.dtype is not None else dtype, device=device)
+                                 for t in g.tensors}
         # One slot more than there can be requests: the padding rows of a captured decode step read and write
         # the spare slot, never a live request's state.
         self.pad_slot = max_requests
@@ -78,7 +81,7 @@ class CacheStorage:
             g = self.entry_group[i]
             owner = reads if reads is not None else i
             out.append(LayerCache(
-                k_pages=self.k.get(owner), v_pages=self.v.get(owner),
+                pages=self.pages.get(owner, {}),
                 block_table=block_tables.get(g) if g >= 0 else None,
                 page_size=self.page_size, writes=reads is None and need is not None,
                 state=self.state.get(i)))
@@ -86,7 +89,7 @@ class CacheStorage:
 
     def bytes_per_token(self) -> int:
         total = 0
-        for g in self.groups:
-            for e in g.entries:
-                total += 2 * g.kv_heads * g.head_dim * self.k[e].element_size()
+        for per_entry in self.pages.values():
+            for t in per_entry.values():
+                total += t.shape[1] * t.shape[3] * t.element_size()
         return total

@@ -8,6 +8,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+from .kernel_options import KernelOptions
+
 
 _DTYPES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp32": "float32"}
 
@@ -22,6 +24,7 @@ class EngineConfig:
     max_tokens_per_step: int = 2048  # token budget of one step (scheduler)
     device: str = "cuda:0"
     cuda_graphs: bool = True         # replay captured graphs for pure-decode steps
+    kernel_options: KernelOptions = KernelOptions()   # pins kernel paths; the defaults leave the choice to the library
 
     def __post_init__(self):
         if self.dtype not in _DTYPES:

@@ -11,6 +11,8 @@ from typing import Optional
 import torch
 
 from . import build as _build
+from ..config.kernel_options import KernelOptions
+from ..parts.base import LazyNorm
 
 
 class KernelError(RuntimeError):
@@ -49,33 +51,22 @@ class _StreamScope:
 
 
 class Kernels:
-    """One instance per process; stateless apart from the loaded library."""
+    """The kernel library as one engine sees it: the loaded library (shared by all instances of the process), this
+    instance's options, which never change, and its scratch memory."""
 
     name = "cuda-sm100a"
 
-    def __init__(self, lib_path: str):
+    def __init__(self, lib_path: str, options: Optional[KernelOptions] = None):
         self.lib_path = lib_path
+        self.options = options if options is not None else KernelOptions()
         self.launches = 0           # kernel launches issued through this object (graph replays add theirs)
         self._bound_stream = None   # the stream of the enclosing stream_scope(), if any
         self._op_events = None      # time_ops(): (what, event) behind every launch
         self._timeline = None       # timeline_start(): the device buffer the kernels note their times in
-        self.force_general_attention = False   # tests: run the general attention kernel for bfloat16 too
-        self.fixed_decode_splits = 0           # tests: a fixed split count for the decode kernel
-        self.force_mma_prefill = False         # tests: prompt portions on the mma.sync kernel instead of tcgen05
-        self.force_simt_gemm = False           # tests: run the CUDA-core GEMM for bfloat16 too
-        self.tc_token_tile = 0                 # tests: a fixed token tile for the tensor-core GEMM (0 = chosen)
-        self.smallm_ksplit = 0                 # tests: the K split of the small-M GEMM (0 = chosen, 1 or 4)
-        self.sm_count = 148
-        self.smallm_cross = 0                  # tests: CTAs that split K in the small-M GEMM (0 = chosen)
-        self.gemm_route = None                 # tests: "smallm" | "smallm_fused" | "tc" instead of the measured choice
-        self.pair_n_tile = 0               # tests: feature tile of the two-SM GEMM (0 = chosen, 128, 256)
-        self.tc_splits = 0                     # tests: work items along K per tile of the tcgen05 GEMM (0 = chosen, 1 = none)
+        self.sm_count = 0           # SMs of the device, asked when the instance is made ready (load_kernels)
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
         self._ws_attn_counters = None
-        self.decode_tma = True                 # decode attention with TMA page loads where the shape allows (else mma.sync + cp.async)
-        self.separate_combine = True           # merge the decode splits in a second kernel (measured faster than letting the last CTA do it)
-        self.fuse_qkv = True                   # up to 16 tokens: bias, rotation and the page write are the q/k/v product's epilogue
         try:
             self._lib = ctypes.CDLL(lib_path)
         except OSError as e:
@@ -183,6 +174,15 @@ class Kernels:
         self._check(self._lib.nib_rmsnorm(_ptr(x32), _ptr(gain32), _ptr(rows), _ptr(out), c_int(n), c_int(hidden),
                                           c_float(eps), c_int(_DT[out.dtype]), self._stream()), "rmsnorm")
 
+    def with_options(self, options: Optional[KernelOptions] = None, **changes) -> "Kernels":
+        """Another instance on the same library and the same scratch memory (so: for use on the same stream) whose
+        options are ``options``, or this instance's with ``changes``. Its launch counter starts at this one's value."""
+        import copy
+        import dataclasses
+        k = copy.copy(self)
+        k.options = options if options is not None else dataclasses.replace(self.options, **changes)
+        return k
+
     def ensure_workspace(self, device) -> None:
         """Scratch memory that kernels share between launches (allocated once, outside any graph capture)."""
         if self._ws_scratch is None:
@@ -194,10 +194,10 @@ class Kernels:
 
     def linear(self, a, w, bias32, out, mode):
         """out[M,N] (=, +=) a[M,K] . w[N,K]^T (+ bias). mode: 'store' | 'add' (float out) | 'f32' (float out).
-        ``a`` may be a DeferredNorm: the small-M kernel then applies the norm while it reads the residual stream."""
-        deferred = a if hasattr(a, "materialize") else None
+        ``a`` may be a LazyNorm: the small-M kernel then applies the norm while it reads the residual stream."""
+        lazy = a if isinstance(a, LazyNorm) else None
         dtype = a.dtype
-        if deferred is None:
+        if lazy is None:
             _need(a, None, "linear a")
         _need(w, dtype, "linear w"); _need(out, None, "linear out")
         if bias32 is not None:
@@ -212,16 +212,16 @@ class Kernels:
         self._gemm(a, w, bias32, out, m, n, k, _EPI[mode])
 
     def _route(self, m: int, rows: int, k: int, epi: int, has_norm: bool):
-        """Which kernel multiplies ``m`` tokens with ``rows x k`` bfloat16 weights, and whether a deferred
+        """Which kernel multiplies ``m`` tokens with ``rows x k`` bfloat16 weights, and whether a lazy
         norm is applied inside it. Measured on B200 with cold weights at the projection sizes of the 0.5B,
         1.5B and 7B models: the small-M kernel (weights streamed straight into mma.sync fragments) wins
         while the weights are few or the tcgen05 kernel would have few tiles and cannot split K cheaply;
         the tcgen05 kernel wins for wide outputs, for more tokens, and, with K split over CTAs and summed
         by reductions in memory, for every sum into the residual stream with a long K. The fused norm
         re-reads the 32-bit activations in every CTA, which pays only for few tokens and narrow outputs."""
-        if self.gemm_route is not None:
-            return ("tc", False) if self.gemm_route in ("tc", "tc_pair") else ("smallm", has_norm and self.gemm_route == "smallm_fused")
-        if self.smallm_ksplit or self.smallm_cross:
+        if self.options.gemm_route is not None:
+            return ("tc", False) if self.options.gemm_route in ("tc", "tc_pair") else ("smallm", has_norm and self.options.gemm_route == "smallm_fused")
+        if self.options.smallm_ksplit or self.options.smallm_cross:
             return "smallm", has_norm
         weight_bytes = 2 * rows * k
         if epi == _EPI["add"]:
@@ -239,13 +239,14 @@ class Kernels:
 
     def _use_pair(self, m: int, rows: int, k: int, epi: int) -> bool:
         """Whether pairs of SMs (cta_group::2, tiles of 256 features) take this product."""
-        if self.gemm_route is not None:
-            return self.gemm_route == "tc_pair"
-        if self.tc_token_tile or self.tc_splits or m < 256:
+        if self.options.gemm_route is not None:
+            return self.options.gemm_route == "tc_pair"
+        if self.options.tc_token_tile or self.options.tc_splits or m < 256:
             return False
         if epi == _EPI["add"]:      # with K split over pairs of SMs (at least 8 blocks of 64 per item)
             tiles = -(-rows // 256) * -(-m // 256)
-            splits = max(1, min(74 // tiles, (k // 64) // 8)) if tiles < 74 else 1
+            pairs = self.sm_count // 2
+            splits = max(1, min(pairs // tiles, (k // 64) // 8)) if tiles < pairs else 1
             return tiles * splits >= 48
         # measured on B200 at the projection sizes of the 0.5B, 1.5B and 7B models, 512..4096 tokens: tiles
         # of 256 tokens x 256 features on two SMs win once there are enough of them to fill the GPU; the
@@ -255,40 +256,48 @@ class Kernels:
         tiles = -(-rows // 256) * -(-m // 256)
         return tiles >= 48
 
+    @staticmethod
+    def _foldable(lazy) -> bool:
+        """Whether the kernels can apply this norm themselves: the kinds they know, and only while nobody has
+        computed it (a computed norm is just a tensor)."""
+        return lazy is not None and lazy.resolved is None and lazy.fold.kind == "rms"
+
     def _gemm(self, a, w, bias32, out, m, n, k, epi):
         """bfloat16 goes to the small-M kernel or to the tcgen05 kernel (see ``_route``); shapes neither
         takes, and 32-bit, run the CUDA-core kernel."""
-        deferred = a if hasattr(a, "materialize") else None
-        bf16 = a.dtype == torch.bfloat16 and not self.force_simt_gemm
-        if bf16 and self.tc_token_tile == 0:
-            kernel, fuse = self._route(m, w.shape[0], k, epi, deferred is not None)
-            if deferred is not None and not fuse:
-                a, deferred = deferred.materialize(), None
-            src = deferred.x32 if deferred is not None else a
+        lazy = a if isinstance(a, LazyNorm) else None
+        if lazy is not None and not self._foldable(lazy):
+            a, lazy = lazy.resolve(), None
+        bf16 = a.dtype == torch.bfloat16 and not self.options.force_simt_gemm
+        if bf16 and self.options.tc_token_tile == 0:
+            kernel, fuse = self._route(m, w.shape[0], k, epi, lazy is not None)
+            if lazy is not None and not fuse:
+                a, lazy = lazy.resolve(), None
+            src = lazy.fold.x32 if lazy is not None else a
             if kernel == "smallm" and self._lib.nib_gemm_smallm_supported(
-                    _ptr(src), _ptr(w), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if deferred is not None else 2)) == 1:
+                    _ptr(src), _ptr(w), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if lazy is not None else 2)) == 1:
                 self.ensure_workspace(src.device)
-                gain = deferred.gain32 if deferred is not None else None
+                gain = lazy.fold.gain32 if lazy is not None else None
                 self._check(self._lib.nib_gemm_smallm(
                     _ptr(src), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(src.stride(0)),
-                    c_int(out.stride(0)), c_int(epi), _ptr(gain), c_float(deferred.eps if deferred is not None else 0.0),
-                    c_int(self.smallm_ksplit), c_int(self.smallm_cross), _ptr(self._ws_scratch), _ptr(self._ws_counters),
+                    c_int(out.stride(0)), c_int(epi), _ptr(gain), c_float(lazy.fold.eps if lazy is not None else 0.0),
+                    c_int(self.options.smallm_ksplit), c_int(self.options.smallm_cross), _ptr(self._ws_scratch), _ptr(self._ws_counters),
                     c_longlong(self._ws_scratch.numel()), c_int(self._ws_counters.numel()), self._stream()),
                     "linear (small M)")
                 return
-        if deferred is not None:
-            a = deferred.materialize()
+        if lazy is not None:
+            a = lazy.resolve()
         if bf16 and self._lib.nib_gemm_tc_supported(_ptr(a), _ptr(w), c_int(k), c_int(a.stride(0))) == 1:
             if self._use_pair(m, w.shape[0], k, epi):
                 self._check(self._lib.nib_gemm_tc_pair(
                     _ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
-                    c_int(out.stride(0)), c_int(epi), c_int(self.pair_n_tile), c_int(self.tc_splits), self._stream()),
+                    c_int(out.stride(0)), c_int(epi), c_int(self.options.pair_n_tile), c_int(self.options.tc_splits), self._stream()),
                     "linear (tensor cores, two SMs per tile)")
                 return
             self.ensure_workspace(a.device)
             self._check(self._lib.nib_gemm_tc_splitk(
                 _ptr(a), _ptr(w), _ptr(bias32), _ptr(out), c_int(m), c_int(n), c_int(k), c_int(a.stride(0)),
-                c_int(out.stride(0)), c_int(epi), c_int(self.tc_token_tile), c_int(self.tc_splits),
+                c_int(out.stride(0)), c_int(epi), c_int(self.options.tc_token_tile), c_int(self.options.tc_splits),
                 _ptr(self._ws_scratch), _ptr(self._ws_counters), c_longlong(self._ws_scratch.numel()),
                 c_longlong(self._ws_counters.numel()), self._stream()), "linear (tensor cores)")
             return
@@ -302,7 +311,7 @@ class Kernels:
 
     def linear_swiglu(self, a, w_gate_up, out):
         """out[M,I] = silu(a . w[:I]^T) * (a . w[I:]^T)."""
-        if not hasattr(a, "materialize"):
+        if not isinstance(a, LazyNorm):
             _need(a, None, "swiglu a")
         _need(w_gate_up, a.dtype, "swiglu w"); _need(out, a.dtype, "swiglu out")
         m, k = a.shape
@@ -319,19 +328,21 @@ class Kernels:
         Up to 16 tokens of bfloat16 take one kernel for all of it (bias, rotation and the page write are the
         small-M product's epilogue, the norm its prologue); everything else is the product followed by
         ``rope_store``."""
-        deferred = a if hasattr(a, "materialize") else None
+        lazy = a if isinstance(a, LazyNorm) else None
+        if lazy is not None and not self._foldable(lazy):
+            a, lazy = lazy.resolve(), None
         m, k = a.shape
         n = w_qkv.shape[0]
         rot = 0 if rotary is None else rotary[2]
         fused = False
-        if a.dtype == torch.bfloat16 and self.fuse_qkv and not self.force_simt_gemm and self.tc_token_tile == 0 \
-                and self.gemm_route in (None, "smallm", "smallm_fused") and not self.smallm_ksplit and not self.smallm_cross:
-            kernel, with_norm = self._route(m, n, k, _EPI["store"], deferred is not None)
-            if deferred is not None and not with_norm:
-                a, deferred = deferred.materialize(), None
-            src = deferred.x32 if deferred is not None else a
+        if a.dtype == torch.bfloat16 and self.options.fuse_qkv and not self.options.force_simt_gemm and self.options.tc_token_tile == 0 \
+                and self.options.gemm_route in (None, "smallm", "smallm_fused") and not self.options.smallm_ksplit and not self.options.smallm_cross:
+            kernel, with_norm = self._route(m, n, k, _EPI["store"], lazy is not None)
+            if lazy is not None and not with_norm:
+                a, lazy = lazy.resolve(), None
+            src = lazy.fold.x32 if lazy is not None else a
             fused = kernel == "smallm" and qkv.stride(0) % 2 == 0 and self._lib.nib_gemm_smallm_qkv_supported(
-                _ptr(src), _ptr(w_qkv), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if deferred is not None else 2),
+                _ptr(src), _ptr(w_qkv), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if lazy is not None else 2),
                 c_int(head_dim), c_int(rot)) == 1
         if not fused:
             self.linear(a, w_qkv, bias32, qkv, "store")
@@ -357,10 +368,10 @@ class Kernels:
             if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim) or block_table.stride(1) != 1:
                 raise KernelError("qkv_project: pages or block table do not fit")
             num_pages, bt_stride = k_pages.shape[0], block_table.stride(0)
-        gain = deferred.gain32 if deferred is not None else None
+        gain = lazy.fold.gain32 if lazy is not None else None
         self._check(self._lib.nib_gemm_smallm_qkv(
             _ptr(src), _ptr(w_qkv), _ptr(bias32), _ptr(qkv), c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim),
-            c_int(k), c_int(src.stride(0)), c_int(qkv.stride(0)), _ptr(gain), c_float(deferred.eps if deferred is not None else 0.0),
+            c_int(k), c_int(src.stride(0)), c_int(qkv.stride(0)), _ptr(gain), c_float(lazy.fold.eps if lazy is not None else 0.0),
             _ptr(positions), _ptr(req_index), _ptr(cos), _ptr(sin), c_int(rot), _ptr(block_table if writes else None),
             c_int(bt_stride), c_int(page_size), _ptr(k_pages if writes else None), _ptr(v_pages if writes else None),
             c_int(num_pages), c_int(1 if writes else 0), self._stream()), "q/k/v projection with rotation and page write")
@@ -413,7 +424,7 @@ class Kernels:
             raise KernelError("attention: block_table rows must be dense")
         m = qkv.shape[0]
         num_pages, bt_stride = k_pages.shape[0], block_table.stride(0)
-        fast = qkv.dtype == torch.bfloat16 and not self.force_general_attention and \
+        fast = qkv.dtype == torch.bfloat16 and not self.options.force_general_attention and \
             self._lib.nib_attention_mma_supported(c_int(heads), c_int(kv_heads), c_int(head_dim)) == 1
         if not fast:
             self._check(self._lib.nib_attention_generic(
@@ -432,7 +443,7 @@ class Kernels:
             tma = self._decode_tma_ok(heads, kv_heads, head_dim, page_size)
             splits = self.decode_splits(n_dec, kv_heads, max(ctx_lens[:n_dec]), window, tma, head_dim)
             part_o = part_ml = counters = None
-            if splits > 1 and not tma and not self.separate_combine and n_dec * kv_heads <= 64 * 1024:
+            if splits > 1 and not tma and not self.options.separate_combine and n_dec * kv_heads <= 64 * 1024:
                 self.ensure_workspace(qkv.device)
                 counters = self._ws_attn_counters
             parts = splits // 8 if tma else splits      # the TMA kernel merges up to eight splits inside a cluster
@@ -455,7 +466,7 @@ class Kernels:
             q_start = c_void_p(ctx.q_start.data_ptr() + 4 * n_dec)
             lens = c_void_p(ctx.ctx_lens.data_ptr() + 4 * n_dec)
             table = c_void_p(block_table.data_ptr() + 4 * n_dec * bt_stride)
-            if not self.force_mma_prefill and self._lib.nib_attention_prefill_tc_supported(
+            if not self.options.force_mma_prefill and self._lib.nib_attention_prefill_tc_supported(
                     c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(page_size), c_int(qkv.stride(0))) == 1:
                 self._check(self._lib.nib_attention_prefill_tc(
                     _ptr(qkv), c_int(qkv.stride(0)), _ptr(out), q_start, lens, table, c_int(bt_stride), c_int(page_size),
@@ -474,7 +485,7 @@ class Kernels:
         return self._lib.nib_attention_tc_error()
 
     def _decode_tma_ok(self, heads, kv_heads, head_dim, page_size) -> bool:
-        return self.decode_tma and page_size > 0 and self._lib.nib_attention_decode_tma_supported(
+        return self.options.decode_tma and page_size > 0 and self._lib.nib_attention_decode_tma_supported(
             c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(page_size)) == 1
 
     def attention_decode_tma_error(self) -> int:
@@ -500,8 +511,8 @@ class Kernels:
         least four of its tiles (128 keys for heads of 64, else 64) each. The cp.async kernel: two key tiles per CTA (both are in flight at once, so a
         CTA waits for memory once), as long as that does not make more CTAs than fill the GPU about eight
         times."""
-        if self.fixed_decode_splits:
-            return _cluster_splits(self.fixed_decode_splits) if tma else self.fixed_decode_splits
+        if self.options.fixed_decode_splits:
+            return _cluster_splits(self.options.fixed_decode_splits) if tma else self.options.fixed_decode_splits
         keys = min(max_ctx, window) if window > 0 else max_ctx
         tiles = -(-keys // 64) + 1
         if tma:
@@ -578,13 +589,15 @@ def raise_device_errors(words) -> None:
         raise KernelError("a kernel gave up waiting; the results of this run are not to be trusted: " + "; ".join(bad))
 
 
-_KERNELS: Optional[Kernels] = None
+_LIBRARY: Optional[Kernels] = None      # the instance that loaded the library; the others share its handle
 
 
-def load_kernels(verbose: bool = True) -> Kernels:
-    """The process-wide kernel library; built on first use. Raises if there is no CUDA device."""
-    global _KERNELS
-    if _KERNELS is None:
+def load_kernels(options: Optional[KernelOptions] = None, verbose: bool = True) -> Kernels:
+    """The kernel library with ``options`` (default: every choice left to the library). The library is built and loaded
+    once per process; every call returns an instance of its own, with its own options and scratch memory. Raises if
+    there is no CUDA device."""
+    global _LIBRARY
+    if _LIBRARY is None:
         lib_path = _build.build(verbose=verbose)
         k = Kernels(lib_path)
         if not torch.cuda.is_available():
@@ -593,6 +606,8 @@ def load_kernels(verbose: bool = True) -> Kernels:
         if arch != 100:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{arch}")
         k.sm_count = max(1, k._lib.nib_sm_count())
-        k.ensure_workspace(torch.device("cuda", torch.cuda.current_device()))
-        _KERNELS = k
-    return _KERNELS
+        _LIBRARY = k
+    k = _LIBRARY.with_options(options if options is not None else KernelOptions())
+    k._ws_scratch = None
+    k.ensure_workspace(torch.device("cuda", torch.cuda.current_device()))
+    return k

@@ -44,7 +44,7 @@ class Engine:
         tensors = load_tensors(model_dir, self.plan)
         if ops is None:
             from ..csrc.lib import load_kernels  # fails loudly when the CUDA library cannot be had
-            ops = load_kernels()
+            ops = load_kernels(engine_config.kernel_options)
         self.device = torch.device(engine_config.device)
         self.dtype = _TORCH_DTYPE[engine_config.dtype]
         self.rt = Runtime(self.device, self.dtype, ops)

@@ -10,7 +10,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import CacheNeed, LayerCache, Runtime, StateNeed, StepContext
+from ..parts.base import CacheNeed, LayerCache, Runtime, StateNeed, StepContext, normed_input
 from ..parts.spec import ModelPlan, PartSpec
 from ..registry import get_arrangement, get_part
 
@@ -85,8 +85,8 @@ class DecoderModel:
             self.layers[e.layer].forward(x32, ctx, caches[i])
         if want_rows is None or want_rows.numel() == 0:
             return None
-        if ctx.all_rows_wanted and getattr(self.head, "accepts_deferred_norm", False):
-            return self.head.forward(self.final_norm.deferred(x32))
+        if ctx.all_rows_wanted:
+            return self.head.forward(normed_input(self.final_norm, self.head, x32))
         return self.head.forward(self.final_norm.forward(x32, rows=want_rows))
 
 

@@ -2,9 +2,9 @@
 from . import spec, base  # noqa: F401
 from . import norm, position, attention, feedforward, embedding, block  # noqa: F401
 from .spec import ModelPlan, LayerSpec, PartSpec, ScheduleEntry, TensorSpec
-from .base import (CacheNeed, StateNeed, StepContext, HostBatch, LayerCache, Runtime, Part, Norm,
+from .base import (CacheNeed, PagedTensor, FoldedNorm, LazyNorm, StateNeed, StepContext, HostBatch, LayerCache, Runtime, Part, Norm,
                    PositionEncoding, Mixer, FeedForward, Embedding, Head)
 
-__all__ = ["ModelPlan", "LayerSpec", "PartSpec", "ScheduleEntry", "TensorSpec", "CacheNeed",
+__all__ = ["ModelPlan", "LayerSpec", "PartSpec", "ScheduleEntry", "TensorSpec", "CacheNeed", "PagedTensor", "FoldedNorm", "LazyNorm",
            "StateNeed", "StepContext", "HostBatch", "LayerCache", "Runtime", "Part", "Norm",
            "PositionEncoding", "Mixer", "FeedForward", "Embedding", "Head"]

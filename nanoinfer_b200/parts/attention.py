@@ -28,7 +28,7 @@ class GroupedQueryAttention(Mixer):
     tensors: ``q_w k_w v_w o_w`` and, with bias, ``q_b k_b v_b``."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
-    accepts_deferred_norm = True   # its first projection can apply the norm while reading its input
+    accepts_lazy_norm = True   # its first projection can apply the norm while reading its input
 
     @staticmethod
     def spec(prefix: str, hidden: int, heads: int, kv_heads: int, head_dim: int, bias: bool,
@@ -68,7 +68,7 @@ class GroupedQueryAttention(Mixer):
         self._rotary = None
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed(self.kv_heads, self.head_dim, self.window)
+        return CacheNeed.keys_and_values(self.kv_heads, self.head_dim, self.window)
 
     def bind_positions(self, positions: Dict[str, PositionEncoding]) -> None:
         self._rotary = positions[self.position_name].rotary()

@@ -7,6 +7,9 @@ Interfaces (duck-typed; the base classes document them):
 
 * ``Norm.forward(x32, rows=None) -> h``: x32 is the 32-bit residual stream ``[M, hidden]``; the
   result has the compute dtype. ``rows`` (int32 device tensor) selects and orders the rows to norm.
+  ``Norm.fold_into_projection(x32)`` may return a ``FoldedNorm`` (x32, gain32, eps, kind); a consumer that
+  sets ``accepts_lazy_norm`` is then given a ``LazyNorm`` in place of ``h`` and hands it to the kernel
+  library's products, which apply the norm inside the product where a kernel can, or resolve it.
 * ``PositionEncoding``: ``rotary()`` returns ``(cos, sin, rotary_dim)`` tables for mixers that
   rotate queries and keys, or None; ``add_to_embedding(x32, ctx)`` may add to the residual stream.
 * ``Mixer.forward(h, residual32, ctx, cache)``: mixes tokens across positions and ADDS its output
@@ -43,14 +46,31 @@ class Runtime:
 
 
 @dataclass(frozen=True)
+class PagedTensor:
+    """One tensor that a mixer keeps per token in the paged cache: ``heads x width`` elements for every position, laid
+    out per page as ``[heads, page_size, width]``. ``dtype`` None = the engine's compute dtype."""
+    name: str
+    heads: int
+    width: int
+    dtype: Optional[torch.dtype] = None
+
+
+@dataclass(frozen=True)
 class CacheNeed:
-    """Paged keys and values a mixer keeps per token. ``window`` 0 = all keys are kept."""
-    kv_heads: int
-    head_dim: int
+    """What a mixer keeps per token: any number of paged tensors (keys and values; keys alone; one latent; keys and
+    values of different widths), all addressed through one block table. ``window`` 0 = every position is kept,
+    ``w`` = only the last ``w`` positions are ever read, so pages behind them are given back."""
+    tensors: Tuple[PagedTensor, ...]
     window: int = 0
 
-    def group_key(self) -> Tuple[int, int, int]:
-        return (self.kv_heads, self.head_dim, self.window)
+    @staticmethod
+    def keys_and_values(kv_heads: int, head_dim: int, window: int = 0) -> "CacheNeed":
+        """The two-tensor case of attention: ``k`` and ``v`` of the same shape in the compute dtype."""
+        return CacheNeed((PagedTensor("k", kv_heads, head_dim), PagedTensor("v", kv_heads, head_dim)), window)
+
+    def group_key(self):
+        """Entries with equal keys share a cache group (one block table per request)."""
+        return (self.tensors, self.window)
 
 
 @dataclass(frozen=True)
@@ -102,35 +122,72 @@ class StepContext:
 @dataclass
 class LayerCache:
     """The cache of one schedule entry, as its mixer sees it."""
-    k_pages: Optional[torch.Tensor]     # [num_pages, kv_heads, page_size, head_dim]
-    v_pages: Optional[torch.Tensor]
+    pages: Dict[str, torch.Tensor]      # PagedTensor.name -> [num_pages, heads, page_size, width]
     block_table: Optional[torch.Tensor]  # [R, max_pages] int32, -1 where no page is held
     page_size: int
     writes: bool                        # False when this entry reads another entry's cache
     state: Optional[torch.Tensor]       # [slots, *StateNeed.shape]
 
+    @property
+    def k_pages(self) -> Optional[torch.Tensor]:
+        """The keys of the two-tensor case (CacheNeed.keys_and_values)."""
+        return self.pages.get("k")
 
-class DeferredNorm:
-    """A norm that has not been computed yet: ``h = norm(x32)``, for a consumer whose kernel can apply the
-    norm while it reads its input (the decode GEMM). It looks like ``h`` (shape, dtype, device); any other
-    consumer gets the tensor from ``materialize()``."""
+    @property
+    def v_pages(self) -> Optional[torch.Tensor]:
+        return self.pages.get("v")
 
-    def __init__(self, norm: "Norm", x32: torch.Tensor, gain32: torch.Tensor, eps: float, dtype: torch.dtype):
-        self.norm, self.x32, self.gain32, self.eps, self.dtype = norm, x32, gain32, eps, dtype
+
+@dataclass(frozen=True)
+class FoldedNorm:
+    """A norm in the form a projection kernel can apply while it reads the 32-bit residual stream:
+    ``h = x32 * f(x32) * gain32`` with ``f`` named by ``kind``. ``"rms"`` is ``1/sqrt(mean(x^2) + eps)`` per
+    row; a norm with another statistic names another kind, and a kernel library that does not know the kind
+    lets the norm compute itself. A norm whose gain is stored in another form (``1 + g``) hands over the
+    vector it multiplies with."""
+    x32: torch.Tensor
+    gain32: torch.Tensor
+    eps: float
+    kind: str = "rms"
+
+
+class LazyNorm:
+    """``h = norm(x32)`` that nobody has computed yet. It stands where ``h`` would (shape, dtype, device).
+    Whoever needs the values calls ``resolve()`` (computed once); a kernel that can apply ``fold`` while it
+    reads its input never does."""
+
+    def __init__(self, norm: "Norm", fold: FoldedNorm, dtype: torch.dtype):
+        self.norm, self.fold, self.dtype = norm, fold, dtype
         self._tensor: Optional[torch.Tensor] = None
 
     @property
     def shape(self):
-        return self.x32.shape
+        return self.fold.x32.shape
 
     @property
     def device(self):
-        return self.x32.device
+        return self.fold.x32.device
 
-    def materialize(self) -> torch.Tensor:
-        if self._tensor is None:
-            self._tensor = self.norm.forward(self.x32)
+    @property
+    def resolved(self) -> Optional[torch.Tensor]:
         return self._tensor
+
+    def resolve(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self.norm.forward(self.fold.x32)
+        return self._tensor
+
+
+def as_tensor(h) -> torch.Tensor:
+    """The values of ``h``, whether it is a tensor or a ``LazyNorm``."""
+    return h.resolve() if isinstance(h, LazyNorm) else h
+
+
+def normed_input(norm, consumer, x32: torch.Tensor):
+    """What ``consumer`` reads: a part that sets ``accepts_lazy_norm`` takes the norm unresolved (if the norm can
+    be folded) and lets its first projection apply it; every other part gets the computed tensor."""
+    h = norm.lazy(x32) if getattr(consumer, "accepts_lazy_norm", False) else None
+    return norm.forward(x32) if h is None else h
 
 
 class Part:
@@ -143,9 +200,15 @@ class Norm(Part):
     def forward(self, x32: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
-    def deferred(self, x32: torch.Tensor):
-        """``forward(x32)``, or a ``DeferredNorm`` that a consumer with ``accepts_deferred_norm`` resolves."""
-        return self.forward(x32)
+    def fold_into_projection(self, x32: torch.Tensor) -> Optional[FoldedNorm]:
+        """The norm of ``x32`` as (x32, gain32, eps, kind) for a projection that applies it while reading its
+        input, or None (the default) if this norm cannot be written so; it is then computed by ``forward``."""
+        return None
+
+    def lazy(self, x32: torch.Tensor) -> Optional[LazyNorm]:
+        """The norm of ``x32`` as a ``LazyNorm`` (nothing is computed or read yet), or None if it cannot be folded."""
+        fold = self.fold_into_projection(x32)
+        return None if fold is None else LazyNorm(self, fold, self.rt.dtype)
 
 
 class PositionEncoding(Part):

@@ -11,7 +11,7 @@ from typing import Dict
 import torch
 
 from ..registry import register_arrangement
-from .base import LayerCache, StepContext
+from .base import LayerCache, StepContext, normed_input
 
 
 class PreNormBlock:
@@ -25,10 +25,8 @@ class PreNormBlock:
 
     def forward(self, x32: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
         # A part that says so takes its norm unresolved and lets its first projection apply it.
-        norm = self.mixer_norm.deferred if getattr(self.mixer, "accepts_deferred_norm", False) else self.mixer_norm.forward
-        self.mixer.forward(norm(x32), x32, ctx, cache)
-        norm = self.ffn_norm.deferred if getattr(self.ffn, "accepts_deferred_norm", False) else self.ffn_norm.forward
-        self.ffn.forward(norm(x32), x32, ctx)
+        self.mixer.forward(normed_input(self.mixer_norm, self.mixer, x32), x32, ctx, cache)
+        self.ffn.forward(normed_input(self.ffn_norm, self.ffn, x32), x32, ctx)
 
 
 register_arrangement("pre_norm", PreNormBlock)

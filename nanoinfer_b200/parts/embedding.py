@@ -39,7 +39,7 @@ class LinearHead(Head):
     """params: ``vocab``, ``hidden``. tensors: ``weight [vocab, hidden]`` (the embedding table when tied)."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
-    accepts_deferred_norm = True   # its projection can apply the norm while reading its input
+    accepts_lazy_norm = True   # its projection can apply the norm while reading its input
 
     @staticmethod
     def spec(name: str, vocab: int, hidden: int) -> PartSpec:

@@ -19,7 +19,7 @@ class SwiGLU(FeedForward):
     ``down_w [hidden, intermediate]``."""
 
     graph_safe = True   # launches do not depend on which requests are in the batch
-    accepts_deferred_norm = True   # its first projection can apply the norm while reading its input
+    accepts_lazy_norm = True   # its first projection can apply the norm while reading its input
 
     @staticmethod
     def spec(prefix: str, hidden: int, intermediate: int) -> PartSpec:

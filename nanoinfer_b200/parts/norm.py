@@ -10,7 +10,7 @@ from typing import Dict, Optional
 import torch
 
 from ..registry import register_part
-from .base import DeferredNorm, Norm, Runtime
+from .base import FoldedNorm, Norm, Runtime
 from .spec import PartSpec, TensorSpec
 
 
@@ -36,8 +36,8 @@ class RMSNorm(Norm):
         self.ops.rmsnorm(x32, self.gain, self.eps, out, rows)
         return out
 
-    def deferred(self, x32: torch.Tensor):
-        return DeferredNorm(self, x32, self.gain, self.eps, self.rt.dtype)
+    def fold_into_projection(self, x32: torch.Tensor) -> Optional[FoldedNorm]:
+        return FoldedNorm(x32, self.gain, self.eps, "rms")
 
 
 register_part("rmsnorm", RMSNorm)

@@ -89,9 +89,9 @@ def test_pool_under_random_orders_agrees_with_a_plain_model_of_it():
 
 
 def groups(window=0):
-    g = [GroupSpec(2, 16, 0, (0, 1))]
+    g = [GroupSpec(0, (0, 1))]
     if window:
-        g.append(GroupSpec(2, 16, window, (2,)))
+        g.append(GroupSpec(window, (2,)))
     return g
 
 
@@ -210,8 +210,8 @@ def test_random_orders_keep_every_page_accounted_for(seed):
 def test_group_planning_from_needs():
     from nanoinfer_b200.cache.storage import plan_groups
     from nanoinfer_b200.parts.base import CacheNeed, StateNeed
-    needs = [(CacheNeed(2, 16, 0), None, None), (CacheNeed(2, 16, 8), None, None), (None, StateNeed((4,)), None),
-             (CacheNeed(2, 16, 0), None, None), (None, None, 1)]
+    needs = [(CacheNeed.keys_and_values(2, 16, 0), None, None), (CacheNeed.keys_and_values(2, 16, 8), None, None), (None, StateNeed((4,)), None),
+             (CacheNeed.keys_and_values(2, 16, 0), None, None), (None, None, 1)]
     g, entry_group = plan_groups(needs)
     assert [(x.window, x.entries) for x in g] == [(0, (0, 3)), (8, (1,))]
     assert entry_group == [0, 1, -1, 0, 1]

@@ -2,9 +2,12 @@
 (``Kernels._route``, ``_use_pair``, ``decode_splits``). These rules were fitted to measurements at the
 projection sizes of the 0.5B, 1.5B and 7B models; the test pins them for those sizes so that a change of a
 threshold shows up as a decision that moved. No GPU and no library are needed: the rules read nothing but
-their arguments and the object's switches."""
+their arguments, the object's options and its count of SMs."""
 import pytest
 
+import dataclasses
+
+from nanoinfer_b200.config import KernelOptions
 from nanoinfer_b200.csrc.lib import Kernels, _EPI
 
 SHAPES = {      # hidden, q heads, kv heads, head dim, intermediate
@@ -17,10 +20,7 @@ SHAPES = {      # hidden, q heads, kv heads, head dim, intermediate
 @pytest.fixture()
 def rules():
     k = Kernels.__new__(Kernels)          # the decision rules only: nothing is loaded
-    k.gemm_route = None
-    k.smallm_ksplit = k.smallm_cross = 0
-    k.tc_token_tile = k.tc_splits = 0
-    k.fixed_decode_splits = 0
+    k.options = KernelOptions()
     k.sm_count = 148
     return k
 
@@ -68,7 +68,7 @@ def test_prefill_products_go_to_pairs_of_sms_when_there_are_tiles_enough(rules):
     for name in ("qkv", "o", "down"):
         rows, k, epi, _ = projections("7b")[name]
         assert rules._use_pair(2048, rows, k, epi)
-    rules.gemm_route = "tc"
+    rules.options = dataclasses.replace(rules.options, gemm_route="tc")
     assert not rules._use_pair(2048, 9728, 896, _EPI["swiglu"])          # a forced route overrides the rule
 
 
@@ -81,8 +81,8 @@ def test_decode_attention_splits(rules):
     assert rules.decode_splits(64, 4, 4096, 0, True, 128) == 1
     assert rules.decode_splits(8, 2, 100, 0, True, 64) == 1              # a short context is not split
     assert rules.decode_splits(8, 2, 4096, 512, True, 64) == 1           # nor is a window of 512 keys
-    rules.fixed_decode_splits = 5
+    rules.options = dataclasses.replace(rules.options, fixed_decode_splits=5)
     assert rules.decode_splits(8, 2, 4096, 0, True, 64) == 4             # the TMA kernel's clusters: 1, 2, 4, 8, 16, 24, ...
     assert rules.decode_splits(8, 2, 4096, 0, False, 64) == 5
-    rules.fixed_decode_splits = 21
+    rules.options = dataclasses.replace(rules.options, fixed_decode_splits=21)
     assert rules.decode_splits(8, 2, 4096, 0, True, 64) == 16

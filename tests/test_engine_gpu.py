@@ -2,6 +2,8 @@
 through the entry point, continuous batching against generation alone, and each part alone against the
 plain implementation's function for it. In 32-bit and in bfloat16."""
 
+import dataclasses
+
 import pytest
 import torch
 
@@ -172,6 +174,28 @@ def test_lookahead_scheduling_generates_the_same(model_dirs, dtype):
                 assert_diverges_only_at_a_close_call(oracle, prompts[i], a, b, f"request {i} with lookahead")
 
 
+def test_two_engines_in_one_process_keep_their_own_kernel_options(model_dirs):
+    """The options that pin kernel paths belong to an engine: one engine on the general attention kernel and the
+    CUDA-core products, one on the library's own choice, side by side, each used while the other exists. Both are
+    held against the plain implementation; neither sees the other's options."""
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.config import KernelOptions
+    d, page = model_dirs["A"]
+    plain = PlainModel(d)
+    pinned = KernelOptions(force_general_attention=True, force_simt_gemm=True, fuse_qkv=False)
+    a = load_model(d, dtype="bfloat16", page_size=page, num_pages=32, kernel_options=pinned)
+    b = load_model(d, dtype="bfloat16", page_size=page, num_pages=32)
+    assert a.engine.rt.ops.options == pinned and b.engine.rt.ops.options == KernelOptions()
+    assert a.engine.rt.ops is not b.engine.rt.ops
+    prompt = [5, 17, 3, 250, 9, 77, 41]
+    from gpu_util import assert_diverges_only_at_a_close_call
+    want = plain.greedy(prompt, 12)
+    for model in (a, b, a):
+        assert_diverges_only_at_a_close_call(plain, prompt, model.generate(prompt, max_tokens=12), want, "two engines")
+    with pytest.raises(dataclasses.FrozenInstanceError):
+        a.engine.rt.ops.options.gemm_route = "tc"
+
+
 # ------------------------------------------------------------------------------- parts alone
 def _runtime(dtype):
     from nanoinfer_b200.csrc.lib import load_kernels
@@ -263,7 +287,7 @@ def test_part_attention_whole_and_cut(dtype, heads, kv_heads, hd, window, bias):
         for n in cuts:
             ctx, bt = make_paged_batch([n], [done], page, 16, "cuda", shuffle=False)
             res = torch.zeros(n, hidden, device="cuda")
-            part.forward(h[done:done + n].cuda().contiguous(), res, ctx, LayerCache(kp, vp, bt, page, True, None))
+            part.forward(h[done:done + n].cuda().contiguous(), res, ctx, LayerCache({"k": kp, "v": vp}, bt, page, True, None))
             outs.append(res)
             done += n
         assert_close(torch.cat(outs), want, rt.dtype, f"attention part cuts={cuts}")

@@ -232,15 +232,11 @@ def test_attention_decode_long_context_split_over_ctas(K, heads, kv_heads, hd, w
     qkv = rnd((len(before), (heads + 2 * kv_heads) * hd), dtype, 52)
     out, ref = (torch.empty(len(before), heads * hd, dtype=dtype, device="cuda") for _ in range(2))
     scale = 1.0 / math.sqrt(hd)
-    K.fixed_decode_splits, K.decode_tma = splits, tma
+    K = K.with_options(fixed_decode_splits=splits, decode_tma=tma)
     two = torch.empty_like(out)
-    try:
-        K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
-        K.separate_combine = False          # the splits merged by the CTA that finishes last: the same sums in the same order
-        K.attention(qkv, two, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
-    finally:
-        K.fixed_decode_splits = 0
-        K.separate_combine = K.decode_tma = True
+    K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+    K = K.with_options(separate_combine=False)          # the splits merged by the CTA that finishes last: the same sums in the same order
+    K.attention(qkv, two, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert K.attention_decode_tma_error() == 0
     REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert_close(out, ref, dtype, "decode attention")
@@ -270,11 +266,8 @@ def test_attention_decode_takes_the_own_key_and_value_from_the_row(K, heads, kv_
     vp[phys, :, pos % page, :] = -55.0
     got, ref = (torch.empty(n, heads * hd, dtype=dtype, device="cuda") for _ in range(2))
     scale = 1.0 / math.sqrt(hd)
-    K.fixed_decode_splits = splits
-    try:
-        K.attention(qkv, got, heads, kv_heads, hd, scale, 0, ctx, bt, page, kp, vp, own_kv=True)
-    finally:
-        K.fixed_decode_splits = 0
+    K = K.with_options(fixed_decode_splits=splits)
+    K.attention(qkv, got, heads, kv_heads, hd, scale, 0, ctx, bt, page, kp, vp, own_kv=True)
     assert K.attention_decode_tma_error() == 0
     REF.attention(qkv, ref, heads, kv_heads, hd, scale, 0, ctx, bt, page, true_k, true_v)
     assert_close(got, ref, dtype, "decode attention, own key and value from the row")
@@ -292,11 +285,8 @@ def test_attention_tensor_core_kernels_agree_with_the_general_kernel(K, heads, k
     fast, general = (torch.empty(m, heads * hd, dtype=dtype, device="cuda") for _ in range(2))
     scale = 1.0 / math.sqrt(hd)
     K.attention(qkv, fast, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
-    K.force_general_attention = True
-    try:
-        K.attention(qkv, general, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
-    finally:
-        K.force_general_attention = False
+    K = K.with_options(force_general_attention=True)
+    K.attention(qkv, general, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert_close(fast, general.double(), dtype, "tensor-core vs general attention")
 
 
@@ -309,27 +299,24 @@ def test_tensor_core_gemm_tiles_and_ragged_shapes(K, m, n, k, tile):
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 70), rnd((n, k), dtype, 71, scale=0.05)
     bias = rnd((n,), torch.float32, 72)
-    K.tc_token_tile = tile
-    try:
-        out = torch.empty(m, n, dtype=dtype, device="cuda")
-        K.linear(a, w, bias, out, "store")
-        assert_close(out, _ref_linear_f64(a, w, bias), dtype, "tc store")
-        out32 = torch.empty(m, n, device="cuda")
-        K.linear(a, w, None, out32, "f32")
-        assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "tc f32")
-        res = rnd((m, n), torch.float32, 73)
-        acc = res.clone()
-        K.linear(a, w, bias, acc, "add")
-        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "tc add")
-        inter = max(1, n // 2)
-        sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
-        if tile == 256:
-            K.tc_token_tile = 128      # two accumulators, double buffered: up to 128 tokens per tile
-        K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
-        REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
-        assert_close(sw, ref, dtype, "tc swiglu")
-    finally:
-        K.tc_token_tile = 0
+    K = K.with_options(tc_token_tile=tile)
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    K.linear(a, w, bias, out, "store")
+    assert_close(out, _ref_linear_f64(a, w, bias), dtype, "tc store")
+    out32 = torch.empty(m, n, device="cuda")
+    K.linear(a, w, None, out32, "f32")
+    assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "tc f32")
+    res = rnd((m, n), torch.float32, 73)
+    acc = res.clone()
+    K.linear(a, w, bias, acc, "add")
+    assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "tc add")
+    inter = max(1, n // 2)
+    sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+    if tile == 256:
+        K = K.with_options(tc_token_tile=128)      # two accumulators, double buffered: up to 128 tokens per tile
+    K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+    REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+    assert_close(sw, ref, dtype, "tc swiglu")
     assert K.gemm_tc_error() == 0
 
 
@@ -342,29 +329,26 @@ def test_tensor_core_gemm_split_k(K, m, n, k, splits):
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 74), rnd((n, k), dtype, 75, scale=0.05)
     bias = rnd((n,), torch.float32, 76)
-    K.gemm_route, K.tc_splits = "tc", splits
-    try:
-        for _ in range(2):
-            out = torch.empty(m, n, dtype=dtype, device="cuda")
-            K.linear(a, w, bias, out, "store")
-            assert_close(out, _ref_linear_f64(a, w, bias), dtype, "split store")
-            out32 = torch.empty(m, n, device="cuda")
-            K.linear(a, w, None, out32, "f32")
-            assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "split f32")
-            again = torch.empty_like(out32)
-            K.linear(a, w, None, again, "f32")
-            assert torch.equal(out32, again)
-            res = rnd((m, n), torch.float32, 77)
-            acc = res.clone()
-            K.linear(a, w, bias, acc, "add")
-            assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "split add")
-            inter = n // 2
-            sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
-            K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
-            REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
-            assert_close(sw, ref, dtype, "split swiglu")
-    finally:
-        K.gemm_route, K.tc_splits = None, 0
+    K = K.with_options(gemm_route="tc", tc_splits=splits)
+    for _ in range(2):
+        out = torch.empty(m, n, dtype=dtype, device="cuda")
+        K.linear(a, w, bias, out, "store")
+        assert_close(out, _ref_linear_f64(a, w, bias), dtype, "split store")
+        out32 = torch.empty(m, n, device="cuda")
+        K.linear(a, w, None, out32, "f32")
+        assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "split f32")
+        again = torch.empty_like(out32)
+        K.linear(a, w, None, again, "f32")
+        assert torch.equal(out32, again)
+        res = rnd((m, n), torch.float32, 77)
+        acc = res.clone()
+        K.linear(a, w, bias, acc, "add")
+        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "split add")
+        inter = n // 2
+        sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+        K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+        REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+        assert_close(sw, ref, dtype, "split swiglu")
     assert K.gemm_tc_error() == 0
 
 
@@ -378,32 +362,29 @@ def test_tensor_core_gemm_on_pairs_of_sms(K, m, n, k, tile):
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 170), rnd((n, k), dtype, 171, scale=0.05)
     bias = rnd((n,), torch.float32, 172)
-    K.gemm_route, K.pair_n_tile = "tc_pair", tile
-    try:
-        for splits in (2, 5):       # K split over clusters, partial sums added in memory
-            K.tc_splits = splits
-            res = rnd((m, n), torch.float32, 174)
-            acc = res.clone()
-            K.linear(a, w, bias, acc, "add")
-            assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, f"pair add, {splits} splits")
-        K.tc_splits = 0
-        out = torch.empty(m, n, dtype=dtype, device="cuda")
-        K.linear(a, w, bias, out, "store")
-        assert_close(out, _ref_linear_f64(a, w, bias), dtype, "pair store")
-        out32 = torch.empty(m, n, device="cuda")
-        K.linear(a, w, None, out32, "f32")
-        assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "pair f32")
-        res = rnd((m, n), torch.float32, 173)
+    K = K.with_options(gemm_route="tc_pair", pair_n_tile=tile)
+    for splits in (2, 5):       # K split over clusters, partial sums added in memory
+        K = K.with_options(tc_splits=splits)
+        res = rnd((m, n), torch.float32, 174)
         acc = res.clone()
         K.linear(a, w, bias, acc, "add")
-        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "pair add")
-        inter = n // 2
-        sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
-        K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
-        REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
-        assert_close(sw, ref, dtype, "pair swiglu")
-    finally:
-        K.gemm_route, K.pair_n_tile, K.tc_splits = None, 0, 0
+        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, f"pair add, {splits} splits")
+    K = K.with_options(tc_splits=0)
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    K.linear(a, w, bias, out, "store")
+    assert_close(out, _ref_linear_f64(a, w, bias), dtype, "pair store")
+    out32 = torch.empty(m, n, device="cuda")
+    K.linear(a, w, None, out32, "f32")
+    assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "pair f32")
+    res = rnd((m, n), torch.float32, 173)
+    acc = res.clone()
+    K.linear(a, w, bias, acc, "add")
+    assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "pair add")
+    inter = n // 2
+    sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+    K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+    REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+    assert_close(sw, ref, dtype, "pair swiglu")
     assert K.gemm_tc_error() == 0
 
 
@@ -425,39 +406,35 @@ def test_small_m_gemm(K, m, n, k, ksplit, cross):
     dtype = torch.bfloat16
     a, w = rnd((m, k), dtype, 90), rnd((n, k), dtype, 91, scale=0.05)
     bias = rnd((n,), torch.float32, 92)
-    K.smallm_ksplit, K.smallm_cross, K.gemm_route = ksplit, cross, "smallm"
-    try:
-        out = torch.empty(m, n, dtype=dtype, device="cuda")
-        K.linear(a, w, bias, out, "store")
-        assert_close(out, _ref_linear_f64(a, w, bias), dtype, "smallm store")
-        again = torch.empty_like(out)
-        K.linear(a, w, bias, again, "store")
-        assert torch.equal(out, again)            # the split over CTAs is summed in a fixed order
-        out32 = torch.empty(m, n, device="cuda")
-        K.linear(a, w, None, out32, "f32")
-        assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "smallm f32")
-        res = rnd((m, n), torch.float32, 93)
-        acc = res.clone()
-        K.linear(a, w, bias, acc, "add")
-        assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "smallm add")
-        inter = n // 2
-        sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
-        K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
-        REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
-        assert_close(sw, ref, dtype, "smallm swiglu")
-        one = torch.empty(1, n, device="cuda")
-        K.linear(a[m - 1:m].contiguous(), w, None, one, "f32")
-        assert torch.equal(one[0], out32[m - 1])
-    finally:
-        K.smallm_ksplit = K.smallm_cross = 0
-        K.gemm_route = None
+    K = K.with_options(smallm_ksplit=ksplit, smallm_cross=cross, gemm_route="smallm")
+    out = torch.empty(m, n, dtype=dtype, device="cuda")
+    K.linear(a, w, bias, out, "store")
+    assert_close(out, _ref_linear_f64(a, w, bias), dtype, "smallm store")
+    again = torch.empty_like(out)
+    K.linear(a, w, bias, again, "store")
+    assert torch.equal(out, again)            # the split over CTAs is summed in a fixed order
+    out32 = torch.empty(m, n, device="cuda")
+    K.linear(a, w, None, out32, "f32")
+    assert_close(out32, _ref_linear_f64(a, w, None), torch.float32, "smallm f32")
+    res = rnd((m, n), torch.float32, 93)
+    acc = res.clone()
+    K.linear(a, w, bias, acc, "add")
+    assert_close(acc, res.double() + _ref_linear_f64(a, w, bias), torch.float32, "smallm add")
+    inter = n // 2
+    sw, ref = (torch.empty(m, inter, dtype=dtype, device="cuda") for _ in range(2))
+    K.linear_swiglu(a, w[:2 * inter].contiguous(), sw)
+    REF.linear_swiglu(a, w[:2 * inter].contiguous(), ref)
+    assert_close(sw, ref, dtype, "smallm swiglu")
+    one = torch.empty(1, n, device="cuda")
+    K.linear(a[m - 1:m].contiguous(), w, None, one, "f32")
+    assert torch.equal(one[0], out32[m - 1])
 
 
 @pytest.mark.parametrize("m,n,k,eps", [(1, 1152, 896, 1e-6), (8, 320, 192, 1e-5), (20, 200, 64, 1e-3), (64, 503, 320, 1e-6)])
 def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     """The decode GEMM that reads the 32-bit residual stream and applies RMSNorm on the fly, against the
     separate norm kernel followed by the same GEMM, and against float64."""
-    from nanoinfer_b200.parts.base import DeferredNorm
+    from nanoinfer_b200.parts.base import FoldedNorm, LazyNorm
 
     class _Norm:
         def forward(self_, x32, rows=None):
@@ -469,9 +446,9 @@ def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     gain = 1 + 0.1 * rnd((k,), torch.float32, 96)
     w = rnd((n, k), torch.bfloat16, 97, scale=0.05)
     fused, two_step = torch.empty(m, n, device="cuda"), torch.empty(m, n, device="cuda")
-    K.gemm_route = "smallm_fused"
-    K.linear(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w, None, fused, "f32")
-    K.gemm_route = "smallm"
+    K = K.with_options(gemm_route="smallm_fused")
+    K.linear(LazyNorm(_Norm(), FoldedNorm(x32, gain, eps), torch.bfloat16), w, None, fused, "f32")
+    K = K.with_options(gemm_route="smallm")
     h = _Norm().forward(x32)
     K.linear(h, w, None, two_step, "f32")
     ref = _ref_linear_f64(h, w, None)
@@ -481,11 +458,50 @@ def test_small_m_gemm_with_fused_rmsnorm(K, m, n, k, eps):
     assert_close(fused, exact, torch.bfloat16, "fused norm gemm")
     inter = n // 2
     sw, sw_ref = (torch.empty(m, inter, dtype=torch.bfloat16, device="cuda") for _ in range(2))
-    K.gemm_route = "smallm_fused"
-    K.linear_swiglu(DeferredNorm(_Norm(), x32, gain, eps, torch.bfloat16), w[:2 * inter].contiguous(), sw)
-    K.gemm_route = None
+    K = K.with_options(gemm_route="smallm_fused")
+    K.linear_swiglu(LazyNorm(_Norm(), FoldedNorm(x32, gain, eps), torch.bfloat16), w[:2 * inter].contiguous(), sw)
+    K = K.with_options(gemm_route=None)
     REF.linear_swiglu(h, w[:2 * inter].contiguous(), sw_ref)
     assert_close(sw, sw_ref, torch.bfloat16, "fused norm swiglu")
+
+
+def test_other_norms_use_the_fold_hook_without_a_change_to_the_library(K):
+    """Two norms the library has never seen, defined here. One stores its gain as ``g`` and multiplies with ``1 + g``:
+    it hands over the vector it multiplies with and is applied inside the small-M product like the built-in norm.
+    The other subtracts the mean first (kind "layer"): the library does not know that kind and lets the norm compute
+    itself. Both against float64."""
+    from nanoinfer_b200.parts.base import FoldedNorm, LazyNorm
+    m, n, k, eps = 5, 320, 192, 1e-5
+    x32 = rnd((m, k), torch.float32, 151, scale=2.0)
+    g = 0.1 * rnd((k,), torch.float32, 152)
+    w = rnd((n, k), torch.bfloat16, 153, scale=0.05)
+    calls = []
+
+    class OnePlusGain:
+        def forward(self, x, rows=None):
+            calls.append("one_plus")
+            out = torch.empty(x.shape, dtype=torch.bfloat16, device="cuda")
+            K.rmsnorm(x, 1 + g, eps, out, rows)
+            return out
+
+    class MeanFree:
+        def forward(self, x, rows=None):
+            calls.append("layer")
+            xd = x.double() - x.double().mean(-1, keepdim=True)
+            return (xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps) * (1 + g).double()).to(torch.bfloat16)
+
+    out = torch.empty(m, n, device="cuda")
+    K = K.with_options(gemm_route="smallm_fused")
+    K.linear(LazyNorm(OnePlusGain(), FoldedNorm(x32, 1 + g, eps, "rms"), torch.bfloat16), w, None, out, "f32")
+    assert calls == [], "applied inside the product"
+    xd = x32.double()
+    exact = (xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps) * (1 + g).double()) @ w.double().t()
+    assert_close(out, exact, torch.bfloat16, "1 + g norm folded")
+    K.linear(LazyNorm(MeanFree(), FoldedNorm(x32, 1 + g, eps, "layer"), torch.bfloat16), w, None, out, "f32")
+    assert calls == ["layer"], "computed by the norm itself"
+    xd = xd - xd.mean(-1, keepdim=True)
+    exact = (xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps) * (1 + g).double()) @ w.double().t()
+    assert_close(out, exact, torch.bfloat16, "mean-free norm resolved")
 
 
 @pytest.mark.parametrize("heads,kv_heads,hd,page,window", [
@@ -507,11 +523,8 @@ def test_attention_tcgen05_prefill(K, heads, kv_heads, hd, page, window):
     scale = 1.0 / math.sqrt(hd)
     K.attention(qkv, fast, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert K.attention_tc_error() == 0
-    K.force_mma_prefill = True
-    try:
-        K.attention(qkv, legacy, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
-    finally:
-        K.force_mma_prefill = False
+    K = K.with_options(force_mma_prefill=True)
+    K.attention(qkv, legacy, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert_close(fast, legacy.double(), dtype, "tcgen05 vs mma.sync attention")
     REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
     assert_close(fast, ref, dtype, "tcgen05 attention")
@@ -595,7 +608,7 @@ def test_qkv_projection_with_rotation_and_cache_write(K, heads, kv_heads, hd, ro
     values into the pages as its epilogue, in one kernel: against float64 for the whole row, and the pages
     against the separate rotation kernel's pages (which other tests hold against float64). Tokens of several
     requests at different positions, one request with two tokens, pages in shuffled order."""
-    from nanoinfer_b200.parts.base import DeferredNorm
+    from nanoinfer_b200.parts.base import FoldedNorm, LazyNorm
     from nanoinfer_b200.parts.position import rotary_tables
     dtype = torch.bfloat16
     q_lens, before = [1, 1, 2, 1, 1], [0, 63, 64, 300, 17]
@@ -621,7 +634,7 @@ def test_qkv_projection_with_rotation_and_cache_write(K, heads, kv_heads, hd, ro
             return out
 
     h = _Norm().forward(x32)
-    a = DeferredNorm(_Norm(), x32, gain, eps, dtype) if with_norm else h
+    a = LazyNorm(_Norm(), FoldedNorm(x32, gain, eps), dtype) if with_norm else h
     kp, vp = torch.zeros(shape, dtype=dtype, device="cuda"), torch.zeros(shape, dtype=dtype, device="cuda")
     qkv = torch.empty(m, n, dtype=dtype, device="cuda")
     before_launches = K.launches

@@ -286,3 +286,23 @@ def test_toy_model_generates_through_the_scheduler(tmp_path):
         ids.append(expect[-1])
     assert model.generate(prompt, max_tokens=6) == expect
     assert model.engine.cache.num_free(0) == 40
+
+
+def test_toy_mixer_that_keeps_keys_alone_and_unequal_keys_and_values(tmp_path):
+    """What a mixer keeps per token is a list of paged tensors: a toy mixer that keeps 32-bit keys alone in one
+    layer and keys beside wider values in another (tests/toy_memory_mixer.py) is registered, built and stepped,
+    whole and mixed in portions, with no change to the framework's files."""
+    import toy_memory_mixer as toy
+    from nanoinfer_b200.config import EngineConfig
+    from nanoinfer_b200.engine import Engine
+    from nanoinfer_b200.registry import config_from_json_dict
+    from nanoinfer_b200.weights import write_random_model
+    toy.register()
+    d = str(tmp_path / "toy_memory")
+    write_random_model(config_from_json_dict(toy.TOY), d, seed=17)
+    eng = Engine(d, EngineConfig(dtype="float32", page_size=4, num_pages=22, max_batch=3, device="cpu"), ops=TorchOps())
+    assert eng.storage.bytes_per_token() == 2 * (2 * 12 * 4) + (2 * 12 * 4 + 2 * 20 * 4)
+
+    def close_enough(got, ref, what):
+        assert (got.double().cpu() - ref).abs().max().item() < 1e-4, what
+    toy.run_through_the_engine(eng, read_weights(d), close_enough)

@@ -193,3 +193,24 @@ def test_toy_mixer_with_state_runs_beside_attention(tmp_path, dtype):
     assert_close(eng.step([StepEntry(rc, seqs["b"], [len(seqs["b"]) - 1])]), want["b"][-1:], tdt, "toy slot reuse")
     eng.close(rc)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_that_keeps_keys_alone_and_unequal_keys_and_values(tmp_path, dtype):
+    """What a mixer keeps per token is a list of paged tensors: a toy mixer that keeps 32-bit keys alone in one
+    layer and keys beside wider values (in the compute dtype) in another is registered, built and stepped on the
+    device, whole and mixed in portions, with no change to the framework's files."""
+    import toy_memory_mixer as toy
+    from nanoinfer_b200.config import EngineConfig
+    from nanoinfer_b200.engine import Engine
+    from nanoinfer_b200.registry import config_from_json_dict
+    from nanoinfer_b200.weights import write_random_model
+    toy.register()
+    d = str(tmp_path / "toy_memory")
+    write_random_model(config_from_json_dict(toy.TOY), d, seed=17)
+    eng = Engine(d, EngineConfig(dtype=dtype, page_size=4, num_pages=22, max_batch=3))
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    pages = eng.storage.pages
+    assert pages[0]["keys"].dtype == torch.float32 and pages[1]["values"].dtype == tdt and "values" not in pages[2]
+    assert tuple(pages[1]["values"].shape) == (22, 2, 4, 20) and tuple(pages[1]["keys"].shape) == (22, 2, 4, 12)
+    toy.run_through_the_engine(eng, read_weights(d), lambda got, ref, what: assert_close(got, ref, tdt, what))

@@ -8,6 +8,8 @@ from __future__ import annotations
 
 import torch
 
+from nanoinfer_b200.parts.base import as_tensor
+
 
 class TorchOps:
     name = "torch-reference"
@@ -21,7 +23,7 @@ class TorchOps:
         out.copy_(y.to(out.dtype))
 
     def linear(self, a, w, bias32, out, mode):
-        a = a.materialize() if hasattr(a, "materialize") else a
+        a = as_tensor(a)
         y = a.double() @ w.double().t()
         if bias32 is not None:
             y = y + bias32.double()
@@ -33,7 +35,7 @@ class TorchOps:
             raise ValueError(mode)
 
     def linear_swiglu(self, a, w_gate_up, out):
-        a = a.materialize() if hasattr(a, "materialize") else a
+        a = as_tensor(a)
         inter = w_gate_up.shape[0] // 2
         g = a.double() @ w_gate_up[:inter].double().t()
         u = a.double() @ w_gate_up[inter:].double().t()
