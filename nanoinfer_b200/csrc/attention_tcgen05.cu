@@ -22,9 +22,10 @@
 //
 // Formula as in attention_generic.cu (cpp/src/ops.cpp:206-270); the reference's prefill attention is a
 // SIMT kernel with 32-key shared-memory slabs (cpp/src/cuda/cuda_backend.cu:489-575).
-#include "pipeline.cuh"
+#include "tcgen05.cuh"
 
 using namespace nibp;
+using namespace nibt;
 
 namespace {
 
@@ -43,25 +44,6 @@ __device__ __forceinline__ bool mbar_spin(unsigned long long* bar, unsigned pari
     }
     return false;
 }
-__device__ __forceinline__ void tmem_alloc(unsigned* dst_smem, unsigned cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc(unsigned addr, unsigned cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                       unsigned idesc, bool accumulate) {
-    const unsigned acc = accumulate ? 1u : 0u;
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
 __device__ __forceinline__ unsigned pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -71,56 +53,6 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-// 32 columns of this thread's TMEM lane; the values may be used only after tmem_wait_ld().
-__device__ __forceinline__ void tmem_ld32_async(unsigned addr, unsigned (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(addr));
-}
-// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ unsigned long long desc_kmajor(unsigned smem_addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (unsigned long long)1 << 16;
-    d |= (unsigned long long)(1024 >> 4) << 32;
-    d |= (unsigned long long)1 << 46;
-    d |= (unsigned long long)2 << 61;
-    return d;
-}
-// MN-major operand with the 128-byte swizzle (cute/atom/mma_traits_sm100.hpp, canonical layout
-// ((8,n),(8,k)):((1,LBO),(8,SBO)) in 16-byte units): 64 elements of MN are contiguous in a 128-byte row,
-// 8 rows of K form a 1024-byte group (SBO), the next 64 elements of MN start `lbo_bytes` further on.
-__device__ __forceinline__ unsigned long long desc_mnmajor(unsigned smem_addr, unsigned lbo_bytes) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (unsigned long long)(1024 >> 4) << 32;
-    d |= (unsigned long long)1 << 46;
-    d |= (unsigned long long)2 << 61;
-    return d;
-}
-// D float, A and B bfloat16, M = 128, N = n; b_mn: the B operand is MN-major.
-__host__ __device__ constexpr unsigned instr_desc(int n, bool b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(ROWS >> 4) << 24);
-}
-
-// 32 columns of this thread's TMEM lane, written from registers; complete after tmem_wait_st().
-__device__ __forceinline__ void tmem_st32(unsigned addr, const unsigned (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-                 ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
 // Keys per block: 128 for heads of 64; 64 for heads of 128, where two query tiles, the key and value stages and two
 // tiles of probabilities of 128 keys would not fit the shared memory of an SM.
 template <int HD> constexpr int keys_of() { return HD == 64 ? 128 : 64; }
@@ -274,8 +206,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer: S(0); then for every block j: S(j+1) into the other buffer of scores at once (so
         // the softmax of block j+1 never waits for the tensor core), and O += P(j) . V(j) when P(j) is there.
-        constexpr unsigned idesc_s = instr_desc(KEYS, false);
-        constexpr unsigned idesc_o = instr_desc(HD, true);
+        constexpr unsigned idesc_s = instr_desc(ROWS, KEYS, false);
+        constexpr unsigned idesc_o = instr_desc(ROWS, HD, true);
         const unsigned q_addr = smem_u32(smem + C::OFF_Q);
         auto issue_qk = [&](int j) {
             const unsigned k_addr = smem_u32(smem + C::OFF_K + (j % STAGES) * C::KV_BYTES);

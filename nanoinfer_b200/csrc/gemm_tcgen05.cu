@@ -31,10 +31,12 @@
 // SWIGLU (two accumulators from W rows n and n + N: silu(gate) * up). Reference formulas:
 // cpp/src/ops.cpp:42-69 (linear), :86-93 (silu). The reference's tensor-core GEMMs are wmma kernels
 // for sm_89 (cpp/src/cuda/cuda_gemm.cu:484-622).
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 #include <mutex>
 #include <unordered_map>
+
+using namespace nibp;
+using namespace nibt;
 
 namespace {
 
@@ -44,87 +46,8 @@ constexpr int BLOCK_F = 128;     // output features per CTA (UMMA M)
 constexpr int BLOCK_K = 64;      // elements of K per stage: 128 bytes, one swizzle atom
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 __device__ int g_tc_error = 0;   // 0, or (code << 16 | blockIdx.x) of the first wait that ran out
-
-// ---------------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if (i > 128) __nanosleep(100);
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(unsigned* dst_smem, unsigned cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned addr, unsigned cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                       unsigned idesc, bool accumulate) {
-    const unsigned acc = accumulate ? 1u : 0u;
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(unsigned addr, float (&v)[16]) {
-    unsigned r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (cute/arch/mma_sm100_desc.hpp: SmemDescriptor).
-__device__ __forceinline__ unsigned long long smem_desc(unsigned smem_addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0,14)
-    d |= (unsigned long long)1 << 16;                             // leading byte offset (unused with swizzle), encoded 1
-    d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset: 8 rows * 128 bytes
-    d |= (unsigned long long)1 << 46;                             // descriptor version of sm_100
-    d |= (unsigned long long)2 << 61;                             // layout type: SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = tokens per tile
-// (cute/arch/mma_sm100_desc.hpp: InstrDescriptor).
-__host__ __device__ constexpr unsigned instr_desc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BLOCK_F >> 4) << 24);
-}
-
-constexpr int tmem_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
 template <int TOK, bool DUAL> struct Cfg {
     static constexpr int W_BYTES = BLOCK_F * BLOCK_K * 2;                 // 16 KB
@@ -136,10 +59,6 @@ template <int TOK, bool DUAL> struct Cfg {
     static constexpr int TMEM_COLS = tmem_cols(2 * ACC_COLS);             // two buffers
     static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 };
-
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // The epilogue of 16 consecutive tokens (first_token ..) of output feature f: v = accumulator, u = the
 // second accumulator of the swiglu form, b = bias.
@@ -196,12 +115,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (threadIdx.x == 0) {
         s_failed = 0;
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_a) : "memory");
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_a);
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full_bar[b], 1); mbar_init(&acc_empty_bar[b], 4); }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_fence_init();
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -243,7 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        constexpr unsigned idesc = instr_desc(TOK);
+        constexpr unsigned idesc = instr_desc(BLOCK_F, TOK);
         int it = 0, local = 0;
         for (int item = blockIdx.x; item < items && !s_failed; item += gridDim.x, ++local) {
             const int buf = local & 1;
@@ -266,9 +184,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 tc_fence_after();
                 const unsigned st = smem_u32(smem + s * C::STAGE_BYTES);
-                const unsigned long long w_desc = smem_desc(st);
-                const unsigned long long u_desc = smem_desc(st + C::W_BYTES);
-                const unsigned long long a_desc = smem_desc(st + (DUAL ? 2 : 1) * C::W_BYTES);
+                const unsigned long long w_desc = desc_kmajor(st);
+                const unsigned long long u_desc = desc_kmajor(st + C::W_BYTES);
+                const unsigned long long a_desc = desc_kmajor(st + (DUAL ? 2 : 1) * C::W_BYTES);
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
@@ -411,55 +329,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // both CTAs; the epilogue warps of both CTAs arrive on the even CTA's accumulator-empty barrier. No TMA
 // multicast. The cluster meets at a hardware barrier twice, after the barriers are initialised and before
 // tensor memory is freed; every other wait is bounded as above, so every thread reaches those two.
-__device__ __forceinline__ unsigned cluster_ctarank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ unsigned map_to_cta(unsigned smem_addr, unsigned rank) {
-    unsigned r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, unsigned bar_cluster_addr, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc_pair(unsigned* dst_smem, unsigned cols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(unsigned addr, unsigned cols) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_mma_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                            unsigned idesc, bool accumulate) {
-    const unsigned acc = accumulate ? 1u : 0u;
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-// arrives on the barrier at this offset in both CTAs of the pair when the MMAs issued so far are done
-__device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
-    const unsigned short mask = 3;
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
-                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
-}
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
-__host__ __device__ constexpr unsigned instr_desc_pair(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
-}
-
 constexpr int PAIR_M = 256;      // tokens per cluster tile
 constexpr int PAIR_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps: two per TMEM lane quadrant, half of the columns each
 
@@ -549,7 +421,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const unsigned rank = cluster_ctarank();                       // 0: issues the MMAs and owns the shared barriers
+    const unsigned rank = cluster_rank();                       // 0: issues the MMAs and owns the shared barriers
     const int n_tiles = (n_out + FEAT - 1) / FEAT, m_tiles = (tokens + PAIR_M - 1) / PAIR_M;
     // work item = (tile, split of K); splits fastest, feature tiles next. More than one split only with the
     // ADD epilogue: every item adds its partial sums into the output (reductions in memory).
@@ -559,12 +431,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
 
     if (threadIdx.x == 0) {
         s_failed = 0;
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_m) : "memory");
-        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_n) : "memory");
+        prefetch_tensormap(&map_m);
+        prefetch_tensormap(&map_n);
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full_bar[b], 1); mbar_init(&acc_empty_bar[b], 16); }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_fence_init();
     }
     __syncthreads();
     if (warp == 1) {
@@ -573,7 +444,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
     }
     tc_fence_before();
     __syncthreads();
-    cluster_sync_all();            // the peer's barriers exist before anything signals them
+    cluster_sync();            // the peer's barriers exist before anything signals them
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_wait();
@@ -595,7 +466,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
                     break;
                 }
                 unsigned char* st = smem + s * C::STAGE_BYTES;
-                const unsigned bar0 = map_to_cta(smem_u32(&full_bar[s]), 0);
+                const unsigned bar0 = peer_smem(&full_bar[s], 0);
                 if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
                 tma_load_2d_pair(st, &map_m, bar0, kb * BLOCK_K, t0);
                 tma_load_2d_pair(st + C::M_BYTES, &map_n, bar0, kb * BLOCK_K, w0);
@@ -603,7 +474,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ---------------- MMA issuer: one thread of the even CTA, for both
-        constexpr unsigned idesc = instr_desc_pair(NT);
+        constexpr unsigned idesc = instr_desc(PAIR_M, NT);
         int it = 0, local = 0;
         for (int item = cluster_id; item < items && !s_failed; item += n_clusters, ++local) {
             const int buf = local & 1;
@@ -625,8 +496,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
                 }
                 tc_fence_after();
                 const unsigned st = smem_u32(smem + s * C::STAGE_BYTES);
-                const unsigned long long m_desc = smem_desc(st);
-                const unsigned long long n_desc = smem_desc(st + C::M_BYTES);
+                const unsigned long long m_desc = desc_kmajor(st);
+                const unsigned long long n_desc = desc_kmajor(st + C::M_BYTES);
 #pragma unroll
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);
@@ -641,7 +512,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
         // ---------------- epilogue (in both CTAs): one token row per thread, half of the tile's features per warp
         const int quad = warp & 3;
         const int c_begin = ((warp - 2) >> 2) * (FEAT / 2), c_end = c_begin + FEAT / 2;
-        const unsigned acc_empty0 = map_to_cta(smem_u32(&acc_empty_bar[0]), 0);
+        const unsigned acc_empty0 = peer_smem(&acc_empty_bar[0], 0);
         int local = 0;
         for (int item = cluster_id; item < items; item += n_clusters, ++local) {
             const int buf = local & 1;
@@ -668,12 +539,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(acc_empty0 + buf * 8);    // to the even CTA, from both
+            if (lane == 0) mbar_arrive_peer(acc_empty0 + buf * 8);    // to the even CTA, from both
         }
     }
     tc_fence_before();
     __syncthreads();
-    cluster_sync_all();            // the peer no longer reads this CTA's shared memory or signals its barriers
+    cluster_sync();            // the peer no longer reads this CTA's shared memory or signals its barriers
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
@@ -681,27 +552,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 // Map of a row-major bfloat16 matrix [rows, k] with row stride ld elements; box = 64 x box_rows, 128-byte swizzle.
 int make_map(CUtensorMap* map, const void* ptr, long long rows, long long k, long long ld, int box_rows) {
-    EncodeTiledFn enc = get_encode();
+    NibEncodeTiledFn enc = nib_tensor_map_encoder();
     NIB_REQUIRE(enc != nullptr, "gemm (tensor cores): cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
@@ -829,7 +682,7 @@ int launch_pair_epi(int epi, const CUtensorMap& mm, const CUtensorMap& mn, const
 NIB_API int nib_gemm_tc_supported(const void* A, const void* W, int K, int lda) {
     if (K <= 0 || K % 8 || lda % 8) return 0;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 0;
-    return get_encode() != nullptr;
+    return nib_tensor_map_encoder() != nullptr;
 }
 
 // The error word of the kernels' bounded waits: 0, or (role << 16 | block) of the first wait that ran
