@@ -85,7 +85,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ q_start, const int* __restrict__ ctx_lens,
                             const int* __restrict__ block_table, int bt_stride, int page_size, int num_pages,
-                            int heads, int kv_heads, float scale, int window) {
+                            int heads, int kv_heads, float scale, int window, unsigned long long* trace, int trace_cap) {
     using C = Cfg<HD>;
     constexpr int KEYS = C::KEYS, STAGES = C::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -105,6 +105,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __shared__ volatile int s_failed;
 
     pdl_launch_dependents();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ATTN_PREFILL, 0, 0);
     const int req = blockIdx.y, kvh = blockIdx.z;
     const int n_rep = heads / kv_heads;
     const int tpt = ROWS / n_rep;                         // tokens per tile
@@ -146,6 +147,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_wait();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ATTN_PREFILL, 0, 1);
 
     if (warp == 0) {
         // ---------------- producer: lane 0 fetches Q and arms the barriers; lane i fetches page i of every block of
@@ -389,6 +391,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ATTN_PREFILL, 0, 2);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -425,7 +428,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     dim3 grid(ceil_div(max_q_len, tpt), n_req, kv_heads);
     NIB_CUDA(launch_pdl(attention_prefill_tc_kernel<HD>, grid, dim3(THREADS), (size_t)Cfg<HD>::SMEM, stream, mq, mk, mv,
                         (__nv_bfloat16*)out, q_start, ctx_lens, block_table, bt_stride, page_size, num_pages, heads,
-                        kv_heads, scale, window));
+                        kv_heads, scale, window, nib_trace_buffer(), nib_trace_capacity()));
     return 0;
 }
 

@@ -93,6 +93,7 @@ static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 b
 enum NibTraceKernel : int {
     NIB_TK_EMBED = 1, NIB_TK_RMSNORM = 2, NIB_TK_ROPE = 3, NIB_TK_GEMM_SMALLM = 4, NIB_TK_GEMM_STREAM = 5,
     NIB_TK_GEMM_TC = 6, NIB_TK_ATTN_DECODE = 7, NIB_TK_ATTN_COMBINE = 8, NIB_TK_ARGMAX = 9, NIB_TK_ATTN_DECODE_MMA = 10,
+    NIB_TK_GEMM_PAIR = 11, NIB_TK_ATTN_PREFILL = 12,
 };
 unsigned long long* nib_trace_buffer();      // nullptr unless a trace is being taken
 int nib_trace_capacity();

@@ -40,7 +40,7 @@ using namespace nibt;
 
 namespace {
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_F32 = 2, EPI_SWIGLU = 3 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_F32 = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
 
 constexpr int BLOCK_F = 128;     // output features per CTA (UMMA M)
 constexpr int BLOCK_K = 64;      // elements of K per stage: 128 bytes, one swizzle atom
@@ -49,16 +49,146 @@ constexpr int THREADS = 192;
 
 __device__ int g_tc_error = 0;   // 0, or (code << 16 | blockIdx.x) of the first wait that ran out
 
-template <int TOK, bool DUAL> struct Cfg {
+// HD != 0 (the q/k/v form): four stages, and room for the rotation tables' rows of the tile's 128 tokens (cos and sin,
+// HD/2 values each, rows padded by one float so that a thread per row reads them without bank conflicts).
+template <int TOK, bool DUAL, int HD = 0> struct Cfg {
     static constexpr int W_BYTES = BLOCK_F * BLOCK_K * 2;                 // 16 KB
     static constexpr int A_BYTES = TOK * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * W_BYTES + A_BYTES;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+    static constexpr int STAGES = HD ? 4 : ((200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES));
+    static constexpr int TAB_ROW = HD / 2 + 1;                            // floats per staged table row
+    static constexpr int TAB_BYTES = HD ? 2 * BLOCK_F * TAB_ROW * 4 : 0;
+    static constexpr int OFF_TAB = STAGES * STAGE_BYTES + 256;            // behind the barriers
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */ + TAB_BYTES;
     static constexpr int ACC_COLS = (DUAL ? 2 : 1) * TOK;                 // columns of one accumulator buffer
     static constexpr int TMEM_COLS = tmem_cols(2 * ACC_COLS);             // two buffers
     static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 };
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+// 16 consecutive features (first .. first+15) of one token row. v: accumulators (for SWIGLU the gate), u: the up values.
+template <int EPI>
+__device__ __forceinline__ void emit_row16(void* __restrict__ out, const float (&v)[16], const float (&u)[16],
+                                           const float* __restrict__ bias, size_t row_off, int first, int n_out, bool vec_ok) {
+    float x[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) x[j] = v[j];
+    if (bias != nullptr) {
+        if (first + 16 <= n_out) {          // 16 features start on a 64-byte boundary of the bias
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(bias + first) + j);
+                x[4 * j] += b.x; x[4 * j + 1] += b.y; x[4 * j + 2] += b.z; x[4 * j + 3] += b.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (first + j < n_out) x[j] += __ldg(bias + first + j);
+        }
+    }
+    if (EPI == EPI_SWIGLU) {
+        // silu(g) * u with the fast exponential and division (2 ulp): the result is rounded to bfloat16
+#pragma unroll
+        for (int j = 0; j < 16; ++j) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j])) * u[j];
+    }
+    if (vec_ok && first + 16 <= n_out) {
+        if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
+            uint4 p0, p1;
+            __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&p0);
+            __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&p1);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { h0[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]); h1[j] = __floats2bfloat162_rn(x[8 + 2 * j], x[9 + 2 * j]); }
+            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)out + row_off + first);
+            dst[0] = p0;
+            dst[1] = p1;
+        } else if (EPI == EPI_F32) {
+            float4* dst = reinterpret_cast<float4*>((float*)out + row_off + first);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        } else {
+            float* dst = (float*)out + row_off + first;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red_add_v4(dst + 4 * j, x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (first + j >= n_out) break;
+        const size_t o = row_off + first + j;
+        if (EPI == EPI_STORE || EPI == EPI_SWIGLU) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x[j]);
+        else if (EPI == EPI_F32) ((float*)out)[o] = x[j];
+        else atomicAdd((float*)out + o, x[j]);
+    }
+}
+
+// ---- the q/k/v projection's epilogue (EPI_QKV), for the kernels whose threads own a TOKEN row of the accumulator
+// The product's columns are [q heads | k heads | v heads] of HD features each; a tile of 128 columns holds whole heads.
+// Per head: bias, rotation of query and key heads by the token's position (halves paired: d with d + HD/2, the whole
+// head is rotated), one rounding to bfloat16, the row into the activation buffer and, for key and value heads, into the
+// slot of the token's position in its request's page. Reference: cpp/src/ops.cpp:146-168 (rotation),
+// cpp/src/cuda/cuda_backend.cu:354-367 (page write).
+struct QkvRows {
+    int heads, kv_heads, rotate;           // rotate: 1 = rotate q and k heads (tables of HD/2 values per position)
+    const int* positions; const int* req_index; const float* cos_t; const float* sin_t;
+    const int* block_table; int bt_stride, page_size, num_pages;
+    __nv_bfloat16* k_pages; __nv_bfloat16* v_pages; int writes;
+};
+
+// addr: TMEM address of the head's first column in this thread's lane; f: the head's first feature; live: the row exists;
+// cos_row, sin_row: the HD/2 table values of the token's position (staged in shared memory by the caller).
+// Every thread of the warp calls it (the TMEM loads are warp-wide); only live rows store.
+template <int HD>
+__device__ __forceinline__ void emit_qkv_head(unsigned addr, int f, const float* __restrict__ bias, __nv_bfloat16* __restrict__ row_out,
+                                              const QkvRows& q, int pos, long long page, bool live,
+                                              const float* cos_row, const float* sin_row) {
+    unsigned r[HD / 16][16];
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) tmem_ld16_async(addr + 16 * i, r[i]);
+    tmem_wait_ld();
+    if (!live) return;
+    float x[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) x[i] = __uint_as_float(r[i >> 4][i & 15]);
+    if (bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < HD / 4; ++i) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(bias + f) + i);
+            x[4 * i] += b.x; x[4 * i + 1] += b.y; x[4 * i + 2] += b.z; x[4 * i + 3] += b.w;
+        }
+    }
+    const int hs = f / HD;
+    if (q.rotate && hs < q.heads + q.kv_heads) {
+        constexpr int HALF = HD / 2;
+#pragma unroll
+        for (int d = 0; d < HALF; ++d) {
+            const float c = cos_row[d], sn = sin_row[d];
+            const float lo = x[d], hi = x[d + HALF];
+            x[d] = lo * c - hi * sn;
+            x[d + HALF] = hi * c + lo * sn;
+        }
+    }
+    uint4 packed[HD / 8];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(x[8 * i + 2 * j], x[8 * i + 2 * j + 1]);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(row_out + f);
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) dst[i] = packed[i];
+    if (hs >= q.heads && q.writes && page >= 0) {
+        const bool is_v = hs >= q.heads + q.kv_heads;
+        const int kvh = hs - q.heads - (is_v ? q.kv_heads : 0);
+        __nv_bfloat16* pages = is_v ? q.v_pages : q.k_pages;
+        uint4* slot = reinterpret_cast<uint4*>(pages + (((size_t)page * q.kv_heads + kvh) * q.page_size + pos % q.page_size) * HD);
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) slot[i] = packed[i];
+    }
+}
 
 // The epilogue of 16 consecutive tokens (first_token ..) of output feature f: v = accumulator, u = the
 // second accumulator of the swiglu form, b = bias.
@@ -89,14 +219,21 @@ __device__ __forceinline__ void emit16(void* __restrict__ out, const float (&v)[
 }
 
 // grid: persistent CTAs; tile index -> (feature tile, token tile), feature tiles fastest
-template <int TOK, int EPI>
+//
+// SWAP (tiles of 128 tokens): the operands change places, so the TOKENS are the instruction's M side (the TMEM lanes)
+// and the 128 features its columns. The loads and the main loop are the same; the epilogue's thread then owns a token
+// row and finds consecutive features in its lane: 32-byte stores and 16-byte reductions instead of one element at a
+// time, and the q/k/v form (EPI_QKV, heads of HD) can rotate a head and write it to its page from registers.
+template <int TOK, int EPI, bool SWAP = false, int HD = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo,
-               int splits, int kb_per_split, float* __restrict__ scratch, int* __restrict__ counters,
-               unsigned long long* trace, int trace_cap) {
+               int splits, int kb_per_split, float* __restrict__ scratch, int* __restrict__ counters, int vec_ok,
+               const QkvRows qe, unsigned long long* trace, int trace_cap) {
+    static_assert(!SWAP || (TOK == BLOCK_F && EPI != EPI_SWIGLU), "the swapped form has tiles of 128 tokens and one accumulator");
+    static_assert((EPI == EPI_QKV) == (HD != 0) && (EPI != EPI_QKV || SWAP), "the q/k/v epilogue owns token rows");
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
-    using C = Cfg<TOK, DUAL>;
+    using C = Cfg<TOK, DUAL, HD>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned long long* full_bar = reinterpret_cast<unsigned long long*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -104,6 +241,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     unsigned long long* acc_full_bar = empty_bar + C::STAGES;     // [2]
     unsigned long long* acc_empty_bar = acc_full_bar + 2;         // [2]
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty_bar + 2);
+    float* tab_cos = reinterpret_cast<float*>(smem + C::OFF_TAB);            // [128][HD/2 + 1] (q/k/v form only)
+    float* tab_sin = tab_cos + BLOCK_F * C::TAB_ROW;
     __shared__ volatile int s_failed;
 
     pdl_launch_dependents();
@@ -161,7 +300,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        constexpr unsigned idesc = instr_desc(BLOCK_F, TOK);
+        constexpr unsigned idesc = SWAP ? instr_desc(TOK, BLOCK_F) : instr_desc(BLOCK_F, TOK);
         int it = 0, local = 0;
         for (int item = blockIdx.x; item < items && !s_failed; item += gridDim.x, ++local) {
             const int buf = local & 1;
@@ -191,7 +330,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const unsigned long long adv = (unsigned long long)((k * UMMA_K * 2) >> 4);   // 32 bytes per step
                     const bool accumulate = (kb > kb_begin) || (k > 0);
-                    tc_mma(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
+                    if (SWAP) tc_mma(acc, a_desc + adv, w_desc + adv, idesc, accumulate);
+                    else tc_mma(acc, w_desc + adv, a_desc + adv, idesc, accumulate);
                     if (DUAL) tc_mma(acc + TOK, u_desc + adv, a_desc + adv, idesc, accumulate);
                 }
                 tc_commit(&empty_bar[s]);        // the stage is free when these MMAs have read it
@@ -208,6 +348,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int tile = item / splits;
             const int f0 = (tile % f_tiles) * BLOCK_F, t0 = (tile / f_tiles) * TOK;
             const int f = f0 + quad * 32 + lane;
+            // q/k/v form: what the epilogue reads besides the accumulator (the token's position and page, its rows of the
+            // rotation tables, the tile's bias) is nobody's result: fetched while the tensor core still works on the tile
+            int qkv_pos = 0;
+            long long qkv_page = -1;
+            if constexpr (EPI == EPI_QKV) {
+                const int t = t0 + quad * 32 + lane;
+                if (t < tokens) {
+                    qkv_pos = __ldg(qe.positions + t);
+                    if (qe.writes) {
+                        qkv_page = __ldg(qe.block_table + (size_t)__ldg(qe.req_index + t) * qe.bt_stride + qkv_pos / qe.page_size);
+                        if (qkv_page >= qe.num_pages) qkv_page = -1;      // never write outside the pool
+                    }
+                }
+                if (qe.rotate) {
+                    // the tables' rows of this warp's 32 tokens, read with the lanes along a row (coalesced)
+                    __syncwarp();
+                    const int rows_here = min(32, tokens - (t0 + quad * 32));          // warp-uniform
+#pragma unroll 1
+                    for (int r0 = 0; r0 < 32; r0 += 16) {
+                        // sixteen rows' loads are issued before the first is stored: one wait for memory, not sixteen
+                        float vc[16][HD / 64], vs[16][HD / 64];
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) {
+                            const int pos_r = __shfl_sync(0xffffffffu, qkv_pos, r0 + r);
+#pragma unroll
+                            for (int d = 0; d < HD / 64; ++d) {
+                                vc[r][d] = r0 + r < rows_here ? __ldg(qe.cos_t + (size_t)pos_r * (HD / 2) + 32 * d + lane) : 0.f;
+                                vs[r][d] = r0 + r < rows_here ? __ldg(qe.sin_t + (size_t)pos_r * (HD / 2) + 32 * d + lane) : 0.f;
+                            }
+                        }
+#pragma unroll
+                        for (int r = 0; r < 16; ++r)
+#pragma unroll
+                            for (int d = 0; d < HD / 64; ++d) {
+                                tab_cos[(quad * 32 + r0 + r) * C::TAB_ROW + 32 * d + lane] = vc[r][d];
+                                tab_sin[(quad * 32 + r0 + r) * C::TAB_ROW + 32 * d + lane] = vs[r][d];
+                            }
+                    }
+                    __syncwarp();
+                }
+                if (bias != nullptr && lane < 4 && f0 + lane * 32 < n_out) asm volatile("prefetch.global.L1 [%0];\n" ::"l"(bias + f0 + lane * 32));
+            }
             bool ok = !s_failed && mbar_wait(&acc_full_bar[buf], (local >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
@@ -215,8 +397,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 break;
             }
             tc_fence_after();
-            const float b = (bias != nullptr && f < n_out) ? bias[f] : 0.f;
             const unsigned lane_addr = tmem_base + buf * C::ACC_COLS + ((unsigned)(quad * 32) << 16);
+            if constexpr (SWAP) {
+                // ---- this thread owns token row t; its lane holds the tile's 128 features
+                const int t = t0 + quad * 32 + lane;
+                const bool live = t < tokens;
+                if constexpr (EPI == EPI_QKV) {
+#pragma unroll 1
+                    for (int c = 0; c < BLOCK_F; c += HD) {
+                        if (f0 + c >= n_out) break;
+                        emit_qkv_head<HD>(lane_addr + c, f0 + c, bias, (__nv_bfloat16*)out + (size_t)t * ldo, qe, qkv_pos, qkv_page, live,
+                                          tab_cos + (quad * 32 + lane) * C::TAB_ROW, tab_sin + (quad * 32 + lane) * C::TAB_ROW);
+                    }
+                } else {
+                    const float* item_bias = (item - tile * splits == 0) ? bias : nullptr;     // the bias is added once
+#pragma unroll 1
+                    for (int c = 0; c < BLOCK_F; c += 64) {
+                        if (f0 + c >= n_out) break;
+                        unsigned r[4][16];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tmem_ld16_async(lane_addr + c + 16 * j, r[j]);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float v[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[j][i]);
+                            if (live && f0 + c + 16 * j < n_out)
+                                emit_row16<EPI>(out, v, v, item_bias, (size_t)t * ldo, f0 + c + 16 * j, n_out, vec_ok != 0);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+            } else {
+            // ---- this thread owns output feature f; its lane holds the tile's tokens
+            const float b = (bias != nullptr && f < n_out) ? bias[f] : 0.f;
             if (splits == 1) {
 #pragma unroll 1
                 for (int c = 0; c < TOK; c += 16) {
@@ -298,6 +515,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (f < n_out) emit16<EPI>(out, v, u, b, f, t0 + c, tokens, ldo);
             }
+            }   // !SWAP
         }
     }
     tc_fence_before();
@@ -329,9 +547,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // both CTAs; the epilogue warps of both CTAs arrive on the even CTA's accumulator-empty barrier. No TMA
 // multicast. The cluster meets at a hardware barrier twice, after the barriers are initialised and before
 // tensor memory is freed; every other wait is bounded as above, so every thread reaches those two.
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 constexpr int PAIR_M = 256;      // tokens per cluster tile
 constexpr int PAIR_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps: two per TMEM lane quadrant, half of the columns each
 
@@ -345,68 +560,12 @@ template <int NT> struct PairCfg {
     static_assert(2 * NT <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 };
 
-// 16 consecutive features (first .. first+15) of one token row. v: accumulators (for SWIGLU the gate), u: the up values.
-template <int EPI>
-__device__ __forceinline__ void emit_row16(void* __restrict__ out, const float (&v)[16], const float (&u)[16],
-                                           const float* __restrict__ bias, size_t row_off, int first, int n_out, bool vec_ok) {
-    float x[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) x[j] = v[j];
-    if (bias != nullptr) {
-        if (first + 16 <= n_out) {          // 16 features start on a 64-byte boundary of the bias
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float4 b = __ldg(reinterpret_cast<const float4*>(bias + first) + j);
-                x[4 * j] += b.x; x[4 * j + 1] += b.y; x[4 * j + 2] += b.z; x[4 * j + 3] += b.w;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (first + j < n_out) x[j] += __ldg(bias + first + j);
-        }
-    }
-    if (EPI == EPI_SWIGLU) {
-        // silu(g) * u with the fast exponential and division (2 ulp): the result is rounded to bfloat16
-#pragma unroll
-        for (int j = 0; j < 16; ++j) x[j] = __fdividef(x[j], 1.0f + __expf(-x[j])) * u[j];
-    }
-    if (vec_ok && first + 16 <= n_out) {
-        if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
-            uint4 p0, p1;
-            __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&p0);
-            __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&p1);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { h0[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]); h1[j] = __floats2bfloat162_rn(x[8 + 2 * j], x[9 + 2 * j]); }
-            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)out + row_off + first);
-            dst[0] = p0;
-            dst[1] = p1;
-        } else if (EPI == EPI_F32) {
-            float4* dst = reinterpret_cast<float4*>((float*)out + row_off + first);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) dst[j] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
-        } else {
-            float* dst = (float*)out + row_off + first;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) red_add_v4(dst + 4 * j, x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
-        }
-        return;
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        if (first + j >= n_out) break;
-        const size_t o = row_off + first + j;
-        if (EPI == EPI_STORE || EPI == EPI_SWIGLU) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x[j]);
-        else if (EPI == EPI_F32) ((float*)out)[o] = x[j];
-        else atomicAdd((float*)out + o, x[j]);
-    }
-}
-
 // map_m: activations [tokens, K], box 64 x 128 rows; map_n: weights [rows, K], box 64 x NT/2 rows.
 template <int NT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
                  const float* __restrict__ bias, void* __restrict__ out, int tokens, int n_out, int k_dim, int ldo, int vec_ok,
-                 int splits, int kb_per_split) {
+                 int splits, int kb_per_split, unsigned long long* trace, int trace_cap) {
     constexpr bool GU = (EPI == EPI_SWIGLU);                       // the tile's columns: gate rows | up rows of NT/2 features
     constexpr int FEAT = GU ? NT / 2 : NT;                         // output features per tile
     using C = PairCfg<NT>;
@@ -421,6 +580,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_PAIR, EPI, 0);
     const unsigned rank = cluster_rank();                       // 0: issues the MMAs and owns the shared barriers
     const int n_tiles = (n_out + FEAT - 1) / FEAT, m_tiles = (tokens + PAIR_M - 1) / PAIR_M;
     // work item = (tile, split of K); splits fastest, feature tiles next. More than one split only with the
@@ -448,6 +608,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_wait();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_PAIR, EPI, 1);
 
     if (warp == 0 && lane == 0) {
         // ---------------- producer (in both CTAs): this CTA's 128 token rows and its half of the weight rows
@@ -544,6 +705,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constan
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_PAIR, EPI, 2);
     cluster_sync();            // the peer no longer reads this CTA's shared memory or signals its barriers
     if (warp == 1) {
         tc_fence_after();
@@ -596,13 +758,13 @@ int sm_count() {
     return sms;
 }
 
-template <int TOK, int EPI>
+template <int TOK, int EPI, bool SWAP = false, int HD = 0>
 int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, int tokens, int n_out,
-              int k, int ldo, const SplitK& sk, cudaStream_t stream) {
-    using C = Cfg<TOK, EPI == EPI_SWIGLU>;
+              int k, int ldo, const SplitK& sk, cudaStream_t stream, int vec_ok = 0, const QkvRows& qe = QkvRows{}) {
+    using C = Cfg<TOK, EPI == EPI_SWIGLU, HD>;
     static bool configured = false;
     if (!configured) {
-        NIB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TOK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        NIB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<TOK, EPI, SWAP, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
     const int sms = sm_count();
@@ -612,6 +774,7 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, v
     if (splits > k_blocks) splits = k_blocks;
     int kb_per_split = ceil_div(k_blocks, splits);
     splits = ceil_div(k_blocks, kb_per_split);               // no split without work
+    NIB_REQUIRE(!SWAP || splits == 1 || EPI == EPI_ADD, "gemm (tensor cores): token-row tiles split K only for the sum into the output");
     if (splits > 1 && EPI != EPI_ADD) {
         const long long need = (long long)tiles * splits * (EPI == EPI_SWIGLU ? 2 : 1) * TOK * BLOCK_F;
         NIB_REQUIRE(sk.scratch != nullptr && sk.counters != nullptr && need <= sk.scratch_floats && 4LL * tiles <= sk.counter_ints,
@@ -619,8 +782,8 @@ int launch_tc(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, v
                     splits, tiles, need, 4 * tiles, sk.scratch_floats, sk.counter_ints);
     }
     const int items = tiles * splits;
-    NIB_CUDA(launch_pdl(gemm_tc_kernel<TOK, EPI>, dim3(items < sms ? items : sms), dim3(THREADS), (size_t)C::SMEM, stream,
-                        mw, ma, bias, out, tokens, n_out, k, ldo, splits, kb_per_split, sk.scratch, sk.counters,
+    NIB_CUDA(launch_pdl(gemm_tc_kernel<TOK, EPI, SWAP, HD>, dim3(items < sms ? items : sms), dim3(THREADS), (size_t)C::SMEM, stream,
+                        mw, ma, bias, out, tokens, n_out, k, ldo, splits, kb_per_split, sk.scratch, sk.counters, vec_ok, qe,
                         nib_trace_buffer(), nib_trace_capacity()));
     return 0;
 }
@@ -659,7 +822,7 @@ int launch_pair(const CUtensorMap& mm, const CUtensorMap& mn, const float* bias,
     int ctas = 2 * tiles * splits, most = sm_count() & ~1;
     if (ctas > most) ctas = most;
     NIB_CUDA(launch_pdl(gemm_pair_kernel<NT, EPI>, dim3(ctas), dim3(PAIR_THREADS), (size_t)C::SMEM, stream, mm, mn, bias, out,
-                        tokens, n_out, k, ldo, vec_ok, splits, kb_per_split));
+                        tokens, n_out, k, ldo, vec_ok, splits, kb_per_split, nib_trace_buffer(), nib_trace_capacity()));
     return 0;
 }
 
@@ -751,6 +914,19 @@ NIB_API int nib_gemm_tc_splitk(const void* A, const void* W, const float* bias, 
         }
     }
     if (make_map(&ma, A, tokens, K, lda, tok_tile)) return 1;
+    if (tok_tile == BLOCK_F && epi != EPI_SWIGLU && ((uintptr_t)bias & 15) == 0) {
+        // tiles of 128 tokens: the token-row form (its epilogue writes rows, not columns). It splits K only for the sum.
+        int splits_now = sk.splits < 1 ? 1 : sk.splits;
+        if (epi == EPI_ADD || splits_now == 1) {
+            const int elem = epi == EPI_STORE ? 2 : 4;
+            const int vec_ok = (((uintptr_t)out & 15) == 0 && ((long long)ldo * elem) % 16 == 0) ? 1 : 0;
+            switch (epi) {
+                case EPI_STORE: return launch_tc<BLOCK_F, EPI_STORE, true>(mw, ma, bias, out, tokens, N, K, ldo, sk, stream, vec_ok);
+                case EPI_ADD: return launch_tc<BLOCK_F, EPI_ADD, true>(mw, ma, bias, out, tokens, N, K, ldo, sk, stream, vec_ok);
+                case EPI_F32: return launch_tc<BLOCK_F, EPI_F32, true>(mw, ma, bias, out, tokens, N, K, ldo, sk, stream, vec_ok);
+            }
+        }
+    }
     switch (tok_tile) {
         case 16: return launch_tc_epi<16>(epi, mw, ma, bias, out, tokens, N, K, ldo, sk, stream);
         case 32: return launch_tc_epi<32>(epi, mw, ma, bias, out, tokens, N, K, ldo, sk, stream);
@@ -767,6 +943,54 @@ NIB_API int nib_gemm_tc_splitk(const void* A, const void* W, const float* bias, 
 NIB_API int nib_gemm_tc(const void* A, const void* W, const float* bias, void* out, int tokens, int N, int K,
                         int lda, int ldo, int epi, int tok_tile, cudaStream_t stream) {
     return nib_gemm_tc_splitk(A, W, bias, out, tokens, N, K, lda, ldo, epi, tok_tile, 1, nullptr, nullptr, 0, 0, stream);
+}
+
+// 1 if nib_gemm_tc_qkv takes these sizes: heads of 64 or 128 that are rotated whole (rot == head_dim) or not at all,
+// 16-byte aligned rows and bias.
+NIB_API int nib_gemm_tc_qkv_supported(const void* A, const void* W, const void* bias, const void* qkv, int K, int lda,
+                                      int ldq, int head_dim, int rot) {
+    if (head_dim != 64 && head_dim != 128) return 0;
+    if (rot != 0 && rot != head_dim) return 0;
+    if (((uintptr_t)bias & 15) || ((uintptr_t)qkv & 15) || ldq % 8) return 0;
+    return nib_gemm_tc_supported(A, W, K, lda);
+}
+
+// The q/k/v projection of a prompt portion with what follows it, in one kernel: qkv[tokens, (heads + 2 kv_heads) *
+// head_dim] = A . W^T + bias; query and key heads rotated by positions[token] (tables of head_dim/2 values per
+// position, halves paired) when rot == head_dim; the row stored to ``qkv``; with ``writes`` the rotated key and the
+// value also into the slot of the token's position in its request's page (block_table[req_index[token]][position /
+// page_size]; a negative entry is skipped). Tiles of 128 tokens x 128 features on one SM.
+NIB_API int nib_gemm_tc_qkv(const void* A, const void* W, const float* bias, void* qkv, int tokens, int heads, int kv_heads,
+                            int head_dim, int K, int lda, int ldq, const int* positions, const int* req_index,
+                            const float* cos_t, const float* sin_t, int rot, const int* block_table, int bt_stride,
+                            int page_size, void* k_pages, void* v_pages, int num_pages, int writes, cudaStream_t stream) {
+    const int N = (heads + 2 * kv_heads) * head_dim;
+    NIB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && K > 0 && lda >= K && ldq >= N, "gemm (tensor cores, q/k/v): bad sizes");
+    NIB_REQUIRE(nib_gemm_tc_qkv_supported(A, W, bias, qkv, K, lda, ldq, head_dim, rot),
+                "gemm (tensor cores, q/k/v): needs heads of 64 or 128 rotated whole or not at all, K %% 8 == 0 and 16-byte aligned rows (head_dim=%d rot=%d K=%d)", head_dim, rot, K);
+    NIB_REQUIRE(rot == 0 || (cos_t && sin_t), "gemm (tensor cores, q/k/v): rotation needs the tables");
+    NIB_REQUIRE(positions && req_index, "gemm (tensor cores, q/k/v): positions and request rows are needed");
+    NIB_REQUIRE(!writes || (block_table && k_pages && v_pages && page_size > 0 && num_pages > 0), "gemm (tensor cores, q/k/v): writing needs pages and a block table");
+    if (tokens == 0) return 0;
+    CUtensorMap mw, ma;
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        MapKey key{W, N, K, BLOCK_F};
+        auto it = g_weight_maps.find(key);
+        if (it == g_weight_maps.end()) {
+            if (make_map(&mw, W, N, K, K, BLOCK_F)) return 1;
+            if (g_weight_maps.size() > 4096) g_weight_maps.clear();
+            g_weight_maps.emplace(key, mw);
+        } else {
+            mw = it->second;
+        }
+    }
+    if (make_map(&ma, A, tokens, K, lda, BLOCK_F)) return 1;
+    SplitK sk;
+    QkvRows qe{heads, kv_heads, rot != 0 ? 1 : 0, positions, req_index, cos_t, sin_t, block_table, bt_stride, page_size,
+               num_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, writes};
+    if (head_dim == 64) return launch_tc<BLOCK_F, EPI_QKV, true, 64>(mw, ma, bias, qkv, tokens, N, K, ldq, sk, stream, 1, qe);
+    return launch_tc<BLOCK_F, EPI_QKV, true, 128>(mw, ma, bias, qkv, tokens, N, K, ldq, sk, stream, 1, qe);
 }
 
 // The product for many tokens by pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 tokens x n_tile

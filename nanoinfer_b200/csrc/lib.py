@@ -78,7 +78,8 @@ class Kernels:
                      "nib_attention_prefill_mma", "nib_attention_decode_mma", "nib_attention_decode_tma",
                      "nib_attention_decode_tma_supported",
                      "nib_attention_decode_tma_error", "nib_argmax", "nib_argmax_chunked", "nib_sample", "nib_repetition_penalty", "nib_device_arch",
-                     "nib_sm_count", "nib_gemm_smallm_qkv", "nib_gemm_smallm_qkv_supported"):
+                     "nib_sm_count", "nib_gemm_smallm_qkv", "nib_gemm_smallm_qkv_supported", "nib_gemm_tc_qkv",
+                     "nib_gemm_tc_qkv_supported"):
             getattr(self._lib, name).restype = c_int
 
     # ---- plumbing ---------------------------------------------------------------------------
@@ -326,7 +327,8 @@ class Kernels:
         rotated keys and the values also go into the cache pages. ``a`` may be a DeferredNorm.
 
         Up to 16 tokens of bfloat16 take one kernel for all of it (bias, rotation and the page write are the
-        small-M product's epilogue, the norm its prologue); everything else is the product followed by
+        small-M product's epilogue, the norm its prologue); so do the tiles of 128 tokens of the one-CTA tcgen05
+        product (heads of 64 or 128 that are rotated whole); everything else is the product followed by
         ``rope_store``."""
         lazy = a if isinstance(a, LazyNorm) else None
         if lazy is not None and not self._foldable(lazy):
@@ -334,17 +336,23 @@ class Kernels:
         m, k = a.shape
         n = w_qkv.shape[0]
         rot = 0 if rotary is None else rotary[2]
-        fused = False
-        if a.dtype == torch.bfloat16 and self.options.fuse_qkv and not self.options.force_simt_gemm and self.options.tc_token_tile == 0 \
-                and self.options.gemm_route in (None, "smallm", "smallm_fused") and not self.options.smallm_ksplit and not self.options.smallm_cross:
+        fused = fused_tc = False
+        o = self.options
+        if a.dtype == torch.bfloat16 and o.fuse_qkv and not o.force_simt_gemm and o.tc_token_tile in (0, 128) \
+                and o.gemm_route in (None, "smallm", "smallm_fused", "tc") and not o.smallm_ksplit and not o.smallm_cross:
             kernel, with_norm = self._route(m, n, k, _EPI["store"], lazy is not None)
             if lazy is not None and not with_norm:
                 a, lazy = lazy.resolve(), None
             src = lazy.fold.x32 if lazy is not None else a
-            fused = kernel == "smallm" and qkv.stride(0) % 2 == 0 and self._lib.nib_gemm_smallm_qkv_supported(
+            fused = kernel == "smallm" and o.tc_token_tile == 0 and qkv.stride(0) % 2 == 0 and self._lib.nib_gemm_smallm_qkv_supported(
                 _ptr(src), _ptr(w_qkv), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if lazy is not None else 2),
                 c_int(head_dim), c_int(rot)) == 1
-        if not fused:
+            # the one-CTA tcgen05 product takes tiles of 128 tokens from 65 tokens on (nib_gemm_tc_splitk's choice)
+            fused_tc = not fused and kernel == "tc" and (m > 64 or o.tc_token_tile == 128) and o.tc_splits in (0, 1) \
+                and not self._use_pair(m, n, k, _EPI["store"]) and self._lib.nib_gemm_tc_qkv_supported(
+                    _ptr(a), _ptr(w_qkv), _ptr(bias32), _ptr(qkv), c_int(k), c_int(a.stride(0)), c_int(qkv.stride(0)),
+                    c_int(head_dim), c_int(rot)) == 1
+        if not fused and not fused_tc:
             self.linear(a, w_qkv, bias32, qkv, "store")
             self.rope_store(qkv, heads, kv_heads, head_dim, positions, req_index, rotary, block_table, page_size,
                             k_pages, v_pages, writes)
@@ -368,6 +376,14 @@ class Kernels:
             if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim) or block_table.stride(1) != 1:
                 raise KernelError("qkv_project: pages or block table do not fit")
             num_pages, bt_stride = k_pages.shape[0], block_table.stride(0)
+        if fused_tc:
+            self._check(self._lib.nib_gemm_tc_qkv(
+                _ptr(a), _ptr(w_qkv), _ptr(bias32), _ptr(qkv), c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim),
+                c_int(k), c_int(a.stride(0)), c_int(qkv.stride(0)), _ptr(positions), _ptr(req_index), _ptr(cos), _ptr(sin),
+                c_int(rot), _ptr(block_table if writes else None), c_int(bt_stride), c_int(page_size),
+                _ptr(k_pages if writes else None), _ptr(v_pages if writes else None), c_int(num_pages),
+                c_int(1 if writes else 0), self._stream()), "q/k/v projection (tensor cores) with rotation and page write")
+            return
         gain = lazy.fold.gain32 if lazy is not None else None
         self._check(self._lib.nib_gemm_smallm_qkv(
             _ptr(src), _ptr(w_qkv), _ptr(bias32), _ptr(qkv), c_int(m), c_int(heads), c_int(kv_heads), c_int(head_dim),
@@ -554,7 +570,8 @@ class Kernels:
 
 # kernel ids of the timeline (common.cuh: NibTraceKernel)
 TIMELINE_KERNELS = {1: "embed", 2: "rmsnorm", 3: "rope_store", 4: "gemm_smallm", 5: "gemm_stream", 6: "gemm_tc",
-                    7: "attention_decode", 8: "attention_combine", 9: "argmax", 10: "attention_decode_mma"}
+                    7: "attention_decode", 8: "attention_combine", 9: "argmax", 10: "attention_decode_mma",
+                    11: "gemm_pair", 12: "attention_prefill"}
 
 
 def _cluster_splits(n: int) -> int:

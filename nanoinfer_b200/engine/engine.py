@@ -95,10 +95,14 @@ class Engine:
             check()
 
     # ---- the step -------------------------------------------------------------------------
-    def _check(self, entries: Sequence[StepEntry]) -> None:
+    def _check(self, entries: Sequence[StepEntry]) -> List[np.ndarray]:
+        """Refuses what a step cannot run; returns every entry's token ids as an int32 array (made once: a prompt
+        portion has thousands of ids, and turning a Python list into an array is the dearest thing the host does
+        before the first launch; an entry whose ``tokens`` already are an int32 array costs nothing)."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         seen = set()
+        arrays = []
         for e in entries:
             if e.request.closed:
                 raise ValueError(f"request {e.request.request_id!r} is closed")
@@ -112,20 +116,22 @@ class Engine:
                 raise ValueError(
                     f"request {e.request.request_id!r}: position {e.request.length + n} exceeds the "
                     f"model's context length {self.max_positions} (max_position_embeddings)")
-            if n > 32:      # a prompt portion has thousands of ids: one pass in numpy
-                ids = np.asarray(e.tokens, dtype=np.int64)
-                in_range = int(ids.min()) >= 0 and int(ids.max()) < self.vocab_size
-            else:
-                in_range = all(0 <= int(t) < self.vocab_size for t in e.tokens)
+            try:
+                ids = np.asarray(e.tokens, dtype=np.int32)
+                in_range = ids.ndim == 1 and int(ids.min()) >= 0 and int(ids.max()) < self.vocab_size
+            except (OverflowError, TypeError, ValueError):      # an id that no int32 holds, or no integer at all
+                in_range = False
             if not in_range:
-                bad = next(int(t) for t in e.tokens if not (0 <= int(t) < self.vocab_size))
-                raise ValueError(f"token id {bad} outside the vocabulary 0..{self.vocab_size - 1}")
+                bad = next((t for t in e.tokens if not (isinstance(t, (int, np.integer)) and 0 <= int(t) < self.vocab_size)), None)
+                raise ValueError(f"token id {bad!r} outside the vocabulary 0..{self.vocab_size - 1}")
+            arrays.append(ids)
             for w in e.want:
                 if not (0 <= int(w) < n):
                     raise ValueError(f"wanted place {w} outside the entry's {n} tokens")
+        return arrays
 
     def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, widths: Optional[List[int]] = None,
-                      static: Optional[torch.Tensor] = None):
+                      static: Optional[torch.Tensor] = None, token_arrays: Optional[List[np.ndarray]] = None):
         """Host arrays -> one int32 device buffer -> the views a step needs.
 
         With ``pad_to`` the batch is padded to that many requests of one token each; a padding row holds
@@ -141,7 +147,9 @@ class Engine:
         q_lens_p = q_lens + [1] * pad
         q_start = np.zeros(r + 1, dtype=np.int32)
         np.cumsum(q_lens_p, out=q_start[1:])
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries] + [np.zeros(pad, np.int32)])
+        if token_arrays is None:
+            token_arrays = [np.asarray(e.tokens, dtype=np.int32) for e in entries]
+        token_ids = np.concatenate(list(token_arrays) + [np.zeros(pad, np.int32)])
         positions = np.concatenate([np.arange(e.request.length, e.request.length + n, dtype=np.int32)
                                     for e, n in zip(entries, q_lens)] + [np.zeros(pad, np.int32)])
         req_index = np.repeat(np.arange(r, dtype=np.int32), q_lens_p)
@@ -206,7 +214,7 @@ class Engine:
         ``device_tokens`` (int32 on the device, one per entry, every entry of one token): the token ids are
         taken from there instead of from the entries, whose ids are placeholders. A caller that has sampled
         the previous step's tokens on the device can so launch the next step before it has read them."""
-        self._check(entries)
+        token_arrays = self._check(entries)
         if device_tokens is not None:
             if any(len(e.tokens) != 1 for e in entries) or device_tokens.numel() < len(entries) \
                     or device_tokens.dtype != torch.int32 or device_tokens.device != self.device:
@@ -221,7 +229,7 @@ class Engine:
             logits = self._graphs.step(entries, borrow=borrow_logits, device_tokens=device_tokens)
             m_tokens = len(entries)
         else:
-            ctx, want_rows, _ = self.build_context(entries)
+            ctx, want_rows, _ = self.build_context(entries, token_arrays=token_arrays)
             if device_tokens is not None:
                 ctx.token_ids[:len(entries)].copy_(device_tokens[:len(entries)], non_blocking=True)
             caches = self.storage.layer_caches(ctx.block_tables)

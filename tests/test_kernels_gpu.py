@@ -599,6 +599,73 @@ def test_attention_decode_at_benchmark_lengths(K, heads, kv_heads, hd, page, n_r
     assert_close(got, ref, dtype, "decode attention at benchmark lengths")
 
 
+@pytest.mark.parametrize("heads,kv_heads,hd,rot,page,hidden,fused", [
+    (14, 2, 64, 64, 16, 896, True), (12, 2, 128, 128, 16, 1536, True), (3, 1, 64, 0, 8, 72, True), (5, 5, 128, 128, 32, 200, True),
+    (7, 1, 64, 32, 16, 128, False), (3, 3, 48, 48, 8, 160, False)])
+def test_qkv_projection_of_a_prompt_portion_with_rotation_and_cache_write(K, heads, kv_heads, hd, rot, page, hidden, fused):
+    """A prompt portion's q/k/v product on the tcgen05 kernel whose epilogue adds the bias, rotates whole heads and
+    writes keys and values into the pages: the rows against float64, the pages against the rows. Several requests,
+    portions that start inside a page and inside a tile of 128 tokens, a request of one token between them, a row
+    without a page; heads of 64 and 128, no rotation at all. Shapes the fused form does not take (half-rotated heads,
+    heads of 48) run the product and the rotation kernel and must give the same."""
+    from nanoinfer_b200.parts.position import rotary_tables
+    dtype = torch.bfloat16
+    q_lens, before = [150, 1, 70, 2, 130], [0, 63, 61, 300, 17]
+    m = sum(q_lens)
+    ctx, bt = make_paged_batch(q_lens, before, page, 800 // page * 2, "cuda", seed=18)
+    pages = int(bt.max().item()) + 1
+    shape = (pages, kv_heads, page, hd)
+    rotary = None
+    if rot:
+        cos, sin = rotary_tables(600, rot, 10000.0)
+        rotary = (cos.cuda(), sin.cuda(), rot)
+    n = (heads + 2 * kv_heads) * hd
+    w = rnd((n, hidden), dtype, 221, scale=0.05)
+    bias = rnd((n,), torch.float32, 222)
+    h = rnd((m, hidden), dtype, 224, scale=1.0)
+    kp, vp = torch.zeros(shape, dtype=dtype, device="cuda"), torch.zeros(shape, dtype=dtype, device="cuda")
+    qkv = torch.empty(m, n, dtype=dtype, device="cuda")
+    before_launches = K.launches
+    K.qkv_project(h, w, bias, qkv, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, kp, vp, True)
+    assert K.launches == before_launches + (1 if fused else 2)
+    assert K.gemm_tc_error() == 0
+    ref = (h.double() @ w.double().t() + bias.double()).view(m, heads + 2 * kv_heads, hd)
+    if rot:
+        half = rot // 2
+        c = rotary[0][ctx.positions.long()].double()[:, None, :]
+        sn = rotary[1][ctx.positions.long()].double()[:, None, :]
+        qk = ref[:, :heads + kv_heads]
+        x1, x2 = qk[..., :half].clone(), qk[..., half:rot].clone()
+        qk[..., :half] = x1 * c - x2 * sn
+        qk[..., half:rot] = x2 * c + x1 * sn
+    assert_close(qkv, ref.view(m, n), dtype, "q/k/v rows of a portion")
+    kr, vr = torch.zeros_like(kp), torch.zeros_like(vp)
+    pos = ctx.positions.long()
+    page_of = bt[ctx.req_index.long(), pos // page].long()
+    got = qkv.view(m, heads + 2 * kv_heads, hd)
+    kr[page_of, :, pos % page, :] = got[:, heads:heads + kv_heads]
+    vr[page_of, :, pos % page, :] = got[:, heads + kv_heads:]
+    assert torch.equal(kp, kr) and torch.equal(vp, vr)
+    # without writing, pages stay as they are; a request without pages (-1 in its table) writes nothing
+    kp2 = torch.zeros_like(kp)
+    q2 = torch.empty_like(qkv)
+    K.qkv_project(h, w, bias, q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt, page, kp2, kp2, False)
+    assert torch.equal(q2, qkv) and not kp2.any()
+    bt_pad = bt.clone()
+    bt_pad[2] = -1
+    kp3, vp3 = torch.zeros_like(kp), torch.zeros_like(vp)
+    K.qkv_project(h, w, bias, q2, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary, bt_pad, page, kp3, vp3, True)
+    rows2 = (ctx.req_index == 2)
+    keep = torch.ones(pages, dtype=torch.bool, device="cuda")
+    keep[page_of[rows2]] = False
+    assert torch.equal(kp3[keep], kr[keep]) and not kp3[~keep].any() and torch.equal(q2, qkv)
+    # the same rows from the product followed by the rotation kernel (one more rounding: to bfloat16 before the rotation)
+    two = torch.empty_like(qkv)
+    K.with_options(fuse_qkv=False).qkv_project(h, w, bias, two, heads, kv_heads, hd, ctx.positions, ctx.req_index, rotary,
+                                               bt, page, torch.zeros_like(kp), torch.zeros_like(vp), True)
+    assert_close(two, ref.view(m, n), dtype, "q/k/v rows, product then rotation")
+
+
 @pytest.mark.parametrize("with_norm", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,hd,rot,page,hidden", [(14, 2, 64, 64, 16, 896), (6, 1, 32, 32, 8, 192), (3, 3, 48, 48, 8, 160),
                                                                (16, 1, 128, 64, 16, 1536), (4, 2, 16, 16, 16, 64), (28, 4, 128, 128, 32, 3584),
