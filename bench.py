@@ -344,7 +344,7 @@ def run_ours(args) -> dict:
     pre_ms = []
     for i in range((3 + 7) if args.only != "decode" else 0):
         rc = engine.open(f"p{i}")
-        ids = rng.integers(0, vocab, t_pre).tolist()
+        ids = rng.integers(0, vocab, t_pre).astype(np.int32)        # host memory, as a tokenizer's array would be
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()

@@ -61,9 +61,11 @@ class Engine:
         self._stage = None          # pinned host buffer of the step's int32 inputs
         self._stage_event = None
         self._graphs = None
+        self._portion_graphs = None
         if engine_config.cuda_graphs and self.device.type == "cuda" and self.model.graph_safe():
-            from .graphs import DecodeGraphs
+            from .graphs import DecodeGraphs, PortionGraphs
             self._graphs = DecodeGraphs(self)
+            self._portion_graphs = PortionGraphs(self)
 
     # ---- requests -------------------------------------------------------------------------
     def open(self, request_id) -> RequestCache:
@@ -80,11 +82,12 @@ class Engine:
         self.cache.truncate(rc, new_length)
 
     def reset_graphs(self) -> None:
-        """Forget the captured decode graphs; steps capture them anew (after a change of what kernels do at launch)."""
+        """Forget the captured graphs; steps capture them anew (after a change of what kernels do at launch)."""
         if self._graphs is not None:
-            from .graphs import DecodeGraphs
-            self._old_graphs = getattr(self, "_old_graphs", []) + [self._graphs]     # their memory pool stays alive
+            from .graphs import DecodeGraphs, PortionGraphs
+            self._old_graphs = getattr(self, "_old_graphs", []) + [self._graphs, self._portion_graphs]     # their memory pools stay alive
             self._graphs = DecodeGraphs(self)
+            self._portion_graphs = PortionGraphs(self)
 
     def check_device(self) -> None:
         """Raises if a kernel's bounded wait ran out since the last check (the kernel then returned without
@@ -229,12 +232,16 @@ class Engine:
             logits = self._graphs.step(entries, borrow=borrow_logits, device_tokens=device_tokens)
             m_tokens = len(entries)
         else:
-            ctx, want_rows, _ = self.build_context(entries, token_arrays=token_arrays)
-            if device_tokens is not None:
-                ctx.token_ids[:len(entries)].copy_(device_tokens[:len(entries)], non_blocking=True)
-            caches = self.storage.layer_caches(ctx.block_tables)
-            logits = self.model.forward(ctx, caches, want_rows)
-            m_tokens = ctx.num_tokens
+            replayed = False
+            if self._portion_graphs is not None and device_tokens is None:
+                replayed, logits = self._portion_graphs.step(entries, token_arrays, borrow_logits)
+            if not replayed:
+                ctx, want_rows, _ = self.build_context(entries, token_arrays=token_arrays)
+                if device_tokens is not None:
+                    ctx.token_ids[:len(entries)].copy_(device_tokens[:len(entries)], non_blocking=True)
+                caches = self.storage.layer_caches(ctx.block_tables)
+                logits = self.model.forward(ctx, caches, want_rows)
+            m_tokens = sum(n for _, n in demands)
         for rc, n in demands:
             self.cache.commit(rc, n)
         self.steps_run += 1

@@ -1,4 +1,6 @@
-"""CUDA graphs for steps in which every request brings exactly one token (pure decode).
+"""CUDA graphs for the two kinds of step whose launches repeat: pure decode, and prompt portions of a recurring shape.
+
+DecodeGraphs: steps in which every request brings exactly one token.
 
 Such a step launches a fixed sequence of kernels whose sizes depend only on the number of requests
 and, for the split of long contexts, on the context length. The sequence is captured once per
@@ -198,5 +200,93 @@ class DecodeGraphs:
         torch.cuda.current_stream().wait_stream(self.stream)
         cap = _Captured(graph, static, logits, ops.launches - before, _InputMirror(rb, widths, eng.device, eng.storage.pad_slot))
         assert cap.mirror.size == size
+        self.captured[key] = cap
+        return cap
+
+
+class PortionGraphs:
+    """CUDA graphs for steps made of prompt portions only (every entry brings at least two tokens).
+
+    A long prompt is cut into portions of the scheduler's token budget, so the same shape (the entries' token
+    counts, the number of wanted rows, the block tables' widths rounded up to a power of two) comes again and
+    again. Such a step is some two hundred launches whose host side costs about as much as a tenth of the
+    device's work; captured once, the second time its shape is seen, it is one launch. Everything a kernel
+    reads of the step (ids, positions, lengths, wanted rows, block tables) lies in a device buffer of fixed
+    address that one copy refreshes; the launch geometry depends on the shape alone. A shape seen once is
+    never captured, and at most ``capacity`` shapes are kept."""
+
+    def __init__(self, engine, min_tokens: int = 256, capacity: int = 8):
+        self._engine = weakref.ref(engine)
+        self.min_tokens, self.capacity = min_tokens, capacity
+        self.captured: Dict[tuple, _Captured] = {}
+        self.seen: Dict[tuple, int] = {}
+        self.pool = None
+        self.stream = None
+
+    def _key(self, entries):
+        eng = self._engine()
+        q_lens = tuple(len(e.tokens) for e in entries)
+        if min(q_lens) < 2 or sum(q_lens) < self.min_tokens:
+            return None
+        widths = tuple(_bucket(max(1, max(len(e.request.tables[g]) for e in entries))) for g in range(len(eng.cache.groups)))
+        n_want = sum(len(e.want) for e in entries)
+        all_rows = n_want == sum(q_lens) and all(list(e.want) == list(range(len(e.tokens))) for e in entries)
+        return q_lens, widths, n_want, all_rows
+
+    def step(self, entries, token_arrays, borrow: bool):
+        """(True, logits) if the step ran from a graph, (False, None) if the caller has to run it."""
+        eng = self._engine()
+        key = self._key(entries)
+        if key is None or getattr(eng.rt.ops, "_op_events", None) is not None:     # (launches that are being timed one by one run eagerly)
+            return False, None
+        cap = self.captured.get(key)
+        if cap is None:
+            if len(self.seen) > 4096:
+                self.seen.clear()
+            self.seen[key] = self.seen.get(key, 0) + 1
+            if self.seen[key] < 2 or len(self.captured) >= self.capacity:
+                return False, None          # the first step of a shape runs eagerly (and sets up what kernels set up on first use)
+            cap = self._capture(key, entries, token_arrays)
+        else:
+            eng.build_context(entries, widths=list(key[1]), static=cap.inputs, token_arrays=token_arrays)
+        cap.graph.replay()
+        eng.graph_launches += cap.launches
+        if cap.logits is None:
+            return True, None
+        return True, (cap.logits if borrow else cap.logits.clone())
+
+    def _capture(self, key, entries, token_arrays) -> _Captured:
+        eng = self._engine()
+        widths = list(key[1])
+        probe, _, _ = eng.build_context(entries, widths=widths, token_arrays=token_arrays)
+        size = sum(v.numel() for v in (probe.token_ids, probe.positions, probe.req_index, probe.q_start,
+                                       probe.ctx_lens, probe.state_slots)) + key[2] \
+            + sum(t.numel() for t in probe.block_tables.values())
+        static = torch.empty(size, dtype=torch.int32, device=eng.device)
+        ctx, want_rows, _ = eng.build_context(entries, widths=widths, static=static, token_arrays=token_arrays)
+        caches = eng.storage.layer_caches(ctx.block_tables)
+        ops = eng.rt.ops
+        torch.cuda.synchronize()
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        gc_was_on = gc.isenabled()      # see DecodeGraphs._capture: nothing may be freed while a stream captures
+        gc.disable()
+        if self.stream is None:
+            self.stream = torch.cuda.Stream()
+        self.stream.wait_stream(torch.cuda.current_stream())
+        try:
+            with torch.cuda.stream(self.stream):
+                graph.capture_begin(pool=self.pool)
+                try:
+                    logits = eng.model.forward(ctx, caches, want_rows)
+                finally:
+                    graph.capture_end()
+        finally:
+            if gc_was_on:
+                gc.enable()
+        torch.cuda.current_stream().wait_stream(self.stream)
+        cap = _Captured(graph, static, logits, ops.launches - before)
         self.captured[key] = cap
         return cap

@@ -449,3 +449,41 @@ def test_real_layer_widths(tmp_path, dtype, shape):
     rows.append(eng.step([StepEntry(rc, [ids[149]], [0])]).clone())
     assert_close(torch.cat(rows), want, tdt(dtype), "real widths, cut")
     eng.close(rc)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_portions_of_a_recurring_shape_replay_a_captured_graph(model_dirs, dtype):
+    """A step of prompt portions whose shape has been seen before is captured once and replayed from then on: the
+    first step of a shape runs eagerly, the second captures, the third only replays. Different requests, ids,
+    pages and wanted rows each time (those are data the graph reads from its input buffer); every row against the
+    plain implementation; a step of another shape in between runs eagerly and disturbs nothing."""
+    from nanoinfer_b200.engine import StepEntry
+    d, page = model_dirs["C"]
+    plain = PlainModel(d)
+    eng = engine_for(d, page, dtype, num_pages=200, max_batch=4)
+    assert eng._portion_graphs is not None
+    eng._portion_graphs.min_tokens = 64
+    g = torch.Generator().manual_seed(31)
+    vocab = plain.cfg["vocab"]
+    shapes = [(70, 30), (70, 30), (33,), (70, 30), (70, 30)]
+    wants = [([0, 69], [29]), ([5, 17], [0]), ([32],), ([68, 69], [1]), ([1, 2], [3])]
+    for turn, (shape, want) in enumerate(zip(shapes, wants)):
+        prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in shape]
+        reqs = [eng.open(f"t{turn}r{i}") for i in range(len(shape))]
+        replayed_before = eng.graph_launches
+        got = eng.step([StepEntry(rc, p, w) for rc, p, w in zip(reqs, prompts, want)])
+        assert (eng.graph_launches > replayed_before) == (turn in (1, 3, 4)), "which steps ran from the graph"
+        ref = torch.cat([plain.logits(p)[list(w)] for p, w in zip(prompts, want)])
+        assert_close(got, ref, tdt(dtype), f"portion step {turn}")
+        # and the cache it left: one more token for each request, decoded from the pages
+        nxt = [int(torch.randint(0, vocab, (1,), generator=g)) for _ in shape]
+        got = eng.step([StepEntry(rc, [t], [0]) for rc, t in zip(reqs, nxt)])
+        ref = torch.stack([plain.logits(p + [t])[-1] for p, t in zip(prompts, nxt)])
+        assert_close(got, ref, tdt(dtype), f"token after portion step {turn}")
+        for rc in reqs:
+            eng.close(rc)
+        if turn == 0:
+            assert not eng._portion_graphs.captured
+        if turn in (1, 3, 4):
+            assert len(eng._portion_graphs.captured) == 1
+    eng.cache.check()
