@@ -30,7 +30,7 @@ using namespace nibt;
 namespace {
 
 constexpr int ROWS = 128;        // rows of a tile (UMMA M): TMEM lanes
-constexpr int THREADS = 256;     // TMA warp, MMA warp, two idle warps; four softmax warps (a thread per row)
+constexpr int THREADS = 384;     // TMA warp, MMA warp, two idle warps; eight softmax warps (two threads per row, half of a block's keys each)
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ int g_attn_error = 0;
@@ -68,7 +68,8 @@ template <int HD> struct Cfg {
     static constexpr int STAGES = 2;
     static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + STAGES * KV_BYTES, OFF_P = OFF_V + STAGES * KV_BYTES;
     static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
-    static constexpr int SMEM = OFF_BAR + 256 + 1024;
+    static constexpr int OFF_XCH = OFF_BAR + 256;             // what the two threads of a row tell each other: [3][2][128] floats
+    static constexpr int SMEM = OFF_XCH + 3 * 2 * 128 * 4 + 1024;
     static constexpr int COL_S = 0, COL_O = 2 * KEYS;         // two buffers of scores, then the output
     static constexpr int TMEM_COLS = (2 * KEYS + HD) <= 256 ? 256 : 512;
 };
@@ -99,9 +100,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // One barrier per BUFFER (of scores in tensor memory, of probabilities in shared memory): a buffer's next phase
     // cannot complete before its last one was seen, which a single barrier shared by both buffers would not ensure.
     unsigned long long* s_full = bars + 9;        // [2] the scores of a block are in buffer b
-    unsigned long long* p_full = bars + 11;       // [2] 128 arrivals: the probabilities of a block are in buffer b
+    unsigned long long* p_full = bars + 11;       // [2] 256 arrivals: the probabilities of a block are in buffer b
     unsigned long long* o_done = bars + 13;       // [2] P.V of the block whose probabilities were in buffer b has been added
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
+    unsigned long long* pair_bar = bars + 16;     // [4] the two softmax warps of a lane quadrant meet here (one arrival each)
     __shared__ volatile int s_failed;
 
     pdl_launch_dependents();
@@ -133,9 +135,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
             mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 128);
+            mbar_init(&p_full[i], 256);
             mbar_init(&o_done[i], 1);
         }
+        for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -254,18 +257,32 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         if (!ok && !s_failed) { atomicCAS(&g_attn_error, 0, (3 << 16) | (int)(blockIdx.x & 0xffff)); s_failed = 1; }
     } else if (warp >= 4) {
-        // ---------------- softmax and output: a thread owns a row (a warp may read the TMEM lanes 32*(warp%4)...).
-        // No thread needs another's values. Rows past the tile's last (the tile holds a whole number of tokens) see
-        // what the last row sees; nothing of them is stored.
-        const int quad = warp & 3, row = quad * 32 + lane;
+        // ---------------- softmax and output: two threads own a row, in warps that may read the same TMEM lanes
+        // (32*(warp%4)...): each takes half of a block's keys and half of the output row's columns. They tell each other
+        // the maximum of their halves (and at the end the sum) through shared memory, meeting at a barrier of their two
+        // warps. Rows past the tile's last (the tile holds a whole number of tokens) see what the last row sees; nothing
+        // of them is stored.
+        constexpr int HK = KEYS / 2;                      // keys of a block per thread
+        const int quad = warp & 3, half = (warp - 4) >> 2, row = quad * 32 + lane;
         const unsigned lane_addr = tmem_base + ((unsigned)(quad * 32) << 16);
-        const unsigned o_addr = lane_addr + C::COL_O;
+        const unsigned o_addr = lane_addr + C::COL_O + half * (HD / 2);
+        float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);        // [3][2][128]
+        // the meeting of the two warps of a quadrant: an mbarrier, so that the wait is bounded like every other (a warp
+        // that has given up never arrives, and its partner then gives up too instead of waiting for ever)
+        unsigned pair_phase = 0;
+        auto pair_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pair_bar[quad]);
+            const bool met = mbar_spin(&pair_bar[quad], pair_phase & 1);
+            ++pair_phase;
+            return __all_sync(0xffffffffu, met);
+        };
         const bool live = row < n_tok * n_rep;
         const int ti = min(row / n_rep, n_tok - 1), head = kvh * n_rep + (row % n_rep);
         const int hi = pos0 + ti;
         const int lo = window > 0 ? max(0, hi - window + 1) : 0;
         const float scale2 = scale * LOG2E;
-        float m_cur = -INFINITY, l_run = 0.f;       // the maximum that the exponents refer to, and the sum
+        float m_cur = -INFINITY, l_run = 0.f;       // the maximum that the exponents refer to, and this thread's part of the sum
         bool ok = true;
         for (int j = 0; j < n_blk && ok; ++j) {
             const int b = j & 1;
@@ -276,29 +293,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int key0 = (b_begin + j) * KEYS;
             // the same branch for the whole warp: a warp that took both would do the work twice
             const bool all_visible = __all_sync(0xffffffffu, key0 >= lo && key0 + KEYS - 1 <= hi);
-            // the row's scores of the block: all loads are issued, then waited for once (a load from tensor memory takes
-            // hundreds of cycles). Four maxima side by side, so that no instruction waits for the one before it.
-            const unsigned s_addr = lane_addr + C::COL_S + b * KEYS;
-            unsigned raw[KEYS / 32][32];
+            // this thread's scores of the block: all loads are issued, then waited for once (a load from tensor memory
+            // takes hundreds of cycles). Four maxima side by side, so that no instruction waits for the one before it.
+            const unsigned s_addr = lane_addr + C::COL_S + b * KEYS + half * HK;
+            unsigned raw[HK / 32][32];
 #pragma unroll
-            for (int c = 0; c < KEYS / 32; ++c) tmem_ld32_async(s_addr + c * 32, raw[c]);
+            for (int c = 0; c < HK / 32; ++c) tmem_ld32_async(s_addr + c * 32, raw[c]);
             tmem_wait_ld();
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < KEYS / 32; ++c) {
+            for (int c = 0; c < HK / 32; ++c) {
                 if (all_visible) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[c][i]));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int key = key0 + c * 32 + i;
+                        const int key = key0 + half * HK + c * 32 + i;
                         if (!(key >= lo && key <= hi)) raw[c][i] = 0xff800000u;      // -inf: its probability will be 0
                         mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[c][i]));
                     }
                 }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;      // scale2 > 0
+            // the row's maximum over both halves (the slot of block j is written again at block j + 2, after the barrier
+            // of block j + 1, which the other thread reaches only when it has read this one)
+            float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            xch[(b * 2 + half) * 128 + row] = mine;
+            ok = pair_sync();
+            if (!ok) break;
+            const float mx = fmaxf(mine, xch[(b * 2 + (half ^ 1)) * 128 + row]) * scale2;      // scale2 > 0
             float corr = 1.f;
             bool grow = false;
             if (m_cur == -INFINITY) {
@@ -311,13 +334,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float m_use = (m_cur == -INFINITY) ? 0.f : m_cur;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                // rare: the output row is rescaled in tensor memory, once P.V of the block before has been added
+                // rare: the output row is rescaled in tensor memory (each thread its half of the columns), once P.V of
+                // the block before has been added. Both threads of a row decide alike: they see the same maxima.
                 ok = mbar_spin(&o_done[(j - 1) & 1], ((j - 1) >> 1) & 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < HD / 64; ++c) {
                     unsigned ov[32];
                     tmem_ld32_async(o_addr + c * 32, ov);
                     tmem_wait_ld();
@@ -337,7 +361,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             unsigned char* p_row = smem + C::OFF_P + b * C::P_BYTES + (row >> 3) * 1024 + (row & 7) * 128;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < KEYS / 32; ++c) {
+            for (int c = 0; c < HK / 32; ++c) {
                 unsigned pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -346,10 +370,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     sum4[(i >> 1) & 3] += p0 + p1;
                     pk[i >> 1] = pack2(p0, p1);
                 }
-                unsigned char* sub = p_row + (c >> 1) * C::SUBTILE;        // 64 keys per sub-tile
+                const int cg = half * (HK / 32) + c;                        // the chunk of 32 keys within the block
+                unsigned char* sub = p_row + (cg >> 1) * C::SUBTILE;       // 64 keys per sub-tile
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c & 1) << 2) + q4;                  // 16-byte chunk within the 128-byte row
+                    const int chunk = ((cg & 1) << 2) + q4;                 // 16-byte chunk within the 128-byte row
                     *reinterpret_cast<uint4*>(sub + ((chunk ^ (row & 7)) << 4)) =
                         make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
                 }
@@ -364,14 +389,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ok = mbar_spin(&o_done[(n_blk - 1) & 1], ((n_blk - 1) >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
         }
+        if (ok) {
+            // the row's sum: both parts, added in the same order by both threads
+            xch[(4 + half) * 128 + row] = l_run;
+            ok = pair_sync();
+        }
         if (!ok) {
             if (lane == 0 && !s_failed) { atomicCAS(&g_attn_error, 0, (4 << 16) | (int)(blockIdx.x & 0xffff)); s_failed = 1; }
         } else {
             tc_fence_after();
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            __nv_bfloat16* orow = out + ((size_t)(row_begin + tok0 + ti) * heads + head) * HD;
+            const float l_all = xch[4 * 128 + row] + xch[5 * 128 + row];
+            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+            __nv_bfloat16* orow = out + ((size_t)(row_begin + tok0 + ti) * heads + head) * HD + half * (HD / 2);
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
+            for (int c = 0; c < HD / 64; ++c) {
                 unsigned ov[32];
                 tmem_ld32_async(o_addr + c * 32, ov);
                 tmem_wait_ld();
