@@ -113,7 +113,8 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
 
     // The q/k/v epilogue's view of the thread's tokens (2t, 2t+1 of every tile): position, page, cos and sin of the
     // thread's rotated dimension. They are inputs of the step, not results of its kernels: read before the wait.
-    constexpr int QN = (EPI == EPI_QKV) ? NT : 1;
+    constexpr bool QSPREAD = KSPLIT > 1 && NT > 1;        // (the q/k/v form never splits K over CTAs: tile n is warp n's)
+    constexpr int QN = (EPI == EPI_QKV && !QSPREAD) ? NT : 1;
     int q_ra = 0, q_rb = 0, q_pos[QN][2], q_page[QN][2];
     float q_cs[QN][2], q_sn[QN][2], q_bias[2] = {0.f, 0.f};
     bool q_rot = false;
@@ -121,13 +122,13 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
         qkv_group_rows(qe, group, q_ra, q_rb);
         const int hs = q_ra / qe.head_dim, d = q_ra - hs * qe.head_dim + g;
         q_rot = hs < qe.heads + qe.kv_heads && q_rb - q_ra == (qe.rot >> 1) && qe.rot > 0 && d < (qe.rot >> 1);
-        if (KSPLIT == 1 || warp == 0) {
+        if (KSPLIT == 1 || (QSPREAD ? warp < NT : warp == 0)) {
             if (bias) { q_bias[0] = __ldg(bias + q_ra + g); q_bias[1] = __ldg(bias + q_rb + g); }
 #pragma unroll
             for (int n = 0; n < QN; ++n)
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
-                    const int tok = n * 8 + 2 * t + j;
+                    const int tok = (QSPREAD ? warp : n) * 8 + 2 * t + j;
                     q_pos[n][j] = 0; q_page[n][j] = -1; q_cs[n][j] = 1.f; q_sn[n][j] = 0.f;
                     if (tok < tokens) {
                         const int pos = __ldg(qe.positions + tok);
@@ -247,6 +248,11 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
         }
     }
 
+    // Who finishes what. With K split among the warps of a CTA, each token tile of 8 is summed and finished by a warp
+    // of its own (tile n by warp n: there are at most as many tiles as warps), so that 64 tokens are not one warp's
+    // work; with K split over CTAs as well, warp 0 of the CTA that arrives last does all of it.
+    constexpr bool SPREAD = KSPLIT > 1 && NT > 1;
+    const bool spread = SPREAD && cross == 1;
     if (KSPLIT > 1) {
         // the warps of the CTA, in warp order
 #pragma unroll
@@ -256,7 +262,9 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
 #pragma unroll
                 for (int e = 0; e < E; ++e) part[(((warp * ACCS + a) * NT + n) * E + e) * 32 + lane] = acc[a][n][e];
         __syncthreads();
-        if (warp != 0) {
+        if (spread) {
+            if (warp >= NT) return;
+        } else if (warp != 0) {
             if (cross == 1) return;
         } else {
 #pragma unroll
@@ -305,27 +313,33 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
     }
     if (f0 >= n_out) return;
 
-    if (EPI == EPI_QKV) {
-        // the thread's rows q_ra + g (elements 0, 1) and q_rb + g (elements 2, 3) of tokens n*8 + 2t and + 1
-        const int hs = q_ra / qe.head_dim;
-        const int d_lo = q_ra - hs * qe.head_dim + g, d_hi = q_rb - hs * qe.head_dim + g;
-        const bool is_v = hs >= qe.heads + qe.kv_heads;
-        const int kvh = hs - qe.heads - (is_v ? qe.kv_heads : 0);
-        __nv_bfloat16* pages = is_v ? qe.v_pages : qe.k_pages;
+    // ---- one token tile: v[a][0..3] the sums of accumulator a (element e: feature f0 + g + 8*(e/2), token n*8 + 2t + (e&1)),
+    // v[0][4] (NORM) the sum of squares, token n*8 + j in the lanes of quad j. qi: the tile's slot in the q/k/v arrays.
+    const float bias0 = (EPI != EPI_QKV && bias && f0 + g < n_out) ? bias[f0 + g] : 0.f;
+    const float bias1 = (EPI != EPI_QKV && bias && f0 + g + 8 < n_out) ? bias[f0 + g + 8] : 0.f;
+    auto emit = [&](const float (&v)[ACCS][E], const int n, const int qi) {
+        float scale2[2] = {1.f, 1.f};                    // 1/rms of the thread's two tokens
+        if (NORM) {
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
+            for (int j = 0; j < 2; ++j) {
+                const float ss = __shfl_sync(0xffffffffu, v[0][E - 1], (2 * t + j) * 4);
+                scale2[j] = 1.0f / sqrtf(ss / (float)k_dim + eps);
+            }
+        }
+        if (EPI == EPI_QKV) {
+            // the thread's rows q_ra + g (elements 0, 1) and q_rb + g (elements 2, 3) of tokens n*8 + 2t and + 1
+            const int hs = q_ra / qe.head_dim;
+            const int d_lo = q_ra - hs * qe.head_dim + g, d_hi = q_rb - hs * qe.head_dim + g;
+            const bool is_v = hs >= qe.heads + qe.kv_heads;
+            const int kvh = hs - qe.heads - (is_v ? qe.kv_heads : 0);
+            __nv_bfloat16* pages = is_v ? qe.v_pages : qe.k_pages;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int tok = n * 8 + 2 * t + j;
-                float scale = 1.f;
-                if (NORM) {
-                    const float ss = __shfl_sync(0xffffffffu, acc[0][n][E - 1], (2 * t + j) * 4);
-                    scale = 1.0f / sqrtf(ss / (float)k_dim + eps);
-                }
                 if (tok >= tokens) continue;
-                float lo = acc[0][n][j] * scale + q_bias[0], hi = acc[0][n][2 + j] * scale + q_bias[1];
+                float lo = v[0][j] * scale2[j] + q_bias[0], hi = v[0][2 + j] * scale2[j] + q_bias[1];
                 if (q_rot) {
-                    const float c = q_cs[EPI == EPI_QKV ? n : 0][j], sn = q_sn[EPI == EPI_QKV ? n : 0][j];
+                    const float c = q_cs[qi][j], sn = q_sn[qi][j];
                     const float a = lo * c - hi * sn, b = hi * c + lo * sn;
                     lo = a;
                     hi = b;
@@ -334,49 +348,61 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
                 __nv_bfloat16* row = (__nv_bfloat16*)out + (size_t)tok * ldo;
                 row[q_ra + g] = blo;
                 row[q_rb + g] = bhi;
-                const int page = q_page[EPI == EPI_QKV ? n : 0][j];
+                const int page = q_page[qi][j];
                 if (hs >= qe.heads && qe.writes && page >= 0 && page < qe.num_pages) {
-                    __nv_bfloat16* dst = pages + (((size_t)page * qe.kv_heads + kvh) * qe.page_size + q_pos[EPI == EPI_QKV ? n : 0][j] % qe.page_size) * qe.head_dim;
+                    __nv_bfloat16* dst = pages + (((size_t)page * qe.kv_heads + kvh) * qe.page_size + q_pos[qi][j] % qe.page_size) * qe.head_dim;
                     dst[d_lo] = blo;
                     dst[d_hi] = bhi;
                 }
             }
-        if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_SMALLM, EPI, 2);
-        return;
-    }
-    // accumulator element e of tile n: feature f0 + g + 8*(e/2), token n*8 + 2t + (e&1);
-    // the sum of squares of token n*8 + j sits in the lanes of quad j
-    const float bias0 = (bias && f0 + g < n_out) ? bias[f0 + g] : 0.f;
-    const float bias1 = (bias && f0 + g + 8 < n_out) ? bias[f0 + g + 8] : 0.f;
-    float res[NT][4];
-    if (EPI == EPI_ADD) {
-        // the residual stream is read-modify-written: all loads first, so that they wait together
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
+            return;
+        }
+        float res[4] = {0.f, 0.f, 0.f, 0.f};
+        if (EPI == EPI_ADD) {
+            // the residual stream is read-modify-written: all loads first, so that they wait together
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int f = f0 + g + 8 * (e >> 1), tok = n * 8 + 2 * t + (e & 1);
-                res[n][e] = (f < n_out && tok < tokens) ? __ldcg((const float*)out + (size_t)tok * ldo + f) : 0.f;
+                if (f < n_out && tok < tokens) res[e] = __ldcg((const float*)out + (size_t)tok * ldo + f);
             }
-    }
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int f = f0 + g + 8 * (e >> 1), tok = n * 8 + 2 * t + (e & 1);
-            float scale = 1.f;
-            if (NORM) {
-                const float ss = __shfl_sync(0xffffffffu, acc[0][n][E - 1], (2 * t + (e & 1)) * 4);
-                scale = 1.0f / sqrtf(ss / (float)k_dim + eps);
-            }
             if (f >= n_out || tok >= tokens) continue;
-            const float x = acc[0][n][e] * scale + ((e >> 1) ? bias1 : bias0);
+            const float x = v[0][e] * scale2[e & 1] + ((e >> 1) ? bias1 : bias0);
             const size_t o = (size_t)tok * ldo + f;
             if (EPI == EPI_STORE) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(x);
-            else if (EPI == EPI_ADD) ((float*)out)[o] = res[n][e] + x;
+            else if (EPI == EPI_ADD) ((float*)out)[o] = res[e] + x;
             else if (EPI == EPI_F32) ((float*)out)[o] = x;
-            else if (EPI == EPI_SWIGLU) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(__fdividef(x, 1.0f + __expf(-x)) * (acc[ACCS - 1][n][e] * scale));
+            else if (EPI == EPI_SWIGLU) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(__fdividef(x, 1.0f + __expf(-x)) * (v[ACCS - 1][e] * scale2[e & 1]));
         }
+    };
+
+    if (spread) {
+        // this warp's tile: the eight warps' parts, in warp order
+        float v[ACCS][E];
+#pragma unroll
+        for (int a = 0; a < ACCS; ++a)
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < KSPLIT; ++w) s += part[(((w * ACCS + a) * NT + warp) * E + e) * 32 + lane];
+                v[a][e] = s;
+            }
+        emit(v, warp, 0);
+    } else {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            float v[ACCS][E];
+#pragma unroll
+            for (int a = 0; a < ACCS; ++a)
+#pragma unroll
+                for (int e = 0; e < E; ++e) v[a][e] = acc[a][n][e];
+            emit(v, n, SPREAD ? 0 : n);
+        }
+    }
     if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_SMALLM, EPI, 2);
 }
 
@@ -411,7 +437,7 @@ int launch_epi(int epi, const Args& a, cudaStream_t stream) {
         case EPI_F32: return launch_one<NT, KSPLIT, EPI_F32, NORM>(a, stream);
         case EPI_SWIGLU: return launch_one<NT, KSPLIT, EPI_SWIGLU, NORM>(a, stream);
         case EPI_QKV:
-            if constexpr (KSPLIT > 1 && NT <= 2) return launch_one<NT, KSPLIT, EPI_QKV, NORM>(a, stream);
+            if constexpr (KSPLIT > 1) return launch_one<NT, KSPLIT, EPI_QKV, NORM>(a, stream);
             break;
     }
     nib_set_error("gemm (small M): unknown epilogue %d", epi);
@@ -486,10 +512,10 @@ NIB_API int nib_gemm_smallm(const void* A, const void* W, const float* bias, voi
     return launch_tokens<false>(ksplit, epi, a, stream);
 }
 
-// 1 if nib_gemm_smallm_qkv takes these sizes: up to 16 tokens, head size and rotated width multiples of 16.
+// 1 if nib_gemm_smallm_qkv takes these sizes: up to 64 tokens, head size and rotated width multiples of 16.
 NIB_API int nib_gemm_smallm_qkv_supported(const void* A, const void* W, int tokens, int K, int lda, int elem_bytes,
                                           int head_dim, int rot) {
-    if (tokens > 16 || head_dim <= 0 || head_dim % 16 || rot < 0 || rot > head_dim || rot % 16) return 0;
+    if (tokens > MAX_TOKENS || head_dim <= 0 || head_dim % 16 || rot < 0 || rot > head_dim || rot % 16) return 0;
     return nib_gemm_smallm_supported(A, W, tokens, K, lda, elem_bytes);
 }
 
@@ -506,7 +532,7 @@ NIB_API int nib_gemm_smallm_qkv(const void* A, const void* W, const float* bias,
     const int N = (heads + 2 * kv_heads) * head_dim;
     NIB_REQUIRE(heads > 0 && kv_heads > 0 && lda >= K && ldq >= N, "gemm (small M, q/k/v): bad sizes heads=%d/%d head_dim=%d", heads, kv_heads, head_dim);
     NIB_REQUIRE(nib_gemm_smallm_qkv_supported(A, W, tokens, K, lda, gain ? 4 : 2, head_dim, rot),
-                "gemm (small M, q/k/v): needs 1..16 tokens, K %% 32 == 0, head_dim and the rotated width multiples of 16 (tokens=%d K=%d head_dim=%d rot=%d)",
+                "gemm (small M, q/k/v): needs 1..64 tokens, K %% 32 == 0, head_dim and the rotated width multiples of 16 (tokens=%d K=%d head_dim=%d rot=%d)",
                 tokens, K, head_dim, rot);
     NIB_REQUIRE(rot == 0 || (cos_t && sin_t), "gemm (small M, q/k/v): rotation needs the tables");
     NIB_REQUIRE(positions && req_index, "gemm (small M, q/k/v): positions and request rows are needed");

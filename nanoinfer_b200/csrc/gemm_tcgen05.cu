@@ -875,6 +875,9 @@ NIB_API int nib_gemm_tc_splitk(const void* A, const void* W, const float* bias, 
         tok_tile = tokens <= 16 ? 16 : tokens <= 32 ? 32 : tokens <= 64 ? 64 : 128;
         // 256 tokens per tile halves the shared-memory traffic per flop; take it when the grid still fills the GPU
         if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148 && epi != EPI_SWIGLU) tok_tile = 256;
+        // 33..64 tokens with few feature tiles (a decode step of 64 requests): two tiles of 32 tokens put twice the
+        // SMs on the weights, which are what the step has to stream (measured: 3.4 us a layer at the 0.5B widths)
+        if (tok_tile == 64 && 2LL * f_tiles <= sm_count()) tok_tile = 32;
     }
     NIB_REQUIRE(ceil_div(tokens, tok_tile) <= 65535, "gemm (tensor cores): too many token tiles");
     SplitK sk;
