@@ -876,8 +876,10 @@ NIB_API int nib_gemm_tc_splitk(const void* A, const void* W, const float* bias, 
         // 256 tokens per tile halves the shared-memory traffic per flop; take it when the grid still fills the GPU
         if (tokens >= 512 && (long long)f_tiles * ceil_div(tokens, 256) >= 148 && epi != EPI_SWIGLU) tok_tile = 256;
         // 33..64 tokens with few feature tiles (a decode step of 64 requests): two tiles of 32 tokens put twice the
-        // SMs on the weights, which are what the step has to stream (measured: 3.4 us a layer at the 0.5B widths)
-        if (tok_tile == 64 && 2LL * f_tiles <= sm_count()) tok_tile = 32;
+        // SMs on the weights, which are what the step has to stream (measured: 3.4 us a layer at the 0.5B widths).
+        // The sum into the output can split K over CTAs instead, which reads large weights once (measured better from
+        // about 16 MB of weights on: +8 % at the 7B widths, -2 % at the 0.5B widths).
+        if (tok_tile == 64 && 2LL * f_tiles <= sm_count() && (epi != EPI_ADD || 2LL * N * K <= (16LL << 20))) tok_tile = 32;
     }
     NIB_REQUIRE(ceil_div(tokens, tok_tile) <= 65535, "gemm (tensor cores): too many token tiles");
     SplitK sk;
