@@ -172,6 +172,23 @@ def _kind_of(kernel: str, what: str, state: dict) -> str:
     return kernel or what
 
 
+def _rows_from_notes(notes):
+    """{kind: [microseconds]} and the step's length from the kernels' timer notes: a kernel's share runs from the
+    moment its wait for the earlier kernels ended to the moment the next kernel's did."""
+    epi = {0: "store", 1: "add", 2: "f32", 3: "swiglu", 4: "qkv"}
+    starts = [(t, k, tag) for t, k, tag, phase in notes if phase == 1]
+    ends = [t for t, _, _, phase in notes if phase == 2]
+    if len(starts) < 2 or not ends:
+        return {}, 0.0
+    state, rows = {}, {}
+    for i, (t, kernel, tag) in enumerate(starts):
+        state["tag"] = epi.get(tag) if kernel.startswith("gemm") else None
+        kind = _kind_of(kernel, "", state)
+        t_next = starts[i + 1][0] if i + 1 < len(starts) else max(ends)
+        rows.setdefault(kind, []).append((t_next - t) / 1e3)
+    return rows, (max(ends) - starts[0][0]) / 1e3
+
+
 def decode_breakdown(engine, ops, reqs, rng, vocab, batch, mean_ctx, nums, pk) -> dict:
     """Where the time of ONE decode step goes, from the kernels' own notes of the GPU timer (they keep the overlap
     of dependent launches inside the captured graph): a kernel's share is the time from the moment its wait for the
@@ -194,18 +211,9 @@ def decode_breakdown(engine, ops, reqs, rng, vocab, batch, mean_ctx, nums, pk) -
     engine.reset_graphs()
     for rc, n in zip(reqs, base):
         engine.truncate(rc, n)
-    epi = {0: "store", 1: "add", 2: "f32", 3: "swiglu", 4: "qkv"}
-    starts = [(t, k, tag) for t, k, tag, phase in notes if phase == 1]
-    ends = [t for t, _, _, phase in notes if phase == 2]
-    if len(starts) < 2 or not ends:
+    rows, step_us = _rows_from_notes(notes)
+    if not rows:
         return {}
-    state, rows = {}, {}
-    for i, (t, kernel, tag) in enumerate(starts):
-        state["tag"] = epi.get(tag) if kernel.startswith("gemm") else None
-        kind = _kind_of(kernel, "", state)
-        t_next = starts[i + 1][0] if i + 1 < len(starts) else max(ends)
-        rows.setdefault(kind, []).append((t_next - t) / 1e3)
-    step_us = (max(ends) - starts[0][0]) / 1e3
     bytes_of = {k: 2.0 * v for k, v in nums["kinds"].items()}
     bytes_of["attention"] = batch * mean_ctx * nums["kv_bytes_per_token_layer"]
     out = {"step_us": round(step_us, 1)}
@@ -220,32 +228,30 @@ def decode_breakdown(engine, ops, reqs, rng, vocab, batch, mean_ctx, nums, pk) -
 
 
 def prefill_breakdown(engine, ops, rng, vocab, t_pre, nums, pk) -> dict:
-    """Where the time of one prompt portion goes: an event behind every launch (the kernels of a portion run for
-    tens of microseconds, so ending their overlap changes little). FLOPs of a product: 2 x tokens x weights; of
-    the attention: 4 x heads x head size x t(t+1)/2; the fraction is of the measured cuBLAS burst throughput."""
+    """Where the time of one prompt portion goes, from the kernels' own notes of the GPU timer as in
+    ``decode_breakdown`` (the third step of the shape: a replay of its captured graph, so the kernels overlap as
+    they do in production and the host is not in the way). FLOPs of a product: 2 x tokens x weights; of the
+    attention: 4 x heads x head size x t(t+1)/2; the fraction is of the measured cuBLAS burst throughput."""
+    import numpy as np
     import torch
     from nanoinfer_b200.engine import StepEntry
+    ops.timeline_start()
+    engine.reset_graphs()
     rc = engine.open("breakdown")
-    ids = rng.integers(0, vocab, t_pre).tolist()
-    engine.step([StepEntry(rc, ids, [t_pre - 1])])
-    engine.truncate(rc, 0)
-    ops.time_ops(True)
-    engine.step([StepEntry(rc, ids, [t_pre - 1])])
-    times = ops.op_times()
-    ops.time_ops(False)
+    ids = rng.integers(0, vocab, t_pre).astype(np.int32)
+    for i in range(3):
+        if i == 2:
+            ops.timeline_clear()
+        engine.step([StepEntry(rc, ids, [t_pre - 1])])
+        torch.cuda.synchronize()
+        engine.truncate(rc, 0)
+    notes = ops.timeline()
+    ops.timeline_stop()
+    engine.reset_graphs()
     engine.close(rc)
-    state, rows = {}, {}
-    for what, us in times:
-        w = what.lower()
-        state["tag"] = None
-        if "linear" in w or "q/k/v" in w:
-            # the order of a layer's products: q/k/v, output, gate/up, down; the head comes after the last layer
-            n = state.get("linears", 0)
-            state["linears"] = n + 1
-            state["tag"] = ("qkv", "add", "swiglu", "add")[n % 4] if n < 4 * engine.config.num_hidden_layers else "f32"
-        kind = _kind_of("", what, state)
-        rows.setdefault(kind, []).append(us)
-    total = sum(us for _, us in times)
+    rows, total = _rows_from_notes(notes)
+    if not rows:
+        return {}
     flops_of = {k: 2.0 * t_pre * v for k, v in nums["kinds"].items()}
     flops_of["lm_head"] = 2.0 * nums["kinds"]["lm_head"]          # one wanted row
     flops_of["attention"] = nums["attention_flops"](t_pre)

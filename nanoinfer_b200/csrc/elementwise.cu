@@ -248,7 +248,6 @@ rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ p
                       __nv_bfloat16* __restrict__ v_pages, int m_tokens, int heads, int kv_heads, int head_dim, int num_pages,
                       int write_kv, unsigned long long* trace, int trace_cap) {
     pdl_launch_dependents();
-    if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ROPE, 0, 1);
     const int half = rot >> 1;
     const int rot_items = (heads + kv_heads) * (half >> 3);
     const int tail_items = write_kv ? kv_heads * ((head_dim - rot) >> 3) : 0;
@@ -268,6 +267,7 @@ rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ p
     }
     __nv_bfloat16* row = qkv + (size_t)m * (heads + 2 * kv_heads) * head_dim;
     pdl_wait();     // positions and block tables are the step's inputs; qkv is the previous kernel's output
+    if (idx == 0) nib_trace_mark(trace, trace_cap, NIB_TK_ROPE, 0, 1);
     if (item < rot_items) {
         const int per_head = half >> 3;
         const int h = item / per_head, d = (item - h * per_head) << 3;
