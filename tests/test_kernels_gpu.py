@@ -187,6 +187,44 @@ def test_attention_finds_one_far_key(K, dtype, window):
         assert seen == (spot >= lo), f"key at {spot}: seen={seen}, window starts at {lo}"
 
 
+@pytest.mark.parametrize("window", [0, 50])
+@pytest.mark.parametrize("route,hd,q_len,options", [
+    ("tcgen05 prefill", 64, 2, {}), ("tcgen05 prefill", 64, 33, {}), ("tcgen05 prefill", 128, 2, {}), ("tcgen05 prefill", 128, 33, {}),
+    ("mma.sync prefill", 48, 2, {}), ("mma.sync prefill", 48, 33, {}), ("mma.sync prefill", 64, 33, {"force_mma_prefill": True}),
+    ("cp.async decode", 64, 1, {"decode_tma": False}), ("cp.async decode", 128, 1, {"decode_tma": False})])
+def test_attention_routes_find_one_far_key(K, route, hd, q_len, options, window):
+    """The far-key check on the other attention kernels (bfloat16): a prompt portion that starts inside a page on the
+    tcgen05 and the mma.sync prefill kernels, and a decoded token on the cp.async decode kernel. For the first and
+    the last query of the portion, one key carries the whole score: the window's first key, the query's own
+    position, the first position of all (no window), and the key just before the window, which must NOT be seen."""
+    dtype = torch.bfloat16
+    heads, kv_heads, page = 4, 2, 16
+    before = 305                                   # 305 % 16 == 1: the portion starts inside a page
+    ctx_len = before + q_len
+    K = K.with_options(**options)
+    ctx, bt = make_paged_batch([q_len], [before], page, 40, "cuda", seed=3)
+    scale = 1.0 / math.sqrt(hd)
+    for r in sorted({0, q_len - 1}):
+        pos = before + r
+        lo = max(0, pos - window + 1) if window else 0
+        spots = [lo, pos] + ([lo - 1] if window else [0, before - 1, before])
+        for spot in spots:
+            kp, vp = _fill_cache(ctx, bt, page, 40, kv_heads, hd, dtype, 30)
+            kp.mul_(0.05)
+            qkv = rnd((q_len, (heads + 2 * kv_heads) * hd), dtype, 31)
+            phys = bt[0, spot // page].item()
+            q3 = qkv.view(q_len, heads + 2 * kv_heads, hd)[r, 3].float()
+            kp[phys, 1, spot % page] = (q3 / q3.norm() * 40.0).to(dtype)     # aligned with query head 3 of row r
+            out, ref = (torch.empty(q_len, heads * hd, dtype=dtype, device="cuda") for _ in range(2))
+            K.attention(qkv, out, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+            REF.attention(qkv, ref, heads, kv_heads, hd, scale, window, ctx, bt, page, kp, vp)
+            assert_close(out, ref, dtype, f"{route}: far key at {spot}, query {r}")
+            o3 = out.view(q_len, heads, hd)[r, 3].float()
+            seen = (o3 - vp[phys, 1, spot % page].float()).abs().max().item() < 0.05
+            assert seen == (lo <= spot <= pos), f"{route}: key at {spot}, query at {pos}: seen={seen}, window starts at {lo}"
+    assert K.attention_tc_error() == 0 and K.attention_decode_tma_error() == 0
+
+
 @pytest.mark.parametrize("rows", [5, 200])
 @pytest.mark.parametrize("vocab", [11, 503, 4099, 151936])
 def test_argmax_first_maximum(K, vocab, rows):

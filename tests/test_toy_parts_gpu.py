@@ -214,3 +214,140 @@ def test_toy_mixer_that_keeps_keys_alone_and_unequal_keys_and_values(tmp_path, d
     assert pages[0]["keys"].dtype == torch.float32 and pages[1]["values"].dtype == tdt and "values" not in pages[2]
     assert tuple(pages[1]["values"].shape) == (22, 2, 4, 20) and tuple(pages[1]["keys"].shape) == (22, 2, 4, 12)
     toy.run_through_the_engine(eng, read_weights(d), lambda got, ref, what: assert_close(got, ref, tdt, what))
+
+
+# ------------------------------------------------------------------ a mixer with state whose steps are captured in graphs
+TOY_GRAPH = {"architectures": ["ToyGraphForCausalLM"], "vocab_size": 71, "hidden_size": 32, "max_pos": 160,
+             "intermediate_size": 48, "eps": 1e-5}
+
+
+def _register_graph_safe_toy():
+    from nanoinfer_b200.config.model_config import ModelConfig
+    from nanoinfer_b200.parts.base import Mixer, StateNeed, as_tensor
+    from nanoinfer_b200.parts.embedding import LinearHead, TokenEmbedding
+    from nanoinfer_b200.parts.feedforward import SwiGLU
+    from nanoinfer_b200.parts.norm import RMSNorm
+    from nanoinfer_b200.parts.spec import LayerSpec, ModelPlan, PartSpec, ScheduleEntry, TensorSpec
+    from nanoinfer_b200.registry import register_architecture, register_part
+
+    class RunningMeanOnDevice(Mixer):
+        """out_t = W . mean(h_0..h_t), state per request = [sum of inputs | count], computed with device-side index
+        arithmetic only (nothing of the batch is read on the host), so its launches are the same for every batch
+        and a decode step with it may be captured. A padding row of a captured step carries the spare state slot."""
+
+        graph_safe = True
+
+        def __init__(self, spec, tensors, rt):
+            super().__init__(spec, tensors, rt)
+            self.hidden = int(spec.params["hidden"])
+            self.w = rt.matrix(tensors["w"])
+
+        def state_need(self):
+            return StateNeed((self.hidden + 1,), torch.float32)
+
+        def forward(self, h, residual32, ctx, cache):
+            h = as_tensor(h).float()
+            req = ctx.req_index.long()
+            slots = ctx.state_slots.long()
+            start = ctx.q_start.long()
+            csum = torch.cat([torch.zeros_like(h[:1]), h.cumsum(0)])            # csum[i] = sum of rows < i
+            before = csum[start[:-1]]                                          # per request: rows before its first
+            own = csum[1:] - before[req]                                       # inclusive sum within the request's rows
+            nth = torch.arange(1, h.shape[0] + 1, device=h.device) - start[:-1][req]
+            st = cache.state[slots]                                            # [R, hidden + 1]
+            mean = (st[req, :self.hidden] + own) / (st[req, self.hidden] + nth)[:, None]
+            out = torch.empty(h.shape[0], self.hidden, dtype=torch.float32, device=h.device)
+            self.ops.linear(mean.to(self.rt.dtype).contiguous(), self.w, None, out, "f32")
+            residual32 += out
+            totals = csum[start[1:]] - before
+            counts = (start[1:] - start[:-1]).float()
+            cache.state.index_add_(0, slots, torch.cat([totals, counts[:, None]], dim=1))
+
+    register_part("toy_running_mean_on_device", RunningMeanOnDevice)
+
+    @dataclass(frozen=True)
+    class ToyGraphConfig(ModelConfig):
+        intermediate_size: int = 0
+        eps: float = 1e-6
+
+        @classmethod
+        def from_json_dict(cls, d):
+            return cls(architecture="ToyGraphForCausalLM", model_type="toy_graph", vocab_size=d["vocab_size"],
+                       hidden_size=d["hidden_size"], num_hidden_layers=2, max_position_embeddings=d["max_pos"],
+                       tie_word_embeddings=False, eos_token_id=-1, intermediate_size=d["intermediate_size"], eps=d["eps"])
+
+        def to_json_dict(self):
+            return {"architectures": ["ToyGraphForCausalLM"], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                    "max_pos": self.max_position_embeddings, "intermediate_size": self.intermediate_size, "eps": self.eps}
+
+    def plan(c):
+        h = c.hidden_size
+
+        def layer(i):
+            return LayerSpec("pre_norm", {
+                "mixer_norm": RMSNorm.spec(h, c.eps, f"l{i}.n1"),
+                "mixer": PartSpec("toy_running_mean_on_device", {"hidden": h}, {"w": TensorSpec(f"l{i}.toy.w", (h, h))}),
+                "ffn_norm": RMSNorm.spec(h, c.eps, f"l{i}.n2"), "ffn": SwiGLU.spec(f"l{i}.mlp", h, c.intermediate_size)})
+        return ModelPlan(architecture=c.architecture, hidden_size=h, vocab_size=c.vocab_size,
+                         max_position_embeddings=c.max_position_embeddings, embedding=TokenEmbedding.spec("embed", c.vocab_size, h),
+                         positions={}, layers=[layer(0), layer(1)], schedule=[ScheduleEntry(0), ScheduleEntry(1)],
+                         final_norm=RMSNorm.spec(h, c.eps, "norm"), lm_head=LinearHead.spec("head", c.vocab_size, h))
+
+    register_architecture("ToyGraphForCausalLM", ToyGraphConfig, plan)
+
+
+def plain_toy_graph(w, ids):
+    c = TOY_GRAPH
+    T = len(ids)
+    x = w["embed"][torch.tensor(ids)]
+    for i in range(2):
+        h = rms_norm(x, w[f"l{i}.n1"], c["eps"])
+        mean = h.cumsum(0) / torch.arange(1, T + 1, dtype=h.dtype)[:, None]
+        x = x + linear(mean, w[f"l{i}.toy.w"])
+        h = rms_norm(x, w[f"l{i}.n2"], c["eps"])
+        x = x + swiglu(h, w[f"l{i}.mlp.gate_proj.weight"], w[f"l{i}.mlp.up_proj.weight"], w[f"l{i}.mlp.down_proj.weight"])
+    return linear(rms_norm(x, w["norm"], c["eps"]), w["head"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_decodes_through_captured_graphs(tmp_path, dtype):
+    """A mixer with state of its own that declares itself graph safe: its decode steps are captured and replayed.
+    Three live requests decode in a bucket of four, so every replay has a padding row; that row carries the spare
+    state slot, and the live requests' states (sums and counts) stay exactly theirs: every decoded position of every
+    request equals the plain whole-sequence computation, also for a request that takes over a finished one's slot."""
+    from nanoinfer_b200.config import EngineConfig
+    from nanoinfer_b200.engine import Engine, StepEntry
+    from nanoinfer_b200.registry import config_from_json_dict
+    from nanoinfer_b200.weights import write_random_model
+    _register_graph_safe_toy()
+    d = str(tmp_path / "toy_graph")
+    write_random_model(config_from_json_dict(TOY_GRAPH), d, seed=5)
+    w = read_weights(d)
+    eng = Engine(d, EngineConfig(dtype=dtype, page_size=8, num_pages=8, max_batch=4))
+    assert eng._graphs is not None, "the model is graph safe: decode steps are captured"
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    g = torch.Generator().manual_seed(6)
+    seqs = {k: torch.randint(0, 71, (n,), generator=g).tolist() for k, n in (("a", 40), ("b", 33), ("c", 52), ("d", 45))}
+    want = {k: plain_toy_graph(w, v) for k, v in seqs.items()}
+    prompt = {"a": 9, "b": 17, "c": 3, "d": 20}
+    live = {k: eng.open(k) for k in ("a", "b", "c")}
+    got = {k: [] for k in seqs}
+    for k, rc in live.items():          # prompts, eagerly
+        got[k].append(eng.step([StepEntry(rc, seqs[k][:prompt[k]], list(range(prompt[k])))]).clone())
+    fed = dict(prompt)
+    replays_before = eng.graph_launches
+    while live:
+        entries = [StepEntry(rc, [seqs[k][fed[k]]], [0]) for k, rc in live.items()]
+        logits = eng.step(entries)
+        for row, k in enumerate(list(live)):
+            got[k].append(logits[row:row + 1].clone())
+            fed[k] += 1
+        for k in [k for k in live if fed[k] == len(seqs[k])]:
+            eng.close(live.pop(k))
+            if k == "b":                # "d" takes over the slot that "b" gave back: its state starts from zero
+                live["d"] = eng.open("d")
+                got["d"].append(eng.step([StepEntry(live["d"], seqs["d"][:prompt["d"]], list(range(prompt["d"])))]).clone())
+                fed["d"] = prompt["d"]
+    assert eng.graph_launches > replays_before and eng._graphs.captured, "decode steps ran from captured graphs"
+    for k in seqs:
+        assert_close(torch.cat(got[k]), want[k], tdt, f"graph-safe toy mixer, request {k}")
