@@ -220,6 +220,7 @@ class PortionGraphs:
         self.min_tokens, self.capacity = min_tokens, capacity
         self.captured: Dict[tuple, _Captured] = {}
         self.seen: Dict[tuple, int] = {}
+        self.refused = set()        # shapes whose capture failed
         self.pool = None
         self.stream = None
 
@@ -244,9 +245,16 @@ class PortionGraphs:
             if len(self.seen) > 4096:
                 self.seen.clear()
             self.seen[key] = self.seen.get(key, 0) + 1
-            if self.seen[key] < 2 or len(self.captured) >= self.capacity:
+            if self.seen[key] < 2 or len(self.captured) >= self.capacity or key in self.refused:
                 return False, None          # the first step of a shape runs eagerly (and sets up what kernels set up on first use)
-            cap = self._capture(key, entries, token_arrays)
+            try:
+                cap = self._capture(key, entries, token_arrays)
+            except RuntimeError:
+                # a step that cannot be captured (memory for its pool, a part that turns out to need the host) runs
+                # eagerly from now on; the caller builds the step's inputs anew
+                self.refused.add(key)
+                torch.cuda.synchronize()
+                return False, None
         else:
             eng.build_context(entries, widths=list(key[1]), static=cap.inputs, token_arrays=token_arrays)
         cap.graph.replay()
