@@ -79,8 +79,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 template <typename T, int NV>
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain, const int* __restrict__ rows,
-                    T* __restrict__ out, int n_rows, int hidden, float eps, unsigned long long* trace, int trace_cap) {
-    pdl_launch_dependents();
+                    T* __restrict__ out, int n_rows, int hidden, float eps, int late_dependents, unsigned long long* trace, int trace_cap) {
+    // late_dependents: the kernel behind this one starts only when this kernel's loads are out (see nib_rmsnorm)
+    if (!late_dependents) pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_RMSNORM, 0, 0);
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -108,6 +109,7 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain,
         ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
     }
     ss = warp_sum(ss);
+    if (late_dependents) pdl_launch_dependents();
     const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
     T* o = out + (size_t)r * hidden;
 #pragma unroll
@@ -132,27 +134,30 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ gain,
 
 template <typename T>
 int launch_rmsnorm_rows(const float* x, const float* gain, const int* rows, T* out, int n_rows, int hidden, float eps,
-                        cudaStream_t stream) {
+                        int late_dependents, cudaStream_t stream) {
     const int warps = n_rows >= 8 ? 8 : n_rows;           // rows per block
     const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
     if (hidden <= 128 * 8)
-        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 8>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, nib_trace_buffer(), nib_trace_capacity()));
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 8>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, late_dependents, nib_trace_buffer(), nib_trace_capacity()));
     else if (hidden <= 128 * 16)
-        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 16>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, nib_trace_buffer(), nib_trace_capacity()));
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 16>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, late_dependents, nib_trace_buffer(), nib_trace_capacity()));
     else
-        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 32>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, nib_trace_buffer(), nib_trace_capacity()));
+        NIB_CUDA(launch_pdl(rmsnorm_rows_kernel<T, 32>, grid, block, (size_t)0, stream, x, gain, rows, out, n_rows, hidden, eps, late_dependents, nib_trace_buffer(), nib_trace_capacity()));
     return 0;
 }
 
+// late_dependents: the kernel launched behind this one (programmatic dependent launch) may start only when this kernel's
+// loads are out, instead of at once. Right when that kernel has next to no set-up of its own and would only take issue
+// slots and bandwidth meanwhile (the small-M product); wrong when it has a long set-up to hide (the tcgen05 products).
 NIB_API int nib_rmsnorm(const float* x, const float* gain, const int* rows, void* out, int n_rows,
-                        int hidden, float eps, int dtype, cudaStream_t stream) {
+                        int hidden, float eps, int dtype, int late_dependents, cudaStream_t stream) {
     NIB_REQUIRE(n_rows >= 0 && hidden > 0, "rmsnorm: bad sizes rows=%d hidden=%d", n_rows, hidden);
     if (n_rows == 0) return 0;
     // rows of 16-byte multiples up to 4096 wide: a warp per row
     if (hidden % 4 == 0 && hidden <= 4096 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0 &&
         (dtype == NIB_F32 || dtype == NIB_BF16)) {
-        const int rc = dtype == NIB_F32 ? launch_rmsnorm_rows<float>(x, gain, rows, (float*)out, n_rows, hidden, eps, stream)
-                                        : launch_rmsnorm_rows<__nv_bfloat16>(x, gain, rows, (__nv_bfloat16*)out, n_rows, hidden, eps, stream);
+        const int rc = dtype == NIB_F32 ? launch_rmsnorm_rows<float>(x, gain, rows, (float*)out, n_rows, hidden, eps, late_dependents, stream)
+                                        : launch_rmsnorm_rows<__nv_bfloat16>(x, gain, rows, (__nv_bfloat16*)out, n_rows, hidden, eps, late_dependents, stream);
         if (rc) return rc;
         NIB_LAUNCH_CHECK();
         return 0;

@@ -87,7 +87,12 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
     extern __shared__ float part[];                      // [KSPLIT][ACCS][NT][E][32] when KSPLIT > 1
     __shared__ int s_last;
 
-    pdl_launch_dependents();
+    // Up to 16 tokens the kernel behind this one may start only when this kernel's own loads are out (below): measured,
+    // dependents that are resident from this kernel's first instruction on take issue slots and bandwidth from it
+    // (batch 8: 3 us a step at the 0.5B widths, 30 us at the 1.5B widths). With more tokens the attention behind the
+    // q/k/v product wants its keys and values on their way as early as can be (batch 64: 1.53 against 1.56 ms).
+    constexpr bool LATE_DEPENDENTS = NT <= 2;
+    if (!LATE_DEPENDENTS) pdl_launch_dependents();
     bool waited = false;          // pdl_wait() comes after the first batch of weight loads has been issued
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     if (threadIdx.x == 0) nib_trace_mark(trace, trace_cap, NIB_TK_GEMM_SMALLM, EPI, 0);
@@ -236,6 +241,7 @@ gemm_smallm_kernel(const void* __restrict__ A, const __nv_bfloat16* __restrict__
             }
         }
     }
+    if (LATE_DEPENDENTS) pdl_launch_dependents();
     if (!waited) pdl_wait();      // before the first write (shared results, scratch, output)
     if (NORM) {
         // the four threads of a quad hold the same token's partial sums: add them (fixed order)

@@ -63,6 +63,7 @@ class Kernels:
         self._bound_stream = None   # the stream of the enclosing stream_scope(), if any
         self._op_events = None      # time_ops(): (what, event) behind every launch
         self._timeline = None       # timeline_start(): the device buffer the kernels note their times in
+        self._norm_before_small_m = False   # set while a product resolves its LazyNorm: what kernel the norm is followed by
         self.sm_count = 0           # SMs of the device, asked when the instance is made ready (load_kernels)
         self._ws_scratch = None                # scratch and counters of the small-M GEMM's cross-CTA split
         self._ws_counters = None
@@ -173,7 +174,8 @@ class Kernels:
         if x32.shape[1] != hidden or gain32.numel() != hidden:
             raise KernelError("rmsnorm: widths differ")
         self._check(self._lib.nib_rmsnorm(_ptr(x32), _ptr(gain32), _ptr(rows), _ptr(out), c_int(n), c_int(hidden),
-                                          c_float(eps), c_int(_DT[out.dtype]), self._stream()), "rmsnorm")
+                                          c_float(eps), c_int(_DT[out.dtype]), c_int(1 if self._norm_before_small_m else 0),
+                                          self._stream()), "rmsnorm")
 
     def with_options(self, options: Optional[KernelOptions] = None, **changes) -> "Kernels":
         """Another instance on the same library and the same scratch memory (so: for use on the same stream) whose
@@ -257,6 +259,17 @@ class Kernels:
         tiles = -(-rows // 256) * -(-m // 256)
         return tiles >= 48
 
+    def _resolve(self, lazy, before_small_m: bool):
+        """The norm's values for a product that cannot apply the norm itself. The norm kernel is told what follows it: a
+        small-M product of up to 16 tokens has next to no set-up of its own and is let in late (see nib_rmsnorm); measured at batch 8:
+        0.730 -> 0.715 ms a step at the 0.5B widths, 1.72 -> 1.60 ms at the 1.5B widths, and the opposite before a
+        tcgen05 product."""
+        self._norm_before_small_m = before_small_m
+        try:
+            return lazy.resolve()
+        finally:
+            self._norm_before_small_m = False
+
     @staticmethod
     def _foldable(lazy) -> bool:
         """Whether the kernels can apply this norm themselves: the kinds they know, and only while nobody has
@@ -273,7 +286,7 @@ class Kernels:
         if bf16 and self.options.tc_token_tile == 0:
             kernel, fuse = self._route(m, w.shape[0], k, epi, lazy is not None)
             if lazy is not None and not fuse:
-                a, lazy = lazy.resolve(), None
+                a, lazy = self._resolve(lazy, kernel == "smallm" and m <= 16), None
             src = lazy.fold.x32 if lazy is not None else a
             if kernel == "smallm" and self._lib.nib_gemm_smallm_supported(
                     _ptr(src), _ptr(w), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if lazy is not None else 2)) == 1:
@@ -342,7 +355,7 @@ class Kernels:
                 and o.gemm_route in (None, "smallm", "smallm_fused", "tc") and not o.smallm_ksplit and not o.smallm_cross:
             kernel, with_norm = self._route(m, n, k, _EPI["store"], lazy is not None)
             if lazy is not None and not with_norm:
-                a, lazy = lazy.resolve(), None
+                a, lazy = self._resolve(lazy, kernel == "smallm" and m <= 16), None
             src = lazy.fold.x32 if lazy is not None else a
             fused = kernel == "smallm" and o.tc_token_tile == 0 and qkv.stride(0) % 2 == 0 and self._lib.nib_gemm_smallm_qkv_supported(
                 _ptr(src), _ptr(w_qkv), c_int(m), c_int(k), c_int(src.stride(0)), c_int(4 if lazy is not None else 2),
