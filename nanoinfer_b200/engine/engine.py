@@ -141,6 +141,15 @@ class Engine:
         no pages (its block-table row is -1, its context length 0), so kernels write nothing for it and
         its attention is empty; its state slot is the spare one that no request is ever given. ``widths`` fixes the block-table widths; ``static`` is a device buffer of
         the right size that is reused (a captured graph reads its inputs there)."""
+        # Rows are laid out with the one-token entries first, whatever the caller's order: the attention sends the
+        # LEADING one-token requests to the decode kernel, and a decoded token behind a prompt portion would otherwise
+        # take the prefill kernel's path (right, but a tile of 128 rows for one token). The wanted rows keep the
+        # caller's order, so the logits come back as asked.
+        caller = list(entries)
+        order = sorted(range(len(caller)), key=lambda i: len(caller[i].tokens) != 1)        # stable
+        entries = [caller[i] for i in order]
+        if token_arrays is not None:
+            token_arrays = [token_arrays[i] for i in order]
         q_lens = [len(e.tokens) for e in entries]
         r_real = len(entries)
         r = max(r_real, pad_to)
@@ -157,7 +166,8 @@ class Engine:
                                     for e, n in zip(entries, q_lens)] + [np.zeros(pad, np.int32)])
         req_index = np.repeat(np.arange(r, dtype=np.int32), q_lens_p)
         slots = np.asarray([e.request.slot for e in entries] + [self.storage.pad_slot] * pad, dtype=np.int32)
-        want_list = [q_start[i] + int(w) for i, e in enumerate(entries) for w in e.want]
+        row_of = {id(e): int(q_start[i]) for i, e in enumerate(entries)}
+        want_list = [row_of[id(e)] + int(w) for e in caller for w in e.want]
         want = np.asarray(want_list, dtype=np.int32)
         if pad_to:      # a graph computes the logits of every row
             want = np.arange(r, dtype=np.int32)

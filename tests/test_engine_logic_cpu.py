@@ -208,3 +208,27 @@ def test_random_traces_equal_plain(model_dirs, name, seed):
         eng.cache.check()
     assert worst < 1e-4, worst
     assert eng.cache.num_free(0) == num_pages
+
+
+def test_decoded_tokens_are_laid_out_first_whatever_the_callers_order(model_dirs):
+    """A step's rows begin with the entries of one token (the attention sends the leading one-token requests to its
+    decode kernel), in whatever order the caller names the entries; the logits come back in the caller's order."""
+    d, page = model_dirs["A"]
+    plain = PlainModel(d)
+    eng = make_engine(d, page)
+    g = torch.Generator().manual_seed(9)
+    ids = {k: torch.randint(0, eng.vocab_size, (n,), generator=g).tolist() for k, n in (("a", 30), ("b", 12), ("c", 41))}
+    want = {k: plain.logits(v) for k, v in ids.items()}
+    reqs = {k: eng.open(k) for k in ids}
+    eng.step([StepEntry(reqs["a"], ids["a"][:20], []), StepEntry(reqs["c"], ids["c"][:7], [])])
+    # a: one decoded token; b: its whole prompt; c: a portion. Named portion first, decoded token in the middle.
+    entries = [StepEntry(reqs["b"], ids["b"], [0, 11]), StepEntry(reqs["a"], [ids["a"][20]], [0]),
+               StepEntry(reqs["c"], ids["c"][7:30], [22, 0])]
+    ctx, want_rows, want_list = eng.build_context(entries)
+    assert ctx.host.q_lens == [1, 12, 23] and want_list == [1, 12, 0, 13 + 22, 13]
+    logits = eng.step(entries).double().cpu()
+    ref = torch.stack([want["b"][0], want["b"][11], want["a"][20], want["c"][29], want["c"][7]])
+    assert (logits - ref).abs().max().item() < 1e-4
+    for rc in reqs.values():
+        eng.close(rc)
+    eng.cache.check()
