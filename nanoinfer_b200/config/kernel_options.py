@@ -17,7 +17,7 @@ class KernelOptions:
     force_general_attention: bool = False   # the general (CUDA-core) attention kernel for bfloat16 too
     force_mma_prefill: bool = False         # prompt portions on the mma.sync attention kernel instead of tcgen05
     decode_tma: bool = True                 # decode attention with TMA page loads where the shape allows (else mma.sync + cp.async)
-    separate_combine: bool = True           # merge the decode splits that one cluster cannot in a second kernel
+    separate_combine: bool = True           # cp.async decode kernel: merge its splits in a second kernel (False: the CTA that finishes last merges)
     fixed_decode_splits: int = 0            # a fixed split count of the keys for the decode kernels (0 = chosen)
     force_simt_gemm: bool = False           # the CUDA-core product for bfloat16 too
     gemm_route: Optional[str] = None        # "smallm" | "smallm_fused" | "tc" | "tc_pair" instead of the measured choice

@@ -337,7 +337,7 @@ class Kernels:
     def qkv_project(self, a, w_qkv, bias32, qkv, heads, kv_heads, head_dim, positions, req_index, rotary,
                     block_table, page_size, k_pages, v_pages, writes):
         """qkv = a . w_qkv^T + bias with query and key heads rotated by their positions; with ``writes`` the
-        rotated keys and the values also go into the cache pages. ``a`` may be a DeferredNorm.
+        rotated keys and the values also go into the cache pages. ``a`` may be a LazyNorm.
 
         Up to 16 tokens of bfloat16 take one kernel for all of it (bias, rotation and the page write are the
         small-M product's epilogue, the norm its prologue); so do the tiles of 128 tokens of the one-CTA tcgen05
