@@ -205,15 +205,17 @@ class DecodeGraphs:
 
 
 class PortionGraphs:
-    """CUDA graphs for steps made of prompt portions only (every entry brings at least two tokens).
+    """CUDA graphs for steps that hold a prompt portion (alone, beside other portions, or beside decoded tokens).
 
     A long prompt is cut into portions of the scheduler's token budget, so the same shape (the entries' token
     counts, the number of wanted rows, the block tables' widths rounded up to a power of two) comes again and
     again. Such a step is some two hundred launches whose host side costs about as much as a tenth of the
     device's work; captured once, the second time its shape is seen, it is one launch. Everything a kernel
     reads of the step (ids, positions, lengths, wanted rows, block tables) lies in a device buffer of fixed
-    address that one copy refreshes; the launch geometry depends on the shape alone. A shape seen once is
-    never captured, and at most ``capacity`` shapes are kept."""
+    address that one copy refreshes; the launch geometry depends on the shape alone (for the decoded tokens of
+    a mixed step: on the power of two that bounds their contexts, as in DecodeGraphs). A shape seen once is
+    never captured, and at most ``capacity`` shapes are kept. A request that decodes while a long prompt is
+    fed in portions of the token budget repeats one shape step after step: n ones and a portion of budget - n."""
 
     def __init__(self, engine, min_tokens: int = 256, capacity: int = 8):
         self._engine = weakref.ref(engine)
@@ -227,12 +229,15 @@ class PortionGraphs:
     def _key(self, entries):
         eng = self._engine()
         q_lens = tuple(len(e.tokens) for e in entries)
-        if min(q_lens) < 2 or sum(q_lens) < self.min_tokens:
+        if max(q_lens) < 2 or sum(q_lens) < self.min_tokens:
             return None
         widths = tuple(_bucket(max(1, max(len(e.request.tables[g]) for e in entries))) for g in range(len(eng.cache.groups)))
         n_want = sum(len(e.want) for e in entries)
         all_rows = n_want == sum(q_lens) and all(list(e.want) == list(range(len(e.tokens))) for e in entries)
-        return q_lens, widths, n_want, all_rows
+        # decoded tokens: how their keys are split over CTAs is chosen for the power of two that bounds their contexts
+        decode_ctx = [e.request.length + 1 for e, n in zip(entries, q_lens) if n == 1]
+        cb = max(256, _bucket(max(decode_ctx))) if decode_ctx else 0
+        return q_lens, widths, n_want, all_rows, cb
 
     def step(self, entries, token_arrays, borrow: bool):
         """(True, logits) if the step ran from a graph, (False, None) if the caller has to run it."""
@@ -272,6 +277,8 @@ class PortionGraphs:
             + sum(t.numel() for t in probe.block_tables.values())
         static = torch.empty(size, dtype=torch.int32, device=eng.device)
         ctx, want_rows, _ = eng.build_context(entries, widths=widths, static=static, token_arrays=token_arrays)
+        n_dec = sum(1 for n in key[0] if n == 1)
+        ctx.host.ctx_lens[:n_dec] = [key[4]] * n_dec        # (the rows of one token come first: build_context)
         caches = eng.storage.layer_caches(ctx.block_tables)
         ops = eng.rt.ops
         torch.cuda.synchronize()

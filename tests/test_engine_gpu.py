@@ -487,3 +487,40 @@ def test_prompt_portions_of_a_recurring_shape_replay_a_captured_graph(model_dirs
         if turn in (1, 3, 4):
             assert len(eng._portion_graphs.captured) == 1
     eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixed_steps_of_a_recurring_shape_replay_a_captured_graph(model_dirs, dtype):
+    """Decoded tokens beside a prompt portion, the shape a long prompt fed under the token budget repeats while
+    other requests decode: captured the second time, replayed from then on, with the decoding requests' contexts
+    growing across a page edge meanwhile (the graph reads lengths and block tables from its input buffer). Named
+    portion first on purpose: the step lays the decoded tokens out first and returns the logits in the caller's order."""
+    from nanoinfer_b200.engine import StepEntry
+    d, page = model_dirs["C"]
+    plain = PlainModel(d)
+    eng = engine_for(d, page, dtype, num_pages=200, max_batch=4)
+    eng._portion_graphs.min_tokens = 64
+    g = torch.Generator().manual_seed(37)
+    vocab = plain.cfg["vocab"]
+    decoding = {k: torch.randint(0, vocab, (n,), generator=g).tolist() for k, n in (("x", 60), ("y", 27))}
+    reqs = {k: eng.open(k) for k in decoding}
+    fed = {"x": 44, "y": 11}
+    for k, rc in reqs.items():
+        eng.step([StepEntry(rc, decoding[k][:fed[k]], [])])
+    for turn in range(5):
+        prompt = torch.randint(0, vocab, (90,), generator=g).tolist()
+        new = eng.open(f"p{turn}")
+        entries = [StepEntry(new, prompt, [0, 89])] + [StepEntry(reqs[k], [decoding[k][fed[k]]], [0]) for k in reqs]
+        before = eng.graph_launches
+        got = eng.step(entries)
+        assert (eng.graph_launches > before) == (turn >= 1), "which steps ran from the graph"
+        ref = torch.stack([plain.logits(prompt)[0], plain.logits(prompt)[89]] +
+                          [plain.logits(decoding[k][:fed[k] + 1])[-1] for k in reqs])
+        assert_close(got, ref, tdt(dtype), f"mixed step {turn}")
+        for k in reqs:
+            fed[k] += 1
+        eng.close(new)
+    assert len(eng._portion_graphs.captured) == 1
+    for rc in reqs.values():
+        eng.close(rc)
+    eng.cache.check()
