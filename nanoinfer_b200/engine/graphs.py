@@ -210,16 +210,20 @@ class PortionGraphs:
     A long prompt is cut into portions of the scheduler's token budget, so the same shape (the entries' token
     counts, the number of wanted rows, the block tables' widths rounded up to a power of two) comes again and
     again. Such a step is some two hundred launches whose host side costs about as much as a tenth of the
-    device's work; captured once, the second time its shape is seen, it is one launch. Everything a kernel
+    device's work; captured once, the third time its shape is seen, it is one launch. Everything a kernel
     reads of the step (ids, positions, lengths, wanted rows, block tables) lies in a device buffer of fixed
     address that one copy refreshes; the launch geometry depends on the shape alone (for the decoded tokens of
     a mixed step: on the power of two that bounds their contexts, as in DecodeGraphs). A shape seen once is
     never captured, and at most ``capacity`` shapes are kept. A request that decodes while a long prompt is
     fed in portions of the token budget repeats one shape step after step: n ones and a portion of budget - n."""
 
-    def __init__(self, engine, min_tokens: int = 256, capacity: int = 8):
+    def __init__(self, engine, min_tokens: int = 256, capacity: int = 8, sightings: int = 3):
         self._engine = weakref.ref(engine)
         self.min_tokens, self.capacity = min_tokens, capacity
+        # A capture costs about ten eager steps' host time: a shape is captured when it is seen for the third time (a
+        # prompt cut by the budget, or decoding beside one, comes dozens of times; a batch of prompts of odd lengths
+        # that happens to recur once does not pay for a capture).
+        self.sightings = sightings
         self.captured: Dict[tuple, _Captured] = {}
         self.seen: Dict[tuple, int] = {}
         self.refused = set()        # shapes whose capture failed
@@ -250,7 +254,7 @@ class PortionGraphs:
             if len(self.seen) > 4096:
                 self.seen.clear()
             self.seen[key] = self.seen.get(key, 0) + 1
-            if self.seen[key] < 2 or len(self.captured) >= self.capacity or key in self.refused:
+            if self.seen[key] < self.sightings or len(self.captured) >= self.capacity or key in self.refused:
                 return False, None          # the first step of a shape runs eagerly (and sets up what kernels set up on first use)
             try:
                 cap = self._capture(key, entries, token_arrays)

@@ -462,7 +462,7 @@ def test_prompt_portions_of_a_recurring_shape_replay_a_captured_graph(model_dirs
     plain = PlainModel(d)
     eng = engine_for(d, page, dtype, num_pages=200, max_batch=4)
     assert eng._portion_graphs is not None
-    eng._portion_graphs.min_tokens = 64
+    eng._portion_graphs.min_tokens, eng._portion_graphs.sightings = 64, 2
     g = torch.Generator().manual_seed(31)
     vocab = plain.cfg["vocab"]
     shapes = [(70, 30), (70, 30), (33,), (70, 30), (70, 30)]
@@ -499,7 +499,7 @@ def test_mixed_steps_of_a_recurring_shape_replay_a_captured_graph(model_dirs, dt
     d, page = model_dirs["C"]
     plain = PlainModel(d)
     eng = engine_for(d, page, dtype, num_pages=200, max_batch=4)
-    eng._portion_graphs.min_tokens = 64
+    eng._portion_graphs.min_tokens, eng._portion_graphs.sightings = 64, 2
     g = torch.Generator().manual_seed(37)
     vocab = plain.cfg["vocab"]
     decoding = {k: torch.randint(0, vocab, (n,), generator=g).tolist() for k, n in (("x", 60), ("y", 27))}
