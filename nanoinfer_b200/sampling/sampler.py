@@ -88,19 +88,7 @@ class Sampler:
         if rows[0].params.greedy:
             self.ops.argmax(logits, out)
         else:
-            # temperature, top-k, top-p and the uniform numbers travel as one array (top-k as integer bits)
-            par = np.empty((4, n), dtype=np.float32)
-            par[0] = [r.params.temperature for r in rows]
-            par[1].view(np.int32)[:] = [r.params.k for r in rows]
-            par[2] = [r.params.p for r in rows]
-            par[3] = [uniform_for(r.seed, r.generated) for r in rows]
-            if on_gpu:
-                stage[:4 * n].numpy()[:] = par.reshape(-1)
-                dev = torch.empty(4 * n, dtype=torch.float32, device=out.device)
-                dev.copy_(stage[:4 * n], non_blocking=True)
-            else:
-                dev = torch.from_numpy(par.reshape(-1).copy())
-            self.ops.sample(logits, dev[:n], dev[n:2 * n].view(torch.int32), dev[2 * n:3 * n], dev[3 * n:], out)
+            self.ops.sample(logits, *self._device_parameters(rows, out.device, stage), out)
         if not on_gpu:       # a host backend (tests): nothing is asynchronous
             return PendingTokens(out, out, None, n)
         host[:n].copy_(out, non_blocking=True)
@@ -133,13 +121,33 @@ class Sampler:
         if all(r.params.greedy for r in rows):
             self.ops.argmax(logits, out)
             return out.tolist()
-        greedy = torch.empty(n, dtype=torch.int32, device=dev)
-        self.ops.argmax(logits, greedy)
-        temp = torch.tensor([r.params.temperature if not r.params.greedy else 1.0 for r in rows],
-                            dtype=torch.float32, device=dev)
-        top_k = torch.tensor([r.params.k for r in rows], dtype=torch.int32, device=dev)
-        top_p = torch.tensor([r.params.p for r in rows], dtype=torch.float32, device=dev)
-        uni = torch.tensor([uniform_for(r.seed, r.generated) for r in rows], dtype=torch.float32, device=dev)
-        self.ops.sample(logits, temp, top_k, top_p, uni, out)
-        g, s = greedy.tolist(), out.tolist()
+        any_greedy = any(r.params.greedy for r in rows)
+        greedy = None
+        if any_greedy:
+            greedy = torch.empty(n, dtype=torch.int32, device=dev)
+            self.ops.argmax(logits, greedy)
+        self.ops.sample(logits, *self._device_parameters(rows, dev), out)
+        s = out.tolist()
+        if not any_greedy:
+            return s
+        g = greedy.tolist()
         return [g[i] if rows[i].params.greedy else s[i] for i in range(n)]
+
+    def _device_parameters(self, rows: Sequence[SampleRow], dev, stage=None):
+        """Temperature, top-k, top-p and the uniform numbers of the rows on the device: one array (top-k as integer
+        bits), one copy from pinned memory. A greedy row's temperature is 1 (its sample is not used)."""
+        n = len(rows)
+        par = np.empty((4, n), dtype=np.float32)
+        par[0] = [r.params.temperature if not r.params.greedy else 1.0 for r in rows]
+        par[1].view(np.int32)[:] = [r.params.k for r in rows]
+        par[2] = [r.params.p for r in rows]
+        par[3] = [uniform_for(r.seed, r.generated) for r in rows]
+        if torch.device(dev).type == "cuda":
+            if stage is None:
+                _, stage = self._pinned_pair(n)
+            stage[:4 * n].numpy()[:] = par.reshape(-1)
+            d = torch.empty(4 * n, dtype=torch.float32, device=dev)
+            d.copy_(stage[:4 * n], non_blocking=True)
+        else:
+            d = torch.from_numpy(par.reshape(-1).copy())
+        return d[:n], d[n:2 * n].view(torch.int32), d[2 * n:3 * n], d[3 * n:]
