@@ -178,6 +178,47 @@ __device__ float block_sum(float v, float* scratch) {
 // order in which threads add (integer addition is associative): sampling stays reproducible.
 constexpr float FIX_ONE = 1099511627776.0f;  // 2^40
 
+// The first radix pass (the key's top 8 bits: sign and exponent of the scaled logit) puts almost every element of a
+// row into a handful of bins, and a thousand threads queueing at five shared-memory addresses, with 64-bit adds, made a
+// pure top-p row cost two milliseconds (counts alone, as in top-k, are 32-bit adds that the hardware takes in its
+// stride: there the plain adds measured faster). In that pass a thread therefore gathers its elements' counts and masses in a
+// four-entry cache of bins held in registers and adds an entry to the shared histogram when it is evicted and at the
+// end. The sums are integers, so the histogram is the same whatever the order.
+struct BinCache {
+    unsigned bin[4], count[4];
+    unsigned long long mass[4];
+    int next;
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { bin[e] = 0xffffffffu; count[e] = 0u; mass[e] = 0ull; }
+        next = 0;
+    }
+    template <bool MASS>
+    __device__ __forceinline__ void flush_entry(int e, unsigned* hist, unsigned long long* m) {
+        if (count[e] != 0u) {
+            atomicAdd(&hist[bin[e]], count[e]);
+            if (MASS && mass[e] != 0ull) atomicAdd(&m[bin[e]], mass[e]);
+        }
+    }
+    template <bool MASS>
+    __device__ __forceinline__ void add(unsigned b, unsigned long long q, unsigned* hist, unsigned long long* m) {
+        bool hit = false;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (!hit && bin[e] == b) { count[e] += 1u; mass[e] += q; hit = true; }
+        if (hit) return;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (e == next) { flush_entry<MASS>(e, hist, m); bin[e] = b; count[e] = 1u; mass[e] = q; }
+        next = (next + 1) & 3;
+    }
+    template <bool MASS>
+    __device__ __forceinline__ void flush(unsigned* hist, unsigned long long* m) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) flush_entry<MASS>(e, hist, m);
+    }
+};
+
 // One block per row. temperature > 0 for every row given to this kernel.
 __global__ void __launch_bounds__(SAMP_THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
@@ -253,13 +294,24 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
             __syncthreads();
             const unsigned prefix = s_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = tid; i < vocab; i += SAMP_THREADS) {
-                const float x = l[i] * inv_t;
-                const unsigned key = key_of(x);
-                if (key >= kth_key && (key & mask) == prefix) {
-                    const unsigned long long q = (unsigned long long)(expf(x - mx) / z * FIX_ONE);
-                    atomicAdd(&mass[(key >> shift) & 255u], q);
-                    atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            if (shift == 24) {
+                BinCache cache;
+                cache.clear();
+                for (int i = tid; i < vocab; i += SAMP_THREADS) {
+                    const float x = l[i] * inv_t;
+                    const unsigned key = key_of(x);
+                    if (key >= kth_key) cache.add<true>(key >> 24, (unsigned long long)(expf(x - mx) / z * FIX_ONE), hist, mass);
+                }
+                cache.flush<true>(hist, mass);
+            } else {
+                for (int i = tid; i < vocab; i += SAMP_THREADS) {
+                    const float x = l[i] * inv_t;
+                    const unsigned key = key_of(x);
+                    if (key >= kth_key && (key & mask) == prefix) {
+                        const unsigned long long q = (unsigned long long)(expf(x - mx) / z * FIX_ONE);
+                        atomicAdd(&mass[(key >> shift) & 255u], q);
+                        atomicAdd(&hist[(key >> shift) & 255u], 1u);
+                    }
                 }
             }
             __syncthreads();
