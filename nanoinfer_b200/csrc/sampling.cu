@@ -178,46 +178,70 @@ __device__ float block_sum(float v, float* scratch) {
 // order in which threads add (integer addition is associative): sampling stays reproducible.
 constexpr float FIX_ONE = 1099511627776.0f;  // 2^40
 
-// The first radix pass (the key's top 8 bits: sign and exponent of the scaled logit) puts almost every element of a
-// row into a handful of bins, and a thousand threads queueing at five shared-memory addresses, with 64-bit adds, made a
-// pure top-p row cost two milliseconds (counts alone, as in top-k, are 32-bit adds that the hardware takes in its
-// stride: there the plain adds measured faster). In that pass a thread therefore gathers its elements' counts and masses in a
-// four-entry cache of bins held in registers and adds an entry to the shared histogram when it is evicted and at the
-// end. The sums are integers, so the histogram is the same whatever the order.
-struct BinCache {
-    unsigned bin[4], count[4];
-    unsigned long long mass[4];
-    int next;
-    __device__ __forceinline__ void clear() {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { bin[e] = 0xffffffffu; count[e] = 0u; mass[e] = 0ull; }
-        next = 0;
+// A mass into the three histograms of 14-bit chunks. 64-bit adds to shared memory are loops of compare-and-swap, and
+// the first radix pass (the key's top 8 bits: sign and exponent of the scaled logit) puts almost every element of a
+// row into a handful of bins: a thousand threads queueing there with such loops made a pure top-p row cost two
+// milliseconds. 32-bit adds to one address are combined by the hardware. A row's masses sum to 2^40, so every
+// chunk's sum over up to 2^17 elements stays below 2^32.
+__device__ __forceinline__ void mass_add(unsigned (*m)[256], unsigned bin, unsigned long long q) {
+    const unsigned a = (unsigned)(q & 0x3fffull), b = (unsigned)((q >> 14) & 0x3fffull), c = (unsigned)(q >> 28);
+    if (a) atomicAdd(&m[0][bin], a);
+    if (b) atomicAdd(&m[1][bin], b);
+    if (c) atomicAdd(&m[2][bin], c);
+}
+
+// f(x) for every scaled logit x = l[i] / temperature of a row, in no particular order: 16-byte loads, two of them in
+// flight per thread, where the row allows (a thread with one 4-byte load in flight waits out the whole latency of the
+// memory system for every element; a pass over 152K logits took 30 us that way). Rows that are not 16-byte aligned or
+// whose length is no multiple of 4 are read element by element.
+template <typename F>
+__device__ __forceinline__ void for_each_scaled(const float* __restrict__ l, int vocab, float inv_t, F&& f) {
+    const int tid = threadIdx.x;
+    if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(l) & 15) == 0) {
+        const float4* l4 = reinterpret_cast<const float4*>(l);
+        const int n4 = vocab >> 2;
+        int i = tid;
+        for (; i + SAMP_THREADS < n4; i += 2 * SAMP_THREADS) {
+            const float4 a = l4[i], b = l4[i + SAMP_THREADS];
+            f(a.x * inv_t); f(a.y * inv_t); f(a.z * inv_t); f(a.w * inv_t);
+            f(b.x * inv_t); f(b.y * inv_t); f(b.z * inv_t); f(b.w * inv_t);
+        }
+        if (i < n4) {
+            const float4 a = l4[i];
+            f(a.x * inv_t); f(a.y * inv_t); f(a.z * inv_t); f(a.w * inv_t);
+        }
+    } else {
+        for (int i = tid; i < vocab; i += SAMP_THREADS) f(l[i] * inv_t);
     }
-    template <bool MASS>
-    __device__ __forceinline__ void flush_entry(int e, unsigned* hist, unsigned long long* m) {
-        if (count[e] != 0u) {
-            atomicAdd(&hist[bin[e]], count[e]);
-            if (MASS && mass[e] != 0ull) atomicAdd(&m[bin[e]], mass[e]);
+}
+
+// f(i, x) for i = begin .. end - 1 in ascending order (a thread's chunk of a row), until f returns false. 16-byte loads,
+// all of a group of 16 elements issued before the first is used, where begin is a multiple of 4 and the row is aligned.
+template <typename F>
+__device__ __forceinline__ void for_chunk(const float* __restrict__ l, int begin, int end, float inv_t, F&& f) {
+    int i = begin;
+    if ((begin & 3) == 0 && (reinterpret_cast<uintptr_t>(l) & 15) == 0) {
+        for (; i + 16 <= end; i += 16) {
+            float4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(l + i + 4 * j);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (!f(i + 4 * j, v[j].x * inv_t)) return;
+                if (!f(i + 4 * j + 1, v[j].y * inv_t)) return;
+                if (!f(i + 4 * j + 2, v[j].z * inv_t)) return;
+                if (!f(i + 4 * j + 3, v[j].w * inv_t)) return;
+            }
         }
     }
-    template <bool MASS>
-    __device__ __forceinline__ void add(unsigned b, unsigned long long q, unsigned* hist, unsigned long long* m) {
-        bool hit = false;
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-            if (!hit && bin[e] == b) { count[e] += 1u; mass[e] += q; hit = true; }
-        if (hit) return;
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-            if (e == next) { flush_entry<MASS>(e, hist, m); bin[e] = b; count[e] = 1u; mass[e] = q; }
-        next = (next + 1) & 3;
-    }
-    template <bool MASS>
-    __device__ __forceinline__ void flush(unsigned* hist, unsigned long long* m) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) flush_entry<MASS>(e, hist, m);
-    }
-};
+    for (; i < end; ++i)
+        if (!f(i, l[i] * inv_t)) return;
+}
+
+// The unnormalised probability of a scaled logit d = x - max <= 0, the same function wherever the kernel needs it. The
+// fast exponential (2 ulp) is plenty for a draw: one SM works through a whole row, several times, and the accurate
+// one tripled the instructions per element.
+__device__ __forceinline__ float weight(float d) { return __expf(d); }
 
 // One block per row. temperature > 0 for every row given to this kernel.
 __global__ void __launch_bounds__(SAMP_THREADS)
@@ -226,7 +250,9 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
               int* __restrict__ out) {
     __shared__ float scratch[SAMP_THREADS / 32];
     __shared__ unsigned hist[256];
-    __shared__ unsigned long long mass[256];
+    // the masses of a radix pass as three histograms of 14-bit chunks (64-bit adds to shared memory are loops of
+    // compare-and-swap; a chunk's sum over a row of up to 2^18 elements fits 32 bits): mass = m0 + m1 * 2^14 + m2 * 2^28
+    __shared__ unsigned mass3[3][256];
     __shared__ unsigned s_prefix;
     __shared__ unsigned s_remaining;
     __shared__ unsigned long long s_above;
@@ -239,7 +265,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     const int tid = threadIdx.x;
 
     float mx = -INFINITY;
-    for (int i = tid; i < vocab; i += SAMP_THREADS) mx = fmaxf(mx, l[i] * inv_t);
+    for_each_scaled(l, vocab, inv_t, [&](float x) { mx = fmaxf(mx, x); });
     mx = block_max(mx, scratch);
 
     // ---- top-k: key of the k-th largest scaled logit (0 keeps everything)
@@ -253,10 +279,10 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
             __syncthreads();
             const unsigned prefix = s_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = tid; i < vocab; i += SAMP_THREADS) {
-                const unsigned key = key_of(l[i] * inv_t);
+            for_each_scaled(l, vocab, inv_t, [&](float x) {
+                const unsigned key = key_of(x);
                 if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-            }
+            });
             __syncthreads();
             if (tid == 0) {
                 unsigned remaining = s_remaining;
@@ -275,11 +301,11 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 
     // ---- normaliser over what top-k kept
     float z = 0.f;
-    for (int i = tid; i < vocab; i += SAMP_THREADS) {
-        const float x = l[i] * inv_t;
-        if (key_of(x) >= kth_key) z += expf(x - mx);
-    }
+    for_each_scaled(l, vocab, inv_t, [&](float x) {
+        if (key_of(x) >= kth_key) z += weight(x - mx);
+    });
     z = block_sum(z, scratch);
+    const float fix_over_z = FIX_ONE / z;
 
     // ---- top-p: smallest key whose "probability of strictly larger keys" is <= p
     unsigned p_key = kth_key;
@@ -290,30 +316,17 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         if (tid == 0) { s_prefix = 0u; s_above = 0ull; }
         __syncthreads();
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += SAMP_THREADS) { mass[b] = 0ull; hist[b] = 0u; }
+            for (int b = tid; b < 256; b += SAMP_THREADS) { mass3[0][b] = mass3[1][b] = mass3[2][b] = 0u; hist[b] = 0u; }
             __syncthreads();
             const unsigned prefix = s_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            if (shift == 24) {
-                BinCache cache;
-                cache.clear();
-                for (int i = tid; i < vocab; i += SAMP_THREADS) {
-                    const float x = l[i] * inv_t;
-                    const unsigned key = key_of(x);
-                    if (key >= kth_key) cache.add<true>(key >> 24, (unsigned long long)(expf(x - mx) / z * FIX_ONE), hist, mass);
+            for_each_scaled(l, vocab, inv_t, [&](float x) {
+                const unsigned key = key_of(x);
+                if (key >= kth_key && (key & mask) == prefix) {
+                    mass_add(mass3, (key >> shift) & 255u, (unsigned long long)(weight(x - mx) * fix_over_z));
+                    atomicAdd(&hist[(key >> shift) & 255u], 1u);
                 }
-                cache.flush<true>(hist, mass);
-            } else {
-                for (int i = tid; i < vocab; i += SAMP_THREADS) {
-                    const float x = l[i] * inv_t;
-                    const unsigned key = key_of(x);
-                    if (key >= kth_key && (key & mask) == prefix) {
-                        const unsigned long long q = (unsigned long long)(expf(x - mx) / z * FIX_ONE);
-                        atomicAdd(&mass[(key >> shift) & 255u], q);
-                        atomicAdd(&hist[(key >> shift) & 255u], 1u);
-                    }
-                }
-            }
+            });
             __syncthreads();
             if (tid == 0) {
                 // walk down from the largest bin; stay in the lowest non-empty bin whose
@@ -327,7 +340,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
                         if (above <= limit || chosen < 0) { chosen = b; chosen_above = above; }
                     }
                     if (above > limit) break;
-                    above += mass[b];
+                    above += (unsigned long long)mass3[0][b] + ((unsigned long long)mass3[1][b] << 14) + ((unsigned long long)mass3[2][b] << 28);
                 }
                 s_prefix = prefix | ((unsigned)(chosen < 0 ? 0 : chosen) << shift);
                 s_above = chosen_above;
@@ -338,57 +351,91 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         if (p_key < kth_key) p_key = kth_key;
         // ties at p_key: the r-th of them (in vocabulary order) stays iff above + r*q <= limit
         const float xv = float_of_key(p_key);
-        const unsigned long long q = (unsigned long long)(expf(xv - mx) / z * FIX_ONE);
+        const unsigned long long q = (unsigned long long)(weight(xv - mx) * fix_over_z);
         const unsigned long long above = s_above;
         if (q > 0ull && above <= limit) ties_kept = (long long)((limit - above) / q) + 1;
         else ties_kept = 1;
     }
 
     // ---- inverse CDF in vocabulary order over what is kept
-    const int per = (vocab + SAMP_THREADS - 1) / SAMP_THREADS;
+    const int per = ((vocab + SAMP_THREADS - 1) / SAMP_THREADS + 3) & ~3;       // a multiple of 4: chunks start on 16 bytes
     const int begin = min(vocab, tid * per), end = min(vocab, begin + per);
     // rank of ties before this thread's chunk
     __shared__ int tie_count[SAMP_THREADS];
     int my_ties = 0;
     if (ties_kept >= 0)
-        for (int i = begin; i < end; ++i) my_ties += key_of(l[i] * inv_t) == p_key;
+        for_chunk(l, begin, end, inv_t, [&](int, float x) { my_ties += key_of(x) == p_key; return true; });
     tie_count[tid] = my_ties;
     __syncthreads();
-    if (ties_kept >= 0 && tid == 0) {   // exclusive scan, serial (1024 adds)
-        int run = 0;
-        for (int t = 0; t < SAMP_THREADS; ++t) { const int c = tie_count[t]; tie_count[t] = run; run += c; }
+    if (ties_kept >= 0 && tid < 32) {   // exclusive scan by one warp: lane j takes chunks 32j..32j+31 (integers: any order)
+        int mine = 0;
+        for (int t = 0; t < 32; ++t) mine += tie_count[tid * 32 + t];
+        int before = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, before, o);
+            if (tid >= o) before += v;
+        }
+        int run = before - mine;
+        for (int t = 0; t < 32; ++t) { const int c = tie_count[tid * 32 + t]; tie_count[tid * 32 + t] = run; run += c; }
     }
     __syncthreads();
     float csum = 0.f;
     {
         long long tie_rank = tie_count[tid];
-        for (int i = begin; i < end; ++i) {
-            const float x = l[i] * inv_t;
+        for_chunk(l, begin, end, inv_t, [&](int, float x) {
             const unsigned key = key_of(x);
             bool keep = key >= p_key;
             if (keep && ties_kept >= 0 && key == p_key) keep = (tie_rank++) < ties_kept;
-            if (keep) csum += expf(x - mx);
-        }
+            if (keep) csum += weight(x - mx);
+            return true;
+        });
     }
     chunk_sum[tid] = csum;
     __syncthreads();
-    if (tid == 0) {
+    // Which chunk holds the drawn point of the row's mass. The order of the sums is fixed, in two levels, so that one
+    // warp does in a hundred steps what one thread did in three thousand: lane j adds the sums of chunks 32j..32j+31 in
+    // order; lane 0 adds the 32 lane totals in order and finds the lane whose chunks hold the target; that lane then
+    // walks its 32 chunks.
+    __shared__ float lane_total[32];
+    if (tid < 32) {
+        float mine = 0.f;
+        for (int t = 0; t < 32; ++t) mine += chunk_sum[tid * 32 + t];
+        lane_total[tid] = mine;
+        __syncwarp();
         float total = 0.f;
-        for (int t = 0; t < SAMP_THREADS; ++t) total += chunk_sum[t];
+        for (int j = 0; j < 32; ++j) total += lane_total[j];              // every lane: the same sum in the same order
         const float target = uniform[row] * total;
         float run = 0.f;
-        int pick = SAMP_THREADS - 1;
-        for (int t = 0; t < SAMP_THREADS; ++t) {
-            if (chunk_sum[t] > 0.f) pick = t;             // last chunk with mass, if rounding runs past
-            if (run + chunk_sum[t] > target && chunk_sum[t] > 0.f) { pick = t; break; }
-            run += chunk_sum[t];
+        int lane_pick = -1, last_lane = 31;
+        for (int j = 0; j < 32; ++j) {
+            if (lane_total[j] > 0.f) last_lane = j;                      // last lane with mass, if rounding runs past
+            if (lane_pick < 0 && run + lane_total[j] > target && lane_total[j] > 0.f) lane_pick = j;
+            if (lane_pick < 0) run += lane_total[j];
         }
-        s_pick = pick;
-        scratch[0] = target;
-        // mass before the picked chunk
-        float before = 0.f;
-        for (int t = 0; t < pick; ++t) before += chunk_sum[t];
-        scratch[1] = before;
+        if (lane_pick < 0) {                                             // rounding ran past the end: the last chunk with mass
+            lane_pick = last_lane;
+            run = 0.f;
+            for (int j = 0; j < lane_pick; ++j) run += lane_total[j];
+        }
+        if (tid == lane_pick) {
+            int pick = tid * 32 + 31;
+            float before = run;
+            bool found = false;
+            for (int t = 0; t < 32; ++t) {
+                const float c = chunk_sum[tid * 32 + t];
+                if (c > 0.f) pick = tid * 32 + t;                        // last chunk with mass so far
+                if (before + c > target && c > 0.f) { pick = tid * 32 + t; found = true; break; }
+                before += c;
+            }
+            if (!found) {                                                // take the last chunk with mass, and the mass before it
+                before = run;
+                for (int t = tid * 32; t < pick; ++t) before += chunk_sum[t];
+            }
+            s_pick = pick;
+            scratch[0] = target;
+            scratch[1] = before;
+        }
     }
     __syncthreads();
     if (tid == s_pick) {
@@ -396,16 +443,16 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         float run = scratch[1];
         long long tie_rank = tie_count[tid];
         int chosen = -1, last_kept = -1;
-        for (int i = begin; i < end; ++i) {
-            const float x = l[i] * inv_t;
+        for_chunk(l, begin, end, inv_t, [&](int i, float x) {
             const unsigned key = key_of(x);
             bool keep = key >= p_key;
             if (keep && ties_kept >= 0 && key == p_key) keep = (tie_rank++) < ties_kept;
-            if (!keep) continue;
+            if (!keep) return true;
             last_kept = i;
-            run += expf(x - mx);
-            if (run > target) { chosen = i; break; }
-        }
+            run += weight(x - mx);
+            if (run > target) { chosen = i; return false; }
+            return true;
+        });
         out[row] = chosen >= 0 ? chosen : (last_kept >= 0 ? last_kept : 0);
     }
 }
