@@ -7,7 +7,7 @@
 // draw. The draw is an inverse CDF in vocabulary order with a uniform number that the host derives
 // from (seed, number of tokens generated), so a request's tokens do not depend on the batch it
 // was sampled in. The reference samples on the host (cpp/python/ni/scheduler.py:89-147).
-#include "common.cuh"
+#include "pipeline.cuh"
 
 // ---------------------------------------------------------------------------------- penalty
 // seen: flat list of distinct token ids per row, seen_start[row]..seen_start[row+1].
@@ -153,27 +153,6 @@ __device__ __forceinline__ float float_of_key(unsigned k) {
     return __uint_as_float(b);
 }
 
-__device__ float block_max(float v, float* scratch) {
-    v = warp_max(v);
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float r = scratch[0];
-    for (int i = 1; i < SAMP_THREADS / 32; ++i) r = fmaxf(r, scratch[i]);
-    __syncthreads();
-    return r;
-}
-
-// Sum over the block in a fixed order.
-__device__ float block_sum(float v, float* scratch) {
-    v = warp_sum(v);
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float r = 0.f;
-    for (int i = 0; i < SAMP_THREADS / 32; ++i) r += scratch[i];
-    __syncthreads();
-    return r;
-}
-
 // Scaled probabilities are histogrammed as 64-bit fixed point so that sums do not depend on the
 // order in which threads add (integer addition is associative): sampling stays reproducible.
 constexpr float FIX_ONE = 1099511627776.0f;  // 2^40
@@ -190,19 +169,39 @@ __device__ __forceinline__ void mass_add(unsigned (*m)[256], unsigned bin, unsig
     if (c) atomicAdd(&m[2][bin], c);
 }
 
-// f(x) for every scaled logit x = l[i] / temperature of a row, in no particular order: 16-byte loads, two of them in
-// flight per thread, where the row allows (a thread with one 4-byte load in flight waits out the whole latency of the
-// memory system for every element; a pass over 152K logits took 30 us that way). Rows that are not 16-byte aligned or
-// whose length is no multiple of 4 are read element by element.
+// ---- the sampling kernel: a cluster of CS CTAs per row. One SM working through a row of 152K logits a dozen times was
+// the whole cost (0.1 to 2 ms for eight rows); with the row cut into CS slices every pass is CS times shorter, and what
+// the CTAs have to tell each other (maxima, sums, histograms, the radix digit chosen) goes through distributed shared
+// memory between cluster barriers. Everything that decides a token is either an integer sum (histograms of counts
+// and of fixed-point masses: any order gives the same) or a float sum in a fixed order (threads, warps, lanes and CTAs
+// in ascending order), so a row's token depends on the row alone.
+constexpr int ST = 256;      // threads of a CTA
+constexpr int CS = 8;        // CTAs of the cluster that shares a row
+
+__device__ __forceinline__ unsigned ld_peer_u32(unsigned addr) {
+    unsigned v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];\n" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_peer_u64(unsigned addr) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];\n" : "=l"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// f(x) for every scaled logit x = l[i] / temperature of the CTA's slice [begin, end) of a row, in no particular order:
+// 16-byte loads, two of them in flight per thread, where the slice allows (a thread with one 4-byte load in flight waits
+// out the whole latency of the memory system for every element). begin is a multiple of 4.
 template <typename F>
-__device__ __forceinline__ void for_each_scaled(const float* __restrict__ l, int vocab, float inv_t, F&& f) {
+__device__ __forceinline__ void for_each_scaled(const float* __restrict__ l, int begin, int end, float inv_t, F&& f) {
     const int tid = threadIdx.x;
-    if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(l) & 15) == 0) {
-        const float4* l4 = reinterpret_cast<const float4*>(l);
-        const int n4 = vocab >> 2;
+    int done = begin;
+    if ((reinterpret_cast<uintptr_t>(l) & 15) == 0) {
+        const float4* l4 = reinterpret_cast<const float4*>(l + begin);
+        const int n4 = (end - begin) >> 2;
         int i = tid;
-        for (; i + SAMP_THREADS < n4; i += 2 * SAMP_THREADS) {
-            const float4 a = l4[i], b = l4[i + SAMP_THREADS];
+        for (; i + ST < n4; i += 2 * ST) {
+            const float4 a = l4[i], b = l4[i + ST];
             f(a.x * inv_t); f(a.y * inv_t); f(a.z * inv_t); f(a.w * inv_t);
             f(b.x * inv_t); f(b.y * inv_t); f(b.z * inv_t); f(b.w * inv_t);
         }
@@ -210,9 +209,9 @@ __device__ __forceinline__ void for_each_scaled(const float* __restrict__ l, int
             const float4 a = l4[i];
             f(a.x * inv_t); f(a.y * inv_t); f(a.z * inv_t); f(a.w * inv_t);
         }
-    } else {
-        for (int i = tid; i < vocab; i += SAMP_THREADS) f(l[i] * inv_t);
+        done = begin + 4 * n4;
     }
+    for (int i = done + tid; i < end; i += ST) f(l[i] * inv_t);
 }
 
 // f(i, x) for i = begin .. end - 1 in ascending order (a thread's chunk of a row), until f returns false. 16-byte loads,
@@ -239,72 +238,144 @@ __device__ __forceinline__ void for_chunk(const float* __restrict__ l, int begin
 }
 
 // The unnormalised probability of a scaled logit d = x - max <= 0, the same function wherever the kernel needs it. The
-// fast exponential (2 ulp) is plenty for a draw: one SM works through a whole row, several times, and the accurate
-// one tripled the instructions per element.
+// fast exponential (2 ulp) is plenty for a draw.
 __device__ __forceinline__ float weight(float d) { return __expf(d); }
 
-// One block per row. temperature > 0 for every row given to this kernel.
-__global__ void __launch_bounds__(SAMP_THREADS)
+// temperature > 0 for every row given to this kernel. grid: CS CTAs (one cluster) per row.
+__global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
               int* __restrict__ out) {
-    __shared__ float scratch[SAMP_THREADS / 32];
-    __shared__ unsigned hist[256];
-    // the masses of a radix pass as three histograms of 14-bit chunks (64-bit adds to shared memory are loops of
-    // compare-and-swap; a chunk's sum over a row of up to 2^18 elements fits 32 bits): mass = m0 + m1 * 2^14 + m2 * 2^28
+    using namespace nibp;
+    __shared__ float scratch[ST / 32];
+    __shared__ unsigned hist[256];                  // this CTA's histogram of a radix pass
+    // ... and its masses as three histograms of 14-bit chunks: mass = m0 + m1 * 2^14 + m2 * 2^28
     __shared__ unsigned mass3[3][256];
-    __shared__ unsigned s_prefix;
-    __shared__ unsigned s_remaining;
-    __shared__ unsigned long long s_above;
-    __shared__ float chunk_sum[SAMP_THREADS];
+    __shared__ unsigned tot_hist[256];              // CTA 0: the cluster's sums
+    __shared__ unsigned long long tot_mass[256];
+    __shared__ unsigned dec_prefix, dec_remaining;  // CTA 0: what a radix pass decided, read by every CTA
+    __shared__ unsigned long long dec_above;
+    __shared__ float x_max, x_z, x_total;           // what this CTA tells the others
+    __shared__ int x_ties;
+    __shared__ float chunk_sum[ST];
+    __shared__ int tie_count[ST];
+    __shared__ float lane_total[32];
     __shared__ int s_pick;
 
-    const int row = blockIdx.x;
+    const int row = blockIdx.x / CS;
+    const unsigned rank = cluster_rank();
     const float* l = logits + (size_t)row * vocab;
     const float inv_t = 1.0f / temperature[row];
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+    // a thread's chunk of the row (vocabulary order: rank, then thread), a multiple of 4 long so that chunks start on 16 bytes
+    const int per = ((vocab + CS * ST - 1) / (CS * ST) + 3) & ~3;
+    const int begin = min(vocab, ((int)rank * ST + tid) * per), end = min(vocab, begin + per);
+    const int s_begin = min(vocab, (int)rank * ST * per), s_end = min(vocab, s_begin + ST * per);
+
+    auto cta_reduce = [&](float v, bool is_max) -> float {      // over the CTA, in a fixed order
+        v = is_max ? warp_max(v) : warp_sum(v);
+        if (lane == 0) scratch[warp] = v;
+        __syncthreads();
+        float r = scratch[0];
+        for (int i = 1; i < ST / 32; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
+        __syncthreads();
+        return r;
+    };
+
+    // ---- the row's maximum
     float mx = -INFINITY;
-    for_each_scaled(l, vocab, inv_t, [&](float x) { mx = fmaxf(mx, x); });
-    mx = block_max(mx, scratch);
+    for_each_scaled(l, s_begin, s_end, inv_t, [&](float x) { mx = fmaxf(mx, x); });
+    mx = cta_reduce(mx, true);
+    if (tid == 0) x_max = mx;
+    cluster_sync();
+    for (unsigned r = 0; r < CS; ++r) mx = fmaxf(mx, ld_peer_f32(peer_smem(&x_max, r)));
+
+    // One radix pass over the slice: histogram (and masses), summed over the cluster by CTA 0, whose thread 0 then
+    // chooses the digit (``choose``) and leaves the decision where every CTA reads it after the second barrier.
+    auto radix_pass = [&](bool with_mass, auto&& add, auto&& choose) {
+        for (int b = tid; b < 256; b += ST) { hist[b] = 0u; mass3[0][b] = mass3[1][b] = mass3[2][b] = 0u; }
+        __syncthreads();
+        for_each_scaled(l, s_begin, s_end, inv_t, add);
+        __syncthreads();
+        cluster_sync();
+        if (rank == 0) {
+            for (int b = tid; b < 256; b += ST) {
+                unsigned n = 0u;
+                unsigned long long m = 0ull;
+                for (unsigned r = 0; r < CS; ++r) {
+                    n += ld_peer_u32(peer_smem(&hist[b], r));
+                    if (with_mass)
+                        m += (unsigned long long)ld_peer_u32(peer_smem(&mass3[0][b], r)) +
+                             ((unsigned long long)ld_peer_u32(peer_smem(&mass3[1][b], r)) << 14) +
+                             ((unsigned long long)ld_peer_u32(peer_smem(&mass3[2][b], r)) << 28);
+                }
+                tot_hist[b] = n;
+                tot_mass[b] = m;
+            }
+            __syncthreads();
+            if (tid < 32) choose();          // warp 0: lane j looks at the bins 8j..8j+7
+        }
+        cluster_sync();
+    };
 
     // ---- top-k: key of the k-th largest scaled logit (0 keeps everything)
     unsigned kth_key = 0u;
-    int k = top_k[row];
+    const int k = top_k[row];
     if (k > 0 && k < vocab) {
-        if (tid == 0) { s_prefix = 0u; s_remaining = (unsigned)k; }
-        __syncthreads();
+        unsigned prefix = 0u, remaining = (unsigned)k;
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += SAMP_THREADS) hist[b] = 0u;
-            __syncthreads();
-            const unsigned prefix = s_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            for_each_scaled(l, vocab, inv_t, [&](float x) {
-                const unsigned key = key_of(x);
-                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-            });
-            __syncthreads();
-            if (tid == 0) {
-                unsigned remaining = s_remaining;
-                int b = 255;
-                for (; b > 0; --b) {
-                    if (hist[b] >= remaining) break;
-                    remaining -= hist[b];
-                }
-                s_prefix = prefix | ((unsigned)b << shift);
-                s_remaining = remaining;
-            }
-            __syncthreads();
+            radix_pass(false,
+                       [&](float x) {
+                           const unsigned key = key_of(x);
+                           if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+                       },
+                       [&]() {
+                           // the highest bin b >= 1 with (elements in bins >= b) >= remaining, else bin 0; what is still to
+                           // find inside it: remaining - (elements in the bins above b)
+                           unsigned mine = 0u;
+                           for (int i = 0; i < 8; ++i) mine += tot_hist[lane * 8 + i];
+                           unsigned above = mine;                       // inclusive sum over this lane and the lanes above
+#pragma unroll
+                           for (int o = 1; o < 32; o <<= 1) {
+                               const unsigned v = __shfl_down_sync(0xffffffffu, above, o);
+                               if (lane + o < 32) above += v;
+                           }
+                           above -= mine;                               // elements in the bins above this lane's
+                           int found = -1;
+                           unsigned rem_found = 0u, run = above;
+                           for (int i = 7; i >= 0; --i) {
+                               const int b = lane * 8 + i;
+                               if (found < 0 && b > 0 && run + tot_hist[b] >= remaining) { found = b; rem_found = remaining - run; }
+                               run += tot_hist[b];
+                           }
+                           const unsigned has = __ballot_sync(0xffffffffu, found >= 0);
+                           const int top = has ? 31 - __clz(has) : 0;   // the highest lane that found one holds the highest bin
+                           const int b = __shfl_sync(0xffffffffu, found, top);
+                           const unsigned r = __shfl_sync(0xffffffffu, rem_found, top);
+                           const unsigned all = __shfl_sync(0xffffffffu, above + mine, 0);       // every element that matched
+                           if (lane == 0) {
+                               dec_prefix = prefix | ((unsigned)(has ? b : 0) << shift);
+                               dec_remaining = has ? r : remaining - (all - tot_hist[0]);
+                           }
+                       });
+            prefix = ld_peer_u32(peer_smem(&dec_prefix, 0));
+            remaining = ld_peer_u32(peer_smem(&dec_remaining, 0));
         }
-        kth_key = s_prefix;
+        kth_key = prefix;
     }
 
-    // ---- normaliser over what top-k kept
+    // ---- normaliser over what top-k kept: threads, warps, CTAs in ascending order
     float z = 0.f;
-    for_each_scaled(l, vocab, inv_t, [&](float x) {
+    for_each_scaled(l, s_begin, s_end, inv_t, [&](float x) {
         if (key_of(x) >= kth_key) z += weight(x - mx);
     });
-    z = block_sum(z, scratch);
+    z = cta_reduce(z, false);
+    if (tid == 0) x_z = z;
+    cluster_sync();
+    z = 0.f;
+    for (unsigned r = 0; r < CS; ++r) z += ld_peer_f32(peer_smem(&x_z, r));
     const float fix_over_z = FIX_ONE / z;
 
     // ---- top-p: smallest key whose "probability of strictly larger keys" is <= p
@@ -313,155 +384,217 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     const float tp = top_p[row];
     if (tp < 1.0f) {
         const unsigned long long limit = (unsigned long long)((double)tp * (double)FIX_ONE);
-        if (tid == 0) { s_prefix = 0u; s_above = 0ull; }
-        __syncthreads();
+        unsigned prefix = 0u;
+        unsigned long long above0 = 0ull;
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += SAMP_THREADS) { mass3[0][b] = mass3[1][b] = mass3[2][b] = 0u; hist[b] = 0u; }
-            __syncthreads();
-            const unsigned prefix = s_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            for_each_scaled(l, vocab, inv_t, [&](float x) {
-                const unsigned key = key_of(x);
-                if (key >= kth_key && (key & mask) == prefix) {
-                    mass_add(mass3, (key >> shift) & 255u, (unsigned long long)(weight(x - mx) * fix_over_z));
-                    atomicAdd(&hist[(key >> shift) & 255u], 1u);
-                }
-            });
-            __syncthreads();
-            if (tid == 0) {
-                // walk down from the largest bin; stay in the lowest non-empty bin whose
-                // "mass above" is still within the limit
-                unsigned long long above = s_above;
-                int chosen = -1;
-                unsigned long long chosen_above = above;
-                for (int b = 255; b >= 0; --b) {
-                    if (hist[b] == 0u) continue;
-                    if (above <= limit || chosen < 0) {   // the very first (largest) element always stays
-                        if (above <= limit || chosen < 0) { chosen = b; chosen_above = above; }
-                    }
-                    if (above > limit) break;
-                    above += (unsigned long long)mass3[0][b] + ((unsigned long long)mass3[1][b] << 14) + ((unsigned long long)mass3[2][b] << 28);
-                }
-                s_prefix = prefix | ((unsigned)(chosen < 0 ? 0 : chosen) << shift);
-                s_above = chosen_above;
-            }
-            __syncthreads();
+            radix_pass(true,
+                       [&](float x) {
+                           const unsigned key = key_of(x);
+                           if (key >= kth_key && (key & mask) == prefix) {
+                               mass_add(mass3, (key >> shift) & 255u, (unsigned long long)(weight(x - mx) * fix_over_z));
+                               atomicAdd(&hist[(key >> shift) & 255u], 1u);
+                           }
+                       },
+                       [&]() {
+                           // the lowest non-empty bin whose "mass above" (the bins above it, and what earlier passes left
+                           // above) is still within the limit; the very first (largest) element always stays, so if even
+                           // the highest non-empty bin is past the limit, that one
+                           unsigned long long mine = 0ull;
+                           for (int i = 0; i < 8; ++i) mine += tot_mass[lane * 8 + i];
+                           unsigned long long above = mine;
+#pragma unroll
+                           for (int o = 1; o < 32; o <<= 1) {
+                               const unsigned long long v = __shfl_down_sync(0xffffffffu, above, o);
+                               if (lane + o < 32) above += v;
+                           }
+                           above = above - mine + above0;               // mass above this lane's bins
+                           int low = -1, high = -1;
+                           unsigned long long low_above = 0ull, high_above = 0ull, run = above;
+                           for (int i = 7; i >= 0; --i) {
+                               const int b = lane * 8 + i;
+                               if (tot_hist[b] != 0u) {
+                                   if (high < 0) { high = b; high_above = run; }
+                                   if (run <= limit) { low = b; low_above = run; }
+                               }
+                               run += tot_mass[b];
+                           }
+                           const unsigned within = __ballot_sync(0xffffffffu, low >= 0), any = __ballot_sync(0xffffffffu, high >= 0);
+                           int chosen = 0;
+                           unsigned long long chosen_above = above0;
+                           if (within) {                                // the lowest lane with one holds the lowest such bin
+                               const int src = __ffs(within) - 1;
+                               chosen = __shfl_sync(0xffffffffu, low, src);
+                               chosen_above = __shfl_sync(0xffffffffu, low_above, src);
+                           } else if (any) {
+                               const int src = 31 - __clz(any);
+                               chosen = __shfl_sync(0xffffffffu, high, src);
+                               chosen_above = __shfl_sync(0xffffffffu, high_above, src);
+                           }
+                           if (lane == 0) {
+                               dec_prefix = prefix | ((unsigned)chosen << shift);
+                               dec_above = chosen_above;
+                           }
+                       });
+            prefix = ld_peer_u32(peer_smem(&dec_prefix, 0));
+            above0 = ld_peer_u64(peer_smem(&dec_above, 0));
         }
-        p_key = s_prefix;
+        p_key = prefix;
         if (p_key < kth_key) p_key = kth_key;
         // ties at p_key: the r-th of them (in vocabulary order) stays iff above + r*q <= limit
         const float xv = float_of_key(p_key);
         const unsigned long long q = (unsigned long long)(weight(xv - mx) * fix_over_z);
-        const unsigned long long above = s_above;
-        if (q > 0ull && above <= limit) ties_kept = (long long)((limit - above) / q) + 1;
+        if (q > 0ull && above0 <= limit) ties_kept = (long long)((limit - above0) / q) + 1;
         else ties_kept = 1;
     }
 
     // ---- inverse CDF in vocabulary order over what is kept
-    const int per = ((vocab + SAMP_THREADS - 1) / SAMP_THREADS + 3) & ~3;       // a multiple of 4: chunks start on 16 bytes
-    const int begin = min(vocab, tid * per), end = min(vocab, begin + per);
-    // rank of ties before this thread's chunk
-    __shared__ int tie_count[SAMP_THREADS];
-    int my_ties = 0;
-    if (ties_kept >= 0)
+    // rank of the ties before this thread's chunk: the CTAs before this one, then the threads before it (lane j of warp
+    // 0 takes the chunks 8j..8j+7; integers, so any order gives the same)
+    long long tie_rank = 0;
+    if (ties_kept >= 0) {
+        int my_ties = 0;
         for_chunk(l, begin, end, inv_t, [&](int, float x) { my_ties += key_of(x) == p_key; return true; });
-    tie_count[tid] = my_ties;
-    __syncthreads();
-    if (ties_kept >= 0 && tid < 32) {   // exclusive scan by one warp: lane j takes chunks 32j..32j+31 (integers: any order)
-        int mine = 0;
-        for (int t = 0; t < 32; ++t) mine += tie_count[tid * 32 + t];
-        int before = mine;
+        tie_count[tid] = my_ties;
+        __syncthreads();
+        if (tid < 32) {
+            constexpr int G = ST / 32;
+            int mine = 0;
+            for (int t = 0; t < G; ++t) mine += tie_count[tid * G + t];
+            int before = mine;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, before, o);
-            if (tid >= o) before += v;
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, before, o);
+                if (tid >= o) before += v;
+            }
+            if (tid == 31) x_ties = before;
+            int run = before - mine;
+            for (int t = 0; t < G; ++t) { const int c = tie_count[tid * G + t]; tie_count[tid * G + t] = run; run += c; }
         }
-        int run = before - mine;
-        for (int t = 0; t < 32; ++t) { const int c = tie_count[tid * 32 + t]; tie_count[tid * 32 + t] = run; run += c; }
+        __syncthreads();
+        cluster_sync();
+        tie_rank = tie_count[tid];
+        for (unsigned r = 0; r < rank; ++r) tie_rank += (int)ld_peer_u32(peer_smem(&x_ties, r));
     }
-    __syncthreads();
     float csum = 0.f;
     {
-        long long tie_rank = tie_count[tid];
+        long long tr = tie_rank;
         for_chunk(l, begin, end, inv_t, [&](int, float x) {
             const unsigned key = key_of(x);
             bool keep = key >= p_key;
-            if (keep && ties_kept >= 0 && key == p_key) keep = (tie_rank++) < ties_kept;
+            if (keep && ties_kept >= 0 && key == p_key) keep = (tr++) < ties_kept;
             if (keep) csum += weight(x - mx);
             return true;
         });
     }
     chunk_sum[tid] = csum;
     __syncthreads();
-    // Which chunk holds the drawn point of the row's mass. The order of the sums is fixed, in two levels, so that one
-    // warp does in a hundred steps what one thread did in three thousand: lane j adds the sums of chunks 32j..32j+31 in
-    // order; lane 0 adds the 32 lane totals in order and finds the lane whose chunks hold the target; that lane then
-    // walks its 32 chunks.
-    __shared__ float lane_total[32];
+    // The sums in a fixed order, in three levels: lane j of warp 0 adds the sums of the CTA's chunks 8j..8j+7 in order and
+    // the 32 lane totals in order; the CTAs' totals are added in rank order. The CTA whose chunks hold the drawn point
+    // of the row's mass finds the lane, the lane its chunk, the chunk's thread the element.
+    constexpr int G = ST / 32;
     if (tid < 32) {
         float mine = 0.f;
-        for (int t = 0; t < 32; ++t) mine += chunk_sum[tid * 32 + t];
+        for (int t = 0; t < G; ++t) mine += chunk_sum[tid * G + t];
         lane_total[tid] = mine;
         __syncwarp();
-        float total = 0.f;
-        for (int j = 0; j < 32; ++j) total += lane_total[j];              // every lane: the same sum in the same order
-        const float target = uniform[row] * total;
-        float run = 0.f;
-        int lane_pick = -1, last_lane = 31;
-        for (int j = 0; j < 32; ++j) {
-            if (lane_total[j] > 0.f) last_lane = j;                      // last lane with mass, if rounding runs past
-            if (lane_pick < 0 && run + lane_total[j] > target && lane_total[j] > 0.f) lane_pick = j;
-            if (lane_pick < 0) run += lane_total[j];
-        }
-        if (lane_pick < 0) {                                             // rounding ran past the end: the last chunk with mass
-            lane_pick = last_lane;
-            run = 0.f;
-            for (int j = 0; j < lane_pick; ++j) run += lane_total[j];
-        }
-        if (tid == lane_pick) {
-            int pick = tid * 32 + 31;
-            float before = run;
-            bool found = false;
-            for (int t = 0; t < 32; ++t) {
-                const float c = chunk_sum[tid * 32 + t];
-                if (c > 0.f) pick = tid * 32 + t;                        // last chunk with mass so far
-                if (before + c > target && c > 0.f) { pick = tid * 32 + t; found = true; break; }
-                before += c;
-            }
-            if (!found) {                                                // take the last chunk with mass, and the mass before it
-                before = run;
-                for (int t = tid * 32; t < pick; ++t) before += chunk_sum[t];
-            }
-            s_pick = pick;
-            scratch[0] = target;
-            scratch[1] = before;
+        if (tid == 0) {
+            float total = 0.f;
+            for (int j = 0; j < 32; ++j) total += lane_total[j];
+            x_total = total;
         }
     }
     __syncthreads();
-    if (tid == s_pick) {
-        const float target = scratch[0];
-        float run = scratch[1];
-        long long tie_rank = tie_count[tid];
-        int chosen = -1, last_kept = -1;
-        for_chunk(l, begin, end, inv_t, [&](int i, float x) {
-            const unsigned key = key_of(x);
-            bool keep = key >= p_key;
-            if (keep && ties_kept >= 0 && key == p_key) keep = (tie_rank++) < ties_kept;
-            if (!keep) return true;
-            last_kept = i;
-            run += weight(x - mx);
-            if (run > target) { chosen = i; return false; }
-            return true;
-        });
-        out[row] = chosen >= 0 ? chosen : (last_kept >= 0 ? last_kept : 0);
+    cluster_sync();
+    float cta_total[CS], total = 0.f;
+    for (unsigned r = 0; r < CS; ++r) { cta_total[r] = ld_peer_f32(peer_smem(&x_total, r)); total += cta_total[r]; }
+    const float target = uniform[row] * total;
+    // which CTA: the first whose totals reach past the target; if rounding runs past the end, the last with mass
+    int cta_pick = -1, last_cta = CS - 1;
+    float cta_before = 0.f;
+    {
+        float run = 0.f;
+        for (int r = 0; r < CS; ++r) {
+            if (cta_total[r] > 0.f) last_cta = r;
+            if (cta_pick < 0 && run + cta_total[r] > target && cta_total[r] > 0.f) { cta_pick = r; cta_before = run; }
+            if (cta_pick < 0) run += cta_total[r];
+        }
+        if (cta_pick < 0) {
+            cta_pick = last_cta;
+            cta_before = 0.f;
+            for (int r = 0; r < cta_pick; ++r) cta_before += cta_total[r];
+        }
     }
+    if ((int)rank == cta_pick) {
+        if (tid < 32) {
+            float run = cta_before;
+            int lane_pick = -1, last_lane = 31;
+            for (int j = 0; j < 32; ++j) {
+                if (lane_total[j] > 0.f) last_lane = j;
+                if (lane_pick < 0 && run + lane_total[j] > target && lane_total[j] > 0.f) lane_pick = j;
+                if (lane_pick < 0) run += lane_total[j];
+            }
+            if (lane_pick < 0) {
+                lane_pick = last_lane;
+                run = cta_before;
+                for (int j = 0; j < lane_pick; ++j) run += lane_total[j];
+            }
+            if (tid == lane_pick) {
+                int pick = tid * G + G - 1;
+                float before = run;
+                bool found = false;
+                for (int t = 0; t < G; ++t) {
+                    const float c = chunk_sum[tid * G + t];
+                    if (c > 0.f) pick = tid * G + t;
+                    if (before + c > target && c > 0.f) { pick = tid * G + t; found = true; break; }
+                    before += c;
+                }
+                if (!found) {
+                    before = run;
+                    for (int t = tid * G; t < pick; ++t) before += chunk_sum[t];
+                }
+                s_pick = pick;
+                scratch[0] = before;
+            }
+        }
+        __syncthreads();
+        if (tid == s_pick) {
+            float run = scratch[0];
+            long long tr = tie_rank;
+            int chosen = -1, last_kept = -1;
+            for_chunk(l, begin, end, inv_t, [&](int i, float x) {
+                const unsigned key = key_of(x);
+                bool keep = key >= p_key;
+                if (keep && ties_kept >= 0 && key == p_key) keep = (tr++) < ties_kept;
+                if (!keep) return true;
+                last_kept = i;
+                run += weight(x - mx);
+                if (run > target) { chosen = i; return false; }
+                return true;
+            });
+            out[row] = chosen >= 0 ? chosen : (last_kept >= 0 ? last_kept : 0);
+        }
+    }
+    cluster_sync();         // nobody leaves while a peer may still read its shared memory
 }
 
 NIB_API int nib_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,
                        const float* top_p, const float* uniform, int* out, cudaStream_t stream) {
     NIB_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes");
     if (rows == 0) return 0;
-    sample_kernel<<<rows, SAMP_THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, uniform, out);
+    NIB_REQUIRE((long long)vocab <= (1LL << 17) * 8, "sample: a row of %d logits is more than the fixed-point histograms hold", vocab);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * CS);
+    cfg.blockDim = dim3(ST);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    NIB_CUDA(cudaLaunchKernelEx(&cfg, sample_kernel, logits, vocab, temperature, top_k, top_p, uniform, out));
     NIB_LAUNCH_CHECK();
     return 0;
 }
