@@ -294,7 +294,7 @@ def test_part_attention_whole_and_cut(dtype, heads, kv_heads, hd, window, bias):
 
 
 # ------------------------------------------------------------------------------- sampling kernels
-@pytest.mark.parametrize("vocab", [503, 151936])
+@pytest.mark.parametrize("vocab", [13, 503, 4100, 151936])      # a row smaller than the cluster's slices; odd; aligned; the real one
 def test_sampling_kernels_follow_the_plain_pipeline(vocab):
     import numpy as np
     from plain_qwen2 import greedy_pick, sampling_distribution
@@ -304,7 +304,7 @@ def test_sampling_kernels_follow_the_plain_pipeline(vocab):
     g = torch.Generator().manual_seed(5)
     base = torch.randn(1, vocab, generator=g) * 3.0
     base[0, 7] = base[0, 11] = base.max() + 0.5       # a tie at the top
-    context = [7, 3, 3, 100, vocab - 1]
+    context = [7, 3, 3, min(100, vocab - 3), vocab - 1]
     cases = [SamplingParams(temperature=0.7), SamplingParams(temperature=1.3, top_k=40),
              SamplingParams(temperature=0.9, top_p=0.8), SamplingParams(temperature=1.0, top_k=200, top_p=0.5),
              SamplingParams(temperature=0.5, repetition_penalty=1.7, top_k=5), SamplingParams(temperature=2.0, top_k=1)]
