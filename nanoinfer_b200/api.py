@@ -47,6 +47,14 @@ class Model:
                           seed=seed, eos_id=eos_id))
         return sched.run()["generate"]      # run() gives back what the request holds if a step raises
 
+    def weight_bytes(self):
+        """(bytes the weights take on the device, the same with every element in 32-bit), as the reference's
+        ``Model.weight_bytes`` (cpp/bindings/nicpp.cpp:317)."""
+        return self.engine.model.weight_bytes()
+
+    def weight_breakdown(self):
+        """dtype name -> (tensors, bytes) (the reference lists its storage formats: cpp/src/model.cpp:320-334)."""
+        return self.engine.model.weight_breakdown()
 
     def _generate_recomputing(self, ids: List[int], max_tokens: int, params: SamplingParams, seed: int,
                               eos_id: int) -> List[int]:

@@ -47,7 +47,12 @@ def main(argv=None) -> int:
     print(f"served {len(prompts)} prompts, max_batch={args.max_batch}, "
           f"cache=paged(block_size={args.page_size}, {args.num_pages} blocks): {sched.steps} steps, "
           f"peak_batch={sched.peak_batch}, preemptions={sched.preemptions}, "
-          f"{n_tok} tokens in {dt:.2f}s ({n_tok / dt:.1f} tok/s)\n")
+          f"{n_tok} tokens in {dt:.2f}s ({n_tok / dt:.1f} tok/s)")
+    st = sched.stats()
+    actual, as_fp32 = model.weight_bytes()
+    print(f"steps: {st['tokens_per_step']:.1f} tokens a step, at most {st['peak_step_tokens']}; "
+          f"{st['prompt_steps']} with a prompt's portion at {100 * st['budget_use']:.0f}% of the budget of "
+          f"{sched.max_tokens_per_step}; weights {actual / 2**20:.1f} MiB ({as_fp32 / 2**20:.1f} MiB in 32-bit)\n")
     for rid, text in prompts.items():
         print(f"Prompt: {text}")
         print(f"Completion: {tok.decode(out[rid])}\n")

@@ -124,6 +124,9 @@ class Scheduler:
         self.steps = 0
         self.peak_batch = 0
         self.tokens_run = 0
+        self.peak_step_tokens = 0       # the most tokens that one step carried
+        self.prompt_steps = 0           # steps that carried a portion of a prompt ...
+        self.prompt_step_tokens = 0     # ... and the tokens of those steps (against the budget: stats())
         self.preemptions = 0
 
     # ---- queue ----------------------------------------------------------------------------
@@ -280,6 +283,7 @@ class Scheduler:
         self._resolve_inflight()
         self._inflight = (list(seqs), nxt)
         self.tokens_run += len(seqs)
+        self.peak_step_tokens = max(self.peak_step_tokens, len(seqs))
         self.peak_batch = max(self.peak_batch, len(seqs))
         self.steps += 1
         self.steps_ahead += 1
@@ -319,10 +323,24 @@ class Scheduler:
                 if e.samples and e.seq.req.max_tokens <= 0 and e.seq.state is State.RUNNING:
                     self._finish(e.seq)
             self.tokens_run += plan.num_tokens
+            self.peak_step_tokens = max(self.peak_step_tokens, plan.num_tokens)
+            if any(e.count > 1 or not e.samples for e in plan.entries):
+                self.prompt_steps += 1
+                self.prompt_step_tokens += plan.num_tokens
         self.running = [s for s in self.running if s.state is State.RUNNING]
         self.peak_batch = max(self.peak_batch, len(plan.entries))
         self.steps += 1
         return plan
+
+    def stats(self) -> Dict[str, float]:
+        """Counters of what ran so far. ``budget_use`` is the mean share of ``max_tokens_per_step`` that the steps
+        with a portion of a prompt carried (1.0 = every such step was full); the reference's scheduler keeps
+        ``peak_batch`` alone (cpp/src/scheduler.cpp)."""
+        use = self.prompt_step_tokens / (self.prompt_steps * self.max_tokens_per_step) if self.prompt_steps else 0.0
+        return {"steps": self.steps, "tokens_run": self.tokens_run, "peak_batch": self.peak_batch,
+                "peak_step_tokens": self.peak_step_tokens, "prompt_steps": self.prompt_steps,
+                "tokens_per_step": self.tokens_run / self.steps if self.steps else 0.0, "budget_use": use,
+                "steps_ahead": self.steps_ahead, "preemptions": self.preemptions}
 
     def cancel(self, request_id: str) -> bool:
         """Queued: dropped with an empty output. Running: finished with what it has; pages are freed."""

@@ -27,7 +27,8 @@ class DecoderModel:
         self.plan, self.rt = plan, rt
         # A tensor used by two parts (a tied head) is moved to the device once.
         memo: Dict[Tuple[int, str], torch.Tensor] = {}
-        shared = _SharingRuntime(rt, memo)
+        self._weights: List[torch.Tensor] = []       # every device tensor handed to a part, once each
+        shared = _SharingRuntime(rt, memo, self._weights)
         self.embedding = _build_part(plan.embedding, tensors, shared)
         self.positions = {name: _build_part(p, tensors, shared) for name, p in plan.positions.items()}
         self.layers = []
@@ -66,6 +67,22 @@ class DecoderModel:
                 return False
         return all(getattr(p, "graph_safe", False) for p in parts)
 
+    # -- what the weights take -------------------------------------------------------------------
+    def weight_breakdown(self) -> Dict[str, Tuple[int, int]]:
+        """dtype name -> (tensors, bytes) over the device tensors that the parts were given (a tied head counts once)."""
+        out: Dict[str, Tuple[int, int]] = {}
+        for t in self._weights:
+            name = str(t.dtype).replace("torch.", "")
+            n, b = out.get(name, (0, 0))
+            out[name] = (n + 1, b + t.numel() * t.element_size())
+        return out
+
+    def weight_bytes(self) -> Tuple[int, int]:
+        """(bytes the weights take on the device, bytes they would take with every element in 32-bit): the pair
+        that the reference reports (cpp/src/model.cpp:298-318)."""
+        actual = sum(t.numel() * t.element_size() for t in self._weights)
+        return actual, sum(t.numel() * 4 for t in self._weights)
+
     # -- one step ------------------------------------------------------------------------------
     def forward(self, ctx: StepContext, caches: List[LayerCache],
                 want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -93,18 +110,20 @@ class DecoderModel:
 class _SharingRuntime(Runtime):
     """A runtime whose ``matrix`` / ``vector32`` return one device copy per source tensor."""
 
-    def __init__(self, rt: Runtime, memo):
+    def __init__(self, rt: Runtime, memo, made):
         super().__init__(rt.device, rt.dtype, rt.ops)
-        self._memo = memo
+        self._memo, self._made = memo, made
 
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
         key = (id(t), "m")
         if key not in self._memo:
             self._memo[key] = (t, Runtime.matrix(self, t))
+            self._made.append(self._memo[key][1])
         return self._memo[key][1]
 
     def vector32(self, t: torch.Tensor) -> torch.Tensor:
         key = (id(t), "v")
         if key not in self._memo:
             self._memo[key] = (t, Runtime.vector32(self, t))
+            self._made.append(self._memo[key][1])
         return self._memo[key][1]

@@ -100,3 +100,19 @@ def test_error_words_are_decoded():
     assert "kernel one: a bounded wait ran out in block 7 (copy warp)" in str(e.value)
     assert "kernel two: the error word could not be read" in str(e.value)
     assert "code 9" in str(e.value)
+
+
+@pytest.mark.parametrize("tied", [False, True])
+def test_weight_bytes_count_every_tensor_of_the_file_once(tmp_path, tied):
+    """(actual, 32-bit) as the reference reports them (cpp/src/model.cpp:298-318); a tied head is one tensor."""
+    import math
+    from nanoinfer_b200.weights.safetensors_io import open_model_files
+    config = config_from_json_dict(dict(TINY_A, tie_word_embeddings=tied))
+    write_random_model(config, str(tmp_path), seed=3)
+    shapes = [f.shape(n) for f in open_model_files(str(tmp_path)) for n in f.names()]
+    elements = sum(math.prod(s) for s in shapes)
+    assert sum(s == (config.vocab_size, config.hidden_size) for s in shapes) == (1 if tied else 2)
+    m = host_model(str(tmp_path))
+    actual, as_fp32 = m.weight_bytes()
+    assert actual == as_fp32 == 4 * elements                   # the host model of the tests is 32-bit throughout
+    assert list(m.weight_breakdown()) == ["float32"] and m.weight_breakdown()["float32"][1] == actual

@@ -74,6 +74,7 @@ def test_serve_cli(model_dirs, host_engine, capsys):
     assert serve.main(argv) == 0
     out = capsys.readouterr().out
     assert "served 3 prompts, max_batch=2" in out and "peak_batch=2" in out and "18 tokens" in out
+    assert "tokens a step, at most " in out and "% of the budget of " in out and "MiB in 32-bit" in out
     want = [" ".join(map(str, plain.greedy([int(t) for t in p.split()], 6))) for p in prompts]
     assert completions(out) == want
     assert [line for line in out.splitlines() if line.startswith("Prompt: ")] == [f"Prompt: {p}" for p in prompts]

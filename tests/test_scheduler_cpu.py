@@ -49,6 +49,10 @@ def test_budget_cuts_prompts_and_decodes_come_first(model_dirs):
     assert [(e.seq.req.request_id, e.count, e.samples) for e in plan.entries] == [("a", 1, True), ("b", 3, True)]
     out = s.run()
     assert len(out["a"]) == 4 and len(out["b"]) == 4
+    st = s.stats()      # four steps carried a prompt's portion: 10, 10, 10 and 4 tokens of a budget of 10
+    assert (st["prompt_steps"], st["peak_step_tokens"], st["peak_batch"]) == (4, 10, 2)
+    assert st["budget_use"] == pytest.approx(34 / 40)
+    assert st["tokens_run"] == 25 + 8 + 3 + 3 and st["tokens_per_step"] == pytest.approx(st["tokens_run"] / st["steps"])
     plain = PlainModel(d)
     assert out["a"] == plain.greedy(a, 4) and out["b"] == plain.greedy(b, 4)
 
