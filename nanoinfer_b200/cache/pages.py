@@ -285,6 +285,13 @@ class CacheManager:
     def table_width(self, rcs: Sequence[RequestCache]) -> int:
         return max((len(t) for rc in rcs for t in rc.tables), default=0)
 
+    def table_widths(self, positions: int) -> List[int]:
+        """Per group, the block-table entries that address ``positions`` positions of a request. A captured step asks
+        here for its tables' widths, so a group with pages of another size, or with a table of fixed width, answers
+        for itself in this one place. (A windowed group keeps one entry per page of the whole sequence, the ones
+        behind the window being -1, so today every group answers alike.)"""
+        return [max(1, -(-positions // self.page_size)) for _ in self.groups]
+
     def num_free(self, group: int = 0) -> int:
         return self.pools[group].num_free
 

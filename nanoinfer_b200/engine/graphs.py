@@ -126,9 +126,7 @@ class DecodeGraphs:
         rb = _bucket(len(entries))
         max_ctx = max(e.request.length + 1 for e in entries)
         cb = max(256, _bucket(max_ctx))
-        page = eng.cache.page_size
-        widths = [max(1, -(-cb // page)) for _ in eng.cache.groups]
-        return rb, cb, widths
+        return rb, cb, eng.cache.table_widths(cb)
 
     def step(self, entries, borrow: bool = False, device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         eng = self.engine
