@@ -565,12 +565,17 @@ class Kernels:
             return
         self._check(self._lib.nib_argmax(_ptr(logits), c_int(rows), c_int(vocab), _ptr(out), self._stream()), "argmax")
 
-    def repetition_penalty(self, logits, seen, seen_start, penalty):
+    def repetition_penalty(self, logits, seen, seen_start, penalty, pending=None):
+        """``pending`` [rows] int32 on the device: one more id per row, penalised unless the row's list holds it."""
         _need(logits, torch.float32, "penalty logits"); _need(seen, torch.int32, "seen")
         _need(seen_start, torch.int32, "seen_start"); _need(penalty, torch.float32, "penalty")
         rows, vocab = logits.shape
-        self._check(self._lib.nib_repetition_penalty(_ptr(logits), c_int(rows), c_int(vocab), _ptr(seen),
-                                                     _ptr(seen_start), _ptr(penalty), self._stream()), "repetition_penalty")
+        if pending is not None:
+            _need(pending, torch.int32, "pending tokens")
+            if pending.numel() < rows:
+                raise KernelError("repetition_penalty: fewer pending tokens than rows")
+        self._check(self._lib.nib_repetition_penalty(_ptr(logits), c_int(rows), c_int(vocab), _ptr(seen), _ptr(seen_start),
+                                                     _ptr(penalty), _ptr(pending), self._stream()), "repetition_penalty")
 
     def sample(self, logits, temperature, top_k, top_p, uniform, out):
         _need(logits, torch.float32, "sample logits"); _need(temperature, torch.float32, "temperature")

@@ -10,26 +10,39 @@
 #include "pipeline.cuh"
 
 // ---------------------------------------------------------------------------------- penalty
-// seen: flat list of distinct token ids per row, seen_start[row]..seen_start[row+1].
+// seen: flat list of distinct token ids per row, seen_start[row]..seen_start[row+1]. pending (may be null): one more id
+// per row that is still on the device (the token of a step whose result the host has not read yet); it is penalised
+// too unless the row's list holds it already, so no logit is penalised twice.
 __global__ void penalty_kernel(float* __restrict__ logits, int vocab, const int* __restrict__ seen,
-                               const int* __restrict__ seen_start, const float* __restrict__ penalty) {
+                               const int* __restrict__ seen_start, const float* __restrict__ penalty,
+                               const int* __restrict__ pending) {
+    __shared__ int listed;
     const int row = blockIdx.x;
     const float p = penalty[row];
     if (p == 1.0f) return;
+    const int extra = pending ? pending[row] : -1;
+    if (threadIdx.x == 0) listed = 0;
+    __syncthreads();
     float* l = logits + (size_t)row * vocab;
     for (int i = seen_start[row] + threadIdx.x; i < seen_start[row + 1]; i += blockDim.x) {
         const int id = seen[i];
         if (id < 0 || id >= vocab) continue;
+        if (id == extra) listed = 1;
         const float s = l[id];
         l[id] = s > 0.f ? s / p : s * p;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && extra >= 0 && extra < vocab && !listed) {
+        const float s = l[extra];
+        l[extra] = s > 0.f ? s / p : s * p;
     }
 }
 
 NIB_API int nib_repetition_penalty(float* logits, int rows, int vocab, const int* seen, const int* seen_start,
-                                   const float* penalty, cudaStream_t stream) {
+                                   const float* penalty, const int* pending, cudaStream_t stream) {
     NIB_REQUIRE(rows >= 0 && vocab > 0, "penalty: bad sizes");
     if (rows == 0) return 0;
-    penalty_kernel<<<rows, 256, 0, stream>>>(logits, vocab, seen, seen_start, penalty);
+    penalty_kernel<<<rows, 256, 0, stream>>>(logits, vocab, seen, seen_start, penalty, pending);
     NIB_LAUNCH_CHECK();
     return 0;
 }

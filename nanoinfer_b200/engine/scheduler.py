@@ -18,6 +18,8 @@ from dataclasses import dataclass, field
 from enum import Enum
 from typing import Deque, Dict, List, Optional
 
+import numpy as np
+
 from ..cache.pages import OutOfPages
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import SampleRow
@@ -61,10 +63,31 @@ class Sequence:
         self.fed = 0               # tokens of (prompt + output) that the cache holds
         self.order = order         # admission order; the largest is preempted first
         self.preemptions = 0
+        self._distinct = np.empty(64, dtype=np.int32)      # the distinct ids of ``ids`` in order of first appearance
+        self._distinct_set: set = set()
+        self._distinct_upto = 0                             # how many of ``ids`` they cover
 
     @property
     def all_ids(self) -> List[int]:
         return self.ids
+
+    def distinct_ids(self) -> np.ndarray:
+        """Every id of prompt + output once (what a repetition penalty applies to), kept up to date token by token."""
+        have = self._distinct_set
+        for tok in self.ids[self._distinct_upto:]:
+            if tok not in have:
+                if len(have) == self._distinct.size:
+                    self._distinct = np.concatenate([self._distinct, np.empty_like(self._distinct)])
+                self._distinct[len(have)] = tok
+                have.add(tok)
+        self._distinct_upto = len(self.ids)
+        return self._distinct[:len(have)]
+
+    def sample_row(self, generated: int) -> SampleRow:
+        """The row that draws this request's token number ``generated``."""
+        if self.params.repetition_penalty != 1.0:
+            return SampleRow(self.params, self.distinct_ids(), generated, self.req.seed, distinct=True)
+        return SampleRow(self.params, None, generated, self.req.seed)
 
     @property
     def pending(self) -> int:
@@ -102,7 +125,7 @@ class Scheduler:
 
     def __init__(self, model, max_batch: Optional[int] = None, max_tokens_per_step: Optional[int] = None,
                  lookahead: bool = False):
-        """``lookahead``: decoding steps (greedy or sampled, without a repetition penalty) are launched with the previous step's tokens still on the
+        """``lookahead``: decoding steps (greedy and sampled rows in any mix, with or without a repetition penalty) are launched with the previous step's tokens still on the
         device; the host reads them while the new step runs, so ``finished`` and the sequences' outputs lag
         one step behind the device, and a request that stops at EOS has run one step too many (its result is
         dropped). What is generated is the same."""
@@ -249,9 +272,9 @@ class Scheduler:
 
     def _continuation(self):
         """The sequences of the step in flight, if the next step is exactly one more token for each of them:
-        nobody waits to be admitted, nobody's token in flight is its last by count, nobody has a repetition
-        penalty (it needs the ids on the host), all are greedy or all are sampled, and the pages for one more
-        token each are there."""
+        nobody waits to be admitted, nobody's token in flight is its last by count, and the pages for one more token
+        each are there. Greedy and sampled rows may stand in one batch (the sampling kernel takes both), and so may
+        rows with a repetition penalty (the id that the host has not read yet is penalised from the device's copy)."""
         if self._inflight is None or self.waiting:
             return None
         seqs, _ = self._inflight
@@ -260,12 +283,8 @@ class Scheduler:
         for a, b in zip(seqs, sorted(self.running, key=lambda s: s.order)):
             if a is not b or a.state is not State.RUNNING:
                 return None
-            if a.params.repetition_penalty != 1.0:
-                return None
             if len(a.output_ids) + 1 >= a.req.max_tokens or len(a.ids) + 2 >= self.engine.max_positions:
                 return None
-        if len({s.params.greedy for s in seqs}) != 1:
-            return None             # greedy and sampled rows in one batch are merged on the host
         if not self.engine.cache.fits([(s.cache, 1) for s in seqs]):
             return None
         return seqs
@@ -274,9 +293,9 @@ class Scheduler:
         """Launch the next decode step from the device's copy of the tokens in flight, then read those."""
         _, pending = self._inflight
         entries = [StepEntry(s.cache, [0], [0]) for s in seqs]       # the ids are placeholders
-        rows = [SampleRow(s.params, None, len(s.output_ids) + 1, s.req.seed) for s in seqs]
+        rows = [s.sample_row(len(s.output_ids) + 1) for s in seqs]      # the host's ids lack the token in flight:
         logits = self.engine.step(entries, borrow_logits=True, device_tokens=pending.device)
-        nxt = self.model.sampler.sample_async(logits, rows)
+        nxt = self.model.sampler.sample_async(logits, rows, pending=pending.device)   # a penalty reads it there
         plan = StepPlan(entries=[PlannedEntry(s, s.fed, 1, True) for s in seqs])
         for s in seqs:
             s.fed += 1              # the token in flight is in the cache now; ``ids`` gets it below
@@ -304,14 +323,13 @@ class Scheduler:
                 entries.append(StepEntry(e.seq.cache, ids, [e.count - 1] if wants else []))
                 if wants:
                     samplers.append(e.seq)
-                    rows.append(SampleRow(e.seq.params, e.seq.all_ids if e.seq.params.repetition_penalty != 1.0 else None,
-                                          len(e.seq.output_ids), e.seq.req.seed))
+                    rows.append(e.seq.sample_row(len(e.seq.output_ids)))
             logits = self.engine.step(entries, borrow_logits=True)
             for e in plan.entries:
                 e.seq.fed += e.count
             if self.lookahead and rows and len(samplers) == len(plan.entries) and \
                     all(e.count == 1 for e in plan.entries) and self.model.sampler.can_sample_async(rows):
-                # a pure greedy decode step: leave its tokens on the device for the next step to start from
+                # a pure decode step without penalties: leave its tokens on the device for the next step to start from
                 self._inflight = (samplers, self.model.sampler.sample_async(logits, rows))
                 toks = []
             else:

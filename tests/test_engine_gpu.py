@@ -165,6 +165,19 @@ def test_lookahead_scheduling_generates_the_same(model_dirs, dtype):
             assert got == plain
             assert with_eos[0] == plain[0][:stop] and with_eos[1:] == plain[1:]
             assert run(True, -1, temperature=0.8) == run(False, -1, temperature=0.8)      # sampled rows start early too
+
+            def mixed(lookahead):       # greedy, sampled, greedy with a penalty, sampled with a penalty in one batch
+                sched = Scheduler(model, lookahead=lookahead)
+                kinds = [dict(), dict(temperature=0.9, top_k=30, seed=3), dict(repetition_penalty=25.0),
+                         dict(temperature=0.7, top_p=0.9, repetition_penalty=1.6, seed=4)]
+                for i, kw in enumerate(kinds):
+                    sched.add(Request(f"m{i}", prompts[i], max_tokens=16, **kw))
+                out = sched.run()
+                assert (sched.steps_ahead >= 10) == lookahead
+                return [out[f"m{i}"] for i in range(4)]
+            ahead = mixed(True)
+            assert ahead == mixed(False)
+            assert ahead[0] == plain[0][:16] and ahead[2] != plain[2][:16]      # the penalty changed what is generated
         else:   # bfloat16: another batch may round a near tie the other way; lengths and stop rules must hold
             assert [len(o) for o in got] == limits
             assert eos not in with_eos[0] and len(with_eos[0]) <= limits[0]
@@ -329,6 +342,30 @@ def test_sampling_kernels_follow_the_plain_pipeline(vocab):
     toks = sampler.sample(base.repeat(2, 1).cuda().contiguous(), rows)
     assert toks == [greedy_pick(base[0].numpy(), context, 3.0), 7]
     assert toks[0] == 11
+    # greedy rows beside sampled ones take the sampling kernel too (one launch, nothing for the host to merge): the
+    # first of the tied maxima, whatever the row's seed; the sampled rows draw what they draw alone
+    sampled = SamplingParams(temperature=0.8, top_k=30, top_p=0.9)
+    rows = [SampleRow(SamplingParams(), None, i, seed=i) if i % 3 else SampleRow(sampled, None, i, seed=40) for i in range(12)]
+    assert sampler.can_sample_async(rows)
+    alone = sampler.sample(base.repeat(4, 1).cuda().contiguous(), [r for r in rows if not r.params.greedy])
+    for toks in (sampler.sample(base.repeat(12, 1).cuda().contiguous(), rows),
+                 sampler.sample_async(base.repeat(12, 1).cuda().contiguous(), rows).wait()):
+        assert [t for t, r in zip(toks, rows) if r.params.greedy] == [7] * 8
+        assert [t for t, r in zip(toks, rows) if not r.params.greedy] == alone
+    # a penalty with one more id per row on the device (the token of a step in flight): penalised once, whether the
+    # row's own list holds it already (row 0), not (row 1), or the row has no penalty (row 2)
+    K = load_kernels()
+    l3 = base.repeat(3, 1).cuda().contiguous()
+    K.repetition_penalty(l3, torch.tensor([7, 3, 3], dtype=torch.int32, device="cuda"), torch.tensor([0, 2, 3, 3], dtype=torch.int32, device="cuda"),
+                         torch.tensor([2.0, 4.0, 1.0], device="cuda"), torch.tensor([3, 7, 7], dtype=torch.int32, device="cuda"))
+    want3 = base.repeat(3, 1)
+    for r, ids, p in ((0, [7, 3], 2.0), (1, [3, 7], 4.0)):
+        for i in ids:
+            want3[r, i] = want3[r, i] / p if want3[r, i] > 0 else want3[r, i] * p
+    assert torch.equal(l3.cpu(), want3)
+    shifted = base.clone()
+    shifted[0, 11] += 1e-3          # no tie: the one maximum
+    assert sampler.sample(shifted.repeat(2, 1).cuda().contiguous(), rows[:2]) [1] == 11
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

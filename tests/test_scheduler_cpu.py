@@ -187,6 +187,47 @@ def test_sampling_is_reproducible_and_independent_of_the_batch(model_dirs):
     assert other != alone
 
 
+def test_greedy_sampled_and_penalised_requests_share_steps_ahead(model_dirs):
+    """A batch that holds greedy and sampled requests, with and without a repetition penalty, is decoded ahead like
+    any other (one sampling launch takes both kinds; the id that the host has not read yet is penalised from the
+    device's copy): every request's tokens equal what it generates alone, one step at a time."""
+    d, page = model_dirs["A"]
+    ps = prompts(256, [5, 12, 21, 8, 30, 3], seed=8)
+    kinds = [SamplingParams(), SamplingParams(temperature=0.9, top_k=20, seed=3), SamplingParams(),
+             SamplingParams(temperature=1.2, top_p=0.85, seed=4), SamplingParams(repetition_penalty=40.0),
+             SamplingParams(temperature=0.8, repetition_penalty=1.4, seed=5)]
+
+    def requests():
+        return [Request(f"r{i}", p, max_tokens=14, temperature=k.temperature, top_k=k.k, top_p=k.p,
+                        repetition_penalty=k.repetition_penalty, seed=k.seed or 0) for i, (p, k) in enumerate(zip(ps, kinds))]
+    alone = []
+    for r in requests():
+        s = Scheduler(make_model(d, page), lookahead=False)
+        s.add(r)
+        alone.append(s.run()[r.request_id])
+        assert s.steps_ahead == 0
+    plain = PlainModel(d)
+    assert alone[0] == plain.greedy(ps[0], 14)
+    assert alone[4] != plain.greedy(ps[4], 14)          # the penalty does something here
+    s = Scheduler(make_model(d, page, max_batch=6), lookahead=True)
+    for r in requests():
+        s.add(r)
+    out = s.run()
+    assert s.steps_ahead >= 10
+    assert [out[f"r{i}"] for i in range(6)] == alone
+
+
+def test_a_sequence_keeps_its_distinct_ids_up_to_date():
+    from nanoinfer_b200.engine.scheduler import Sequence
+    seq = Sequence(Request("x", [5, 3, 5, 9] * 40, max_tokens=200, repetition_penalty=1.2), 0)
+    assert seq.distinct_ids().tolist() == [5, 3, 9]
+    for tok in [3, 70, 5, 71] + list(range(100, 200)):
+        seq.emit(tok)
+    assert seq.distinct_ids().tolist() == [5, 3, 9, 70, 71] + list(range(100, 200))
+    row = seq.sample_row(7)
+    assert row.distinct and row.context.tolist() == seq.distinct_ids().tolist() and row.generated == 7
+
+
 @pytest.mark.parametrize("seed", range(8))
 def test_random_arrivals_cancels_and_tight_pools(model_dirs, seed):
     """A seeded random run: requests arrive at random steps, some are cancelled at random steps, the pool,

@@ -97,13 +97,15 @@ class TorchOps:
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(out.dtype))
 
-    def repetition_penalty(self, logits, seen, seen_start, penalty):
+    def repetition_penalty(self, logits, seen, seen_start, penalty, pending=None):
         starts = seen_start.tolist()
         for r in range(logits.shape[0]):
             p = float(penalty[r])
             if p == 1.0:
                 continue
             ids = seen[starts[r]:starts[r + 1]].long()
+            if pending is not None and int(pending[r]) not in ids.tolist():
+                ids = torch.cat([ids, pending[r:r + 1].long()])
             s = logits[r, ids]
             logits[r, ids] = torch.where(s > 0, s / p, s * p)
 
