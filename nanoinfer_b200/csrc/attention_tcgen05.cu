@@ -38,6 +38,7 @@ __device__ int g_attn_error = 0;
 // The hand-overs between the roles of this kernel are short and on the critical path of every block of keys: poll
 // without sleeping for a long while (the limit still holds).
 __device__ __forceinline__ bool mbar_spin(unsigned long long* bar, unsigned parity) {
+#pragma unroll 1      // (unrolled, each of the kernel's thirty waits would be several copies of this loop: instruction cache)
     for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (i > (1u << 16)) __nanosleep(100);

@@ -35,6 +35,7 @@ __device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parit
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+#pragma unroll 1      // (unrolled, every one of a kernel's waits would be several copies of this loop: instruction cache)
     for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
         if (mbar_try(bar, parity)) return true;
         if (i > 256) __nanosleep(64);
