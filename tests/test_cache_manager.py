@@ -146,6 +146,20 @@ def test_window_group_returns_pages_while_running():
     m.check()
 
 
+def test_table_widths_cover_what_a_request_of_that_length_holds():
+    """A captured step sizes its block tables by ``table_widths``: for every length up to the bucket, every group's
+    table (the windowed one keeps an entry per page of the whole sequence, dead ones -1) fits the width."""
+    m = CacheManager(groups(window=20), num_pages=40, page_size=8, max_requests=2)
+    assert m.table_widths(1) == [1, 1] and m.table_widths(8) == [1, 1] and m.table_widths(9) == [2, 2]
+    r = m.open("r")
+    for n in range(1, 130):
+        m.extend(r, 1)
+        m.commit(r, 1)
+        assert [len(t) for t in r.tables] == m.table_widths(n)
+        assert all(len(t) <= w for t, w in zip(r.tables, m.table_widths(256)))
+    m.close(r)
+
+
 def test_truncate_gives_back_whole_pages_and_refuses_what_a_window_has_dropped():
     m = CacheManager(groups(), num_pages=8, page_size=8, max_requests=2)
     a = m.open("a")
