@@ -165,18 +165,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         const int pages_per_block = KEYS / page_size;
         const int oob = num_pages * kv_heads;             // a coordinate outside the pool: the box arrives as zeros
-        auto plane_of = [&](int j) -> int {               // third coordinate of this lane's page in block j
+        // This lane's block-table entry of block j, or -1 where it has no page to fetch there. The entry of block j+1 is
+        // asked for while block j is being sent for and is looked at only a block later: the look-up's latency (more
+        // than half a microsecond) must not stand between two blocks' copies.
+        auto entry_of = [&](int j) -> int {
             const int key = (b_begin + j) * KEYS + lane * page_size;
-            if (lane >= pages_per_block || key > hi_cta || key + page_size <= lo_cta) return oob;
-            const int page = __ldg(bt + key / page_size);
-            return (page >= 0 && page < num_pages) ? page * kv_heads + kvh : oob;
+            if (lane >= pages_per_block || key > hi_cta || key + page_size <= lo_cta) return -1;
+            return __ldg(bt + key / page_size);
         };
-        int z_next = plane_of(0);
+        int entry_next = entry_of(0);
         int issued = 0;
         for (int j = 0; j < n_blk; ++j) {
             const int st = j % STAGES;
-            const int z = z_next;
-            if (j + 1 < n_blk) z_next = plane_of(j + 1);
+            const int entry = entry_next;
+            if (j + 1 < n_blk) entry_next = entry_of(j + 1);
+            const int z = (entry >= 0 && entry < num_pages) ? entry * kv_heads + kvh : oob;      // third coordinate of the page
             // keys first (the scores of this block are wanted a whole block ahead), values when their stage is free
             const unsigned par = ((j / STAGES) & 1) ^ 1;
             int ok = 1;
