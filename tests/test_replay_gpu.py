@@ -68,7 +68,7 @@ def test_replay_all_cuts(model_dirs, tmp_path, name, dtype):
         # 32-bit: every reduction's order depends on the position's own data only (ascending k per output in the
         # products, keys in absolute blocks of 32 in the attention, one warp per row in the norms), so the cut,
         # the batch and the pages change NO bit of a logit (the reference holds max|diff| = 0 for changes of
-        # placement: cpp/docs/BASELINE.md:52-54, cpp/tests/run_batch.cpp:79-96)
+        # placement: its cpp/docs notes on batching, lines 52-54, and cpp/tests/run_batch.cpp:79-96)
         for (rid, pos), modes in by_mode.items():
             base = modes["whole"]
             for mode, row in modes.items():
