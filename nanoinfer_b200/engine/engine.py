@@ -119,11 +119,18 @@ class Engine:
                 raise ValueError(
                     f"request {e.request.request_id!r}: position {e.request.length + n} exceeds the "
                     f"model's context length {self.max_positions} (max_position_embeddings)")
-            try:
-                ids = np.asarray(e.tokens, dtype=np.int32)
-                in_range = ids.ndim == 1 and int(ids.min()) >= 0 and int(ids.max()) < self.vocab_size
-            except (OverflowError, TypeError, ValueError):      # an id that no int32 holds, or no integer at all
-                in_range = False
+            first = e.tokens[0]
+            if n == 1 and type(first) is int:       # a decoded token: no array arithmetic for one comparison
+                in_range = 0 <= first < self.vocab_size
+                ids = np.array((first,), dtype=np.int32) if in_range else None
+            else:
+                try:        # integers only: a float or a string is not quietly turned into an id
+                    ids = np.asarray(e.tokens)
+                    in_range = ids.ndim == 1 and ids.dtype.kind in "iu" and int(ids.min()) >= 0 and int(ids.max()) < self.vocab_size
+                    if in_range and ids.dtype != np.int32:
+                        ids = ids.astype(np.int32)
+                except (OverflowError, TypeError, ValueError):      # ids of mixed kinds that no array holds
+                    in_range = False
             if not in_range:
                 bad = next((t for t in e.tokens if not (isinstance(t, (int, np.integer)) and 0 <= int(t) < self.vocab_size)), None)
                 raise ValueError(f"token id {bad!r} outside the vocabulary 0..{self.vocab_size - 1}")

@@ -99,6 +99,14 @@ def test_step_errors(model_dirs):
         eng.step([StepEntry(rc, [], [])])
     with pytest.raises(ValueError):
         eng.step([StepEntry(rc, [999], [0])])
+    # ids that are no ids, alone (a decoded token takes a path of its own) and inside a portion
+    for bad in (-1, 256, 2 ** 40, 1.5, "7", None, True):
+        with pytest.raises(ValueError, match="outside the vocabulary"):
+            eng.step([StepEntry(rc, [bad], [0])])
+        if bad is not True:         # (beside integers numpy reads it as 1, as Python does)
+            with pytest.raises(ValueError, match="outside the vocabulary"):
+                eng.step([StepEntry(rc, [3, bad, 5], [0])])
+    assert rc.length == 0 and eng.cache.num_free(0) == 2
     with pytest.raises(ValueError):
         eng.step([StepEntry(rc, [1, 2], [2])])
     with pytest.raises(OutOfPages):
