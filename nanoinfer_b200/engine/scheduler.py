@@ -66,6 +66,7 @@ class Sequence:
         self._distinct = np.empty(64, dtype=np.int32)      # the distinct ids of ``ids`` in order of first appearance
         self._distinct_set: set = set()
         self._distinct_upto = 0                             # how many of ``ids`` they cover
+        self._prompt_array = None                           # the prompt as an int32 array, once a portion of it is run
 
     @property
     def all_ids(self) -> List[int]:
@@ -82,6 +83,23 @@ class Sequence:
                 have.add(tok)
         self._distinct_upto = len(self.ids)
         return self._distinct[:len(have)]
+
+    def tokens(self, start: int, count: int):
+        """``ids[start:start + count]`` as a step takes them. A portion that lies in the prompt is a view of the prompt as
+        an int32 array, made once (turning two thousand Python integers into an array for every portion is the dearest
+        thing the host does before a prompt step's first launch); anything else, and a prompt that holds something
+        other than integers of 32 bits (the step refuses it by name), is the list's slice."""
+        if count > 1 and start + count <= len(self.req.prompt_ids):
+            if self._prompt_array is None:
+                try:
+                    a = np.asarray(self.req.prompt_ids)
+                    whole = a.ndim == 1 and a.dtype.kind in "iu" and -2 ** 31 <= int(a.min()) and int(a.max()) < 2 ** 31
+                    self._prompt_array = a.astype(np.int32) if whole else False
+                except (OverflowError, TypeError, ValueError):
+                    self._prompt_array = False
+            if self._prompt_array is not False:
+                return self._prompt_array[start:start + count]
+        return self.ids[start:start + count]
 
     def sample_row(self, generated: int) -> SampleRow:
         """The row that draws this request's token number ``generated``."""
@@ -318,7 +336,7 @@ class Scheduler:
         if plan.entries:
             entries, rows, samplers = [], [], []
             for e in plan.entries:
-                ids = e.seq.ids[e.start:e.start + e.count]
+                ids = e.seq.tokens(e.start, e.count)
                 wants = e.samples and e.seq.req.max_tokens > 0
                 entries.append(StepEntry(e.seq.cache, ids, [e.count - 1] if wants else []))
                 if wants:

@@ -217,6 +217,22 @@ def test_greedy_sampled_and_penalised_requests_share_steps_ahead(model_dirs):
     assert [out[f"r{i}"] for i in range(6)] == alone
 
 
+def test_prompt_portions_are_views_of_one_array(model_dirs):
+    import numpy as np
+    from nanoinfer_b200.engine.scheduler import Sequence
+    seq = Sequence(Request("x", list(range(40)), max_tokens=8), 0)
+    a, b = seq.tokens(0, 16), seq.tokens(16, 24)
+    assert a.dtype == np.int32 and a.base is b.base and a.tolist() == list(range(16)) and b.tolist() == list(range(16, 40))
+    seq.emit(7)
+    assert seq.tokens(38, 3) == [38, 39, 7] and seq.tokens(40, 1) == [7] and seq.tokens(39, 1) == [39]
+    # a prompt that holds something else than integers stays a list, and the step names the id
+    d, page = model_dirs["A"]
+    s = Scheduler(make_model(d, page))
+    s.add(Request("bad", [5, 6.5, 7], max_tokens=2))
+    with pytest.raises(ValueError, match="6.5"):
+        s.step()
+
+
 def test_a_sequence_keeps_its_distinct_ids_up_to_date():
     from nanoinfer_b200.engine.scheduler import Sequence
     seq = Sequence(Request("x", [5, 3, 5, 9] * 40, max_tokens=200, repetition_penalty=1.2), 0)
